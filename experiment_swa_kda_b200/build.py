@@ -1,0 +1,71 @@
+"""In-tree build of libkda_b200.so for sm_100a with nvcc (cross-compiles without a GPU).
+
+    python -m experiment_swa_kda_b200.build          # build if sources are newer than the library
+    python -m experiment_swa_kda_b200.build --force
+
+Plays the role of the reference's build loader (nanochat/research/cuda_build.py:116-181,
+nanochat/mixers/cuda_kda/__init__.py:33-46): one shared library from the sources under csrc/,
+with the exact compiler command recorded next to it (lib/build_receipt.json).
+"""
+
+from __future__ import annotations
+
+import json
+import os
+import shutil
+import subprocess
+import sys
+
+PKG = os.path.dirname(os.path.abspath(__file__))
+CSRC = os.path.join(PKG, "csrc")
+LIBDIR = os.path.join(PKG, "lib")
+LIB = os.path.join(LIBDIR, "libkda_b200.so")
+RECEIPT = os.path.join(LIBDIR, "build_receipt.json")
+ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
+
+
+def sources():
+    return sorted(os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith(".cu"))
+
+
+def _deps():
+    inc = os.path.join(os.path.dirname(PKG), "include", "kda_b200.h")
+    return sources() + [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith(".cuh")] + [inc]
+
+
+def is_stale() -> bool:
+    if not os.path.exists(LIB):
+        return True
+    t = os.path.getmtime(LIB)
+    return any(os.path.getmtime(p) > t for p in _deps())
+
+
+def nvcc_path() -> str:
+    cand = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    if not os.path.exists(cand):
+        raise RuntimeError("nvcc not found: cannot build libkda_b200.so")
+    return cand
+
+
+def build(force: bool = False, verbose: bool = False) -> str:
+    if not force and not is_stale():
+        return LIB
+    os.makedirs(LIBDIR, exist_ok=True)
+    cmd = [nvcc_path(), *ARCH_FLAGS, "-lineinfo", "-O3", "-std=c++17", "--shared", "-Xcompiler", "-fPIC",
+           "-lcuda", "-o", LIB, *sources()]
+    if verbose:
+        cmd.insert(1, "-Xptxas")
+        cmd.insert(2, "-v")
+    proc = subprocess.run(cmd, capture_output=True, text=True)
+    if proc.returncode != 0:
+        raise RuntimeError("nvcc failed:\n" + proc.stdout + proc.stderr)
+    if verbose:
+        sys.stderr.write(proc.stderr)
+    with open(RECEIPT, "w") as f:
+        json.dump({"library_path": LIB, "source_paths": sources(), "compiler_command": cmd,
+                   "target_arch": "sm_100a"}, f, indent=1)
+    return LIB
+
+
+if __name__ == "__main__":
+    print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))

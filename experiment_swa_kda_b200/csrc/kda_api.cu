@@ -1,0 +1,168 @@
+// C ABI for the chunked KDA operator: argument checks and lane dispatch.
+
+#include <cstdio>
+#include <cstring>
+#include <map>
+#include <mutex>
+#include <string>
+#include <vector>
+
+#include "common.cuh"
+#include "simt_ws.cuh"
+
+namespace kda {
+int simt_chunk_fwd(const KdaChunkShape* sh, const void* q, const void* k, const void* v, const void* g, const void* beta,
+                   const float* h0, const int32_t* cu, void* o, float* final_state, void* workspace, cudaStream_t st);
+int simt_chunk_bwd(const KdaChunkShape* sh, const void* q, const void* k, const void* v, const void* g, const void* beta,
+                   const int32_t* cu, const void* d_o, const float* d_final, const void* workspace, void* scratch,
+                   void* dq, void* dk, void* dv, void* dg, void* dbeta, float* dh0, cudaStream_t st);
+}  // namespace kda
+
+using namespace kda;
+
+static int check_shape(const KdaChunkShape* s, const int32_t* cu) {
+    if (!s) return KDA_ERR_NULL;
+    if (s->n_seq <= 0 || s->heads <= 0 || s->key_dim <= 0 || s->value_dim <= 0 || s->tokens < 0 || s->seq_len < 0)
+        return KDA_ERR_BAD_SHAPE;
+    if (s->key_dim > KDA_MAX_DIM || s->value_dim > KDA_MAX_DIM) return KDA_ERR_BAD_SHAPE;
+    if (s->io_dtype != KDA_DTYPE_F32 && s->io_dtype != KDA_DTYPE_BF16) return KDA_ERR_UNSUPPORTED;
+    if (s->gate_dtype != KDA_DTYPE_F32 && s->gate_dtype != KDA_DTYPE_BF16) return KDA_ERR_UNSUPPORTED;
+    if (cu) {
+        if (s->seq_len != 0) return KDA_ERR_BAD_SHAPE;   // packed batches describe lengths through cu_seqlens only
+    } else {
+        if ((long long)s->n_seq * s->seq_len != s->tokens) return KDA_ERR_BAD_SHAPE;
+    }
+    if (s->lane != KDA_LANE_FP32) return KDA_ERR_UNSUPPORTED;
+    return KDA_OK;
+}
+
+extern "C" const char* kda_error_string(int code) {
+    switch (code) {
+        case KDA_OK: return "ok";
+        case KDA_ERR_BAD_SHAPE: return "bad shape: a dimension is non-positive, above 256, or inconsistent with tokens / cu_seqlens";
+        case KDA_ERR_UNSUPPORTED: return "unsupported lane, dtype or size for this entry point";
+        case KDA_ERR_WORKSPACE: return "workspace or scratch buffer missing, misaligned or too small";
+        case KDA_ERR_CUDA: return "CUDA runtime reported an error at launch";
+        case KDA_ERR_NULL: return "required pointer is null";
+        case KDA_ERR_DEVICE_STATUS: return "kernel reported a device-side status (bounded wait expired)";
+        default: return "unknown error";
+    }
+}
+
+extern "C" const char* kda_build_arch(void) { return "sm_100a"; }
+
+extern "C" size_t kda_chunk_workspace_bytes(const KdaChunkShape* shape) {
+    if (!shape || shape->n_seq <= 0 || shape->heads <= 0 || shape->key_dim <= 0 || shape->value_dim <= 0) return 0;
+    size_t bytes = 0;
+    simt::carve_ws(*shape, nullptr, &bytes);
+    return bytes;
+}
+
+extern "C" size_t kda_chunk_bwd_scratch_bytes(const KdaChunkShape* shape) {
+    if (!shape || shape->n_seq <= 0 || shape->heads <= 0 || shape->key_dim <= 0 || shape->value_dim <= 0) return 0;
+    size_t bytes = 0;
+    simt::carve_scr(*shape, nullptr, &bytes);
+    return bytes;
+}
+
+extern "C" int kda_chunk_fwd(const KdaChunkShape* shape, const void* q, const void* k, const void* v, const void* g,
+                             const void* beta, const float* h0, const int32_t* cu_seqlens, void* o, float* final_state,
+                             void* workspace, size_t workspace_bytes, void* stream) {
+    int rc = check_shape(shape, cu_seqlens);
+    if (rc) return rc;
+    if (shape->tokens > 0 && (!q || !k || !v || !g || !beta || !o)) return KDA_ERR_NULL;
+    if (!workspace || (reinterpret_cast<uintptr_t>(workspace) % 256) != 0 ||
+        workspace_bytes < kda_chunk_workspace_bytes(shape))
+        return KDA_ERR_WORKSPACE;
+    return simt_chunk_fwd(shape, q, k, v, g, beta, h0, cu_seqlens, o, final_state, workspace, (cudaStream_t)stream);
+}
+
+extern "C" int kda_chunk_bwd(const KdaChunkShape* shape, const void* q, const void* k, const void* v, const void* g,
+                             const void* beta, const int32_t* cu_seqlens, const void* d_o, const float* d_final_state,
+                             const void* workspace, size_t workspace_bytes, void* scratch, size_t scratch_bytes,
+                             void* dq, void* dk, void* dv, void* dg, void* dbeta, float* dh0, void* stream) {
+    int rc = check_shape(shape, cu_seqlens);
+    if (rc) return rc;
+    if (shape->tokens > 0 && (!q || !k || !v || !g || !beta || !d_o || !dq || !dk || !dv || !dg || !dbeta))
+        return KDA_ERR_NULL;
+    if (!workspace || (reinterpret_cast<uintptr_t>(workspace) % 256) != 0 ||
+        workspace_bytes < kda_chunk_workspace_bytes(shape))
+        return KDA_ERR_WORKSPACE;
+    if (!scratch || (reinterpret_cast<uintptr_t>(scratch) % 256) != 0 ||
+        scratch_bytes < kda_chunk_bwd_scratch_bytes(shape))
+        return KDA_ERR_WORKSPACE;
+    return simt_chunk_bwd(shape, q, k, v, g, beta, cu_seqlens, d_o, d_final_state, workspace, scratch, dq, dk, dv, dg,
+                          dbeta, dh0, (cudaStream_t)stream);
+}
+
+// ---------------------------------------------------------------------------------------------
+// launch accounting
+// ---------------------------------------------------------------------------------------------
+namespace kda {
+namespace prof {
+namespace {
+struct Rec {
+    const char* name;
+    cudaEvent_t a, b;
+};
+std::mutex mu;
+bool enabled = false;
+unsigned long long launches = 0;
+std::vector<Rec> recs;
+}  // namespace
+
+void begin(const char* name, cudaStream_t st) {
+    std::lock_guard<std::mutex> lk(mu);
+    ++launches;
+    if (!enabled) return;
+    Rec r{name, nullptr, nullptr};
+    if (cudaEventCreate(&r.a) != cudaSuccess || cudaEventCreate(&r.b) != cudaSuccess) return;
+    cudaEventRecord(r.a, st);
+    recs.push_back(r);
+}
+
+void end(cudaStream_t st) {
+    std::lock_guard<std::mutex> lk(mu);
+    if (!enabled || recs.empty()) return;
+    cudaEventRecord(recs.back().b, st);
+}
+}  // namespace prof
+}  // namespace kda
+
+extern "C" unsigned long long kda_launch_count(void) {
+    std::lock_guard<std::mutex> lk(kda::prof::mu);
+    return kda::prof::launches;
+}
+
+extern "C" void kda_profile_enable(int on) {
+    std::lock_guard<std::mutex> lk(kda::prof::mu);
+    kda::prof::enabled = on != 0;
+}
+
+extern "C" int kda_profile_report(char* out, size_t cap) {
+    using namespace kda::prof;
+    std::lock_guard<std::mutex> lk(mu);
+    std::map<std::string, std::pair<int, double>> agg;
+    for (auto& r : recs) {
+        float ms = 0.f;
+        if (cudaEventSynchronize(r.b) == cudaSuccess && cudaEventElapsedTime(&ms, r.a, r.b) == cudaSuccess) {
+            auto& e = agg[r.name];
+            e.first += 1;
+            e.second += ms;
+        }
+        cudaEventDestroy(r.a);
+        cudaEventDestroy(r.b);
+    }
+    recs.clear();
+    std::string text;
+    char line[256];
+    for (auto& kv : agg) {
+        snprintf(line, sizeof line, "%s,%d,%.6f\n", kv.first.c_str(), kv.second.first, kv.second.second);
+        text += line;
+    }
+    if (!out || cap == 0) return (int)text.size();
+    size_t n = text.size() < cap - 1 ? text.size() : cap - 1;
+    memcpy(out, text.data(), n);
+    out[n] = 0;
+    return (int)n;
+}

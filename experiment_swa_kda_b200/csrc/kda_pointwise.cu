@@ -1,0 +1,860 @@
+// Bandwidth-bound KDA kernels: gate activations, recurrent decode step, short causal
+// depthwise convolution (+SiLU) and gated RMSNorm, forward and backward.  All are
+// HBM-bound: wide coalesced loads, warp-shuffle reductions, deterministic two-stage
+// reductions for the weight gradients (no floating-point atomics).
+
+#include <algorithm>
+
+#include "common.cuh"
+
+namespace kda {
+namespace pw {
+
+// =============================================================================================
+// gate / beta activations
+// =============================================================================================
+__global__ void gate_fwd_kernel(size_t n_gate, size_t n_beta, int H, int K, int bf16, const void* __restrict__ raw,
+                                const void* __restrict__ bl, const float* __restrict__ A_log,
+                                const float* __restrict__ dt_bias, float lb, float* __restrict__ g,
+                                float* __restrict__ beta) {
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n_gate; i += stride) {
+        const int kk = (int)(i % K), h = (int)((i / K) % H);
+        const float z = expf(A_log[h]) * (ld_io(raw, i, bf16) + dt_bias[h * K + kk]);
+        g[i] = lb * sigmoidf_(z);
+    }
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n_beta; i += stride)
+        beta[i] = sigmoidf_(ld_io(bl, i, bf16));
+}
+
+constexpr int kGateRows = 64;  // tokens per first-stage reduction block
+
+// stage 1: d_raw, d_beta_logits and per-block column partials of ddt_bias / dA_log
+__global__ void gate_bwd_kernel(int tokens, int H, int K, int bf16, const void* __restrict__ raw,
+                                const void* __restrict__ bl, const float* __restrict__ A_log,
+                                const float* __restrict__ dt_bias, float lb, const float* __restrict__ dg,
+                                const float* __restrict__ dbeta, void* __restrict__ d_raw, void* __restrict__ d_bl,
+                                float* __restrict__ part_b, float* __restrict__ part_a) {
+    const int HK = H * K;
+    const int t0 = blockIdx.x * kGateRows, t1 = min(tokens, t0 + kGateRows);
+    for (int c = threadIdx.x; c < HK; c += blockDim.x) {
+        const int h = c / K;
+        const float ea = expf(A_log[h]), bias = dt_bias[c];
+        float sb = 0.f, sa = 0.f;
+        for (int t = t0; t < t1; ++t) {
+            const size_t i = (size_t)t * HK + c;
+            const float x = ld_io(raw, i, bf16) + bias;
+            const float sg = sigmoidf_(ea * x);
+            const float dr = dg[i] * lb * sg * (1.f - sg) * ea;
+            st_io(d_raw, i, bf16, dr);
+            sb += dr;
+            sa += dr * x;
+        }
+        part_b[(size_t)blockIdx.x * HK + c] = sb;
+        part_a[(size_t)blockIdx.x * HK + c] = sa;
+    }
+    for (int c = threadIdx.x; c < H; c += blockDim.x) {
+        for (int t = t0; t < t1; ++t) {
+            const size_t i = (size_t)t * H + c;
+            const float b = sigmoidf_(ld_io(bl, i, bf16));
+            st_io(d_bl, i, bf16, dbeta[i] * b * (1.f - b));
+        }
+    }
+}
+
+// stage 2: one block per head; fixed summation order
+__global__ void gate_bwd_reduce_kernel(int nblk, int H, int K, const float* __restrict__ part_b,
+                                       const float* __restrict__ part_a, float* __restrict__ ddt_bias,
+                                       float* __restrict__ dA_log) {
+    __shared__ float red[256];
+    const int h = blockIdx.x, HK = H * K;
+    float accA = 0.f;
+    for (int kk = threadIdx.x; kk < K; kk += 256) {
+        const int c = h * K + kk;
+        float sb = 0.f, sa = 0.f;
+        for (int b = 0; b < nblk; ++b) {
+            sb += part_b[(size_t)b * HK + c];
+            sa += part_a[(size_t)b * HK + c];
+        }
+        ddt_bias[c] = sb;
+        accA += sa;
+    }
+    red[threadIdx.x] = accA;
+    __syncthreads();
+    for (int o = 128; o > 0; o >>= 1) {
+        if (threadIdx.x < o) red[threadIdx.x] += red[threadIdx.x + o];
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) dA_log[h] = red[0];
+}
+
+// =============================================================================================
+// recurrent decode step
+//   S' = S * exp(g);  r = v - k^T S';  S'' = S' + beta k r^T;  o = q^T S''
+// The state is V-first [n_seq,H,V,K]: a row (fixed value index) is K contiguous floats.  One
+// warp owns a row at a time: a single coalesced read and a single coalesced write per row, two
+// shuffle reductions, and o_v = q.S'_v + beta r_v (q.k) so the row is never re-read.
+// =============================================================================================
+constexpr int kDecRows = 4;  // rows a warp keeps in flight
+
+template <bool VEC>
+__global__ void __launch_bounds__(256) decode_kernel(int H, int K, int V, int bf16, int gbf16, int l2norm, float scale,
+                                                     const void* __restrict__ q, const void* __restrict__ k,
+                                                     const void* __restrict__ v, const void* __restrict__ g,
+                                                     const void* __restrict__ beta, const float* s_in, float* s_out,
+                                                     void* __restrict__ o, int rows_per_cta) {
+    const int bh = blockIdx.x;            // sequence * H + head
+    const int v_base = blockIdx.y * rows_per_cta;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // lane-owned key indices: VEC: kidx(e) = 128*(e/4) + 4*lane + e%4 ; scalar: kidx(e) = lane + 32*e
+    float qe[8], ke[8], dec[8];
+    float sq = 0.f, sk = 0.f;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+        const int kk = VEC ? (128 * (e >> 2) + 4 * lane + (e & 3)) : (lane + 32 * e);
+        if (kk < K) {
+            const size_t i = (size_t)bh * K + kk;
+            qe[e] = ld_io(q, i, bf16);
+            ke[e] = ld_io(k, i, bf16);
+            dec[e] = expf(ld_io(g, i, gbf16));
+        } else {
+            qe[e] = 0.f; ke[e] = 0.f; dec[e] = 0.f;
+        }
+        sq += qe[e] * qe[e];
+        sk += ke[e] * ke[e];
+    }
+    sq = warp_sum(sq);
+    sk = warp_sum(sk);
+    const float qi = (l2norm ? 1.f / fmaxf(sqrtf(sq), 1e-12f) : 1.f) * scale;
+    const float ki = l2norm ? 1.f / fmaxf(sqrtf(sk), 1e-12f) : 1.f;
+    const float bt = ld_io(beta, bh, gbf16);
+    float qk = 0.f;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+        qe[e] *= qi;
+        ke[e] *= ki;
+        qk += qe[e] * ke[e];
+    }
+    qk = warp_sum(qk);
+    const int v_end = min(V, v_base + rows_per_cta);
+    for (int r0 = v_base + warp * kDecRows; r0 < v_end; r0 += 8 * kDecRows) {
+        float s[kDecRows][8];
+#pragma unroll
+        for (int j = 0; j < kDecRows; ++j) {
+            const int row = r0 + j;
+            const float* src = s_in + ((size_t)bh * V + row) * K;
+            if (row < v_end) {
+                if (VEC) {
+#pragma unroll
+                    for (int e4 = 0; e4 < 2; ++e4) {
+                        const int kk = 128 * e4 + 4 * lane;
+                        float4 x = (kk < K) ? __ldcs(reinterpret_cast<const float4*>(src + kk)) : make_float4(0, 0, 0, 0);
+                        s[j][4 * e4 + 0] = x.x; s[j][4 * e4 + 1] = x.y; s[j][4 * e4 + 2] = x.z; s[j][4 * e4 + 3] = x.w;
+                    }
+                } else {
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) {
+                        const int kk = lane + 32 * e;
+                        s[j][e] = (kk < K) ? src[kk] : 0.f;
+                    }
+                }
+            } else {
+#pragma unroll
+                for (int e = 0; e < 8; ++e) s[j][e] = 0.f;
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < kDecRows; ++j) {
+            const int row = r0 + j;
+            float a = 0.f, b = 0.f;
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                s[j][e] *= dec[e];
+                a += ke[e] * s[j][e];
+                b += qe[e] * s[j][e];
+            }
+            a = warp_sum(a);
+            b = warp_sum(b);
+            if (row < v_end) {
+                const float res = ld_io(v, (size_t)bh * V + row, bf16) - a;
+                const float br = bt * res;
+                float* dst = s_out + ((size_t)bh * V + row) * K;
+                if (VEC) {
+#pragma unroll
+                    for (int e4 = 0; e4 < 2; ++e4) {
+                        const int kk = 128 * e4 + 4 * lane;
+                        if (kk < K)
+                            __stcs(reinterpret_cast<float4*>(dst + kk),
+                                   make_float4(s[j][4 * e4 + 0] + br * ke[4 * e4 + 0], s[j][4 * e4 + 1] + br * ke[4 * e4 + 1],
+                                               s[j][4 * e4 + 2] + br * ke[4 * e4 + 2], s[j][4 * e4 + 3] + br * ke[4 * e4 + 3]));
+                    }
+                } else {
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) {
+                        const int kk = lane + 32 * e;
+                        if (kk < K) dst[kk] = s[j][e] + br * ke[e];
+                    }
+                }
+                if (lane == 0) st_io(o, (size_t)bh * V + row, bf16, b + br * qk);
+            }
+        }
+    }
+}
+
+// =============================================================================================
+// short causal depthwise convolution (+ SiLU)
+//   xx = [cache[..., :], x] along time (cache slot p <-> time p - W);  y[t] = act(sum_j w[c][j] xx[t + 1 + j])
+// One thread: VEC adjacent channels x kConvTT consecutive tokens, sliding window in registers.
+// =============================================================================================
+constexpr int kConvTT = 16;
+
+template <int VEC, bool BF16>
+__device__ __forceinline__ void ld_vec(float (&dst)[VEC], const void* p, size_t i) {
+    if (BF16) {
+        if (VEC == 8) {
+            uint4 u = *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(p) + i);
+            const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                float2 f = __bfloat1622float2(h[j]);
+                dst[2 * j] = f.x;
+                dst[2 * j + 1] = f.y;
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < VEC; ++j) dst[j] = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p)[i + j]);
+        }
+    } else {
+        if (VEC == 4) {
+            float4 f = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p) + i);
+            dst[0] = f.x; dst[1] = f.y; dst[2] = f.z; dst[3] = f.w;
+        } else {
+#pragma unroll
+            for (int j = 0; j < VEC; ++j) dst[j] = reinterpret_cast<const float*>(p)[i + j];
+        }
+    }
+}
+
+template <int VEC, bool BF16>
+__device__ __forceinline__ void st_vec(void* p, size_t i, const float (&src)[VEC]) {
+    if (BF16) {
+        if (VEC == 8) {
+            uint4 u;
+            __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&u);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) h[j] = __floats2bfloat162_rn(src[2 * j], src[2 * j + 1]);
+            *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p) + i) = u;
+        } else {
+#pragma unroll
+            for (int j = 0; j < VEC; ++j) reinterpret_cast<__nv_bfloat16*>(p)[i + j] = __float2bfloat16(src[j]);
+        }
+    } else {
+        if (VEC == 4) {
+            *reinterpret_cast<float4*>(reinterpret_cast<float*>(p) + i) = make_float4(src[0], src[1], src[2], src[3]);
+        } else {
+#pragma unroll
+            for (int j = 0; j < VEC; ++j) reinterpret_cast<float*>(p)[i + j] = src[j];
+        }
+    }
+}
+
+// xx at time tau (tau < 0 reaches into the cache: slot W + tau), for VEC channels starting at c0
+template <int VEC, bool BF16>
+__device__ __forceinline__ void ld_xx(float (&dst)[VEC], const void* x, const void* cache, int b, int tau, int c0, int T,
+                                      int C, int W) {
+    if (tau >= 0) {
+        ld_vec<VEC, BF16>(dst, x, ((size_t)b * T + tau) * C + c0);
+    } else if (cache != nullptr && W + tau >= 0) {
+#pragma unroll
+        for (int j = 0; j < VEC; ++j) dst[j] = ld_io(cache, ((size_t)b * C + c0 + j) * W + (W + tau), BF16);
+    } else {
+#pragma unroll
+        for (int j = 0; j < VEC; ++j) dst[j] = 0.f;
+    }
+}
+
+template <int W, int VEC, bool BF16>
+__global__ void __launch_bounds__(256) conv_fwd_kernel(int B, int T, int C, int silu, const void* __restrict__ x,
+                                                       const void* __restrict__ wgt, const void* __restrict__ cache,
+                                                       void* __restrict__ y, void* __restrict__ fin) {
+    const int ncg = C / VEC, ntile = (T + kConvTT - 1) / kConvTT;
+    const size_t gid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (gid >= (size_t)B * ntile * ncg) return;
+    const int cg = (int)(gid % ncg), tile = (int)((gid / ncg) % ntile), b = (int)(gid / ((size_t)ncg * ntile));
+    const int c0 = cg * VEC, t0 = tile * kConvTT, t1 = min(T, t0 + kConvTT);
+    float wv[W][VEC];
+#pragma unroll
+    for (int j = 0; j < W; ++j)
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) wv[j][e] = ld_io(wgt, (size_t)(c0 + e) * W + j, BF16);
+    float win[W][VEC];   // win[j] = xx at time t - (W-1) + j
+#pragma unroll
+    for (int j = 0; j < W - 1; ++j) ld_xx<VEC, BF16>(win[j + 1], x, cache, b, t0 - (W - 1) + j, c0, T, C, W);
+    for (int t = t0; t < t1; ++t) {
+#pragma unroll
+        for (int j = 0; j < W - 1; ++j)
+#pragma unroll
+            for (int e = 0; e < VEC; ++e) win[j][e] = win[j + 1][e];
+        ld_vec<VEC, BF16>(win[W - 1], x, ((size_t)b * T + t) * C + c0);
+        float out[VEC];
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) {
+            float z = 0.f;
+#pragma unroll
+            for (int j = 0; j < W; ++j) z += wv[j][e] * win[j][e];
+            out[e] = silu ? z * sigmoidf_(z) : z;
+        }
+        st_vec<VEC, BF16>(y, ((size_t)b * T + t) * C + c0, out);
+    }
+    if (fin != nullptr && t1 == T) {
+        // cache slot j holds xx at time T - W + j
+        for (int j = 0; j < W; ++j) {
+            float tmp[VEC];
+            ld_xx<VEC, BF16>(tmp, x, cache, b, T - W + j, c0, T, C, W);
+#pragma unroll
+            for (int e = 0; e < VEC; ++e) st_io(fin, ((size_t)b * C + c0 + e) * W + j, BF16, tmp[e]);
+        }
+    }
+}
+
+// Backward.  blockDim = (32 channel groups, 8 time tiles).  Each thread recomputes the
+// pre-activations of its tile plus W-1 following tokens, emits dx for its tile and a
+// register partial of dweight; the 8 tiles of a block are summed in shared memory and
+// written as one partial per block, reduced in fixed order by conv_dw_reduce_kernel.
+constexpr int kConvBT = 32;  // tokens per thread in the backward
+
+template <int W, int VEC, bool BF16>
+__global__ void __launch_bounds__(256) conv_bwd_kernel(int B, int T, int C, int silu, const void* __restrict__ x,
+                                                       const void* __restrict__ wgt, const void* __restrict__ cache,
+                                                       const void* __restrict__ dy, const void* __restrict__ dfin,
+                                                       void* __restrict__ dx, void* __restrict__ dcache,
+                                                       float* __restrict__ dw_part) {
+    __shared__ float red[8][32][W * VEC];
+    const int ncg = C / VEC, ntile = (T + kConvBT - 1) / kConvBT;
+    const int cg = blockIdx.x * 32 + threadIdx.x;
+    const int tile = blockIdx.y * 8 + threadIdx.y;
+    const int b = blockIdx.z;
+    const bool active = cg < ncg && tile < ntile;
+    float dwv[W][VEC];
+#pragma unroll
+    for (int j = 0; j < W; ++j)
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) dwv[j][e] = 0.f;
+    if (active) {
+        const int c0 = cg * VEC, t0 = tile * kConvBT, t1 = min(T, t0 + kConvBT);
+        float wv[W][VEC];
+#pragma unroll
+        for (int j = 0; j < W; ++j)
+#pragma unroll
+            for (int e = 0; e < VEC; ++e) wv[j][e] = ld_io(wgt, (size_t)(c0 + e) * W + j, BF16);
+        float win[W][VEC];   // xx window ending at the token whose dz is being produced
+        float dzw[W][VEC];   // dzw[m] = dz at token (cur - (W-1) + m)
+#pragma unroll
+        for (int j = 0; j < W; ++j)
+#pragma unroll
+            for (int e = 0; e < VEC; ++e) dzw[j][e] = 0.f;
+#pragma unroll
+        for (int j = 0; j < W - 1; ++j) ld_xx<VEC, BF16>(win[j + 1], x, cache, b, t0 - (W - 1) + j, c0, T, C, W);
+        // walk cur over [t0, t1 + W - 1): produce dz[cur]; once W-1 tokens ahead, emit dx[cur - (W-1)]
+        for (int cur = t0; cur < t1 + W - 1; ++cur) {
+#pragma unroll
+            for (int j = 0; j < W - 1; ++j)
+#pragma unroll
+                for (int e = 0; e < VEC; ++e) {
+                    win[j][e] = win[j + 1][e];
+                    dzw[j][e] = dzw[j + 1][e];
+                }
+            if (cur < T) {
+                ld_vec<VEC, BF16>(win[W - 1], x, ((size_t)b * T + cur) * C + c0);
+                float g[VEC];
+                ld_vec<VEC, BF16>(g, dy, ((size_t)b * T + cur) * C + c0);
+#pragma unroll
+                for (int e = 0; e < VEC; ++e) {
+                    float z = 0.f;
+#pragma unroll
+                    for (int j = 0; j < W; ++j) z += wv[j][e] * win[j][e];
+                    if (silu) {
+                        const float sg = sigmoidf_(z);
+                        g[e] *= sg * (1.f + z * (1.f - sg));
+                    }
+                    dzw[W - 1][e] = g[e];
+                    if (cur < t1) {
+#pragma unroll
+                        for (int j = 0; j < W; ++j) dwv[j][e] += g[e] * win[j][e];
+                    }
+                }
+            } else {
+#pragma unroll
+                for (int e = 0; e < VEC; ++e) { dzw[W - 1][e] = 0.f; win[W - 1][e] = 0.f; }
+            }
+            const int t = cur - (W - 1);     // dx[t] = sum_j w[j] dz[t + W-1-j] = sum_j w[j] dzw[W-1-j]
+            if (t >= t0 && t < t1) {
+                float out[VEC];
+#pragma unroll
+                for (int e = 0; e < VEC; ++e) {
+                    float a = 0.f;
+#pragma unroll
+                    for (int j = 0; j < W; ++j) a += wv[j][e] * dzw[W - 1 - j][e];
+                    if (dfin != nullptr && t >= T - W) a += ld_io(dfin, ((size_t)b * C + c0 + e) * W + (W + t - T), BF16);
+                    out[e] = a;
+                }
+                st_vec<VEC, BF16>(dx, ((size_t)b * T + t) * C + c0, out);
+            }
+        }
+        if (dcache != nullptr && tile == 0) {
+            // cache slot p is time p - W (< 0): d = sum_j w[j] dz[p - W + W-1-j] = sum_j w[j] dz[p-1-j], plus the
+            // final-state cotangent when the sequence is shorter than the window.  Needs dz[0 .. W-2]: recompute.
+            float dz0[W][VEC];
+#pragma unroll
+            for (int m = 0; m < W; ++m)
+#pragma unroll
+                for (int e = 0; e < VEC; ++e) dz0[m][e] = 0.f;
+            float w2[W][VEC];
+#pragma unroll
+            for (int j = 0; j < W - 1; ++j) ld_xx<VEC, BF16>(w2[j + 1], x, cache, b, -(W - 1) + j, c0, T, C, W);
+            for (int t = 0; t < W - 1 && t < T; ++t) {
+#pragma unroll
+                for (int j = 0; j < W - 1; ++j)
+#pragma unroll
+                    for (int e = 0; e < VEC; ++e) w2[j][e] = w2[j + 1][e];
+                ld_vec<VEC, BF16>(w2[W - 1], x, ((size_t)b * T + t) * C + c0);
+                float g[VEC];
+                ld_vec<VEC, BF16>(g, dy, ((size_t)b * T + t) * C + c0);
+#pragma unroll
+                for (int e = 0; e < VEC; ++e) {
+                    float z = 0.f;
+#pragma unroll
+                    for (int j = 0; j < W; ++j) z += wv[j][e] * w2[j][e];
+                    if (silu) {
+                        const float sg = sigmoidf_(z);
+                        g[e] *= sg * (1.f + z * (1.f - sg));
+                    }
+#pragma unroll
+                    for (int m = 0; m < W; ++m)
+                        if (m == t) dz0[m][e] = g[e];
+                }
+            }
+#pragma unroll
+            for (int p = 0; p < W; ++p)
+#pragma unroll
+                for (int e = 0; e < VEC; ++e) {
+                    float a = 0.f;
+#pragma unroll
+                    for (int j = 0; j < W; ++j) {
+                        const int m = p - 1 - j;
+                        if (m >= 0 && m < W) a += wv[j][e] * dz0[m][e];
+                    }
+                    if (dfin != nullptr && p - T >= 0) a += ld_io(dfin, ((size_t)b * C + c0 + e) * W + (p - T), BF16);
+                    st_io(dcache, ((size_t)b * C + c0 + e) * W + p, BF16, a);
+                }
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < W; ++j)
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) red[threadIdx.y][threadIdx.x][j * VEC + e] = dwv[j][e];
+    __syncthreads();
+    if (threadIdx.y == 0 && cg < ncg) {
+        const size_t pblk = (size_t)blockIdx.z * gridDim.y + blockIdx.y;
+#pragma unroll
+        for (int j = 0; j < W; ++j)
+#pragma unroll
+            for (int e = 0; e < VEC; ++e) {
+                float a = 0.f;
+#pragma unroll
+                for (int r = 0; r < 8; ++r) a += red[r][threadIdx.x][j * VEC + e];
+                dw_part[(pblk * C + cg * VEC + e) * W + j] = a;
+            }
+    }
+}
+
+__global__ void conv_dw_reduce_kernel(int nblk, int CW, const float* __restrict__ part, float* __restrict__ dw) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= CW) return;
+    float a = 0.f;
+    for (int b = 0; b < nblk; ++b) a += part[(size_t)b * CW + i];
+    dw[i] = a;
+}
+
+// =============================================================================================
+// gated RMSNorm:  y = x * inv * w * sigmoid(gate),  inv = rsqrt(mean(x^2) + eps).  One warp per row.
+// =============================================================================================
+template <bool BF16>
+__device__ __forceinline__ void ld4(float (&d)[4], const void* p, size_t i) {
+    if (BF16) {
+        uint2 u = *reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(p) + i);
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+        float2 a = __bfloat1622float2(h[0]), b = __bfloat1622float2(h[1]);
+        d[0] = a.x; d[1] = a.y; d[2] = b.x; d[3] = b.y;
+    } else {
+        float4 f = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p) + i);
+        d[0] = f.x; d[1] = f.y; d[2] = f.z; d[3] = f.w;
+    }
+}
+template <bool BF16>
+__device__ __forceinline__ void st4(void* p, size_t i, const float (&s)[4]) {
+    if (BF16) {
+        uint2 u;
+        __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&u);
+        h[0] = __floats2bfloat162_rn(s[0], s[1]);
+        h[1] = __floats2bfloat162_rn(s[2], s[3]);
+        *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(p) + i) = u;
+    } else {
+        *reinterpret_cast<float4*>(reinterpret_cast<float*>(p) + i) = make_float4(s[0], s[1], s[2], s[3]);
+    }
+}
+
+// VEC4: dim % 128 == 0, lane owns 4 contiguous elements per 128-wide segment; else scalar stride-32.
+template <bool BF16, bool VEC4>
+__global__ void __launch_bounds__(256) rmsnorm_fwd_kernel(long long rows, int D, float eps, const void* __restrict__ x,
+                                                          const void* __restrict__ gate, const float* __restrict__ w,
+                                                          void* __restrict__ y, float* __restrict__ inv_rms) {
+    const int lane = threadIdx.x & 31;
+    const long long warp0 = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+    const long long nwarp = (long long)gridDim.x * 8;
+    for (long long row = warp0; row < rows; row += nwarp) {
+        const size_t base = (size_t)row * D;
+        float ss = 0.f;
+        if (VEC4) {
+            for (int d = 4 * lane; d < D; d += 128) {
+                float a[4];
+                ld4<BF16>(a, x, base + d);
+                ss += a[0] * a[0] + a[1] * a[1] + a[2] * a[2] + a[3] * a[3];
+            }
+        } else {
+            for (int d = lane; d < D; d += 32) {
+                float a = ld_io(x, base + d, BF16);
+                ss += a * a;
+            }
+        }
+        ss = warp_sum(ss);
+        const float inv = rsqrtf(ss / (float)D + eps);
+        if (lane == 0) inv_rms[row] = inv;
+        if (VEC4) {
+            for (int d = 4 * lane; d < D; d += 128) {
+                float a[4], gt[4], out[4];
+                ld4<BF16>(a, x, base + d);
+                ld4<BF16>(gt, gate, base + d);
+                const float4 ww = *reinterpret_cast<const float4*>(w + d);
+                const float wa[4] = {ww.x, ww.y, ww.z, ww.w};
+#pragma unroll
+                for (int e = 0; e < 4; ++e) out[e] = a[e] * inv * wa[e] * sigmoidf_(gt[e]);
+                st4<BF16>(y, base + d, out);
+            }
+        } else {
+            for (int d = lane; d < D; d += 32)
+                st_io(y, base + d, BF16, ld_io(x, base + d, BF16) * inv * w[d] * sigmoidf_(ld_io(gate, base + d, BF16)));
+        }
+    }
+}
+
+// Backward: u = n*w, y = u*s;  dgate = dy*u*s*(1-s);  du = dy*s;  dw += du*n;  dn = du*w;
+//           dx = inv * (dn - n * mean(dn*n)).
+// dweight: every warp accumulates its rows into its own shared-memory row, the block sums the
+// eight rows in fixed order and writes one partial per block.
+template <bool BF16, bool VEC4>
+__global__ void __launch_bounds__(256) rmsnorm_bwd_kernel(long long rows, int D, const void* __restrict__ x,
+                                                          const void* __restrict__ gate, const float* __restrict__ w,
+                                                          const float* __restrict__ inv_rms, const void* __restrict__ dy,
+                                                          void* __restrict__ dx, void* __restrict__ dgate,
+                                                          float* __restrict__ dw_part) {
+    extern __shared__ float dws[];   // [8][D]
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    float* mine = dws + (size_t)wid * D;
+    for (int d = lane; d < D; d += 32) mine[d] = 0.f;
+    const long long warp0 = (long long)blockIdx.x * 8 + wid;
+    const long long nwarp = (long long)gridDim.x * 8;
+    for (long long row = warp0; row < rows; row += nwarp) {
+        const size_t base = (size_t)row * D;
+        const float inv = inv_rms[row];
+        float dot = 0.f;
+        if (VEC4) {
+            for (int d = 4 * lane; d < D; d += 128) {
+                float a[4], gt[4], gy[4];
+                ld4<BF16>(a, x, base + d);
+                ld4<BF16>(gt, gate, base + d);
+                ld4<BF16>(gy, dy, base + d);
+                const float4 ww = *reinterpret_cast<const float4*>(w + d);
+                const float wa[4] = {ww.x, ww.y, ww.z, ww.w};
+#pragma unroll
+                for (int e = 0; e < 4; ++e) dot += gy[e] * sigmoidf_(gt[e]) * wa[e] * a[e] * inv;
+            }
+        } else {
+            for (int d = lane; d < D; d += 32)
+                dot += ld_io(dy, base + d, BF16) * sigmoidf_(ld_io(gate, base + d, BF16)) * w[d] * ld_io(x, base + d, BF16) * inv;
+        }
+        dot = warp_sum(dot) / (float)D;
+        if (VEC4) {
+            for (int d = 4 * lane; d < D; d += 128) {
+                float a[4], gt[4], gy[4], ox[4], og[4];
+                ld4<BF16>(a, x, base + d);
+                ld4<BF16>(gt, gate, base + d);
+                ld4<BF16>(gy, dy, base + d);
+                const float4 ww = *reinterpret_cast<const float4*>(w + d);
+                const float wa[4] = {ww.x, ww.y, ww.z, ww.w};
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float n = a[e] * inv, s = sigmoidf_(gt[e]);
+                    const float du = gy[e] * s;
+                    og[e] = gy[e] * n * wa[e] * s * (1.f - s);
+                    ox[e] = inv * (du * wa[e] - n * dot);
+                    mine[d + e] += du * n;
+                }
+                st4<BF16>(dx, base + d, ox);
+                st4<BF16>(dgate, base + d, og);
+            }
+        } else {
+            for (int d = lane; d < D; d += 32) {
+                const float n = ld_io(x, base + d, BF16) * inv, s = sigmoidf_(ld_io(gate, base + d, BF16));
+                const float gyv = ld_io(dy, base + d, BF16);
+                const float du = gyv * s;
+                st_io(dgate, base + d, BF16, gyv * n * w[d] * s * (1.f - s));
+                st_io(dx, base + d, BF16, inv * (du * w[d] - n * dot));
+                mine[d] += du * n;
+            }
+        }
+    }
+    __syncthreads();
+    for (int d = threadIdx.x; d < D; d += 256) {
+        float a = 0.f;
+#pragma unroll
+        for (int r = 0; r < 8; ++r) a += dws[(size_t)r * D + d];
+        dw_part[(size_t)blockIdx.x * D + d] = a;
+    }
+}
+
+__global__ void rmsnorm_dw_reduce_kernel(int nblk, int D, const float* __restrict__ part, float* __restrict__ dw) {
+    const int d = blockIdx.x * blockDim.x + threadIdx.x;
+    if (d >= D) return;
+    float a = 0.f;
+    for (int b = 0; b < nblk; ++b) a += part[(size_t)b * D + d];
+    dw[d] = a;
+}
+
+}  // namespace pw
+}  // namespace kda
+
+// =============================================================================================
+// C ABI
+// =============================================================================================
+using namespace kda;
+
+extern "C" int kda_gate_fwd(int32_t tokens, int32_t heads, int32_t key_dim, int32_t io_dtype, const void* raw_gate,
+                            const void* beta_logits, const float* A_log, const float* dt_bias, float lower_bound,
+                            float* g_out, float* beta_out, void* stream) {
+    if (tokens < 0 || heads <= 0 || key_dim <= 0) return KDA_ERR_BAD_SHAPE;
+    if (tokens == 0) return KDA_OK;
+    if (!raw_gate || !beta_logits || !A_log || !dt_bias || !g_out || !beta_out) return KDA_ERR_NULL;
+    const size_t n = (size_t)tokens * heads * key_dim;
+    const int blocks = (int)std::min<size_t>((n + 255) / 256, 148 * 16);
+    KDA_LAUNCH("gate_fwd_kernel", (cudaStream_t)stream, pw::gate_fwd_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(n, (size_t)tokens * heads, heads, key_dim,
+                                                                   io_dtype == KDA_DTYPE_BF16, raw_gate, beta_logits,
+                                                                   A_log, dt_bias, lower_bound, g_out, beta_out));
+    return launch_status();
+}
+
+extern "C" size_t kda_gate_bwd_scratch_bytes(int32_t tokens, int32_t heads, int32_t key_dim) {
+    const size_t nblk = (size_t)ceil_div(tokens > 0 ? tokens : 1, pw::kGateRows);
+    return align_up(2 * nblk * heads * key_dim * sizeof(float), 256);
+}
+
+extern "C" int kda_gate_bwd(int32_t tokens, int32_t heads, int32_t key_dim, int32_t io_dtype, const void* raw_gate,
+                            const void* beta_logits, const float* A_log, const float* dt_bias, float lower_bound,
+                            const float* dg, const float* dbeta, void* d_raw_gate, void* d_beta_logits, float* dA_log,
+                            float* ddt_bias, void* scratch, size_t scratch_bytes, void* stream) {
+    if (tokens < 0 || heads <= 0 || key_dim <= 0) return KDA_ERR_BAD_SHAPE;
+    if (!A_log || !dt_bias || !dA_log || !ddt_bias) return KDA_ERR_NULL;
+    if (tokens > 0 && (!raw_gate || !beta_logits || !dg || !dbeta || !d_raw_gate || !d_beta_logits)) return KDA_ERR_NULL;
+    if (!scratch || scratch_bytes < kda_gate_bwd_scratch_bytes(tokens, heads, key_dim)) return KDA_ERR_WORKSPACE;
+    cudaStream_t st = (cudaStream_t)stream;
+    const int nblk = tokens > 0 ? ceil_div(tokens, pw::kGateRows) : 0;
+    float* part_b = static_cast<float*>(scratch);
+    float* part_a = part_b + (size_t)(nblk > 0 ? nblk : 1) * heads * key_dim;
+    if (nblk > 0)
+        KDA_LAUNCH("gate_bwd_kernel", st, pw::gate_bwd_kernel<<<nblk, 256, 0, st>>>(tokens, heads, key_dim, io_dtype == KDA_DTYPE_BF16, raw_gate,
+                                                  beta_logits, A_log, dt_bias, lower_bound, dg, dbeta, d_raw_gate,
+                                                  d_beta_logits, part_b, part_a));
+    KDA_LAUNCH("gate_bwd_reduce_kernel", st, pw::gate_bwd_reduce_kernel<<<heads, 256, 0, st>>>(nblk, heads, key_dim, part_b, part_a, ddt_bias, dA_log));
+    return launch_status();
+}
+
+extern "C" int kda_decode_step(int32_t n_seq, int32_t heads, int32_t key_dim, int32_t value_dim, int32_t io_dtype,
+                               int32_t gate_dtype, int32_t l2norm, float scale, const void* q, const void* k, const void* v, const void* g,
+                               const void* beta, const float* state_in, float* state_out, void* o, void* stream) {
+    if (n_seq < 0 || heads <= 0 || key_dim <= 0 || value_dim <= 0 || key_dim > KDA_MAX_DIM || value_dim > KDA_MAX_DIM)
+        return KDA_ERR_BAD_SHAPE;
+    if (n_seq == 0) return KDA_OK;
+    if (!q || !k || !v || !g || !beta || !state_in || !state_out || !o) return KDA_ERR_NULL;
+    const int bf16 = io_dtype == KDA_DTYPE_BF16, gbf16 = gate_dtype == KDA_DTYPE_BF16;
+    // rows per CTA: 32 (8 warps x 4 rows); fewer CTAs per (sequence, head) once the grid is large enough
+    const int rows_per_cta = 32;
+    dim3 grid(n_seq * heads, ceil_div(value_dim, rows_per_cta));
+    const bool vec = (key_dim % 4 == 0) && ((reinterpret_cast<uintptr_t>(state_in) | reinterpret_cast<uintptr_t>(state_out)) % 16 == 0);
+    if (vec)
+        KDA_LAUNCH("decode_kernel", (cudaStream_t)stream, pw::decode_kernel<true><<<grid, 256, 0, (cudaStream_t)stream>>>(heads, key_dim, value_dim, bf16, gbf16, l2norm, scale, q, k,
+                                                                         v, g, beta, state_in, state_out, o, rows_per_cta));
+    else
+        KDA_LAUNCH("decode_kernel", (cudaStream_t)stream, pw::decode_kernel<false><<<grid, 256, 0, (cudaStream_t)stream>>>(heads, key_dim, value_dim, bf16, gbf16, l2norm, scale, q,
+                                                                          k, v, g, beta, state_in, state_out, o, rows_per_cta));
+    return launch_status();
+}
+
+namespace {
+
+template <int W>
+int conv_fwd_w(int B, int T, int C, int bf16, int silu, const void* x, const void* w, const void* cache, void* y,
+               void* fin, cudaStream_t st) {
+    const int ntile = ceil_div(T, pw::kConvTT);
+    auto blocks = [&](int vec) { return (unsigned)(((size_t)B * ntile * (C / vec) + 255) / 256); };
+    const bool al16 = ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y)) % 16) == 0;
+    if (bf16) {
+        if (C % 8 == 0 && al16) KDA_LAUNCH("conv_fwd_kernel", st, pw::conv_fwd_kernel<W, 8, true><<<blocks(8), 256, 0, st>>>(B, T, C, silu, x, w, cache, y, fin));
+        else KDA_LAUNCH("conv_fwd_kernel", st, pw::conv_fwd_kernel<W, 1, true><<<blocks(1), 256, 0, st>>>(B, T, C, silu, x, w, cache, y, fin));
+    } else {
+        if (C % 4 == 0 && al16) KDA_LAUNCH("conv_fwd_kernel", st, pw::conv_fwd_kernel<W, 4, false><<<blocks(4), 256, 0, st>>>(B, T, C, silu, x, w, cache, y, fin));
+        else KDA_LAUNCH("conv_fwd_kernel", st, pw::conv_fwd_kernel<W, 1, false><<<blocks(1), 256, 0, st>>>(B, T, C, silu, x, w, cache, y, fin));
+    }
+    return launch_status();
+}
+
+inline void conv_bwd_grid(int B, int T, int C, int vec, dim3& grid) {
+    grid = dim3(ceil_div(C / vec, 32), ceil_div(ceil_div(T, pw::kConvBT), 8), B);
+}
+
+template <int W>
+int conv_bwd_w(int B, int T, int C, int bf16, int silu, const void* x, const void* w, const void* cache, const void* dy,
+               const void* dfin, void* dx, void* dcache, float* dwgt, float* part, cudaStream_t st) {
+    const bool al16 = ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(dy) | reinterpret_cast<uintptr_t>(dx)) % 16) == 0;
+    dim3 grid, block(32, 8);
+    // the vector path keeps W*VEC partials per thread in shared memory; wide windows use the scalar path
+    constexpr bool kVecOk = W <= 4;
+    if (bf16) {
+        if constexpr (kVecOk) {
+            if (C % 8 == 0 && al16) {
+                conv_bwd_grid(B, T, C, 8, grid);
+                KDA_LAUNCH("conv_bwd_kernel", st, pw::conv_bwd_kernel<W, 8, true><<<grid, block, 0, st>>>(B, T, C, silu, x, w, cache, dy, dfin, dx, dcache, part));
+            }
+        }
+        if (!(kVecOk && C % 8 == 0 && al16)) {
+            conv_bwd_grid(B, T, C, 1, grid);
+            KDA_LAUNCH("conv_bwd_kernel", st, pw::conv_bwd_kernel<W, 1, true><<<grid, block, 0, st>>>(B, T, C, silu, x, w, cache, dy, dfin, dx, dcache, part));
+        }
+    } else {
+        if constexpr (kVecOk) {
+            if (C % 4 == 0 && al16) {
+                conv_bwd_grid(B, T, C, 4, grid);
+                KDA_LAUNCH("conv_bwd_kernel", st, pw::conv_bwd_kernel<W, 4, false><<<grid, block, 0, st>>>(B, T, C, silu, x, w, cache, dy, dfin, dx, dcache, part));
+            }
+        }
+        if (!(kVecOk && C % 4 == 0 && al16)) {
+            conv_bwd_grid(B, T, C, 1, grid);
+            KDA_LAUNCH("conv_bwd_kernel", st, pw::conv_bwd_kernel<W, 1, false><<<grid, block, 0, st>>>(B, T, C, silu, x, w, cache, dy, dfin, dx, dcache, part));
+        }
+    }
+    const int nblk = grid.y * grid.z;
+    KDA_LAUNCH("conv_dw_reduce_kernel", st, pw::conv_dw_reduce_kernel<<<ceil_div(C * W, 256), 256, 0, st>>>(nblk, C * W, part, dwgt));
+    return launch_status();
+}
+
+}  // namespace
+
+#define KDA_CONV_SWITCH(CALL)            \
+    switch (width) {                     \
+        case 1: return CALL(1);          \
+        case 2: return CALL(2);          \
+        case 3: return CALL(3);          \
+        case 4: return CALL(4);          \
+        case 5: return CALL(5);          \
+        case 6: return CALL(6);          \
+        case 7: return CALL(7);          \
+        case 8: return CALL(8);          \
+        default: return KDA_ERR_UNSUPPORTED; \
+    }
+
+extern "C" int kda_conv_fwd(int32_t batch, int32_t seq_len, int32_t channels, int32_t width, int32_t io_dtype,
+                            int32_t silu, const void* x, const void* weight, const void* initial_state, void* y,
+                            void* final_state, void* stream) {
+    if (batch <= 0 || seq_len <= 0 || channels <= 0 || width <= 0) return KDA_ERR_BAD_SHAPE;
+    if (!x || !weight || !y) return KDA_ERR_NULL;
+    const int bf16 = io_dtype == KDA_DTYPE_BF16;
+    cudaStream_t st = (cudaStream_t)stream;
+#define CALL(WW) conv_fwd_w<WW>(batch, seq_len, channels, bf16, silu, x, weight, initial_state, y, final_state, st)
+    KDA_CONV_SWITCH(CALL)
+#undef CALL
+}
+
+extern "C" size_t kda_conv_bwd_scratch_bytes(int32_t batch, int32_t seq_len, int32_t channels, int32_t width) {
+    const size_t nblk = (size_t)ceil_div(ceil_div(seq_len > 0 ? seq_len : 1, pw::kConvBT), 8) * (batch > 0 ? batch : 1);
+    return align_up(nblk * channels * width * sizeof(float), 256);
+}
+
+extern "C" int kda_conv_bwd(int32_t batch, int32_t seq_len, int32_t channels, int32_t width, int32_t io_dtype,
+                            int32_t silu, const void* x, const void* weight, const void* initial_state, const void* d_y,
+                            const void* d_final_state, void* dx, float* dweight, void* d_initial_state, void* scratch,
+                            size_t scratch_bytes, void* stream) {
+    if (batch <= 0 || seq_len <= 0 || channels <= 0 || width <= 0) return KDA_ERR_BAD_SHAPE;
+    if (!x || !weight || !d_y || !dx || !dweight) return KDA_ERR_NULL;
+    if (!scratch || scratch_bytes < kda_conv_bwd_scratch_bytes(batch, seq_len, channels, width)) return KDA_ERR_WORKSPACE;
+    const int bf16 = io_dtype == KDA_DTYPE_BF16;
+    cudaStream_t st = (cudaStream_t)stream;
+#define CALL(WW)                                                                                                  \
+    conv_bwd_w<WW>(batch, seq_len, channels, bf16, silu, x, weight, initial_state, d_y, d_final_state, dx,        \
+                   d_initial_state, dweight, static_cast<float*>(scratch), st)
+    KDA_CONV_SWITCH(CALL)
+#undef CALL
+}
+
+namespace {
+inline int rms_blocks(long long rows) { return (int)std::min<long long>((rows + 7) / 8, 148LL * 8); }
+}  // namespace
+
+extern "C" int kda_rmsnorm_gate_fwd(int64_t rows, int32_t dim, int32_t io_dtype, float eps, const void* x,
+                                    const void* gate, const float* weight, void* y, float* inv_rms, void* stream) {
+    if (rows < 0 || dim <= 0 || dim > 1024) return KDA_ERR_BAD_SHAPE;
+    if (rows == 0) return KDA_OK;
+    if (!x || !gate || !weight || !y || !inv_rms) return KDA_ERR_NULL;
+    cudaStream_t st = (cudaStream_t)stream;
+    const int nb = rms_blocks(rows);
+    const bool vec = dim % 128 == 0 &&
+                     ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(gate) | reinterpret_cast<uintptr_t>(y) |
+                       reinterpret_cast<uintptr_t>(weight)) % 16) == 0;
+    if (io_dtype == KDA_DTYPE_BF16) {
+        if (vec) KDA_LAUNCH("rmsnorm_fwd_kernel", st, pw::rmsnorm_fwd_kernel<true, true><<<nb, 256, 0, st>>>(rows, dim, eps, x, gate, weight, y, inv_rms));
+        else KDA_LAUNCH("rmsnorm_fwd_kernel", st, pw::rmsnorm_fwd_kernel<true, false><<<nb, 256, 0, st>>>(rows, dim, eps, x, gate, weight, y, inv_rms));
+    } else {
+        if (vec) KDA_LAUNCH("rmsnorm_fwd_kernel", st, pw::rmsnorm_fwd_kernel<false, true><<<nb, 256, 0, st>>>(rows, dim, eps, x, gate, weight, y, inv_rms));
+        else KDA_LAUNCH("rmsnorm_fwd_kernel", st, pw::rmsnorm_fwd_kernel<false, false><<<nb, 256, 0, st>>>(rows, dim, eps, x, gate, weight, y, inv_rms));
+    }
+    return launch_status();
+}
+
+extern "C" size_t kda_rmsnorm_gate_bwd_scratch_bytes(int64_t rows, int32_t dim) {
+    return align_up((size_t)rms_blocks(rows > 0 ? rows : 1) * dim * sizeof(float), 256);
+}
+
+extern "C" int kda_rmsnorm_gate_bwd(int64_t rows, int32_t dim, int32_t io_dtype, const void* x, const void* gate,
+                                    const float* weight, const float* inv_rms, const void* d_y, void* dx, void* dgate,
+                                    float* dweight, void* scratch, size_t scratch_bytes, void* stream) {
+    if (rows < 0 || dim <= 0 || dim > 1024) return KDA_ERR_BAD_SHAPE;
+    if (!weight || !dweight) return KDA_ERR_NULL;
+    if (rows > 0 && (!x || !gate || !inv_rms || !d_y || !dx || !dgate)) return KDA_ERR_NULL;
+    if (!scratch || scratch_bytes < kda_rmsnorm_gate_bwd_scratch_bytes(rows, dim)) return KDA_ERR_WORKSPACE;
+    cudaStream_t st = (cudaStream_t)stream;
+    const int nb = rows > 0 ? rms_blocks(rows) : 0;
+    float* part = static_cast<float*>(scratch);
+    const size_t smem = (size_t)8 * dim * sizeof(float);
+    const bool vec = dim % 128 == 0 &&
+                     ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(gate) | reinterpret_cast<uintptr_t>(d_y) |
+                       reinterpret_cast<uintptr_t>(dx) | reinterpret_cast<uintptr_t>(dgate) | reinterpret_cast<uintptr_t>(weight)) % 16) == 0;
+    if (nb > 0) {
+        if (io_dtype == KDA_DTYPE_BF16) {
+            if (vec) KDA_LAUNCH("rmsnorm_bwd_kernel", st, pw::rmsnorm_bwd_kernel<true, true><<<nb, 256, smem, st>>>(rows, dim, x, gate, weight, inv_rms, d_y, dx, dgate, part));
+            else KDA_LAUNCH("rmsnorm_bwd_kernel", st, pw::rmsnorm_bwd_kernel<true, false><<<nb, 256, smem, st>>>(rows, dim, x, gate, weight, inv_rms, d_y, dx, dgate, part));
+        } else {
+            if (vec) KDA_LAUNCH("rmsnorm_bwd_kernel", st, pw::rmsnorm_bwd_kernel<false, true><<<nb, 256, smem, st>>>(rows, dim, x, gate, weight, inv_rms, d_y, dx, dgate, part));
+            else KDA_LAUNCH("rmsnorm_bwd_kernel", st, pw::rmsnorm_bwd_kernel<false, false><<<nb, 256, smem, st>>>(rows, dim, x, gate, weight, inv_rms, d_y, dx, dgate, part));
+        }
+    }
+    KDA_LAUNCH("rmsnorm_dw_reduce_kernel", st, pw::rmsnorm_dw_reduce_kernel<<<ceil_div(dim, 256), 256, 0, st>>>(nb, dim, part, dweight));
+    return launch_status();
+}

@@ -1,0 +1,320 @@
+"""Tensor-level operators over the C ABI: allocation, stream and autograd plumbing only.
+
+PyTorch is used for device memory, the current CUDA stream and autograd bookkeeping;
+every arithmetic step runs in libkda_b200.so.  Nothing here falls back to PyTorch math.
+"""
+
+from __future__ import annotations
+
+from typing import Optional, Tuple
+
+import torch
+
+from . import _lib
+
+Tensor = torch.Tensor
+
+_DT = {torch.float32: _lib.DTYPE_F32, torch.bfloat16: _lib.DTYPE_BF16}
+
+
+def _dt(t: Tensor) -> int:
+    try:
+        return _DT[t.dtype]
+    except KeyError:
+        raise RuntimeError(f"KDA kernels take float32 or bfloat16 tensors, got {t.dtype}") from None
+
+
+def _ptr(t: Optional[Tensor]):
+    return None if t is None else t.data_ptr()
+
+
+def _stream(dev) -> int:
+    return torch.cuda.current_stream(dev).cuda_stream
+
+
+def _need_cuda(*ts):
+    dev = None
+    for t in ts:
+        if t is None:
+            continue
+        if not t.is_cuda:
+            raise RuntimeError("KDA CUDA operators cannot run on CPU tensors (there is no CPU fallback)")
+        if dev is None:
+            dev = t.device
+        elif t.device != dev:
+            raise RuntimeError("all KDA tensors must be on the same CUDA device")
+    return dev
+
+
+def _bytes(n: int, dev) -> Tensor:
+    return torch.empty(max(int(n), 256), dtype=torch.uint8, device=dev)
+
+
+# --------------------------------------------------------------------------------------------
+# chunked KDA on activated inputs
+# --------------------------------------------------------------------------------------------
+
+def _shape(q, v, g, n_seq, seq_len, scale, l2norm, lane) -> "_lib.ChunkShape":
+    tokens = q.shape[0] * q.shape[1]
+    return _lib.ChunkShape(n_seq, seq_len, tokens, q.shape[2], q.shape[3], v.shape[3], _dt(q), _dt(g), lane,
+                           1 if l2norm else 0, float(scale))
+
+
+def chunk_kda_fwd(q, k, v, g, beta, h0, cu_seqlens, scale, l2norm, want_final, lane=_lib.LANE_FP32):
+    """Returns (o, final_state or None, saved) where saved = (shape, workspace) for the backward."""
+    lib = _lib.load()
+    dev = _need_cuda(q, k, v, g, beta, h0, cu_seqlens)
+    B, T, H, K = q.shape
+    V = v.shape[-1]
+    if cu_seqlens is not None:
+        n_seq, seq_len = cu_seqlens.numel() - 1, 0
+    else:
+        n_seq, seq_len = B, T
+    sh = _shape(q, v, g, n_seq, seq_len, scale, l2norm, lane)
+    o = torch.empty(B, T, H, V, dtype=v.dtype, device=dev)
+    fs = torch.empty(n_seq, H, V, K, dtype=torch.float32, device=dev) if want_final else None
+    nbytes = lib.kda_chunk_workspace_bytes(sh)
+    ws = _bytes(nbytes, dev)
+    with torch.cuda.device(dev):
+        rc = lib.kda_chunk_fwd(sh, _ptr(q), _ptr(k), _ptr(v), _ptr(g), _ptr(beta), _ptr(h0), _ptr(cu_seqlens), _ptr(o),
+                               _ptr(fs), _ptr(ws), ws.numel(), _stream(dev))
+    _lib.check(rc, "kda_chunk_fwd")
+    return o, fs, (sh, ws)
+
+
+def chunk_kda_bwd(q, k, v, g, beta, cu_seqlens, do, dfs, saved, want_dh0):
+    lib = _lib.load()
+    sh, ws = saved
+    dev = q.device
+    dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+    dg, db = torch.empty_like(g), torch.empty_like(beta)
+    n_seq = sh.n_seq
+    dh0 = torch.empty(n_seq, sh.heads, sh.value_dim, sh.key_dim, dtype=torch.float32, device=dev) if want_dh0 else None
+    scr = _bytes(lib.kda_chunk_bwd_scratch_bytes(sh), dev)
+    with torch.cuda.device(dev):
+        rc = lib.kda_chunk_bwd(sh, _ptr(q), _ptr(k), _ptr(v), _ptr(g), _ptr(beta), _ptr(cu_seqlens), _ptr(do), _ptr(dfs),
+                               _ptr(ws), ws.numel(), _ptr(scr), scr.numel(), _ptr(dq), _ptr(dk), _ptr(dv), _ptr(dg),
+                               _ptr(db), _ptr(dh0), _stream(dev))
+    _lib.check(rc, "kda_chunk_bwd")
+    return dq, dk, dv, dg, db, dh0
+
+
+class ChunkKDAFunction(torch.autograd.Function):
+    """Autograd boundary of the chunked operator on activated inputs.
+
+    Argument list of the operator surface: (q, k, v, g, beta, initial_state,
+    output_final_state, cu_seqlens) plus scale / l2norm / lane.  Mirrors the role of
+    the reference's _ProjectKDAAutograd (nanochat/mixers/kda.py:383-415).
+    """
+
+    @staticmethod
+    def forward(ctx, q, k, v, g, beta, initial_state, output_final_state, cu_seqlens, scale, l2norm, lane):
+        q, k, v, g, beta = (t.contiguous() for t in (q, k, v, g, beta))
+        h0 = None if initial_state is None else initial_state.contiguous()
+        o, fs, saved = chunk_kda_fwd(q, k, v, g, beta, h0, cu_seqlens, scale, l2norm, output_final_state, lane)
+        ctx.saved = saved
+        ctx.cu = cu_seqlens
+        ctx.has_h0 = initial_state is not None
+        ctx.save_for_backward(q, k, v, g, beta)
+        ctx.set_materialize_grads(False)
+        return o, fs
+
+    @staticmethod
+    def backward(ctx, do, dfs):
+        q, k, v, g, beta = ctx.saved_tensors
+        do = torch.zeros_like(v) if do is None else do.contiguous()
+        if dfs is not None:
+            dfs = dfs.contiguous().float()
+        dq, dk, dv, dg, db, dh0 = chunk_kda_bwd(q, k, v, g, beta, ctx.cu, do, dfs, ctx.saved, ctx.has_h0)
+        ctx.saved = None
+        return dq, dk, dv, dg, db, dh0, None, None, None, None, None
+
+
+# --------------------------------------------------------------------------------------------
+# gate activations
+# --------------------------------------------------------------------------------------------
+
+class GateFunction(torch.autograd.Function):
+    """(raw_gate, beta_logits, A_log, dt_bias) -> (g, beta) in float32, with the parameter
+    gradients reduced deterministically (reference chunk_wy_backward.cu:3881-3987)."""
+
+    @staticmethod
+    def forward(ctx, raw_gate, beta_logits, A_log, dt_bias, lower_bound):
+        lib = _lib.load()
+        dev = _need_cuda(raw_gate, beta_logits, A_log, dt_bias)
+        raw_gate, beta_logits = raw_gate.contiguous(), beta_logits.contiguous()
+        A32, b32 = A_log.contiguous().float(), dt_bias.contiguous().float().reshape(-1)
+        B, T, H, K = raw_gate.shape
+        if beta_logits.dtype != raw_gate.dtype:
+            beta_logits = beta_logits.to(raw_gate.dtype)
+        g = torch.empty(B, T, H, K, dtype=torch.float32, device=dev)
+        beta = torch.empty(B, T, H, dtype=torch.float32, device=dev)
+        with torch.cuda.device(dev):
+            rc = lib.kda_gate_fwd(B * T, H, K, _dt(raw_gate), _ptr(raw_gate), _ptr(beta_logits), _ptr(A32), _ptr(b32),
+                                  float(lower_bound), _ptr(g), _ptr(beta), _stream(dev))
+        _lib.check(rc, "kda_gate_fwd")
+        ctx.save_for_backward(raw_gate, beta_logits, A32, b32)
+        ctx.lb = float(lower_bound)
+        ctx.bias_shape = dt_bias.shape
+        ctx.out_dtypes = (A_log.dtype, dt_bias.dtype)
+        return g, beta
+
+    @staticmethod
+    def backward(ctx, dg, dbeta):
+        lib = _lib.load()
+        raw_gate, beta_logits, A32, b32 = ctx.saved_tensors
+        dev = raw_gate.device
+        B, T, H, K = raw_gate.shape
+        dg = dg.contiguous().float()
+        dbeta = dbeta.contiguous().float()
+        d_raw = torch.empty_like(raw_gate)
+        d_bl = torch.empty_like(beta_logits)
+        dA = torch.empty(H, dtype=torch.float32, device=dev)
+        dbias = torch.empty(H * K, dtype=torch.float32, device=dev)
+        scr = _bytes(lib.kda_gate_bwd_scratch_bytes(B * T, H, K), dev)
+        with torch.cuda.device(dev):
+            rc = lib.kda_gate_bwd(B * T, H, K, _dt(raw_gate), _ptr(raw_gate), _ptr(beta_logits), _ptr(A32), _ptr(b32),
+                                  ctx.lb, _ptr(dg), _ptr(dbeta), _ptr(d_raw), _ptr(d_bl), _ptr(dA), _ptr(dbias),
+                                  _ptr(scr), scr.numel(), _stream(dev))
+        _lib.check(rc, "kda_gate_bwd")
+        return d_raw, d_bl, dA.to(ctx.out_dtypes[0]), dbias.reshape(ctx.bias_shape).to(ctx.out_dtypes[1]), None
+
+
+# --------------------------------------------------------------------------------------------
+# decode
+# --------------------------------------------------------------------------------------------
+
+def decode_step(q, k, v, g, beta, state, scale, l2norm=True, out_state: Optional[Tensor] = None):
+    """One token per sequence.  q,k,g [B,1,H,K] (or [B,H,K]); state [B,H,V,K] float32.
+    Returns (o shaped like v, new state).  The input state is left untouched unless
+    out_state aliases it."""
+    lib = _lib.load()
+    dev = _need_cuda(q, k, v, g, beta, state)
+    q, k, v, g, beta = (t.contiguous() for t in (q, k, v, g, beta))
+    if g.dtype != beta.dtype:
+        beta = beta.to(g.dtype)
+    H, K = q.shape[-2], q.shape[-1]
+    V = v.shape[-1]
+    n = q.numel() // (H * K)
+    if state.dtype != torch.float32 or not state.is_contiguous() or tuple(state.shape) != (n, H, V, K):
+        raise ValueError(f"state must be contiguous float32 V-first [B, H, V, K] with shape {(n, H, V, K)}")
+    new_state = torch.empty_like(state) if out_state is None else out_state
+    o = torch.empty_like(v)
+    with torch.cuda.device(dev):
+        rc = lib.kda_decode_step(n, H, K, V, _dt(q), _dt(g), 1 if l2norm else 0, float(scale), _ptr(q), _ptr(k), _ptr(v),
+                                 _ptr(g), _ptr(beta), _ptr(state), _ptr(new_state), _ptr(o), _stream(dev))
+    _lib.check(rc, "kda_decode_step")
+    return o, new_state
+
+
+# --------------------------------------------------------------------------------------------
+# short convolution
+# --------------------------------------------------------------------------------------------
+
+def conv_fwd(x, weight, initial_state, want_final, silu=True):
+    lib = _lib.load()
+    dev = _need_cuda(x, weight, initial_state)
+    B, T, Cc = x.shape
+    W = weight.shape[-1]
+    y = torch.empty_like(x)
+    fin = torch.empty(B, Cc, W, dtype=x.dtype, device=dev) if want_final else None
+    with torch.cuda.device(dev):
+        rc = lib.kda_conv_fwd(B, T, Cc, W, _dt(x), 1 if silu else 0, _ptr(x), _ptr(weight), _ptr(initial_state), _ptr(y),
+                              _ptr(fin), _stream(dev))
+    _lib.check(rc, "kda_conv_fwd")
+    return y, fin
+
+
+def conv_bwd(x, weight, initial_state, dy, dfin, silu=True):
+    lib = _lib.load()
+    dev = x.device
+    B, T, Cc = x.shape
+    W = weight.shape[-1]
+    dx = torch.empty_like(x)
+    dw = torch.empty(Cc, W, dtype=torch.float32, device=dev)
+    dinit = torch.empty_like(initial_state) if initial_state is not None else None
+    scr = _bytes(lib.kda_conv_bwd_scratch_bytes(B, T, Cc, W), dev)
+    with torch.cuda.device(dev):
+        rc = lib.kda_conv_bwd(B, T, Cc, W, _dt(x), 1 if silu else 0, _ptr(x), _ptr(weight), _ptr(initial_state), _ptr(dy),
+                              _ptr(dfin), _ptr(dx), _ptr(dw), _ptr(dinit), _ptr(scr), scr.numel(), _stream(dev))
+    _lib.check(rc, "kda_conv_bwd")
+    return dx, dw, dinit
+
+
+class ConvFunction(torch.autograd.Function):
+    """Causal depthwise convolution + SiLU with an explicit cache
+    (role of the reference's _ProjectConvolutionAutograd, nanochat/mixers/kda.py:439-466)."""
+
+    @staticmethod
+    def forward(ctx, x, weight, initial_state, output_final_state, silu):
+        x = x.contiguous()
+        w = weight.contiguous().to(x.dtype)
+        s0 = None if initial_state is None else initial_state.contiguous().to(x.dtype)
+        y, fin = conv_fwd(x, w, s0, output_final_state, silu)
+        ctx.save_for_backward(x, w, s0)
+        ctx.silu = silu
+        ctx.wdtype = weight.dtype
+        return y, fin
+
+    @staticmethod
+    def backward(ctx, dy, dfin):
+        x, w, s0 = ctx.saved_tensors
+        dy = dy.contiguous().to(x.dtype)
+        if dfin is not None:
+            dfin = dfin.contiguous().to(x.dtype)
+        dx, dw, dinit = conv_bwd(x, w, s0, dy, dfin, ctx.silu)
+        return dx, dw.to(ctx.wdtype), dinit, None, None
+
+
+# --------------------------------------------------------------------------------------------
+# gated RMSNorm
+# --------------------------------------------------------------------------------------------
+
+def rmsnorm_gate_fwd(x, gate, weight, eps):
+    lib = _lib.load()
+    dev = _need_cuda(x, gate, weight)
+    D = x.shape[-1]
+    rows = x.numel() // D
+    y = torch.empty_like(x)
+    inv = torch.empty(rows, dtype=torch.float32, device=dev)
+    with torch.cuda.device(dev):
+        rc = lib.kda_rmsnorm_gate_fwd(rows, D, _dt(x), float(eps), _ptr(x), _ptr(gate), _ptr(weight), _ptr(y), _ptr(inv),
+                                      _stream(dev))
+    _lib.check(rc, "kda_rmsnorm_gate_fwd")
+    return y, inv
+
+
+def rmsnorm_gate_bwd(x, gate, weight, inv, dy):
+    lib = _lib.load()
+    dev = x.device
+    D = x.shape[-1]
+    rows = x.numel() // D
+    dx, dgate = torch.empty_like(x), torch.empty_like(gate)
+    dw = torch.empty(D, dtype=torch.float32, device=dev)
+    scr = _bytes(lib.kda_rmsnorm_gate_bwd_scratch_bytes(rows, D), dev)
+    with torch.cuda.device(dev):
+        rc = lib.kda_rmsnorm_gate_bwd(rows, D, _dt(x), _ptr(x), _ptr(gate), _ptr(weight), _ptr(inv), _ptr(dy), _ptr(dx),
+                                      _ptr(dgate), _ptr(dw), _ptr(scr), scr.numel(), _stream(dev))
+    _lib.check(rc, "kda_rmsnorm_gate_bwd")
+    return dx, dgate, dw
+
+
+class RMSNormGateFunction(torch.autograd.Function):
+    """y = rms_norm(x; w, eps) * sigmoid(gate)
+    (role of the reference's _ProjectRMSNormGateAutograd, nanochat/mixers/kda.py:418-436)."""
+
+    @staticmethod
+    def forward(ctx, x, gate, weight, eps):
+        x = x.contiguous()
+        gate = gate.contiguous().to(x.dtype)
+        w32 = weight.contiguous().float()
+        y, inv = rmsnorm_gate_fwd(x, gate, w32, eps)
+        ctx.save_for_backward(x, gate, w32, inv)
+        ctx.wdtype = weight.dtype
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, gate, w32, inv = ctx.saved_tensors
+        dx, dgate, dw = rmsnorm_gate_bwd(x, gate, w32, inv, dy.contiguous().to(x.dtype))
+        return dx, dgate, dw.to(ctx.wdtype), None

@@ -1,0 +1,74 @@
+"""CPU-only checks of the drop-in boundary: the C-ABI library builds, loads and exports
+every symbol include/kda_b200.h declares; host-side validation mirrors the reference's
+error contract; no compute call is made (no GPU here)."""
+
+import ctypes
+import os
+import re
+
+import pytest
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def declared_symbols():
+    text = open(os.path.join(ROOT, "include", "kda_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(kda_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_library_exports_every_declared_symbol():
+    from experiment_swa_kda_b200 import _lib
+    lib = _lib.load()
+    names = declared_symbols()
+    assert len(names) >= 16
+    for n in names:
+        assert hasattr(lib, n), f"{n} declared in include/kda_b200.h but not exported"
+    assert set(_lib.EXPORTED_SYMBOLS) == set(names)
+    assert lib.kda_build_arch() == b"sm_100a"
+
+
+def test_workspace_queries_and_error_strings():
+    from experiment_swa_kda_b200 import _lib
+    lib = _lib.load()
+    sh = _lib.ChunkShape(2, 4096, 8192, 3, 128, 128, 1, 0, 0, 1, 0.0884)
+    ws, scr = lib.kda_chunk_workspace_bytes(sh), lib.kda_chunk_bwd_scratch_bytes(sh)
+    assert ws % 256 == 0 and scr % 256 == 0 and ws > 384 * 128 * 128 * 4
+    packed = _lib.ChunkShape(5, 0, 263, 2, 32, 48, 0, 0, 0, 1, 0.1)
+    assert lib.kda_chunk_workspace_bytes(packed) > 0
+    assert b"workspace" in lib.kda_error_string(-3)
+    # argument checks run before any CUDA call
+    assert lib.kda_chunk_fwd(sh, *([None] * 10), 0, None) == -5
+    bad = _lib.ChunkShape(2, 4096, 8192, 3, 512, 128, 1, 0, 0, 1, 0.1)
+    assert lib.kda_chunk_fwd(bad, *([None] * 10), 0, None) == -1
+    assert lib.kda_conv_fwd(1, 8, 4, 9, 0, 1, *([None] * 6)) in (-2, -5)
+    assert lib.kda_rmsnorm_gate_bwd_scratch_bytes(24576, 128) > 0
+    assert lib.kda_gate_bwd_scratch_bytes(8192, 3, 128) >= 2 * 128 * 384 * 4
+
+
+def test_host_validation_matches_reference_contract():
+    import experiment_swa_kda_b200 as m
+    q = torch.randn(1, 2, 2, 4)
+    v = torch.randn(1, 2, 2, 3)
+    b = torch.randn(1, 2, 2)
+    A, dt = torch.zeros(2), torch.zeros(2, 4)
+    with pytest.raises(ValueError, match="unknown KDA mode"):
+        m.kda(q, q, v, q, b, A, dt, mode="chunk")
+    with pytest.raises(ValueError, match=r"V-first|\[B, H, V, K\]"):
+        m.kda(q, q, v, q, b, A, dt, initial_state=torch.zeros(1, 2, 4, 3), mode="project_chunk")
+    with pytest.raises(ValueError, match="A_log must have shape"):
+        m.kda(q, q, v, q, b, torch.zeros(3), dt, mode="project_chunk")
+    with pytest.raises(RuntimeError, match="project CUDA KDA backend unavailable: project KDA requires CUDA"):
+        m.kda(q, q, v, q, b, A, dt, mode="project_chunk")          # fail closed: no CPU fallback
+    with pytest.raises(RuntimeError, match="cannot fall back on CPU"):
+        m.ShortConvolution(8, 4)(torch.randn(1, 3, 8))
+    with pytest.raises(ValueError, match="convolution state must have shape"):
+        m.ShortConvolution(8, 4)(torch.randn(1, 3, 8), torch.zeros(1, 8, 3))
+    with pytest.raises(RuntimeError, match="cannot fall back on CPU"):
+        m.RMSNormGated(8)(torch.randn(2, 8), torch.randn(2, 8))
+    with pytest.raises(ValueError, match="hidden_size = num_heads"):
+        m.KimiDeltaAttention(100, 3, 32)
+    prov = m.kda_backend_provenance()
+    assert prov["components"]["chunk_forward"]["torch_operator"] == "nanochat_kda::chunk_forward"
+    assert all(c["owner"] == "project" for c in prov["components"].values())

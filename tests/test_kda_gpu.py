@@ -1,0 +1,286 @@
+"""GPU parity tests: the CUDA path (through the C ABI) against the CPU oracle.
+
+Tolerances: relative L2 <= 1e-5 for float32 I/O ("fp32 mode") and <= 1e-2 for bfloat16
+I/O with float32 accumulation, on outputs, final states and every gradient; plus the
+reference's own element-wise bars (forward 5e-3, q/k/v/h0 gradients 8e-3, gate/beta
+gradients 2e-2; reference configs/research/kda_cuda_ownership.toml:44-47 and
+tests/test_kda_cuda.py:93-147).
+"""
+
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import kda_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+FP32_TOL = 1e-5
+BF16_TOL = 1e-2
+
+
+def dev():
+    return torch.device("cuda:0")
+
+
+def kda_mod():
+    import experiment_swa_kda_b200 as m
+    return m
+
+
+def to_dev(d, dtype=None):
+    out = {}
+    for n, t in d.items():
+        if n == "h0":
+            out[n] = t.float().to(dev())
+        else:
+            out[n] = (t if dtype is None else t.to(dtype)).to(dev())
+    return out
+
+
+def oracle_grads(d, do, ds, cu=None, scale=None):
+    """float32 oracle forward + autograd on CPU, from the (possibly rounded) device inputs."""
+    leaf = {n: t.detach().float().cpu().clone().requires_grad_(True) for n, t in d.items()}
+    if cu is None:
+        o, s = O.kda_recurrence(leaf["q"], leaf["k"], leaf["v"], leaf["g"], leaf["beta"],
+                                initial_state=leaf.get("h0"), scale=scale)
+    else:
+        o, s = O.kda_recurrence_varlen(leaf["q"], leaf["k"], leaf["v"], leaf["g"], leaf["beta"], cu,
+                                       initial_state=leaf.get("h0"), scale=scale)
+    names = [n for n in ("q", "k", "v", "g", "beta", "h0") if n in leaf]
+    grads = torch.autograd.grad((o, s), [leaf[n] for n in names], (do.float().cpu(), ds.float().cpu()))
+    return o.detach(), s.detach(), dict(zip(names, grads))
+
+
+def run_case(B, T, H, K, V, *, dtype, seed, with_state=True, tol, cu=None, n_states=None, gate_scale=1.0):
+    m = kda_mod()
+    d = O.make_inputs(B, T, H, K, V, seed=seed, with_state=with_state, n_states=n_states)
+    d["g"] = d["g"] * gate_scale
+    x = to_dev(d, dtype)
+    for n in x:
+        x[n].requires_grad_(True)
+    cu_dev = None if cu is None else torch.tensor(cu, dtype=torch.int32, device=dev())
+    o, s = m.chunk_kda(x["q"], x["k"], x["v"], x["g"], x["beta"], initial_state=x.get("h0"), output_final_state=True,
+                       cu_seqlens=cu_dev)
+    gen = torch.Generator().manual_seed(seed + 1)
+    do = torch.randn(o.shape, generator=gen).to(o.dtype).to(dev())
+    ds = torch.randn(s.shape, generator=gen).to(dev())
+    names = [n for n in ("q", "k", "v", "g", "beta", "h0") if n in x]
+    grads = torch.autograd.grad((o, s), [x[n] for n in names], (do, ds))
+    eo, es, eg = oracle_grads({n: x[n] for n in names}, do, ds, cu=cu)
+    errs = {"o": O.rel_l2(o.float(), eo), "s": O.rel_l2(s, es)}
+    for n, gr in zip(names, grads):
+        errs["d" + n] = O.rel_l2(gr.float(), eg[n])
+    bad = {n: e for n, e in errs.items() if not (e <= tol)}
+    assert not bad, f"rel-L2 above {tol}: {bad} (all: {errs})"
+    return errs
+
+
+# ---------------------------------------------------------------------------------- config 0
+def test_config0_fp32_forward_backward():
+    run_case(1, 256, 2, 64, 64, dtype=torch.float32, seed=0, with_state=False, tol=FP32_TOL)
+
+
+def test_config0_fp32_with_initial_state_gradient():
+    run_case(1, 256, 2, 64, 64, dtype=torch.float32, seed=1, with_state=True, tol=FP32_TOL)
+
+
+# ---------------------------------------------------------------------------------- boundaries
+@pytest.mark.parametrize("T", [1, 2, 3, 4, 63, 64, 65, 127, 128, 129, 257])
+def test_boundary_lengths_fp32_d128(T):
+    run_case(1, T, 2, 128, 128, dtype=torch.float32, seed=100 + T, tol=FP32_TOL)
+
+
+@pytest.mark.parametrize("T", [1, 31, 33, 64, 65, 129])
+def test_boundary_lengths_bf16_d64(T):
+    run_case(1, T, 2, 64, 64, dtype=torch.bfloat16, seed=200 + T, tol=BF16_TOL)
+
+
+@pytest.mark.parametrize("B,T,H,K,V", [(1, 1, 1, 4, 3), (2, 7, 2, 4, 3), (1, 64, 2, 16, 11), (2, 70, 2, 16, 24),
+                                       (1, 130, 1, 200, 72), (1, 66, 1, 256, 256)])
+def test_odd_head_dimensions_fp32(B, T, H, K, V):
+    run_case(B, T, H, K, V, dtype=torch.float32, seed=300 + K + V, tol=FP32_TOL)
+
+
+def test_strong_decay_fp32():
+    # log-decay near -5 per token for many channels: cumulative decay far below float range
+    run_case(1, 130, 2, 64, 64, dtype=torch.float32, seed=7, tol=FP32_TOL, gate_scale=40.0)
+
+
+# ---------------------------------------------------------------------------------- packed sequences
+def test_varlen_ragged_fp32():
+    cu = [0, 5, 69, 69, 200, 263]       # includes an empty segment and ragged tails
+    run_case(1, 263, 2, 32, 48, dtype=torch.float32, seed=11, tol=FP32_TOL, cu=cu, n_states=5)
+
+
+def test_varlen_bf16_d128():
+    cu = [0, 130, 131, 400]
+    run_case(1, 400, 2, 128, 128, dtype=torch.bfloat16, seed=12, tol=BF16_TOL, cu=cu, n_states=3)
+
+
+# ---------------------------------------------------------------------------------- raw surface vs the reference's vectors
+NAMES = ("q", "k", "v", "raw_gate", "beta_logits", "A_log", "dt_bias", "initial_state")
+
+
+@pytest.mark.parametrize("tag", ["raw_b2_t7_h2_k4_v3", "raw_b1_t64_h2_k16_v11", "raw_b2_t65_h2_k16_v24",
+                                 "raw_b1_t130_h2_k32_v32"])
+def test_raw_surface_fp32_matches_reference_vectors(golden_dir, tag):
+    from experiment_swa_kda_b200 import ops
+    m = kda_mod()
+    z = np.load(os.path.join(golden_dir, tag + ".npz"))
+    x = {n: torch.from_numpy(z[n]).to(dev()).requires_grad_(True) for n in NAMES}
+    g, beta = ops.GateFunction.apply(x["raw_gate"], x["beta_logits"], x["A_log"], x["dt_bias"], -5.0)
+    o, s = m.chunk_kda(x["q"], x["k"], x["v"], g, beta, initial_state=x["initial_state"], output_final_state=True)
+    grads = torch.autograd.grad((o, s), [x[n] for n in NAMES],
+                                (torch.from_numpy(z["cot_o"]).to(dev()), torch.from_numpy(z["cot_s"]).to(dev())))
+    assert O.rel_l2(o, torch.from_numpy(z["oracle_o"])) <= FP32_TOL
+    assert O.rel_l2(s, torch.from_numpy(z["oracle_s"])) <= FP32_TOL
+    for n, gr in zip(NAMES, grads):
+        # the reference's own two float32 implementations differ by up to ~1e-5 on these gradients
+        assert O.rel_l2(gr, torch.from_numpy(z[f"oracle_d_{n}"])) <= 3e-5, n
+
+
+def make_raw_bf16(T, D, seed, heads=2, batch=1, grad=False):
+    gen = torch.Generator().manual_seed(seed)
+    def act(*shape):
+        return torch.randn(*shape, generator=gen).to(torch.bfloat16).to(dev()).requires_grad_(grad)
+    q, k, v, g = (act(batch, T, heads, D) for _ in range(4))
+    beta = act(batch, T, heads)
+    A_log = (torch.randn(heads, generator=gen) * 0.2).to(dev()).requires_grad_(grad)
+    dt_bias = (torch.randn(heads, D, generator=gen) * 0.3).to(dev()).requires_grad_(grad)
+    h0 = (torch.randn(batch, heads, D, D, generator=gen) * 0.05).to(dev()).requires_grad_(grad)
+    return q, k, v, g, beta, A_log, dt_bias, h0
+
+
+@pytest.mark.parametrize("T,D", [(31, 64), (32, 64), (33, 64), (63, 64), (64, 64), (65, 64), (65, 128)])
+def test_raw_bf16_forward_matches_oracle(T, D):
+    m = kda_mod()
+    t = make_raw_bf16(T, D, 20260805 + T + D)
+    o, s = m.kda(*t[:7], initial_state=t[7], output_final_state=True, mode="project_chunk")
+    eo, es = O.kda_raw(*(x.detach().float().cpu() for x in t[:7]), initial_state=t[7].detach().cpu())
+    assert o.dtype == torch.bfloat16 and s.dtype == torch.float32 and s.shape == (1, 2, D, D)
+    torch.testing.assert_close(o.float().cpu(), eo, atol=5e-3, rtol=5e-3)
+    torch.testing.assert_close(s.cpu(), es, atol=5e-3, rtol=5e-3)
+    assert O.rel_l2(o.float(), eo) <= BF16_TOL and O.rel_l2(s, es) <= BF16_TOL
+
+
+def test_raw_bf16_backward_matches_oracle():
+    m = kda_mod()
+    t = make_raw_bf16(33, 64, 99, grad=True)
+    e = tuple(x.detach().float().cpu().clone().requires_grad_(True) for x in t)
+    o, s = m.kda(*t[:7], initial_state=t[7], output_final_state=True, mode="project_chunk")
+    eo, es = O.kda_raw(*e[:7], initial_state=e[7])
+    gen = torch.Generator().manual_seed(5)
+    co, cs = torch.randn(eo.shape, generator=gen), torch.randn(es.shape, generator=gen)
+    got = torch.autograd.grad((o, s), t, (co.to(o.dtype).to(dev()), cs.to(dev())))
+    want = torch.autograd.grad((eo, es), e, (co.to(torch.bfloat16).float(), cs))
+    for name, a, b in zip(NAMES, got, want):
+        tol = 2e-2 if name in {"raw_gate", "beta_logits", "A_log", "dt_bias"} else 8e-3
+        torch.testing.assert_close(a.float().cpu(), b, atol=tol, rtol=tol, msg=lambda s_, n=name: f"{n}: {s_}")
+        assert O.rel_l2(a.float(), b) <= BF16_TOL, name
+
+
+def test_extreme_gate_logits_stay_finite():
+    m = kda_mod()
+    t = list(make_raw_bf16(256, 64, 3, grad=True))
+    with torch.no_grad():
+        t[3][..., ::2].fill_(-100.0)
+        t[3][..., 1::2].fill_(100.0)
+    o, s = m.kda(*t[:7], initial_state=t[7], output_final_state=True, mode="project_chunk")
+    loss = o.float().square().mean() + s.square().mean()
+    grads = torch.autograd.grad(loss, t)
+    assert torch.isfinite(o).all() and torch.isfinite(s).all()
+    for gr in grads:
+        assert torch.isfinite(gr).all()
+    eo, es = O.kda_raw(*(x.detach().float().cpu() for x in t[:7]), initial_state=t[7].detach().cpu())
+    assert O.rel_l2(o.float(), eo) <= BF16_TOL
+
+
+# ---------------------------------------------------------------------------------- decode
+def test_decode_steps_match_chunk_and_oracle_and_leave_state_untouched():
+    m = kda_mod()
+    t = make_raw_bf16(17, 128, 20260822)
+    q, k, v, g, beta, A_log, dt_bias, state = t
+    co, cs = m.kda(*t[:7], initial_state=state, output_final_state=True, mode="project_chunk")
+    original = state.clone()
+    pieces, cur = [], state
+    for i in range(17):
+        o, cur = m.kda(q[:, i:i + 1], k[:, i:i + 1], v[:, i:i + 1], g[:, i:i + 1], beta[:, i:i + 1], A_log, dt_bias,
+                       initial_state=cur, output_final_state=True, mode="project_recurrent")
+        pieces.append(o)
+    ro = torch.cat(pieces, dim=1)
+    assert torch.equal(state, original)
+    torch.testing.assert_close(ro.float(), co.float(), atol=5e-3, rtol=5e-3)
+    torch.testing.assert_close(cur, cs, atol=5e-3, rtol=5e-3)
+    eo, es = O.kda_raw(*(x.detach().float().cpu() for x in t[:7]), initial_state=state.cpu())
+    assert O.rel_l2(ro.float(), eo) <= BF16_TOL and O.rel_l2(cur, es) <= BF16_TOL
+
+
+@pytest.mark.parametrize("K,V,dtype", [(128, 128, torch.bfloat16), (64, 64, torch.float32), (20, 12, torch.float32),
+                                      (256, 64, torch.bfloat16), (7, 5, torch.float32)])
+def test_decode_step_activated_surface(K, V, dtype):
+    m = kda_mod()
+    d = O.make_inputs(3, 1, 2, K, V, seed=K + V, with_state=True)
+    x = to_dev(d, dtype)
+    o, s = m.recurrent_kda_step(x["q"], x["k"], x["v"], x["g"], x["beta"], x["h0"])
+    eo, es = O.decode_step(*(x[n].float().cpu() for n in ("q", "k", "v", "g", "beta")), x["h0"].cpu())
+    tol = FP32_TOL if dtype == torch.float32 else BF16_TOL
+    assert O.rel_l2(o.float(), eo) <= tol and O.rel_l2(s, es) <= (FP32_TOL if dtype == torch.float32 else 1e-4)
+
+
+# ---------------------------------------------------------------------------------- contracts
+def test_contract_errors_and_fail_closed():
+    m = kda_mod()
+    t = list(make_raw_bf16(1, 64, 1))
+    bad = list(t)
+    bad[0] = bad[0].float()
+    with pytest.raises(RuntimeError, match="requires bfloat16"):
+        m.kda(*bad[:7], initial_state=bad[7], mode="project_chunk")
+    tg = make_raw_bf16(1, 64, 1, grad=True)
+    with pytest.raises(RuntimeError, match="inference-only"):
+        m.kda(*tg[:7], initial_state=tg[7], mode="project_recurrent")
+    with pytest.raises(ValueError, match=r"V-first|\[B, H, V, K\]"):
+        m.kda(*t[:7], initial_state=torch.zeros(1, 2, 64, 32, device=dev()), mode="project_chunk")
+    with pytest.raises(ValueError, match="unknown KDA mode"):
+        m.kda(*t[:7], mode="reference")
+    cpu = [x.cpu() for x in t]
+    with pytest.raises(RuntimeError, match="requires CUDA"):
+        m.kda(*cpu[:7], initial_state=cpu[7], mode="project_chunk")
+
+
+def test_deterministic_and_does_not_mutate_inputs():
+    m = kda_mod()
+    t = make_raw_bf16(130, 64, 4, grad=True)
+    keep = [x.detach().clone() for x in t]
+    outs = []
+    for _ in range(2):
+        o, s = m.kda(*t[:7], initial_state=t[7], output_final_state=True, mode="project_chunk")
+        gr = torch.autograd.grad(o.float().sum() + s.sum(), t)
+        outs.append((o, s, gr))
+    assert torch.equal(outs[0][0], outs[1][0]) and torch.equal(outs[0][1], outs[1][1])
+    for a, b in zip(outs[0][2], outs[1][2]):
+        assert torch.equal(a, b)
+    for a, b in zip(t, keep):
+        assert torch.equal(a.detach(), b)
+
+
+# ---------------------------------------------------------------------------------- full-size properties (config 1)
+def test_config1_shape_state_chaining_property():
+    """B2,T4096,H3,D128 bf16: one call over 4096 tokens equals two calls of 2048 chained through the final state,
+    and the first half is independent of the second (causality)."""
+    m = kda_mod()
+    d = O.make_inputs(2, 4096, 3, 128, 128, seed=42)
+    x = to_dev(d, torch.bfloat16)
+    full, fs = m.chunk_kda(x["q"], x["k"], x["v"], x["g"], x["beta"], output_final_state=True)
+    h = {n: t[:, :2048] for n, t in x.items()}
+    a, sa = m.chunk_kda(h["q"], h["k"], h["v"], h["g"], h["beta"], output_final_state=True)
+    h2 = {n: t[:, 2048:] for n, t in x.items()}
+    b, sb = m.chunk_kda(h2["q"], h2["k"], h2["v"], h2["g"], h2["beta"], initial_state=sa, output_final_state=True)
+    assert torch.equal(full[:, :2048], a)
+    assert O.rel_l2(full[:, 2048:].float(), b.float()) <= 1e-3
+    assert O.rel_l2(fs, sb) <= 1e-4
+    # oracle on a prefix the CPU finishes quickly
+    eo, _ = O.kda_recurrence(*(x[n][:1, :256].float().cpu() for n in ("q", "k", "v", "g", "beta")))
+    assert O.rel_l2(full[:1, :256].float(), eo) <= BF16_TOL
