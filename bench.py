@@ -1,0 +1,365 @@
+"""Benchmark of the KDA hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload chain|varlen|decode]
+
+A step is one pass of the hot path over one batch of seeded synthetic input.  Default
+workload ("chain"): B=2, T=4096, H=3, Dk=Dv=128, bf16 I/O with float32 state/accumulation:
+short causal conv (width 4, SiLU) on q/k/v -> chunked KDA forward+backward -> gated RMSNorm
+(eps 1e-6), forward and backward through the whole chain.  With N > 1 (launched by
+torch.distributed.run, one rank per GPU) every rank runs the same per-GPU batch (weak
+scaling, no data-path collective); the time is the maximum over ranks.
+
+Prints ONE JSON line on rank 0.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+
+METRIC = "kda_fwd_bwd_tokens_per_s"
+UNIT = "tokens/s"
+
+CHAIN = dict(B=2, T=4096, H=3, D=128, W=4, eps=1e-6)
+
+
+# ----------------------------------------------------------------------------------------------
+# algorithmic work (multiply-adds at triangular cost, no recompute), per 64-token chunk and head
+# ----------------------------------------------------------------------------------------------
+def kda_kernel_flops(K, V, C=64):
+    tri, stri = C * (C + 1) // 2, C * (C - 1) // 2
+    fwd = {
+        "build_am_kernel": tri * K + stri * K + C ** 3 / 6,
+        "uw_kernel": tri * (V + K),
+        "scan_fwd_kernel": 2 * C * K * V,
+        "out_kernel": C * K * V + tri * V,
+    }
+    fwd_total = sum(fwd.values())
+    bwd = {"scan_bwd_kernel": 3 * C * K * V + tri * V, "pullback_kernel": 2 * (tri + stri) * K}
+    bwd["bwd_local_kernel"] = 2 * fwd_total - sum(bwd.values())
+    out = {k: 2.0 * v for k, v in {**fwd, **bwd}.items()}     # FLOP = 2 * MAC
+    out["_fwd_bwd_total"] = 2.0 * 3 * fwd_total
+    return out
+
+
+def chain_kernel_bytes(cfg):
+    B, T, H, D = cfg["B"], cfg["T"], cfg["H"], cfg["D"]
+    n = B * T * H * D * 2      # one bf16 tensor
+    return {"conv_fwd_kernel": 2 * n, "conv_bwd_kernel": 3 * n, "rmsnorm_fwd_kernel": 3 * n, "rmsnorm_bwd_kernel": 5 * n}
+
+
+# ----------------------------------------------------------------------------------------------
+# clocks during the timed region
+# ----------------------------------------------------------------------------------------------
+class ClockSampler:
+    def __init__(self, index):
+        self.index, self.samples, self.reasons, self.stop_flag, self.max_mhz = index, [], set(), False, None
+        self.thread = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = None
+
+    def _loop(self):
+        nv = self.nv
+        names = {"hw_slowdown": 0x8, "sw_power_cap": 0x4, "sw_thermal_slowdown": 0x20, "hw_thermal_slowdown": 0x40,
+                 "hw_power_brake": 0x80}
+        while not self.stop_flag:
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                r = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                for n, bit in names.items():
+                    if r & bit:
+                        self.reasons.add(n)
+            except Exception:
+                pass
+            time.sleep(0.05)
+
+    def start(self):
+        if self.nv is not None:
+            self.thread = threading.Thread(target=self._loop, daemon=True)
+            self.thread.start()
+
+    def stop(self):
+        self.stop_flag = True
+        if self.thread is not None:
+            self.thread.join(timeout=1.0)
+        med = statistics.median(self.samples) if self.samples else None
+        return {"sm_mhz": med, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons)}
+
+
+# ----------------------------------------------------------------------------------------------
+# the chain workload
+# ----------------------------------------------------------------------------------------------
+class Chain:
+    """conv(q,k,v) -> chunked KDA -> gated RMSNorm, forward and backward, via the public API."""
+
+    def __init__(self, cfg, dev, seed):
+        import experiment_swa_kda_b200 as m
+        self.m, self.cfg, self.dev = m, cfg, dev
+        B, T, H, D, W = cfg["B"], cfg["T"], cfg["H"], cfg["D"], cfg["W"]
+        C = H * D
+        gen = torch.Generator().manual_seed(seed)
+        bf = torch.bfloat16
+        self.host = {
+            "xq": torch.randn(B, T, C, generator=gen).to(bf), "xk": torch.randn(B, T, C, generator=gen).to(bf),
+            "xv": torch.randn(B, T, C, generator=gen).to(bf),
+            "g": (-torch.nn.functional.softplus(torch.randn(B, T, H, D, generator=gen)) * 0.1).clamp(-5, 0).to(bf),
+            "beta": torch.sigmoid(torch.randn(B, T, H, generator=gen)).to(bf),
+            "gate": torch.randn(B, T, H, D, generator=gen).to(bf),
+            "probe": torch.randn(B, T, H, D, generator=gen).to(bf),
+        }
+        self.host = {n: t.pin_memory() for n, t in self.host.items()}
+        self.convs = [m.ShortConvolution(C, W).to(dev) for _ in range(3)]
+        bound = (3 ** 0.5) * C ** -0.5
+        for i, c in enumerate(self.convs):
+            with torch.no_grad():
+                c.weight.copy_((torch.rand(C, 1, W, generator=gen) * 2 - 1) * bound)
+        self.norm = m.RMSNormGated(D, eps=cfg["eps"]).to(dev)
+        self.x = None
+        self.leaf_names = ("xq", "xk", "xv", "g", "beta", "gate")
+        self.host_out = None
+
+    def tokens(self):
+        return self.cfg["B"] * self.cfg["T"]
+
+    def upload(self):
+        self.x = {n: t.to(self.dev, non_blocking=True) for n, t in self.host.items()}
+        for n in self.leaf_names:
+            self.x[n].requires_grad_(True)
+
+    def h2d_bytes(self):
+        return sum(t.numel() * t.element_size() for t in self.host.values())
+
+    def step(self):
+        x, cfg = self.x, self.cfg
+        sh = (cfg["B"], cfg["T"], cfg["H"], cfg["D"])
+        q = self.convs[0](x["xq"])[0].view(sh)
+        k = self.convs[1](x["xk"])[0].view(sh)
+        v = self.convs[2](x["xv"])[0].view(sh)
+        o, _ = self.m.chunk_kda(q, k, v, x["g"], x["beta"])
+        y = self.norm(o, x["gate"])
+        leaves = [x[n] for n in self.leaf_names] + [c.weight for c in self.convs] + [self.norm.weight]
+        grads = torch.autograd.grad(y, leaves, x["probe"])
+        return y, grads
+
+    def download(self, y, grads):
+        outs = [y.detach()] + [g for g in grads]
+        if self.host_out is None:
+            self.host_out = [torch.empty(t.shape, dtype=t.dtype).pin_memory() for t in outs]
+        for h, t in zip(self.host_out, outs):
+            h.copy_(t, non_blocking=True)
+        return sum(h.numel() * h.element_size() for h in self.host_out)
+
+
+def oracle_chain_step(cfg, T, seed, threads):
+    """The CPU oracle on the same chain, T tokens per sequence (cost is linear in T)."""
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import kda_oracle as O
+    torch.set_num_threads(threads)
+    B, H, D, W = cfg["B"], cfg["H"], cfg["D"], cfg["W"]
+    C = H * D
+    gen = torch.Generator().manual_seed(seed)
+    xs = [torch.randn(B, T, C, generator=gen).requires_grad_(True) for _ in range(3)]
+    ws = [((torch.rand(C, W, generator=gen) * 2 - 1) * (3 ** 0.5) * C ** -0.5).requires_grad_(True) for _ in range(3)]
+    g = (-torch.nn.functional.softplus(torch.randn(B, T, H, D, generator=gen)) * 0.1).clamp(-5, 0).requires_grad_(True)
+    beta = torch.sigmoid(torch.randn(B, T, H, generator=gen)).requires_grad_(True)
+    gate = torch.randn(B, T, H, D, generator=gen).requires_grad_(True)
+    nw = torch.ones(D, requires_grad=True)
+    probe = torch.randn(B, T, H, D, generator=gen)
+    t0 = time.perf_counter()
+    q, k, v = (O.causal_conv(x, w)[0].view(B, T, H, D) for x, w in zip(xs, ws))
+    o, _ = O.kda_recurrence(q, k, v, g, beta)
+    y = O.rmsnorm_gated(o, gate, nw, cfg["eps"])
+    torch.autograd.grad(y, xs + ws + [g, beta, gate, nw], probe)
+    return time.perf_counter() - t0
+
+
+# ----------------------------------------------------------------------------------------------
+def run_reference(args, rank, world):
+    if rank != 0:
+        return
+    threads = os.cpu_count() or 1
+    T = 256
+    for _ in range(args.warmup):
+        oracle_chain_step(CHAIN, 64, 0, threads)
+    times = [oracle_chain_step(CHAIN, T, 1 + i, threads) for i in range(args.steps)]
+    dt = sum(times) / len(times)
+    val = CHAIN["B"] * T / dt
+    line = {
+        "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "config1 chain conv4+SiLU -> KDA fwd+bwd -> gated RMSNorm, B2 H3 D128", "chunk": 64,
+                   "sample": f"T={T} tokens per sequence per step (cost linear in T; the GPU arm runs T=4096)"},
+        "cpu_baseline": {"value": val, "unit": UNIT, "cores": threads, "kind": "port",
+                         "sample": f"oracle token loop + autograd, B2 T{T} H3 D128, {args.steps} steps"},
+        "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+        return
+
+    import torch.distributed as dist
+    from experiment_swa_kda_b200 import _lib
+    dev = torch.device(f"cuda:{local}")
+    torch.cuda.set_device(dev)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    _lib.load()
+    chain = Chain(CHAIN, dev, seed=1234 + rank)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)     # larger than the 126 MB L2
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+
+    # ---- device-resident arm -----------------------------------------------------------------
+    chain.upload()
+    for _ in range(max(args.warmup, 3)):
+        chain.step()
+    barrier()
+    sampler = ClockSampler(local)
+    sampler.start()
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    l0 = _lib.launch_count()
+    barrier()
+    for a, b in ev:
+        flush.zero_()
+        a.record()
+        chain.step()
+        b.record()
+    barrier()
+    launches = _lib.launch_count() - l0
+    clocks = sampler.stop()
+    ms = sum(a.elapsed_time(b) for a, b in ev)
+    t = torch.tensor([ms], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_total = float(t.item())
+    ms_step = ms_total / args.steps
+    value = chain.tokens() * world / (ms_step * 1e-3)
+
+    # ---- end-to-end arm: pinned host inputs -> device -> chain -> pinned host results ----------
+    d2h = 0
+    for _ in range(3):
+        chain.upload()
+        d2h = chain.download(*chain.step())
+    barrier()
+    ev2 = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    for a, b in ev2:
+        flush.zero_()
+        a.record()
+        chain.upload()
+        d2h = chain.download(*chain.step())
+        b.record()
+    barrier()
+    t2 = torch.tensor([sum(a.elapsed_time(b) for a, b in ev2)], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t2, op=dist.ReduceOp.MAX)
+    e2e_value = chain.tokens() * world / (float(t2.item()) / args.steps * 1e-3)
+
+    # ---- per-kernel device time (separate pass so the events do not perturb the numbers above) --
+    chain.upload()
+    torch.cuda.synchronize(dev)
+    _lib.profile(True)
+    for _ in range(args.steps):
+        flush.zero_()
+        chain.step()
+    torch.cuda.synchronize(dev)
+    rep = _lib.profile_report()
+    _lib.profile(False)
+
+    if rank == 0:
+        peaks = {}
+        try:
+            peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+        except Exception:
+            pass
+        hbm_peak = peaks.get("hbm_gbs", 6650.0)
+        tf_peak = peaks.get("bf16_tflops", 1590.0)
+        src = "measured" if peaks else "fallback"
+        nch = CHAIN["B"] * (CHAIN["T"] // 64) * CHAIN["H"]
+        flops = kda_kernel_flops(CHAIN["D"], CHAIN["D"])
+        nbytes = chain_kernel_bytes(CHAIN)
+        kern = {}
+        total_ms = sum(v[1] for v in rep.values()) or 1.0
+        for name, (n, tot) in rep.items():
+            avg_ms = tot / n
+            row = {"launches_per_step": n / args.steps, "avg_us": avg_ms * 1e3, "share": tot / total_ms}
+            if name in flops:
+                row["tflops"] = flops[name] * nch / (avg_ms * 1e-3) / 1e12
+            if name in nbytes:
+                row["gbs"] = nbytes[name] / (avg_ms * 1e-3) / 1e9
+            kern[name] = row
+        top = max(rep, key=lambda k: rep[k][1]) if rep else None
+        traffic = None
+        try:
+            traffic = json.load(open(os.path.join(ROOT, "profiles", "ncu_traffic.json"))).get(top)
+        except Exception:
+            pass
+        if top in flops:
+            roof = {"kernel": top, "bound": "tensor", "achieved": kern[top]["tflops"], "peak": tf_peak, "unit": "TFLOP/s",
+                    "frac": kern[top]["tflops"] / tf_peak, "traffic": traffic, "peak_source": src}
+        elif top in nbytes:
+            roof = {"kernel": top, "bound": "hbm", "achieved": kern[top]["gbs"], "peak": hbm_peak, "unit": "GB/s",
+                    "frac": kern[top]["gbs"] / hbm_peak, "traffic": traffic, "peak_source": src}
+        else:
+            roof = {"kernel": top, "bound": "hbm", "achieved": None, "peak": hbm_peak, "unit": "GB/s", "frac": None,
+                    "traffic": traffic, "peak_source": src}
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+            "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic",
+            "config": {"workload": "config1 chain: conv4+SiLU(q,k,v) -> chunked KDA fwd+bwd -> gated RMSNorm fwd+bwd; "
+                                   "B2 T4096 H3 Dk=Dv=128 chunk64, bf16 I/O, fp32 state/accumulation",
+                       "tokens_per_step_per_gpu": chain.tokens(), "l2": "flushed between steps (256 MiB write)",
+                       "lane": "fp32-cuda-core", "sharding": "replicated per-GPU batches, no collective"},
+            "tflops_algorithmic": flops["_fwd_bwd_total"] * nch * world / (ms_step * 1e-3) / 1e12,
+            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": chain.h2d_bytes(), "d2h_bytes_per_step": d2h},
+            "gpu_launches": int(launches), "clocks": clocks, "roofline": roof, "kernels": kern,
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            threads = os.cpu_count() or 1
+            oracle_chain_step(CHAIN, 64, 0, threads)
+            Ts = 512
+            dt = oracle_chain_step(CHAIN, Ts, 1, threads)
+            line["cpu_baseline"] = {"value": CHAIN["B"] * Ts / dt, "unit": UNIT, "cores": threads, "kind": "port",
+                                    "sample": f"oracle token loop + autograd on the same chain, B2 T{Ts} H3 D128, 1 step "
+                                              f"({dt:.1f} s); cost is linear in T"}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
