@@ -343,7 +343,7 @@ def main():
             "config": {"workload": "config1 chain: conv4+SiLU(q,k,v) -> chunked KDA fwd+bwd -> gated RMSNorm fwd+bwd; "
                                    "B2 T4096 H3 Dk=Dv=128 chunk64, bf16 I/O, fp32 state/accumulation",
                        "tokens_per_step_per_gpu": chain.tokens(), "l2": "flushed between steps (256 MiB write)",
-                       "lane": "fp32-cuda-core", "sharding": "replicated per-GPU batches, no collective"},
+                       "lane": "tc scan (tcgen05) + fp32 cuda-core intra-chunk", "sharding": "replicated per-GPU batches, no collective"},
             "tflops_algorithmic": flops["_fwd_bwd_total"] * nch * world / (ms_step * 1e-3) / 1e12,
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": chain.h2d_bytes(), "d2h_bytes_per_step": d2h},
             "gpu_launches": int(launches), "clocks": clocks, "roofline": roof, "kernels": kern,

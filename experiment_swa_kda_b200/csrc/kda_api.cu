@@ -9,6 +9,7 @@
 
 #include "common.cuh"
 #include "simt_ws.cuh"
+#include "tc_ws.cuh"
 
 namespace kda {
 int simt_chunk_fwd(const KdaChunkShape* sh, const void* q, const void* k, const void* v, const void* g, const void* beta,
@@ -32,7 +33,12 @@ static int check_shape(const KdaChunkShape* s, const int32_t* cu) {
     } else {
         if ((long long)s->n_seq * s->seq_len != s->tokens) return KDA_ERR_BAD_SHAPE;
     }
-    if (s->lane != KDA_LANE_FP32) return KDA_ERR_UNSUPPORTED;
+    if (s->lane == KDA_LANE_TC) {
+        // tensor-core tiles are built for 128-wide heads and bf16 activations
+        if (s->key_dim != 128 || s->value_dim != 128 || s->io_dtype != KDA_DTYPE_BF16) return KDA_ERR_UNSUPPORTED;
+    } else if (s->lane != KDA_LANE_FP32) {
+        return KDA_ERR_UNSUPPORTED;
+    }
     return KDA_OK;
 }
 
@@ -53,9 +59,10 @@ extern "C" const char* kda_build_arch(void) { return "sm_100a"; }
 
 extern "C" size_t kda_chunk_workspace_bytes(const KdaChunkShape* shape) {
     if (!shape || shape->n_seq <= 0 || shape->heads <= 0 || shape->key_dim <= 0 || shape->value_dim <= 0) return 0;
-    size_t bytes = 0;
+    size_t bytes = 0, tcb = 0;
     simt::carve_ws(*shape, nullptr, &bytes);
-    return bytes;
+    if (shape->lane == KDA_LANE_TC) tc::carve_tc(*shape, nullptr, &tcb);
+    return bytes + tcb;
 }
 
 extern "C" size_t kda_chunk_bwd_scratch_bytes(const KdaChunkShape* shape) {

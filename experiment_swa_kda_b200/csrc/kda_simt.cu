@@ -16,6 +16,7 @@
 
 #include "common.cuh"
 #include "simt_ws.cuh"
+#include "tc_ws.cuh"
 
 namespace kda {
 namespace simt {
@@ -898,6 +899,11 @@ __global__ void __launch_bounds__(256) finalize_kernel(Ws w, Scr s, const void* 
 using simt::Scr;
 using simt::Ws;
 
+int tc_scan_forward(const simt::Ws& w, const tc::TcWs& t, int n_seq, const float* h0, float* final_state, void* o,
+                    cudaStream_t st);
+int tc_scan_backward(const simt::Ws& w, const simt::Scr& s, const tc::TcWs& t, int n_seq, int tokens, const void* d_o,
+                     const float* d_final, float* dh0, cudaStream_t st);
+
 template <class Kern>
 static int set_smem(Kern kern, size_t bytes) {
     if (bytes > 48 * 1024) {
@@ -922,6 +928,18 @@ int simt_chunk_fwd(const KdaChunkShape* sh, const void* q, const void* k, const 
         size_t sm_uw = (size_t)2 * 64 * kLD * sizeof(float);
         KDA_LAUNCH("uw_kernel", st, simt::uw_kernel<<<dim3(w.nslots, w.H, KT + VT), 256, sm_uw, st>>>(w, v, bf16));
     }
+    if (sh->lane == KDA_LANE_TC) {
+        // tensor-core scan with the chunk output fused in; panels come from the float32 intra-chunk kernels
+        size_t ws_bytes = 0;
+        simt::carve_ws(*sh, nullptr, &ws_bytes);
+        tc::TcWs t = tc::carve_tc(*sh, static_cast<char*>(workspace) + ws_bytes);
+        if (cudaMemsetAsync(t.status, 0, sizeof(int), st) != cudaSuccess) return KDA_ERR_CUDA;
+        if (w.nslots > 0) {
+            int rc = tc_scan_forward(w, t, sh->n_seq, h0, final_state, o, st);
+            if (rc) return rc;
+        }
+        return launch_status();
+    }
     {
         size_t sm_scan = ((size_t)2 * 64 * (w.Kp + 1) + (size_t)w.Kp * simt::kVS + 64 * simt::kVS + w.Kp) * sizeof(float);
         if (set_smem(simt::scan_fwd_kernel, sm_scan)) return KDA_ERR_CUDA;
@@ -942,7 +960,17 @@ int simt_chunk_bwd(const KdaChunkShape* sh, const void* q, const void* k, const 
     Scr s = simt::carve_scr(*sh, scratch);
     const int bf16 = sh->io_dtype == KDA_DTYPE_BF16, gbf16 = sh->gate_dtype == KDA_DTYPE_BF16;
     const int KT = w.Kp / 64;
-    {
+    if (sh->lane == KDA_LANE_TC) {
+        size_t ws_bytes = 0;
+        simt::carve_ws(*sh, nullptr, &ws_bytes);
+        tc::TcWs t = tc::carve_tc(*sh, static_cast<char*>(const_cast<void*>(workspace)) + ws_bytes);
+        if (w.nslots > 0) {
+            int rc = tc_scan_backward(w, s, t, sh->n_seq, sh->tokens, d_o, d_final, dh0, st);
+            if (rc) return rc;
+        } else if (dh0) {
+            return KDA_ERR_UNSUPPORTED;
+        }
+    } else {
         size_t sm_scan = ((size_t)2 * 64 * (w.Kp + 1) + 64 * kLD + (size_t)2 * w.Kp * simt::kVS + 2 * 64 * simt::kVS + w.Kp) *
                          sizeof(float);
         if (set_smem(simt::scan_bwd_kernel, sm_scan)) return KDA_ERR_CUDA;

@@ -60,6 +60,13 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, u
         "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y)
         : "memory");
 }
+// 1-D bulk copy global -> shared (16-byte aligned addresses, size a multiple of 16), completing on `bar`.
+__device__ __forceinline__ void bulk_load_1d(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                     smem_u32(dst)),
+                 "l"(src), "r"(bytes), "r"(smem_u32(bar))
+                 : "memory");
+}
 __device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, const void* src, int x, int y) {
     asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(map),
                  "r"(smem_u32(src)), "r"(x), "r"(y)
@@ -102,9 +109,10 @@ __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.
 constexpr uint32_t kMajorK = 0, kMajorMN = 1;
 
 // kind::f16 instruction descriptor: BF16 operands, FP32 accumulator, dense.
-__host__ __device__ constexpr uint32_t umma_idesc_bf16(int M, int N, uint32_t a_major, uint32_t b_major) {
-    return (1u << 4) | (1u << 7) | (1u << 10) | (a_major << 15) | (b_major << 16) | ((uint32_t)(N >> 3) << 17) |
-           ((uint32_t)(M >> 4) << 24);
+__host__ __device__ constexpr uint32_t umma_idesc_bf16(int M, int N, uint32_t a_major, uint32_t b_major,
+                                                       uint32_t negate_a = 0) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | (negate_a << 13) | (a_major << 15) | (b_major << 16) |
+           ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
 }
 
 // Shared-memory matrix descriptor, 128-byte swizzle.  K-major: rows of 128 bytes (64 bf16), sbo = bytes

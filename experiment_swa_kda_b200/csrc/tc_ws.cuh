@@ -1,0 +1,43 @@
+// Workspace of the tensor-core lane: bf16 operand panels per chunk-head (ch = slot*H + h), K = V = 128.
+#pragma once
+
+#include <cuda_bf16.h>
+
+#include "simt_ws.cuh"
+
+namespace kda {
+namespace tc {
+
+struct TcWs {
+    __nv_bfloat16 *W, *R, *E;   // [nch][64][128]   rows = token, cols = key
+    __nv_bfloat16* AT;          // [nch][64][64]    A transposed: [source s][target i]
+    __nv_bfloat16* UT;          // [nch][128][64]   U transposed: [value][token]
+    __nv_bfloat16* Hp;          // [nch][128][128]  chunk-start state, V-first [value][key]
+    __nv_bfloat16* ZT;          // [nch][128][64]   Z transposed: [value][token]
+    __nv_bfloat16* dHp;         // [nch][128][128]  adjoint of each chunk's outgoing state, V-first
+    __nv_bfloat16* dZT;         // [nch][128][64]   dZ transposed
+    float* decay_end;           // [nch][128]       exp(G_end)
+    int* status;                // device status word (0 = ok)
+};
+
+inline TcWs carve_tc(const KdaChunkShape& sh, void* mem, size_t* bytes = nullptr) {
+    TcWs t;
+    const size_t nch = (size_t)simt::slots_for(sh, false) * sh.heads;
+    simt::Carver c(mem);
+    t.W = c.take<__nv_bfloat16>(nch * 8192);
+    t.R = c.take<__nv_bfloat16>(nch * 8192);
+    t.E = c.take<__nv_bfloat16>(nch * 8192);
+    t.AT = c.take<__nv_bfloat16>(nch * 4096);
+    t.UT = c.take<__nv_bfloat16>(nch * 8192);
+    t.Hp = c.take<__nv_bfloat16>(nch * 16384);
+    t.ZT = c.take<__nv_bfloat16>(nch * 8192);
+    t.dHp = c.take<__nv_bfloat16>(nch * 16384);
+    t.dZT = c.take<__nv_bfloat16>(nch * 8192);
+    t.decay_end = c.take<float>(nch * 128);
+    t.status = c.take<int>(64);
+    if (bytes) *bytes = align_up(c.off, 256);
+    return t;
+}
+
+}  // namespace tc
+}  // namespace kda

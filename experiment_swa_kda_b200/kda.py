@@ -169,16 +169,25 @@ def chunk_kda(q: Tensor, k: Tensor, v: Tensor, g: Tensor, beta: Tensor, *, initi
     if reason is not None:
         raise RuntimeError(f"project CUDA KDA backend unavailable: {reason}")
     sc = float(q.shape[-1] ** -0.5 if scale is None else scale)
-    lane_id = _select_lane(lane, q)
+    lane_id = _select_lane(lane, q, v)
     cu = None if cu_seqlens is None else cu_seqlens.contiguous()
     o, fs = ops.ChunkKDAFunction.apply(q, k, v, g, beta, initial_state, bool(output_final_state), cu, sc,
                                        bool(use_qk_l2norm), lane_id)
     return o, fs
 
 
-def _select_lane(lane: str, q: Tensor) -> int:
-    if lane in ("auto", "fp32"):
+def _select_lane(lane: str, q: Tensor, v: Tensor) -> int:
+    """"tc": tcgen05 tensor-core tiles (128-wide heads, bf16 activations); "fp32": CUDA-core float32
+    arithmetic for any head size up to 256; "auto": tc whenever the shape allows it."""
+    tc_ok = q.dtype == torch.bfloat16 and q.shape[-1] == 128 and v.shape[-1] == 128
+    if lane == "auto":
+        return _lib.LANE_TC if tc_ok else _lib.LANE_FP32
+    if lane == "fp32":
         return _lib.LANE_FP32
+    if lane == "tc":
+        if not tc_ok:
+            raise RuntimeError("project CUDA KDA backend unavailable: the tensor-core lane needs bfloat16 and K = V = 128")
+        return _lib.LANE_TC
     raise ValueError(f"unknown lane: {lane}")
 
 
@@ -191,7 +200,7 @@ def recurrent_kda_step(q, k, v, g, beta, state, *, scale=None, use_qk_l2norm=Tru
 def kda(q: Tensor, k: Tensor, v: Tensor, raw_gate: Tensor, beta_logits: Tensor, A_log: Tensor, dt_bias: Tensor, *,
         initial_state: Optional[Tensor] = None, output_final_state: bool = False, mode: str = "project_chunk",
         lower_bound: float = -5.0, scale: Optional[float] = None, allow_fallback: bool = False,
-        cu_seqlens: Optional[Tensor] = None) -> Tuple[Tensor, Optional[Tensor]]:
+        cu_seqlens: Optional[Tensor] = None, lane: str = "auto") -> Tuple[Tensor, Optional[Tensor]]:
     """Raw-input KDA operator (L2 norm, gate and beta sigmoid fused), reference signature.
 
     Only the project modes exist here; anything else raises (fail closed)."""
@@ -218,7 +227,7 @@ def kda(q: Tensor, k: Tensor, v: Tensor, raw_gate: Tensor, beta_logits: Tensor, 
         return o, (new_state if output_final_state else None)
     cu = None if cu_seqlens is None else cu_seqlens.contiguous()
     o, fs = ops.ChunkKDAFunction.apply(q, k, v, g, beta, initial_state, bool(output_final_state), cu, sc, True,
-                                       _lib.LANE_FP32)
+                                       _select_lane(lane, q, v))
     return o, fs
 
 
