@@ -40,6 +40,7 @@ _SIGNATURES = {
     "kda_rmsnorm_gate_fwd": (C.c_int, [C.c_int64, C.c_int32, C.c_int32, C.c_float] + [_P] * 6),
     "kda_rmsnorm_gate_bwd_scratch_bytes": (C.c_size_t, [C.c_int64, C.c_int32]),
     "kda_rmsnorm_gate_bwd": (C.c_int, [C.c_int64, C.c_int32, C.c_int32] + [_P] * 9 + [C.c_size_t, _P]),
+    "kda_rmsnorm_gate_bwd_static": (C.c_int, [C.c_int64, C.c_int32, C.c_int32] + [_P] * 9),
     "kda_launch_count": (C.c_ulonglong, []),
     "kda_profile_enable": (None, [C.c_int]),
     "kda_profile_report": (C.c_int, [C.c_char_p, C.c_size_t]),

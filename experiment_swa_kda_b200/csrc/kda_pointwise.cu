@@ -858,3 +858,38 @@ extern "C" int kda_rmsnorm_gate_bwd(int64_t rows, int32_t dim, int32_t io_dtype,
     KDA_LAUNCH("rmsnorm_dw_reduce_kernel", st, pw::rmsnorm_dw_reduce_kernel<<<ceil_div(dim, 256), 256, 0, st>>>(nb, dim, part, dweight));
     return launch_status();
 }
+
+// =============================================================================================
+// Allocation-free variant of the gated-RMSNorm backward
+// =============================================================================================
+// The regular backward needs a caller-provided scratch buffer for the per-block partial sums of the
+// weight gradient.  Some callers have nowhere to get one: code running against a frozen memory plan
+// (a serving engine that sized all of its device memory at start-up), a plugin that is handed tensors
+// but no allocator, or anything that must not call cudaMalloc because that call synchronises the
+// device.  For them the partials live in a fixed array inside the library image.
+namespace {
+constexpr int kStaticMaxDim = 256;                 // widest row the static variant accepts
+constexpr int kStaticMaxBlocks = 148 * 8;          // the backward never launches more blocks than this
+constexpr int kMaxDevices = 64;
+static __device__ __align__(256) float g_rms_static_scratch[(size_t)kStaticMaxBlocks * kStaticMaxDim];   // 1.2 MB per GPU
+float* g_rms_static_ptr[kMaxDevices] = {nullptr};  // device address of the array, per device ordinal
+}  // namespace
+
+extern "C" int kda_rmsnorm_gate_bwd_static(int64_t rows, int32_t dim, int32_t io_dtype, const void* x, const void* gate,
+                                           const float* weight, const float* inv_rms, const void* d_y, void* dx,
+                                           void* dgate, float* dweight, void* stream) {
+    if (rows < 0 || dim <= 0) return KDA_ERR_BAD_SHAPE;
+    if (dim > kStaticMaxDim) return KDA_ERR_UNSUPPORTED;   // beyond the built-in scratch: use kda_rmsnorm_gate_bwd
+    int device = -1;
+    if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= kMaxDevices) return KDA_ERR_CUDA;
+    if (g_rms_static_ptr[device] == nullptr) {
+        // In host code the array's name is only a handle; the kernels need its address on the current device.
+        void* p = nullptr;
+        if (cudaGetSymbolAddress(&p, g_rms_static_scratch) != cudaSuccess || p == nullptr) return KDA_ERR_CUDA;
+        g_rms_static_ptr[device] = static_cast<float*>(p);
+    }
+    const size_t bytes = (size_t)kStaticMaxBlocks * kStaticMaxDim * sizeof(float);
+    return kda_rmsnorm_gate_bwd(rows, dim, io_dtype, x, gate, weight, inv_rms, d_y, dx, dgate, dweight,
+                                g_rms_static_ptr[device], bytes, stream);
+}
+

@@ -141,6 +141,21 @@ int kda_rmsnorm_gate_bwd(int64_t rows, int32_t dim, int32_t io_dtype, const void
                          const float* weight, const float* inv_rms, const void* d_y, void* dx, void* dgate,
                          float* dweight, void* scratch, size_t scratch_bytes, void* stream);
 
+/* ---- gated RMSNorm backward without a scratch argument (no counterpart in the reference) ----
+ * Same result as kda_rmsnorm_gate_bwd, for callers that cannot supply scratch memory: a serving
+ * process whose device memory was planned once at start-up, a plugin that receives tensors but no
+ * allocator, or a latency-critical path that must avoid cudaMalloc because it stalls the device.
+ * The partial sums live in a 1.2 MB array built into the library (held by every GPU that loads it
+ * until the process exits).  Limits: dim <= 256, otherwise KDA_ERR_UNSUPPORTED.  Calls no
+ * cudaMalloc / cudaFree and no allocating library routine.  The first call on each device looks up
+ * the array's device address (cudaGetSymbolAddress, with that device current); make that first
+ * call before starting any stream capture.  All calls share the one array and nothing in it needs
+ * to start at zero (every partial read is written earlier in the same call), but two calls that
+ * overlap on the GPU (different streams, no ordering between them) race on it. */
+int kda_rmsnorm_gate_bwd_static(int64_t rows, int32_t dim, int32_t io_dtype, const void* x, const void* gate,
+                                const float* weight, const float* inv_rms, const void* d_y, void* dx, void* dgate,
+                                float* dweight, void* stream);
+
 /* ---- launch accounting (diagnostics; no counterpart in the reference) ---------------
  * kda_launch_count: kernels this library has launched in this process so far.
  * kda_profile_enable(1): from now on every launch is bracketed by CUDA events on its stream.
