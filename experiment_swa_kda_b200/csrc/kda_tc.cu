@@ -4,7 +4,7 @@
 // One CTA owns one (sequence, head) and walks its chunks in order with the full 128x128 state held in
 // registers in V-first form (thread v owns row v, i.e. S[v][0..127]); all products are written transposed so
 // that M = 128 (value index) for every UMMA:
-//     [ (W H)^T | (R H)^T ]  = H^T [ W^T | R^T ]          M=128, N=128, K=128   (one UMMA chain, K-major B)
+//     [ (W H)^T | (R H)^T ]  = H^T [ W^T | R^T ]          M=128, N=128, K=128   (one UMMA chain, MN-major B)
 //     Z^T = U^T - (W H)^T                                  registers
 //     [ dH^T | (A Z)^T ]     = Z^T [ E | A^T ]             M=128, N=192, K=64    (one UMMA chain, MN-major B)
 //     H'^T = exp(G_end) . H^T + dH^T ,  O^T = (R H)^T + (A Z)^T
@@ -88,7 +88,7 @@ constexpr int kStageStride = 32768 + 24576 + 16384 + 1024; // keeps every stage 
 constexpr int kScanFwdSmem = 2 * kStageStride + 32768 + 16384 + 1024;
 
 __global__ void __launch_bounds__(128, 1)
-    scan_fwd_kernel(const __grid_constant__ CUtensorMap mW, const __grid_constant__ CUtensorMap mR,
+    tc_scan_fwd_kernel(const __grid_constant__ CUtensorMap mW, const __grid_constant__ CUtensorMap mR,
                     const __grid_constant__ CUtensorMap mE, const __grid_constant__ CUtensorMap mAT,
                     const __grid_constant__ CUtensorMap mUT, const __grid_constant__ CUtensorMap mH,
                     const __grid_constant__ CUtensorMap mZT, ScanFwdArgs p) {
@@ -140,10 +140,8 @@ __global__ void __launch_bounds__(128, 1)
         uint8_t* b = sm + st * kStageStride;
         mbar_expect_tx(&bar_full[st], kStageBytes);
         bulk_load_1d(b + 73728, p.decay_end + (size_t)ch * 128, 512, &bar_full[st]);
-        for (int kb = 0; kb < 2; ++kb) {
-            tma_load_2d(b + kb * 16384, &mW, &bar_full[st], kb * 64, ch * 64);
-            tma_load_2d(b + kb * 16384 + 8192, &mR, &bar_full[st], kb * 64, ch * 64);
-        }
+        tma_load_2d(b, &mW, &bar_full[st], 0, ch * 128);            // W^T [key][token]: n-block 0
+        tma_load_2d(b + 16384, &mR, &bar_full[st], 0, ch * 128);    // R^T [key][token]: n-block 1
         for (int nb = 0; nb < 2; ++nb) tma_load_2d(b + 32768 + nb * 8192, &mE, &bar_full[st], nb * 64, ch * 64);
         tma_load_2d(b + 32768 + 16384, &mAT, &bar_full[st], 0, ch * 64);
         tma_load_2d(b + 32768 + 24576, &mUT, &bar_full[st], 0, ch * 128);
@@ -155,7 +153,7 @@ __global__ void __launch_bounds__(128, 1)
         if (tid == 0) issue_loads(0);
         loads_issued = 1;
     }
-    const uint32_t idesc1 = umma_idesc_bf16(128, 128, kMajorK, kMajorK);
+    const uint32_t idesc1 = umma_idesc_bf16(128, 128, kMajorK, kMajorMN);
     const uint32_t idesc2 = umma_idesc_bf16(128, 192, kMajorK, kMajorMN);
 
     for (int c = 0; c < n && ok; ++c) {
@@ -191,11 +189,9 @@ __global__ void __launch_bounds__(128, 1)
                 tc_fence_after();
                 const uint32_t a0 = smem_u32(Hop), b0 = smem_u32(sb);
 #pragma unroll
-                for (int k16 = 0; k16 < 8; ++k16) {
-                    const uint32_t off = (k16 >> 2) * 16384 + (k16 & 3) * 32;
-                    umma_bf16_ss(tmem, umma_smem_desc_sw128(a0 + off, 16, 1024), umma_smem_desc_sw128(b0 + off, 16, 1024),
-                                 idesc1, k16 > 0);
-                }
+                for (int k16 = 0; k16 < 8; ++k16)
+                    umma_bf16_ss(tmem, umma_smem_desc_sw128(a0 + (k16 >> 2) * 16384 + (k16 & 3) * 32, 16, 1024),
+                                 umma_smem_desc_sw128(b0 + k16 * 2048, 16384, 1024), idesc1, k16 > 0);
                 umma_commit(&bar_mma1);
                 if (p.save) {
                     tma_store_2d(&mH, Hop, 0, ch * 128);
@@ -314,7 +310,7 @@ struct ScanBwdArgs {
 constexpr int kScanBwdSmem = 2 * kStageStride + 32768 + 16384 + 1024;
 
 __global__ void __launch_bounds__(128, 1)
-    scan_bwd_kernel(const __grid_constant__ CUtensorMap mW, const __grid_constant__ CUtensorMap mR,
+    tc_scan_bwd_kernel(const __grid_constant__ CUtensorMap mW, const __grid_constant__ CUtensorMap mR,
                     const __grid_constant__ CUtensorMap mE, const __grid_constant__ CUtensorMap mAT,
                     const __grid_constant__ CUtensorMap mdO, const __grid_constant__ CUtensorMap mdH,
                     const __grid_constant__ CUtensorMap mdZT, ScanBwdArgs p) {
@@ -370,10 +366,10 @@ __global__ void __launch_bounds__(128, 1)
         bulk_load_1d(b + 73728, p.decay_end + (size_t)ch * 128, 512, &bar_full[st]);
         for (int kb = 0; kb < 2; ++kb) {
             tma_load_2d(b + kb * 8192, &mE, &bar_full[st], kb * 64, ch * 64);
-            tma_load_2d(b + 24576 + kb * 8192, &mR, &bar_full[st], kb * 64, ch * 64);
-            tma_load_2d(b + 40960 + kb * 8192, &mW, &bar_full[st], kb * 64, ch * 64);
             tma_load_2d(b + 57344 + kb * 8192, &mdO, &bar_full[st], h * 128 + kb * 64, tok0);
         }
+        tma_load_2d(b + 24576, &mR, &bar_full[st], 0, ch * 128);    // R^T [key][token], K-major B
+        tma_load_2d(b + 40960, &mW, &bar_full[st], 0, ch * 128);    // W^T [key][token], K-major B
         tma_load_2d(b + 16384, &mAT, &bar_full[st], 0, ch * 64);
     };
 
@@ -385,8 +381,8 @@ __global__ void __launch_bounds__(128, 1)
     }
     const uint32_t id1a = umma_idesc_bf16(128, 64, kMajorMN, kMajorK);
     const uint32_t id1b = umma_idesc_bf16(128, 64, kMajorK, kMajorK);
-    const uint32_t id2a = umma_idesc_bf16(128, 128, kMajorMN, kMajorMN);
-    const uint32_t id2b = umma_idesc_bf16(128, 128, kMajorK, kMajorMN, 1);
+    const uint32_t id2a = umma_idesc_bf16(128, 128, kMajorMN, kMajorK);
+    const uint32_t id2b = umma_idesc_bf16(128, 128, kMajorK, kMajorK, 1);
 
     for (int j = 0; j < n && ok; ++j) {
         const int st = j & 1;
@@ -429,7 +425,7 @@ __global__ void __launch_bounds__(128, 1)
 #pragma unroll
                 for (int k16 = 0; k16 < 4; ++k16)     // dO^T R   (runs while the threads convert dZ)
                     umma_bf16_ss(tmem + 64, umma_smem_desc_sw128(s0 + 57344 + k16 * 2048, 8192, 1024),
-                                 umma_smem_desc_sw128(s0 + 24576 + k16 * 2048, 8192, 1024), id2a, k16 > 0);
+                                 umma_smem_desc_sw128(s0 + 24576 + k16 * 32, 16, 1024), id2a, k16 > 0);
                 tma_store_2d(&mdH, dHop, 0, ch * 128);
                 tma_store_2d(&mdH, dHop + 16384, 64, ch * 128);
                 tma_store_commit();
@@ -462,7 +458,7 @@ __global__ void __launch_bounds__(128, 1)
 #pragma unroll
             for (int k16 = 0; k16 < 4; ++k16)         // - dZ^T W
                 umma_bf16_ss(tmem + 64, umma_smem_desc_sw128(a_dz + k16 * 32, 16, 1024),
-                             umma_smem_desc_sw128(s0 + 40960 + k16 * 2048, 8192, 1024), id2b, 1);
+                             umma_smem_desc_sw128(s0 + 40960 + k16 * 32, 16, 1024), id2b, 1);
             umma_commit(&bar_mma2);
             tma_store_2d(&mdZT, dZop, 0, ch * 128);
             tma_store_commit();
@@ -500,8 +496,8 @@ __global__ void __launch_bounds__(128, 1)
 // ---------------------------------------------------------------------------------------------
 // interim glue between the float32 intra-chunk kernels and the tensor-core scan
 // ---------------------------------------------------------------------------------------------
-// float32 workspace -> bf16 operand panels W, R = qn exp(G), E = kn exp(G_end - G), A^T, U^T, exp(G_end)
-__global__ void __launch_bounds__(256) pack_panels_kernel(simt::Ws w, TcWs t) {
+// float32 workspace -> bf16 operand panels W^T, R^T = (qn exp(G))^T, E = kn exp(G_end - G), A^T, U^T, exp(G_end)
+__global__ void __launch_bounds__(256) tc_pack_panels_kernel(simt::Ws w, TcWs t) {
     const int slot = blockIdx.x, h = blockIdx.y;
     if (w.chunk_len[slot] == 0) return;
     const size_t ch = (size_t)slot * w.H + h;
@@ -513,8 +509,9 @@ __global__ void __launch_bounds__(256) pack_panels_kernel(simt::Ws w, TcWs t) {
     for (int idx = tid; idx < 64 * 128; idx += 256) {
         const int d = idx & 127;
         const float g = G[idx], ge = G[63 * 128 + d];
-        t.W[ch * 8192 + idx] = __float2bfloat16(W[idx]);
-        t.R[ch * 8192 + idx] = __float2bfloat16(qn[idx] * expf(g));
+        const int i = idx >> 7;
+        t.WT[ch * 8192 + d * 64 + i] = __float2bfloat16(W[idx]);                      // [key][token]
+        t.RT[ch * 8192 + d * 64 + i] = __float2bfloat16(qn[idx] * expf(g));
         t.E[ch * 8192 + idx] = __float2bfloat16(kn[idx] * expf(ge - g));
     }
     if (tid < 128) t.decay_end[ch * 128 + tid] = expf(G[63 * 128 + tid]);
@@ -531,7 +528,7 @@ __global__ void __launch_bounds__(256) pack_panels_kernel(simt::Ws w, TcWs t) {
 }
 
 // bf16 panels H [v][k], Z^T [v][i]  ->  float32 workspace Hc [k][v], Z [i][v]
-__global__ void __launch_bounds__(256) unpack_state_kernel(simt::Ws w, TcWs t) {
+__global__ void __launch_bounds__(256) tc_unpack_state_kernel(simt::Ws w, TcWs t) {
     const int slot = blockIdx.x, h = blockIdx.y;
     if (w.chunk_len[slot] == 0) return;
     const size_t ch = (size_t)slot * w.H + h;
@@ -547,7 +544,7 @@ __global__ void __launch_bounds__(256) unpack_state_kernel(simt::Ws w, TcWs t) {
 }
 
 // bf16 panels dH' [v][k], dZ^T [v][i]  ->  float32 scratch dHn [k][v], dZ [i][v]
-__global__ void __launch_bounds__(256) unpack_adjoint_kernel(simt::Ws w, simt::Scr s, TcWs t) {
+__global__ void __launch_bounds__(256) tc_unpack_adjoint_kernel(simt::Ws w, simt::Scr s, TcWs t) {
     const int slot = blockIdx.x, h = blockIdx.y;
     if (w.chunk_len[slot] == 0) return;
     const size_t ch = (size_t)slot * w.H + h;
@@ -573,24 +570,24 @@ int tc_scan_forward(const simt::Ws& w, const tc::TcWs& t, int n_seq, const float
     const uint64_t nch = (uint64_t)w.nslots * w.H;
     CUtensorMap mW, mR, mE, mAT, mUT, mH, mZT;
     int rc = 0;
-    rc |= make_map_bf16(&mW, t.W, nch * 64, 128, 64, 64);
-    rc |= make_map_bf16(&mR, t.R, nch * 64, 128, 64, 64);
+    rc |= make_map_bf16(&mW, t.WT, nch * 128, 64, 64, 128);
+    rc |= make_map_bf16(&mR, t.RT, nch * 128, 64, 64, 128);
     rc |= make_map_bf16(&mE, t.E, nch * 64, 128, 64, 64);
     rc |= make_map_bf16(&mAT, t.AT, nch * 64, 64, 64, 64);
     rc |= make_map_bf16(&mUT, t.UT, nch * 128, 64, 64, 128);
     rc |= make_map_bf16(&mH, t.Hp, nch * 128, 128, 64, 128);
     rc |= make_map_bf16(&mZT, t.ZT, nch * 128, 64, 64, 128);
     if (rc) return KDA_ERR_CUDA;
-    KDA_LAUNCH("tc_pack_panels_kernel", st, pack_panels_kernel<<<dim3(w.nslots, w.H), 256, 0, st>>>(w, t));
+    KDA_LAUNCH("@@tc_pack_panels_kernel", st, tc_pack_panels_kernel<<<dim3(w.nslots, w.H), 256, 0, st>>>(w, t));
     ScanFwdArgs a;
     a.seq_chunk0 = w.seq_chunk0; a.chunk_tok0 = w.chunk_tok0; a.chunk_len = w.chunk_len;
     a.decay_end = t.decay_end; a.h0 = h0; a.final_state = final_state; a.o = static_cast<__nv_bfloat16*>(o);
     a.H = w.H; a.save = 1; a.status = t.status;
-    if (cudaFuncSetAttribute(scan_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kScanFwdSmem) != cudaSuccess)
+    if (cudaFuncSetAttribute(tc_scan_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kScanFwdSmem) != cudaSuccess)
         return KDA_ERR_CUDA;
-    KDA_LAUNCH("tc_scan_fwd_kernel", st,
-               scan_fwd_kernel<<<dim3(n_seq, w.H), 128, kScanFwdSmem, st>>>(mW, mR, mE, mAT, mUT, mH, mZT, a));
-    KDA_LAUNCH("tc_unpack_state_kernel", st, unpack_state_kernel<<<dim3(w.nslots, w.H), 256, 0, st>>>(w, t));
+    KDA_LAUNCH("@@tc_scan_fwd_kernel", st,
+               tc_scan_fwd_kernel<<<dim3(n_seq, w.H), 128, kScanFwdSmem, st>>>(mW, mR, mE, mAT, mUT, mH, mZT, a));
+    KDA_LAUNCH("@@tc_unpack_state_kernel", st, tc_unpack_state_kernel<<<dim3(w.nslots, w.H), 256, 0, st>>>(w, t));
     return launch_status();
 }
 
@@ -600,8 +597,8 @@ int tc_scan_backward(const simt::Ws& w, const simt::Scr& s, const tc::TcWs& t, i
     const uint64_t nch = (uint64_t)w.nslots * w.H;
     CUtensorMap mW, mR, mE, mAT, mdO, mdH, mdZT;
     int rc = 0;
-    rc |= make_map_bf16(&mW, t.W, nch * 64, 128, 64, 64);
-    rc |= make_map_bf16(&mR, t.R, nch * 64, 128, 64, 64);
+    rc |= make_map_bf16(&mW, t.WT, nch * 128, 64, 64, 128);
+    rc |= make_map_bf16(&mR, t.RT, nch * 128, 64, 64, 128);
     rc |= make_map_bf16(&mE, t.E, nch * 64, 128, 64, 64);
     rc |= make_map_bf16(&mAT, t.AT, nch * 64, 64, 64, 64);
     rc |= make_map_bf16(&mdO, d_o, (uint64_t)tokens, (uint64_t)w.H * 128, 64, 64);
@@ -611,11 +608,11 @@ int tc_scan_backward(const simt::Ws& w, const simt::Scr& s, const tc::TcWs& t, i
     ScanBwdArgs a;
     a.seq_chunk0 = w.seq_chunk0; a.chunk_tok0 = w.chunk_tok0; a.decay_end = t.decay_end;
     a.d_final = d_final; a.dh0 = dh0; a.H = w.H; a.status = t.status;
-    if (cudaFuncSetAttribute(scan_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kScanBwdSmem) != cudaSuccess)
+    if (cudaFuncSetAttribute(tc_scan_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kScanBwdSmem) != cudaSuccess)
         return KDA_ERR_CUDA;
-    KDA_LAUNCH("tc_scan_bwd_kernel", st,
-               scan_bwd_kernel<<<dim3(n_seq, w.H), 128, kScanBwdSmem, st>>>(mW, mR, mE, mAT, mdO, mdH, mdZT, a));
-    KDA_LAUNCH("tc_unpack_adjoint_kernel", st, unpack_adjoint_kernel<<<dim3(w.nslots, w.H), 256, 0, st>>>(w, s, t));
+    KDA_LAUNCH("@@tc_scan_bwd_kernel", st,
+               tc_scan_bwd_kernel<<<dim3(n_seq, w.H), 128, kScanBwdSmem, st>>>(mW, mR, mE, mAT, mdO, mdH, mdZT, a));
+    KDA_LAUNCH("@@tc_unpack_adjoint_kernel", st, tc_unpack_adjoint_kernel<<<dim3(w.nslots, w.H), 256, 0, st>>>(w, s, t));
     return launch_status();
 }
 

@@ -9,7 +9,8 @@ namespace kda {
 namespace tc {
 
 struct TcWs {
-    __nv_bfloat16 *W, *R, *E;   // [nch][64][128]   rows = token, cols = key
+    __nv_bfloat16 *WT, *RT;     // [nch][128][64]   rows = key, cols = token
+    __nv_bfloat16* E;           // [nch][64][128]   rows = token, cols = key
     __nv_bfloat16* AT;          // [nch][64][64]    A transposed: [source s][target i]
     __nv_bfloat16* UT;          // [nch][128][64]   U transposed: [value][token]
     __nv_bfloat16* Hp;          // [nch][128][128]  chunk-start state, V-first [value][key]
@@ -24,8 +25,8 @@ inline TcWs carve_tc(const KdaChunkShape& sh, void* mem, size_t* bytes = nullptr
     TcWs t;
     const size_t nch = (size_t)simt::slots_for(sh, false) * sh.heads;
     simt::Carver c(mem);
-    t.W = c.take<__nv_bfloat16>(nch * 8192);
-    t.R = c.take<__nv_bfloat16>(nch * 8192);
+    t.WT = c.take<__nv_bfloat16>(nch * 8192);
+    t.RT = c.take<__nv_bfloat16>(nch * 8192);
     t.E = c.take<__nv_bfloat16>(nch * 8192);
     t.AT = c.take<__nv_bfloat16>(nch * 4096);
     t.UT = c.take<__nv_bfloat16>(nch * 8192);
