@@ -60,8 +60,8 @@ def load(build_if_missing: bool = True):
     global _lib
     if _lib is not None:
         return _lib
-    path = _build.LIB
-    if build_if_missing and _build.is_stale():
+    path = os.environ.get("KDA_B200_LIB") or _build.LIB      # explicit library override (diagnostic builds)
+    if path == _build.LIB and build_if_missing and _build.is_stale():
         try:
             _build.build()
         except RuntimeError:

@@ -206,7 +206,7 @@ __global__ void __launch_bounds__(256) decode_kernel(int H, int K, int V, int bf
 //   xx = [cache[..., :], x] along time (cache slot p <-> time p - W);  y[t] = act(sum_j w[c][j] xx[t + 1 + j])
 // One thread: VEC adjacent channels x kConvTT consecutive tokens, sliding window in registers.
 // =============================================================================================
-constexpr int kConvTT = 16;
+constexpr int kConvTT = 4;
 
 template <int VEC, bool BF16>
 __device__ __forceinline__ void ld_vec(float (&dst)[VEC], const void* p, size_t i) {
@@ -258,6 +258,39 @@ __device__ __forceinline__ void st_vec(void* p, size_t i, const float (&src)[VEC
     }
 }
 
+
+// weights of VEC adjacent channels: W*VEC contiguous elements starting at c0*W
+template <int W, int VEC, bool BF16>
+__device__ __forceinline__ void ld_weights(float (&wv)[W][VEC], const void* wgt, int c0) {
+    float flat[W * VEC];
+    constexpr int N = W * VEC;
+    const size_t base = (size_t)c0 * W;
+    if (BF16 && N % 8 == 0 && (base % 8) == 0) {
+#pragma unroll
+        for (int j = 0; j < N / 8; ++j) {
+            float t[8];
+            ld_vec<8, true>(t, wgt, base + 8 * j);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) flat[8 * j + e] = t[e];
+        }
+    } else if (!BF16 && N % 4 == 0 && (base % 4) == 0) {
+#pragma unroll
+        for (int j = 0; j < N / 4; ++j) {
+            float t[4];
+            ld_vec<4, false>(t, wgt, base + 4 * j);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) flat[4 * j + e] = t[e];
+        }
+    } else {
+#pragma unroll
+        for (int j = 0; j < N; ++j) flat[j] = ld_io(wgt, base + j, BF16);
+    }
+#pragma unroll
+    for (int e = 0; e < VEC; ++e)
+#pragma unroll
+        for (int j = 0; j < W; ++j) wv[j][e] = flat[e * W + j];
+}
+
 // xx at time tau (tau < 0 reaches into the cache: slot W + tau), for VEC channels starting at c0
 template <int VEC, bool BF16>
 __device__ __forceinline__ void ld_xx(float (&dst)[VEC], const void* x, const void* cache, int b, int tau, int c0, int T,
@@ -283,28 +316,39 @@ __global__ void __launch_bounds__(256) conv_fwd_kernel(int B, int T, int C, int 
     const int cg = (int)(gid % ncg), tile = (int)((gid / ncg) % ntile), b = (int)(gid / ((size_t)ncg * ntile));
     const int c0 = cg * VEC, t0 = tile * kConvTT, t1 = min(T, t0 + kConvTT);
     float wv[W][VEC];
+    ld_weights<W, VEC, BF16>(wv, wgt, c0);
+    // inputs at times t0-(W-1) .. t0+kConvTT-1.  Interior tiles issue every load unconditionally (so they
+    // overlap); only the first and last tile of a sequence take the guarded path.
+    float xin[kConvTT + W - 1][VEC];
+    if (t0 >= W - 1 && t0 + kConvTT <= T) {
 #pragma unroll
-    for (int j = 0; j < W; ++j)
+        for (int j = 0; j < kConvTT + W - 1; ++j)
+            ld_vec<VEC, BF16>(xin[j], x, ((size_t)b * T + (t0 - (W - 1) + j)) * C + c0);
+    } else {
 #pragma unroll
-        for (int e = 0; e < VEC; ++e) wv[j][e] = ld_io(wgt, (size_t)(c0 + e) * W + j, BF16);
-    float win[W][VEC];   // win[j] = xx at time t - (W-1) + j
+        for (int j = 0; j < kConvTT + W - 1; ++j) {
+            const int tau = t0 - (W - 1) + j;
+            if (tau < T) ld_xx<VEC, BF16>(xin[j], x, cache, b, tau, c0, T, C, W);
+            else {
 #pragma unroll
-    for (int j = 0; j < W - 1; ++j) ld_xx<VEC, BF16>(win[j + 1], x, cache, b, t0 - (W - 1) + j, c0, T, C, W);
-    for (int t = t0; t < t1; ++t) {
-#pragma unroll
-        for (int j = 0; j < W - 1; ++j)
-#pragma unroll
-            for (int e = 0; e < VEC; ++e) win[j][e] = win[j + 1][e];
-        ld_vec<VEC, BF16>(win[W - 1], x, ((size_t)b * T + t) * C + c0);
-        float out[VEC];
-#pragma unroll
-        for (int e = 0; e < VEC; ++e) {
-            float z = 0.f;
-#pragma unroll
-            for (int j = 0; j < W; ++j) z += wv[j][e] * win[j][e];
-            out[e] = silu ? z * sigmoidf_(z) : z;
+                for (int e = 0; e < VEC; ++e) xin[j][e] = 0.f;
+            }
         }
-        st_vec<VEC, BF16>(y, ((size_t)b * T + t) * C + c0, out);
+    }
+#pragma unroll
+    for (int tt = 0; tt < kConvTT; ++tt) {
+        const int t = t0 + tt;
+        if (t < t1) {
+            float out[VEC];
+#pragma unroll
+            for (int e = 0; e < VEC; ++e) {
+                float z = 0.f;
+#pragma unroll
+                for (int j = 0; j < W; ++j) z += wv[j][e] * xin[tt + j][e];
+                out[e] = silu ? z * sigmoidf_(z) : z;
+            }
+            st_vec<VEC, BF16>(y, ((size_t)b * T + t) * C + c0, out);
+        }
     }
     if (fin != nullptr && t1 == T) {
         // cache slot j holds xx at time T - W + j
@@ -321,7 +365,7 @@ __global__ void __launch_bounds__(256) conv_fwd_kernel(int B, int T, int C, int 
 // pre-activations of its tile plus W-1 following tokens, emits dx for its tile and a
 // register partial of dweight; the 8 tiles of a block are summed in shared memory and
 // written as one partial per block, reduced in fixed order by conv_dw_reduce_kernel.
-constexpr int kConvBT = 32;  // tokens per thread in the backward
+constexpr int kConvBT = 4;   // tokens per thread in the backward
 
 template <int W, int VEC, bool BF16>
 __global__ void __launch_bounds__(256) conv_bwd_kernel(int B, int T, int C, int silu, const void* __restrict__ x,
@@ -343,10 +387,44 @@ __global__ void __launch_bounds__(256) conv_bwd_kernel(int B, int T, int C, int 
     if (active) {
         const int c0 = cg * VEC, t0 = tile * kConvBT, t1 = min(T, t0 + kConvBT);
         float wv[W][VEC];
+        ld_weights<W, VEC, BF16>(wv, wgt, c0);
+        if (t0 >= W - 1 && t0 + kConvBT + W <= T) {
+            // interior tile: every load is unconditional and independent, then pure register arithmetic
+            float xin[kConvBT + 2 * (W - 1)][VEC];   // x at t0-(W-1) .. t0+kConvBT+W-2
+            float gy[kConvBT + W - 1][VEC];          // dy, then dz, at t0 .. t0+kConvBT+W-2
 #pragma unroll
-        for (int j = 0; j < W; ++j)
+            for (int j = 0; j < kConvBT + 2 * (W - 1); ++j)
+                ld_vec<VEC, BF16>(xin[j], x, ((size_t)b * T + (t0 - (W - 1) + j)) * C + c0);
 #pragma unroll
-            for (int e = 0; e < VEC; ++e) wv[j][e] = ld_io(wgt, (size_t)(c0 + e) * W + j, BF16);
+            for (int j = 0; j < kConvBT + W - 1; ++j) ld_vec<VEC, BF16>(gy[j], dy, ((size_t)b * T + t0 + j) * C + c0);
+#pragma unroll
+            for (int j = 0; j < kConvBT + W - 1; ++j)
+#pragma unroll
+                for (int e = 0; e < VEC; ++e) {
+                    float z = 0.f;
+#pragma unroll
+                    for (int m = 0; m < W; ++m) z += wv[m][e] * xin[j + m][e];
+                    if (silu) {
+                        const float sg = sigmoidf_(z);
+                        gy[j][e] *= sg * (1.f + z * (1.f - sg));
+                    }
+                }
+#pragma unroll
+            for (int j = 0; j < kConvBT; ++j) {
+                float out[VEC];
+#pragma unroll
+                for (int e = 0; e < VEC; ++e) {
+                    float a = 0.f;
+#pragma unroll
+                    for (int m = 0; m < W; ++m) {
+                        a += wv[m][e] * gy[j + W - 1 - m][e];
+                        dwv[m][e] += gy[j][e] * xin[j + m][e];
+                    }
+                    out[e] = a;
+                }
+                st_vec<VEC, BF16>(dx, ((size_t)b * T + t0 + j) * C + c0, out);
+            }
+        } else {
         float win[W][VEC];   // xx window ending at the token whose dz is being produced
         float dzw[W][VEC];   // dzw[m] = dz at token (cur - (W-1) + m)
 #pragma unroll
@@ -356,7 +434,10 @@ __global__ void __launch_bounds__(256) conv_bwd_kernel(int B, int T, int C, int 
 #pragma unroll
         for (int j = 0; j < W - 1; ++j) ld_xx<VEC, BF16>(win[j + 1], x, cache, b, t0 - (W - 1) + j, c0, T, C, W);
         // walk cur over [t0, t1 + W - 1): produce dz[cur]; once W-1 tokens ahead, emit dx[cur - (W-1)]
-        for (int cur = t0; cur < t1 + W - 1; ++cur) {
+#pragma unroll
+        for (int step = 0; step < kConvBT + W - 1; ++step) {
+            const int cur = t0 + step;
+            if (cur >= t1 + W - 1) break;
 #pragma unroll
             for (int j = 0; j < W - 1; ++j)
 #pragma unroll
@@ -401,6 +482,7 @@ __global__ void __launch_bounds__(256) conv_bwd_kernel(int B, int T, int C, int 
                 st_vec<VEC, BF16>(dx, ((size_t)b * T + t) * C + c0, out);
             }
         }
+        }   // guarded (boundary) path
         if (dcache != nullptr && tile == 0) {
             // cache slot p is time p - W (< 0): d = sum_j w[j] dz[p - W + W-1-j] = sum_j w[j] dz[p-1-j], plus the
             // final-state cotangent when the sequence is shorter than the window.  Needs dz[0 .. W-2]: recompute.
@@ -468,12 +550,23 @@ __global__ void __launch_bounds__(256) conv_bwd_kernel(int B, int T, int C, int 
     }
 }
 
-__global__ void conv_dw_reduce_kernel(int nblk, int CW, const float* __restrict__ part, float* __restrict__ dw) {
-    const int i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= CW) return;
+// 32 columns per block; 8 warps each sum every 8th partial row, then a fixed-order combine
+__global__ void __launch_bounds__(256) conv_dw_reduce_kernel(int nblk, int CW, const float* __restrict__ part,
+                                                             float* __restrict__ dw) {
+    __shared__ float red[8][32];
+    const int lane = threadIdx.x & 31, seg = threadIdx.x >> 5;
+    const int i = blockIdx.x * 32 + lane;
     float a = 0.f;
-    for (int b = 0; b < nblk; ++b) a += part[(size_t)b * CW + i];
-    dw[i] = a;
+    if (i < CW)
+        for (int b = seg; b < nblk; b += 8) a += part[(size_t)b * CW + i];
+    red[seg][lane] = a;
+    __syncthreads();
+    if (seg == 0 && i < CW) {
+        float t = 0.f;
+#pragma unroll
+        for (int r = 0; r < 8; ++r) t += red[r][lane];
+        dw[i] = t;
+    }
 }
 
 // =============================================================================================
@@ -623,12 +716,23 @@ __global__ void __launch_bounds__(256) rmsnorm_bwd_kernel(long long rows, int D,
     }
 }
 
-__global__ void rmsnorm_dw_reduce_kernel(int nblk, int D, const float* __restrict__ part, float* __restrict__ dw) {
-    const int d = blockIdx.x * blockDim.x + threadIdx.x;
-    if (d >= D) return;
+// 32 columns per block; 8 warps each sum every 8th partial row, then a fixed-order combine
+__global__ void __launch_bounds__(256) rmsnorm_dw_reduce_kernel(int nblk, int D, const float* __restrict__ part,
+                                                                float* __restrict__ dw) {
+    __shared__ float red[8][32];
+    const int lane = threadIdx.x & 31, seg = threadIdx.x >> 5;
+    const int d = blockIdx.x * 32 + lane;
     float a = 0.f;
-    for (int b = 0; b < nblk; ++b) a += part[(size_t)b * D + d];
-    dw[d] = a;
+    if (d < D)
+        for (int b = seg; b < nblk; b += 8) a += part[(size_t)b * D + d];
+    red[seg][lane] = a;
+    __syncthreads();
+    if (seg == 0 && d < D) {
+        float t = 0.f;
+#pragma unroll
+        for (int r = 0; r < 8; ++r) t += red[r][lane];
+        dw[d] = t;
+    }
 }
 
 }  // namespace pw
@@ -752,7 +856,7 @@ int conv_bwd_w(int B, int T, int C, int bf16, int silu, const void* x, const voi
         }
     }
     const int nblk = grid.y * grid.z;
-    KDA_LAUNCH("conv_dw_reduce_kernel", st, pw::conv_dw_reduce_kernel<<<ceil_div(C * W, 256), 256, 0, st>>>(nblk, C * W, part, dwgt));
+    KDA_LAUNCH("conv_dw_reduce_kernel", st, pw::conv_dw_reduce_kernel<<<ceil_div(C * W, 32), 256, 0, st>>>(nblk, C * W, part, dwgt));
     return launch_status();
 }
 
@@ -805,7 +909,7 @@ extern "C" int kda_conv_bwd(int32_t batch, int32_t seq_len, int32_t channels, in
 }
 
 namespace {
-inline int rms_blocks(long long rows) { return (int)std::min<long long>((rows + 7) / 8, 148LL * 8); }
+inline int rms_blocks(long long rows) { return (int)std::min<long long>((rows + 7) / 8, 148LL * 4); }
 }  // namespace
 
 extern "C" int kda_rmsnorm_gate_fwd(int64_t rows, int32_t dim, int32_t io_dtype, float eps, const void* x,
@@ -855,7 +959,7 @@ extern "C" int kda_rmsnorm_gate_bwd(int64_t rows, int32_t dim, int32_t io_dtype,
             else KDA_LAUNCH("rmsnorm_bwd_kernel", st, pw::rmsnorm_bwd_kernel<false, false><<<nb, 256, smem, st>>>(rows, dim, x, gate, weight, inv_rms, d_y, dx, dgate, part));
         }
     }
-    KDA_LAUNCH("rmsnorm_dw_reduce_kernel", st, pw::rmsnorm_dw_reduce_kernel<<<ceil_div(dim, 256), 256, 0, st>>>(nb, dim, part, dweight));
+    KDA_LAUNCH("rmsnorm_dw_reduce_kernel", st, pw::rmsnorm_dw_reduce_kernel<<<ceil_div(dim, 32), 256, 0, st>>>(nb, dim, part, dweight));
     return launch_status();
 }
 

@@ -901,6 +901,8 @@ using simt::Ws;
 
 int tc_scan_forward(const simt::Ws& w, const tc::TcWs& t, int n_seq, const float* h0, float* final_state, void* o,
                     cudaStream_t st);
+int tc_intra_forward(const simt::Ws& w, const tc::TcWs& t, const void* q, const void* k, const void* v, const void* g,
+                     const void* beta, int gbf16, int l2norm, float scale, int tokens, cudaStream_t st);
 int tc_scan_backward(const simt::Ws& w, const simt::Scr& s, const tc::TcWs& t, int n_seq, int tokens, const void* d_o,
                      const float* d_final, float* dh0, cudaStream_t st);
 
@@ -919,6 +921,20 @@ int simt_chunk_fwd(const KdaChunkShape* sh, const void* q, const void* k, const 
     const int bf16 = sh->io_dtype == KDA_DTYPE_BF16, gbf16 = sh->gate_dtype == KDA_DTYPE_BF16;
     const int KT = w.Kp / 64, VT = w.Vp / 64;
     KDA_LAUNCH("chunk_table_kernel", st, simt::chunk_table_kernel<<<1, 256, 0, st>>>(w, cu, sh->n_seq, sh->seq_len));
+    if (sh->lane == KDA_LANE_TC) {
+        // chunk-parallel operand panels on tcgen05, then the tensor-core scan with the chunk output fused in
+        size_t ws_bytes = 0;
+        simt::carve_ws(*sh, nullptr, &ws_bytes);
+        tc::TcWs t = tc::carve_tc(*sh, static_cast<char*>(workspace) + ws_bytes);
+        if (cudaMemsetAsync(t.status, 0, sizeof(int), st) != cudaSuccess) return KDA_ERR_CUDA;
+        if (w.nslots > 0) {
+            int rc = tc_intra_forward(w, t, q, k, v, g, beta, gbf16, sh->l2norm, sh->scale, sh->tokens, st);
+            if (rc) return rc;
+            rc = tc_scan_forward(w, t, sh->n_seq, h0, final_state, o, st);
+            if (rc) return rc;
+        }
+        return launch_status();
+    }
     if (w.nslots > 0) {
         dim3 gch(w.nslots, w.H);
         KDA_LAUNCH("prep_kernel", st, simt::prep_kernel<<<gch, 256, 0, st>>>(w, q, k, g, beta, bf16, gbf16, sh->l2norm, sh->scale));
@@ -927,18 +943,6 @@ int simt_chunk_fwd(const KdaChunkShape* sh, const void* q, const void* k, const 
         KDA_LAUNCH("build_am_kernel", st, simt::build_am_kernel<<<gch, 256, sm_am, st>>>(w));
         size_t sm_uw = (size_t)2 * 64 * kLD * sizeof(float);
         KDA_LAUNCH("uw_kernel", st, simt::uw_kernel<<<dim3(w.nslots, w.H, KT + VT), 256, sm_uw, st>>>(w, v, bf16));
-    }
-    if (sh->lane == KDA_LANE_TC) {
-        // tensor-core scan with the chunk output fused in; panels come from the float32 intra-chunk kernels
-        size_t ws_bytes = 0;
-        simt::carve_ws(*sh, nullptr, &ws_bytes);
-        tc::TcWs t = tc::carve_tc(*sh, static_cast<char*>(workspace) + ws_bytes);
-        if (cudaMemsetAsync(t.status, 0, sizeof(int), st) != cudaSuccess) return KDA_ERR_CUDA;
-        if (w.nslots > 0) {
-            int rc = tc_scan_forward(w, t, sh->n_seq, h0, final_state, o, st);
-            if (rc) return rc;
-        }
-        return launch_status();
     }
     {
         size_t sm_scan = ((size_t)2 * 64 * (w.Kp + 1) + (size_t)w.Kp * simt::kVS + 64 * simt::kVS + w.Kp) * sizeof(float);

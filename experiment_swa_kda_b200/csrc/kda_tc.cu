@@ -578,16 +578,15 @@ int tc_scan_forward(const simt::Ws& w, const tc::TcWs& t, int n_seq, const float
     rc |= make_map_bf16(&mH, t.Hp, nch * 128, 128, 64, 128);
     rc |= make_map_bf16(&mZT, t.ZT, nch * 128, 64, 64, 128);
     if (rc) return KDA_ERR_CUDA;
-    KDA_LAUNCH("@@tc_pack_panels_kernel", st, tc_pack_panels_kernel<<<dim3(w.nslots, w.H), 256, 0, st>>>(w, t));
     ScanFwdArgs a;
     a.seq_chunk0 = w.seq_chunk0; a.chunk_tok0 = w.chunk_tok0; a.chunk_len = w.chunk_len;
     a.decay_end = t.decay_end; a.h0 = h0; a.final_state = final_state; a.o = static_cast<__nv_bfloat16*>(o);
     a.H = w.H; a.save = 1; a.status = t.status;
     if (cudaFuncSetAttribute(tc_scan_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kScanFwdSmem) != cudaSuccess)
         return KDA_ERR_CUDA;
-    KDA_LAUNCH("@@tc_scan_fwd_kernel", st,
+    KDA_LAUNCH("tc_scan_fwd_kernel", st,
                tc_scan_fwd_kernel<<<dim3(n_seq, w.H), 128, kScanFwdSmem, st>>>(mW, mR, mE, mAT, mUT, mH, mZT, a));
-    KDA_LAUNCH("@@tc_unpack_state_kernel", st, tc_unpack_state_kernel<<<dim3(w.nslots, w.H), 256, 0, st>>>(w, t));
+    KDA_LAUNCH("tc_unpack_state_kernel", st, tc_unpack_state_kernel<<<dim3(w.nslots, w.H), 256, 0, st>>>(w, t));
     return launch_status();
 }
 
@@ -610,9 +609,9 @@ int tc_scan_backward(const simt::Ws& w, const simt::Scr& s, const tc::TcWs& t, i
     a.d_final = d_final; a.dh0 = dh0; a.H = w.H; a.status = t.status;
     if (cudaFuncSetAttribute(tc_scan_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kScanBwdSmem) != cudaSuccess)
         return KDA_ERR_CUDA;
-    KDA_LAUNCH("@@tc_scan_bwd_kernel", st,
+    KDA_LAUNCH("tc_scan_bwd_kernel", st,
                tc_scan_bwd_kernel<<<dim3(n_seq, w.H), 128, kScanBwdSmem, st>>>(mW, mR, mE, mAT, mdO, mdH, mdZT, a));
-    KDA_LAUNCH("@@tc_unpack_adjoint_kernel", st, tc_unpack_adjoint_kernel<<<dim3(w.nslots, w.H), 256, 0, st>>>(w, s, t));
+    KDA_LAUNCH("tc_unpack_adjoint_kernel", st, tc_unpack_adjoint_kernel<<<dim3(w.nslots, w.H), 256, 0, st>>>(w, s, t));
     return launch_status();
 }
 
