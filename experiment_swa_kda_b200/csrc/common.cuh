@@ -4,6 +4,8 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdio.h>
+#include <stdlib.h>
 
 #include "../../include/kda_b200.h"
 
@@ -49,6 +51,7 @@ void end(cudaStream_t st);
 // Host-side launch check: returns a KDA_ERR_* code instead of throwing.
 inline int launch_status() {
     cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess && getenv("KDA_B200_VERBOSE")) fprintf(stderr, "libkda_b200: CUDA error: %s\n", cudaGetErrorString(e));
     return e == cudaSuccess ? KDA_OK : KDA_ERR_CUDA;
 }
 

@@ -14,6 +14,8 @@
 // The equations restate reference chunk_wy_forward.cu:125-405, 761-858, 940-1275, 1498-1588
 // and, for the adjoints, chunk_wy_backward.cu:2445-2562, 2818-3331, 3337-3552, 3787-3894.
 
+#include <cstdlib>
+
 #include "common.cuh"
 #include "simt_ws.cuh"
 #include "tc_ws.cuh"
@@ -905,6 +907,9 @@ int tc_intra_forward(const simt::Ws& w, const tc::TcWs& t, const void* q, const 
                      const void* beta, int gbf16, int l2norm, float scale, int tokens, cudaStream_t st);
 int tc_scan_backward(const simt::Ws& w, const simt::Scr& s, const tc::TcWs& t, int n_seq, int tokens, const void* d_o,
                      const float* d_final, float* dh0, cudaStream_t st);
+int tc_intra_backward(const simt::Ws& w, const tc::TcWs& t, int tokens, const void* q, const void* k, const void* v,
+                      const void* g, const void* d_o, int gbf16, int l2norm, float scale, void* dq, void* dk, void* dv,
+                      void* dg, void* dbeta, cudaStream_t st);
 
 template <class Kern>
 static int set_smem(Kern kern, size_t bytes) {
@@ -959,7 +964,7 @@ int simt_chunk_fwd(const KdaChunkShape* sh, const void* q, const void* k, const 
 int simt_chunk_bwd(const KdaChunkShape* sh, const void* q, const void* k, const void* v, const void* g, const void* beta,
                    const int32_t* cu, const void* d_o, const float* d_final, const void* workspace, void* scratch,
                    void* dq, void* dk, void* dv, void* dg, void* dbeta, float* dh0, cudaStream_t st) {
-    (void)g; (void)beta; (void)cu;
+    (void)beta; (void)cu;
     Ws w = simt::carve_ws(*sh, const_cast<void*>(workspace));
     Scr s = simt::carve_scr(*sh, scratch);
     const int bf16 = sh->io_dtype == KDA_DTYPE_BF16, gbf16 = sh->gate_dtype == KDA_DTYPE_BF16;
@@ -971,6 +976,11 @@ int simt_chunk_bwd(const KdaChunkShape* sh, const void* q, const void* k, const 
         if (w.nslots > 0) {
             int rc = tc_scan_backward(w, s, t, sh->n_seq, sh->tokens, d_o, d_final, dh0, st);
             if (rc) return rc;
+            if (!getenv("KDA_DEBUG_FP32_LOCAL_VJP")) {
+                rc = tc_intra_backward(w, t, sh->tokens, q, k, v, g, d_o, gbf16, sh->l2norm, sh->scale, dq, dk, dv, dg,
+                                       dbeta, st);
+                return rc ? rc : launch_status();
+            }
         } else if (dh0) {
             return KDA_ERR_UNSUPPORTED;
         }

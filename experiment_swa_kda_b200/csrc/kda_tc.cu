@@ -47,6 +47,18 @@ int make_map_bf16(CUtensorMap* m, const void* ptr, uint64_t rows, uint64_t cols,
     CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, es,
                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r == CUDA_ERROR_INVALID_CONTEXT) {
+        // a host thread that has made no runtime call yet (e.g. an autograd worker) has no context bound:
+        // bind the current device's primary context and try once more
+        int dev = 0;
+        if (cudaGetDevice(&dev) == cudaSuccess && cudaSetDevice(dev) == cudaSuccess && cudaFree(nullptr) == cudaSuccess)
+            r = enc(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, es,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    }
+    if (r != CUDA_SUCCESS && getenv("KDA_B200_VERBOSE"))
+        fprintf(stderr, "libkda_b200: cuTensorMapEncodeTiled failed (%d): ptr %p rows %llu cols %llu box %u x %u\n", (int)r, ptr,
+                (unsigned long long)rows, (unsigned long long)cols, box_cols, box_rows);
     return r == CUDA_SUCCESS ? KDA_OK : KDA_ERR_CUDA;
 }
 

@@ -327,8 +327,10 @@ __global__ void __launch_bounds__(128, 1)
             for (int c = 0; c < 16; ++c) {
                 const int t = 16 * I + c;
                 const float a = (s <= t) ? __uint_as_float(r[c]) : 0.f;
-                const float m = (s < t) ? bet[t] * __uint_as_float(r[16 + c]) : 0.f;
+                const float mt = (s < t) ? __uint_as_float(r[16 + c]) : 0.f;
+                const float m = bet[t] * mt;
                 Ms[t * kLDs + s] = m;
+                p.t.Mt[ch * 4096 + t * 64 + s] = __float2bfloat16(mt);
                 if (c & 1) at[c >> 1] = pack2(__uint_as_float(at[c >> 1]), a);
                 else at[c >> 1] = __float_as_uint(a);
             }

@@ -1,0 +1,612 @@
+// Tensor-core lane, chunk-parallel part of the backward: one CTA (512 threads) per (chunk, head) turns the
+// adjoints published by the reverse scan into dq, dk, dv, dg, dbeta.  K = V = 128, 64 tokens per chunk, bf16
+// UMMA operands, fp32 accumulation.  Thread (I, d) owns channel d and the 16 tokens of row block I, so every
+// "channel x token" accumulator row (TMEM lane d) is read by the four threads that share that lane.
+//
+// Products (all on tcgen05; "^T" = channel-major result, M = 128; token x token results use M = 64):
+//   dR^T = H dO^T          dW^T = H dZ^T          dE^T = dH' Z^T            (H, dH' V-first panels: MN-major A)
+//   dP^T = dZ^T T          dQ^T = -dW^T T                                   (T row-major: MN-major B)
+//   dA   = tril(dO Z^T)    Xraw^T = v dZ^T - (e^G k) dW^T    (X = Xraw diag(beta) is the adjoint of T)
+//   Y    = T^T X           dM = -stril(Y T^T)
+//   pull-back of dA, dM through the decay-masked products, per 16-row target block I with the block's first
+//   row as decay reference (both exponential factors stay in range for g in [-5, 0]):
+//     RP_I^T = k~_I^T [dA_I ; beta dM_I]^T      CP_I^T = [q~_I ; k-_I]^T [dA_I ; beta dM_I]
+// Restates reference chunk_wy_backward.cu:2818-3331 (local VJP), 3337-3552 (pull-back), 3787-3894 (finalize).
+
+#include <cstdio>
+
+#include "common.cuh"
+#include "simt_ws.cuh"
+#include "tc_common.cuh"
+#include "tc_ws.cuh"
+
+namespace kda {
+namespace tc {
+
+int make_map_bf16(CUtensorMap* m, const void* ptr, uint64_t rows, uint64_t cols, uint32_t box_cols, uint32_t box_rows);
+
+namespace {
+
+__device__ __forceinline__ uint32_t pk2(float a, float b) {
+    __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&h);
+}
+__device__ __forceinline__ void st16(uint8_t* base, uint32_t off, float x) {
+    *reinterpret_cast<__nv_bfloat16*>(base + off) = __float2bfloat16(x);
+}
+__device__ __forceinline__ float ld16(const uint8_t* base, uint32_t off) {
+    return __bfloat162float(*reinterpret_cast<const __nv_bfloat16*>(base + off));
+}
+// element (row r, column d) of a 128-byte-swizzled panel whose 64-column blocks are blk_bytes apart
+__device__ __forceinline__ uint32_t eoff(int r, int d, uint32_t blk_bytes) {
+    return (uint32_t)(d >> 6) * blk_bytes + sw128_off(r, (d & 63) >> 3) + (uint32_t)(d & 7) * 2;
+}
+// 32 lanes x 16 consecutive columns
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&f)[16]) {
+    uint32_t r[16];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr)
+        : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int j = 0; j < 16; ++j) f[j] = __uint_as_float(r[j]);
+}
+
+}  // namespace
+
+struct IntraBwdArgs {
+    const int* chunk_tok0;
+    const int* chunk_len;
+    const __nv_bfloat16 *q, *k, *v;   // caller tensors [tokens][H][128]
+    const void* g;                    // gate dtype
+    const float *qinv, *kinv, *beta;  // [nch][64] from the forward
+    const __nv_bfloat16* Mt;          // [nch][64][64] M~ (before beta)
+    __nv_bfloat16 *dq, *dk, *dv;
+    void *dg, *dbeta;                 // gate dtype
+    int gbf16, l2norm, H;
+    float scale;
+    int* status;
+};
+
+// shared-memory map (bytes, 1024-aligned base)
+constexpr int kR1 = 0;         // 64 KB  H | dH' panels            -> later: k~_I source panels (4 x 16 KB)
+constexpr int kR2 = 65536;     // 16 KB  dO tile                   -> later: X^T tile (8 KB) | Y tile (8 KB)
+constexpr int kR3 = 81920;     // 16 KB  Z^T panel                 -> later: target stacks I = 0,1 (2 x 8 KB)
+constexpr int kR4 = 98304;     // 16 KB  dZ^T panel                -> later: target stacks I = 2,3
+constexpr int kR5 = 114688;    // 48 KB  q | k | v tiles
+constexpr int kR6 = 163840;    //  8 KB  T
+constexpr int kR7 = 172032;    // 16 KB  dW^T                      -> later: [dA_I ; beta dM_I] tiles (4 x 4 KB)
+constexpr int kR8 = 188416;    // 16 KB  Q' = e^G k
+constexpr int kSmall = 204800; // floats: gsum[4][128] cref[4][128] part[4][128] tot[4][128] dots[64][8] rowv[3][64]
+constexpr int kIntraBwdSmem = kSmall + (4 * 4 * 128 + 64 * 8 + 3 * 64) * 4 + 1024;
+
+__global__ void __launch_bounds__(512, 1)
+    tc_intra_bwd_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant__ CUtensorMap mk,
+                        const __grid_constant__ CUtensorMap mv, const __grid_constant__ CUtensorMap mdO,
+                        const __grid_constant__ CUtensorMap mT, const __grid_constant__ CUtensorMap mH,
+                        const __grid_constant__ CUtensorMap mdH, const __grid_constant__ CUtensorMap mZT,
+                        const __grid_constant__ CUtensorMap mdZT, IntraBwdArgs p) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* sm = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint8_t* Hs = sm + kR1;
+    uint8_t* dHs = sm + kR1 + 32768;
+    uint8_t* dOs = sm + kR2;
+    uint8_t* ZTs = sm + kR3;
+    uint8_t* dZTs = sm + kR4;
+    uint8_t* qs = sm + kR5;
+    uint8_t* ks = qs + 16384;
+    uint8_t* vs = ks + 16384;
+    uint8_t* Ts = sm + kR6;
+    uint8_t* dWs = sm + kR7;
+    uint8_t* Qp = sm + kR8;
+    float* gsum = reinterpret_cast<float*>(sm + kSmall);   // [4][128] block sums of g
+    float* cref = gsum + 512;                              // [4][128] G at the first row of each block
+    float* part = cref + 512;                              // [4][128] scratch partials
+    float* tot = part + 512;                               // [4][128] scratch partials
+    float* dots = tot + 512;                               // [64][8]  row dots: [row][quarter*2 + {q,k}]
+    float* rowv = dots + 512;                              // [3][64]  qinv | kinv | beta
+    __shared__ uint64_t bar_in, bar_mma;
+    __shared__ uint32_t tmem_slot;
+
+    const int slot = blockIdx.x, h = blockIdx.y, H = p.H;
+    const int len = p.chunk_len[slot];
+    if (len == 0) return;
+    const int tok0 = p.chunk_tok0[slot];
+    const int ch = slot * H + h;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int I = warp >> 2;             // row block of this thread
+    const int d = tid & 127;             // channel (and TMEM lane) of this thread
+    const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
+
+    if (tid == 0) {
+        mbar_init(&bar_in, 1);
+        mbar_init(&bar_mma, 1);
+        mbar_fence_init();
+        mbar_expect_tx(&bar_in, 65536 + 16384 * 3 + 49152 + 8192);
+        for (int mb = 0; mb < 2; ++mb) {
+            tma_load_2d(Hs + mb * 16384, &mH, &bar_in, mb * 64, ch * 128);
+            tma_load_2d(dHs + mb * 16384, &mdH, &bar_in, mb * 64, ch * 128);
+            tma_load_2d(dOs + mb * 8192, &mdO, &bar_in, h * 128 + mb * 64, tok0);
+            tma_load_2d(qs + mb * 8192, &mq, &bar_in, h * 128 + mb * 64, tok0);
+            tma_load_2d(ks + mb * 8192, &mk, &bar_in, h * 128 + mb * 64, tok0);
+            tma_load_2d(vs + mb * 8192, &mv, &bar_in, h * 128 + mb * 64, tok0);
+        }
+        tma_load_2d(ZTs, &mZT, &bar_in, 0, ch * 128);
+        tma_load_2d(dZTs, &mdZT, &bar_in, 0, ch * 128);
+        tma_load_2d(Ts, &mT, &bar_in, 0, ch * 64);
+    }
+    if (warp == 0) tmem_alloc(&tmem_slot, 512);
+
+    // ---- per-row scalars and the cumulative log-decay of this thread's 16 rows
+    if (tid < 64) {
+        rowv[tid] = p.qinv[ch * 64 + tid];
+        rowv[64 + tid] = p.kinv[ch * 64 + tid];
+        rowv[128 + tid] = p.beta[ch * 64 + tid];
+    }
+    const size_t rstride = (size_t)H * 128;
+    const size_t col = ((size_t)tok0 * H + h) * 128 + d;
+    float G[16];
+    {
+#pragma unroll
+        for (int r = 0; r < 16; ++r) G[r] = ld_io(p.g, col + (size_t)min(16 * I + r, len - 1) * rstride, p.gbf16);
+        float run = 0.f;
+#pragma unroll
+        for (int r = 0; r < 16; ++r) {
+            run += (16 * I + r < len) ? G[r] : 0.f;
+            G[r] = run;
+        }
+        gsum[I * 128 + d] = run;
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = tmem_slot;
+    float gend;
+    {
+        const float s0 = gsum[d], s1 = gsum[128 + d], s2 = gsum[256 + d], s3 = gsum[384 + d];
+        const float pre = I == 0 ? 0.f : (I == 1 ? s0 : (I == 2 ? s0 + s1 : s0 + s1 + s2));
+        gend = s0 + s1 + s2 + s3;
+#pragma unroll
+        for (int r = 0; r < 16; ++r) G[r] += pre;
+        cref[I * 128 + d] = G[0];
+    }
+    bool ok = mbar_wait(&bar_in, 0, p.status, 40);
+    ok = __syncthreads_and(ok);          // also publishes cref
+    const float egend = __expf(gend);
+
+    // TMEM columns
+    constexpr uint32_t cDa = 0, cDb = 64, cDc = 128, cDd = 192, cDg = 256, cDf = 320, cDe = 384;
+
+    // ================================================================ phase 1: state products
+    if (ok && tid == 0) {
+        tc_fence_after();
+        const uint32_t id_mn_k = umma_idesc_bf16(128, 64, kMajorMN, kMajorK);
+        const uint32_t id_mn_mn = umma_idesc_bf16(128, 64, kMajorMN, kMajorMN);
+        const uint32_t id_k_mn = umma_idesc_bf16(128, 64, kMajorK, kMajorMN);
+        const uint32_t id64_k_mn = umma_idesc_bf16(64, 64, kMajorK, kMajorMN);
+        const uint32_t aH = smem_u32(Hs), adH = smem_u32(dHs), bdO = smem_u32(dOs), bZ = smem_u32(ZTs), bdZ = smem_u32(dZTs);
+        const uint32_t aV = smem_u32(vs), bT = smem_u32(Ts);
+#pragma unroll
+        for (int k16 = 0; k16 < 8; ++k16)     // dR^T = H dO^T
+            umma_bf16_ss(tmem + cDa, umma_smem_desc_sw128(aH + k16 * 2048, 16384, 1024),
+                         umma_smem_desc_sw128(bdO + (k16 >> 2) * 8192 + (k16 & 3) * 32, 16, 1024), id_mn_k, k16 > 0);
+#pragma unroll
+        for (int k16 = 0; k16 < 8; ++k16)     // dW^T = H dZ^T
+            umma_bf16_ss(tmem + cDb, umma_smem_desc_sw128(aH + k16 * 2048, 16384, 1024),
+                         umma_smem_desc_sw128(bdZ + k16 * 2048, 8192, 1024), id_mn_mn, k16 > 0);
+#pragma unroll
+        for (int k16 = 0; k16 < 8; ++k16)     // dE^T = dH' Z^T
+            umma_bf16_ss(tmem + cDc, umma_smem_desc_sw128(adH + k16 * 2048, 16384, 1024),
+                         umma_smem_desc_sw128(bZ + k16 * 2048, 8192, 1024), id_mn_mn, k16 > 0);
+#pragma unroll
+        for (int k16 = 0; k16 < 4; ++k16)     // dP^T = dZ^T T
+            umma_bf16_ss(tmem + cDd, umma_smem_desc_sw128(bdZ + k16 * 32, 16, 1024),
+                         umma_smem_desc_sw128(bT + k16 * 2048, 8192, 1024), id_k_mn, k16 > 0);
+#pragma unroll
+        for (int k16 = 0; k16 < 8; ++k16)     // dA = dO Z^T                      (M = 64)
+            umma_bf16_ss(tmem + cDg, umma_smem_desc_sw128(bdO + (k16 >> 2) * 8192 + (k16 & 3) * 32, 16, 1024),
+                         umma_smem_desc_sw128(bZ + k16 * 2048, 8192, 1024), id64_k_mn, k16 > 0);
+#pragma unroll
+        for (int k16 = 0; k16 < 8; ++k16)     // Xraw^T = v dZ^T  (first half)    (M = 64)
+            umma_bf16_ss(tmem + cDf, umma_smem_desc_sw128(aV + (k16 >> 2) * 8192 + (k16 & 3) * 32, 16, 1024),
+                         umma_smem_desc_sw128(bdZ + k16 * 2048, 8192, 1024), id64_k_mn, k16 > 0);
+        umma_commit(&bar_mma);
+    }
+    // while the tensor core works: dD[d] = sum_v dH'[d][v] H[d][v] over this thread's 32 value rows
+    float kn[16], qn[16];
+    {
+        float acc = 0.f;
+        if (ok) {
+#pragma unroll 8
+            for (int vv = 32 * I; vv < 32 * I + 32; ++vv) acc += ld16(Hs, eoff(vv, d, 16384)) * ld16(dHs, eoff(vv, d, 16384));
+        }
+        part[I * 128 + d] = acc;
+#pragma unroll
+        for (int r = 0; r < 16; ++r) {
+            const int i = 16 * I + r;
+            float qv = 0.f, kv = 0.f;
+            if (ok && i < len) {
+                qv = ld16(qs, eoff(i, d, 8192));
+                kv = ld16(ks, eoff(i, d, 8192));
+            }
+            qn[r] = qv * rowv[i] * p.scale;
+            kn[r] = kv * rowv[64 + i];
+            // Q' = e^G k (K-major, rows = token) for Xraw^T -= Q' dW^T
+            st16(Qp, eoff(i, d, 8192), __expf(G[r]) * kn[r]);
+        }
+    }
+    ok = ok && mbar_wait(&bar_mma, 0, p.status, 41);
+    ok = __syncthreads_and(ok);
+    tc_fence_after();
+
+    // ================================================================ phase 2a: first read-out
+    float dqn[16], dkn[16], dG[16];
+    float ge_part = 0.f;
+    {
+        float t[16];
+        // dW^T -> bf16 operand (row = channel d, 16 of its 64 tokens)
+        tmem_ld16(tmem + lane_base + cDb + 16 * I, t);
+        *reinterpret_cast<uint4*>(dWs + sw128_off(d, 2 * I)) =
+            make_uint4(pk2(t[0], t[1]), pk2(t[2], t[3]), pk2(t[4], t[5]), pk2(t[6], t[7]));
+        *reinterpret_cast<uint4*>(dWs + sw128_off(d, 2 * I + 1)) =
+            make_uint4(pk2(t[8], t[9]), pk2(t[10], t[11]), pk2(t[12], t[13]), pk2(t[14], t[15]));
+        // dR, dE
+        tmem_ld16(tmem + lane_base + cDa + 16 * I, t);
+#pragma unroll
+        for (int r = 0; r < 16; ++r) {
+            dqn[r] = t[r] * __expf(G[r]);
+            dG[r] = dqn[r] * qn[r];
+        }
+        tmem_ld16(tmem + lane_base + cDc + 16 * I, t);
+#pragma unroll
+        for (int r = 0; r < 16; ++r) {
+            const float ee = __expf(gend - G[r]);
+            const float eE = t[r] * kn[r] * ee;    // dE * E
+            dkn[r] = t[r] * ee;
+            dG[r] -= eE;
+            ge_part += eE;
+        }
+        // dv = beta dP
+        tmem_ld16(tmem + lane_base + cDd + 16 * I, t);
+#pragma unroll
+        for (int r = 0; r < 16; ++r) {
+            const int i = 16 * I + r;
+            if (i < len) p.dv[col + (size_t)i * rstride] = __float2bfloat16(rowv[128 + i] * t[r]);
+        }
+    }
+    fence_async_smem();
+    tc_fence_before();
+    __syncthreads();
+    if (ok && tid == 0) {
+        tc_fence_after();
+        const uint32_t id64_neg = umma_idesc_bf16(64, 64, kMajorK, kMajorMN, 1);
+        const uint32_t id_k_mn = umma_idesc_bf16(128, 64, kMajorK, kMajorMN);
+        const uint32_t aQ = smem_u32(Qp), aW = smem_u32(dWs), bT = smem_u32(Ts);
+#pragma unroll
+        for (int k16 = 0; k16 < 8; ++k16)     // Xraw^T -= Q' dW^T   (dW^T panel read as MN-major B: [key][token])
+            umma_bf16_ss(tmem + cDf, umma_smem_desc_sw128(aQ + (k16 >> 2) * 8192 + (k16 & 3) * 32, 16, 1024),
+                         umma_smem_desc_sw128(aW + k16 * 2048, 8192, 1024), id64_neg, 1);
+#pragma unroll
+        for (int k16 = 0; k16 < 4; ++k16)     // (T^T dW)^T = dW^T T ;  dQ = -that
+            umma_bf16_ss(tmem + cDe, umma_smem_desc_sw128(aW + k16 * 32, 16, 1024),
+                         umma_smem_desc_sw128(bT + k16 * 2048, 8192, 1024), id_k_mn, k16 > 0);
+        umma_commit(&bar_mma);
+    }
+    ok = ok && mbar_wait(&bar_mma, 1, p.status, 42);
+    ok = __syncthreads_and(ok);
+    tc_fence_after();
+
+    // ================================================================ phase 3: X, Y, dM
+    // M = 64 accumulators keep row (16*w + l) in lane l < 16 of warp w < 4.  tcgen05.ld is warp-collective, so all 32
+    // lanes of those warps run the loads; lanes >= 16 mirror a row and never store.
+    const bool rowwarp = warp < 4;
+    const bool rowown = lane < 16;
+    const int row = 16 * (warp & 3) + (lane & 15);
+    uint8_t* XT = sm + kR2;           // [64 rows s][64 i]   K-major B
+    uint8_t* Yt = sm + kR2 + 8192;    // [64 rows j][64 s]   K-major A
+    float dbeta_acc = 0.f;
+    if (rowwarp) {
+        const float bs = rowv[128 + row];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            float t[16];
+            tmem_ld16(tmem + lane_base + cDf + 16 * c, t);
+            uint32_t pkd[8];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+                const int i = 16 * c + j;
+                dbeta_acc += ld16(Ts, sw128_off(i, row >> 3) + (row & 7) * 2) * t[j];     // T[i][s] * Xraw[i][s]
+                if (j & 1) pkd[j >> 1] = pk2(__uint_as_float(pkd[j >> 1]), bs * t[j]);
+                else pkd[j >> 1] = __float_as_uint(bs * t[j]);
+            }
+            if (rowown) {
+                *reinterpret_cast<uint4*>(XT + sw128_off(row, 2 * c)) = make_uint4(pkd[0], pkd[1], pkd[2], pkd[3]);
+                *reinterpret_cast<uint4*>(XT + sw128_off(row, 2 * c + 1)) = make_uint4(pkd[4], pkd[5], pkd[6], pkd[7]);
+            }
+        }
+    }
+    {   // dQ contributions (all threads)
+        float t[16];
+        tmem_ld16(tmem + lane_base + cDe + 16 * I, t);
+#pragma unroll
+        for (int r = 0; r < 16; ++r) {
+            const float dQ = -t[r] * rowv[128 + 16 * I + r] * __expf(G[r]);   // dQ * beta * e^G
+            dkn[r] += dQ;
+            dG[r] += dQ * kn[r];
+        }
+    }
+    fence_async_smem();
+    tc_fence_before();
+    __syncthreads();
+    if (ok && tid == 0) {
+        tc_fence_after();
+        const uint32_t id = umma_idesc_bf16(64, 64, kMajorMN, kMajorK);
+#pragma unroll
+        for (int k16 = 0; k16 < 4; ++k16)     // Y = T^T X : A[m=j][k=i] = T[i][j] (MN-major), B[n=s][k=i] = X^T rows
+            umma_bf16_ss(tmem + cDb, umma_smem_desc_sw128(smem_u32(Ts) + k16 * 2048, 8192, 1024),
+                         umma_smem_desc_sw128(smem_u32(XT) + k16 * 32, 16, 1024), id, k16 > 0);
+        umma_commit(&bar_mma);
+    }
+    ok = ok && mbar_wait(&bar_mma, 0, p.status, 43);
+    ok = __syncthreads_and(ok);
+    tc_fence_after();
+    if (rowwarp) {
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            float t[16];
+            tmem_ld16(tmem + lane_base + cDb + 16 * c, t);
+            if (rowown) {
+                *reinterpret_cast<uint4*>(Yt + sw128_off(row, 2 * c)) =
+                    make_uint4(pk2(t[0], t[1]), pk2(t[2], t[3]), pk2(t[4], t[5]), pk2(t[6], t[7]));
+                *reinterpret_cast<uint4*>(Yt + sw128_off(row, 2 * c + 1)) =
+                    make_uint4(pk2(t[8], t[9]), pk2(t[10], t[11]), pk2(t[12], t[13]), pk2(t[14], t[15]));
+            }
+        }
+    }
+    fence_async_smem();
+    tc_fence_before();
+    __syncthreads();
+    if (ok && tid == 0) {
+        tc_fence_after();
+        const uint32_t id = umma_idesc_bf16(64, 64, kMajorK, kMajorK);
+#pragma unroll
+        for (int k16 = 0; k16 < 4; ++k16)     // Y T^T : B[n=l][k=s] = T[l][s]
+            umma_bf16_ss(tmem + cDc, umma_smem_desc_sw128(smem_u32(Yt) + k16 * 32, 16, 1024),
+                         umma_smem_desc_sw128(smem_u32(Ts) + k16 * 32, 16, 1024), id, k16 > 0);
+        umma_commit(&bar_mma);
+    }
+    ok = ok && mbar_wait(&bar_mma, 1, p.status, 44);
+    ok = __syncthreads_and(ok);
+    tc_fence_after();
+
+    // ================================================================ phase 4: pull-back operands
+    uint8_t* Sk = sm + kR1;           // k~_I panels: [I][2 blocks][64 rows s x 128 B]     MN-major A
+    uint8_t* Xk = sm + kR3;           // target stacks: [I][2 blocks][32 rows x 128 B]     MN-major A
+    uint8_t* DAt = sm + kR7;          // [I][32 rows: 16 dA rows, 16 beta*dM rows][64 s]   K-major / MN-major B
+    if (rowwarp) {
+        // row j of dM = -stril(Y T^T) and of dA = tril(dO Z^T); dbeta gets sum_l dM[j][l] M~[j][l]
+        const int j = row, Ib = j >> 4, rr = j & 15;
+        const float bj = rowv[128 + j];
+        const __nv_bfloat16* mt = p.Mt + (size_t)ch * 4096 + j * 64;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            float tm[16], ta[16];
+            tmem_ld16(tmem + lane_base + cDc + 16 * c, tm);
+            tmem_ld16(tmem + lane_base + cDg + 16 * c, ta);
+            uint4 m0 = *reinterpret_cast<const uint4*>(mt + 16 * c), m1 = *reinterpret_cast<const uint4*>(mt + 16 * c + 8);
+            float mv16[16];
+            {
+                const __nv_bfloat162* hh = reinterpret_cast<const __nv_bfloat162*>(&m0);
+                const __nv_bfloat162* hg = reinterpret_cast<const __nv_bfloat162*>(&m1);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    float2 f0 = __bfloat1622float2(hh[e]), f1 = __bfloat1622float2(hg[e]);
+                    mv16[2 * e] = f0.x; mv16[2 * e + 1] = f0.y; mv16[8 + 2 * e] = f1.x; mv16[8 + 2 * e + 1] = f1.y;
+                }
+            }
+            uint32_t pa[8], pm[8];
+#pragma unroll
+            for (int e = 0; e < 16; ++e) {
+                const int l = 16 * c + e;
+                const float dm = (l < j) ? -tm[e] : 0.f;
+                const float da = (l <= j) ? ta[e] : 0.f;
+                dbeta_acc += dm * mv16[e];
+                if (e & 1) { pa[e >> 1] = pk2(__uint_as_float(pa[e >> 1]), da); pm[e >> 1] = pk2(__uint_as_float(pm[e >> 1]), bj * dm); }
+                else { pa[e >> 1] = __float_as_uint(da); pm[e >> 1] = __float_as_uint(bj * dm); }
+            }
+            uint8_t* tile = DAt + Ib * 4096;
+            if (rowown) {
+                *reinterpret_cast<uint4*>(tile + sw128_off(rr, 2 * c)) = make_uint4(pa[0], pa[1], pa[2], pa[3]);
+                *reinterpret_cast<uint4*>(tile + sw128_off(rr, 2 * c + 1)) = make_uint4(pa[4], pa[5], pa[6], pa[7]);
+                *reinterpret_cast<uint4*>(tile + sw128_off(16 + rr, 2 * c)) = make_uint4(pm[0], pm[1], pm[2], pm[3]);
+                *reinterpret_cast<uint4*>(tile + sw128_off(16 + rr, 2 * c + 1)) = make_uint4(pm[4], pm[5], pm[6], pm[7]);
+            }
+        }
+        if (rowown && j < len) st_io(p.dbeta, (size_t)(tok0 + j) * H + h, p.gbf16, dbeta_acc);
+    }
+    {
+        const float c0 = cref[d], c1 = cref[128 + d], c2 = cref[256 + d], c3 = cref[384 + d];
+        const float cI = I == 0 ? c0 : (I == 1 ? c1 : (I == 2 ? c2 : c3));
+        const float fb0 = __expf(c1 - c0), fb1 = __expf(c2 - c1), fb2 = __expf(c3 - c2);
+#pragma unroll
+        for (int r = 0; r < 16; ++r) {
+            const int i = 16 * I + r;
+            const float tq = __expf(G[r] - cI);
+            // targets of this row's own block
+            uint8_t* X = Xk + I * 8192;
+            st16(X, eoff(r, d, 4096), qn[r] * tq);
+            st16(X, eoff(16 + r, d, 4096), kn[r] * tq);
+            // this row as a source for its own and every later block
+            float f = kn[r] * __expf(cI - G[r]);
+            float s0v = 0.f, s1v = 0.f, s2v = 0.f, s3v = 0.f;
+            if (I == 0) { s0v = f; f *= fb0; }
+            if (I <= 1) { s1v = f; f *= fb1; }
+            if (I <= 2) { s2v = f; f *= fb2; }
+            s3v = f;
+            st16(Sk, eoff(i, d, 8192), s0v);
+            st16(Sk + 16384, eoff(i, d, 8192), s1v);
+            st16(Sk + 32768, eoff(i, d, 8192), s2v);
+            st16(Sk + 49152, eoff(i, d, 8192), s3v);
+        }
+    }
+    fence_async_smem();
+    tc_fence_before();
+    __syncthreads();
+    // accumulator columns of the pull-back: RP_I (32 columns each) and CP_I (64 columns each)
+    constexpr uint32_t cRP = 192;
+    const uint32_t cCP[4] = {0, 64, 128, 320};
+    if (ok && tid == 0) {
+        tc_fence_after();
+        const uint32_t id_rp = umma_idesc_bf16(128, 32, kMajorMN, kMajorK);
+        const uint32_t id_cp = umma_idesc_bf16(128, 64, kMajorMN, kMajorMN);
+#pragma unroll
+        for (int Ib = 0; Ib < 4; ++Ib) {
+            const uint32_t aS = smem_u32(Sk + Ib * 16384), aX = smem_u32(Xk + Ib * 8192), bD = smem_u32(DAt + Ib * 4096);
+#pragma unroll
+            for (int k16 = 0; k16 < 4; ++k16)     // RP_I^T[d][n] = sum_s k~_I[s][d] * rows_I[n][s]
+                umma_bf16_ss(tmem + cRP + 32 * Ib, umma_smem_desc_sw128(aS + k16 * 2048, 8192, 1024),
+                             umma_smem_desc_sw128(bD + k16 * 32, 16, 1024), id_rp, k16 > 0);
+#pragma unroll
+            for (int k16 = 0; k16 < 2; ++k16)     // CP_I^T[d][s] = sum_{n<32} stack_I[n][d] * rows_I[n][s]
+                umma_bf16_ss(tmem + cCP[Ib], umma_smem_desc_sw128(aX + k16 * 2048, 4096, 1024),
+                             umma_smem_desc_sw128(bD + k16 * 2048, 4096, 1024), id_cp, k16 > 0);
+        }
+        umma_commit(&bar_mma);
+    }
+    ok = ok && mbar_wait(&bar_mma, 0, p.status, 45);
+    ok = __syncthreads_and(ok);
+    tc_fence_after();
+
+    // ================================================================ phase 5: assemble the gradients
+    {
+        float t[16];
+        const float c0 = cref[d], c1 = cref[128 + d], c2 = cref[256 + d], c3 = cref[384 + d];
+        const float cOwn = I == 0 ? c0 : (I == 1 ? c1 : (I == 2 ? c2 : c3));
+        tmem_ld16(tmem + lane_base + cRP + 32 * I, t);          // row part through dA
+#pragma unroll
+        for (int r = 0; r < 16; ++r) {
+            const float x = __expf(G[r] - cOwn) * t[r];
+            dqn[r] += x;
+            dG[r] += qn[r] * x;
+        }
+        tmem_ld16(tmem + lane_base + cRP + 32 * I + 16, t);     // row part through beta*dM
+#pragma unroll
+        for (int r = 0; r < 16; ++r) {
+            const float x = __expf(G[r] - cOwn) * t[r];
+            dkn[r] += x;
+            dG[r] += kn[r] * x;
+        }
+        // column part: sources of block I receive from target blocks I' >= I, each with its own decay reference
+#pragma unroll
+        for (int Ib = 0; Ib < 4; ++Ib) {
+            if (Ib >= I) {
+                const float cI = Ib == 0 ? c0 : (Ib == 1 ? c1 : (Ib == 2 ? c2 : c3));
+                tmem_ld16(tmem + lane_base + cCP[Ib] + 16 * I, t);
+#pragma unroll
+                for (int r = 0; r < 16; ++r) {
+                    const float x = __expf(cI - G[r]) * t[r];
+                    dkn[r] += x;
+                    dG[r] -= kn[r] * x;
+                }
+            }
+        }
+    }
+    // chunk-end term and reverse cumulative sum of dG over the 64 rows of this channel
+    float suffix = 0.f;
+    {
+        float local = 0.f;
+#pragma unroll
+        for (int r = 0; r < 16; ++r) local += dG[r];
+        tot[I * 128 + d] = local;
+        gsum[I * 128 + d] = ge_part;       // gsum is free again
+    }
+    __syncthreads();
+    {
+        const float dGend = gsum[d] + gsum[128 + d] + gsum[256 + d] + gsum[384 + d] +
+                            egend * (part[d] + part[128 + d] + part[256 + d] + part[384 + d]);
+        suffix = dGend;
+#pragma unroll
+        for (int Ib = 3; Ib > 0; --Ib)
+            if (Ib > I) suffix += tot[Ib * 128 + d];
+    }
+    // L2-normalisation VJP needs per-row dots over the channels: unit k is kn, unit q is qn / scale
+    const float inv_scale = p.scale != 0.f ? 1.0f / p.scale : 0.f;
+#pragma unroll
+    for (int r = 0; r < 16; ++r) {
+        const int i = 16 * I + r;
+        const float pq = warp_sum(qn[r] * inv_scale * dqn[r] * p.scale);
+        const float pk = warp_sum(kn[r] * dkn[r]);
+        if (lane == 0) {
+            dots[i * 8 + (warp & 3) * 2] = pq;
+            dots[i * 8 + (warp & 3) * 2 + 1] = pk;
+        }
+    }
+    __syncthreads();
+    if (ok) {
+        float run = suffix;
+#pragma unroll
+        for (int r = 15; r >= 0; --r) {
+            const int i = 16 * I + r;
+            run += dG[r];
+            if (i < len) {
+                const size_t o = col + (size_t)i * rstride;
+                st_io(p.dg, o, p.gbf16, run);
+                float dqv, dkv;
+                if (p.l2norm) {
+                    const float pq = dots[i * 8] + dots[i * 8 + 2] + dots[i * 8 + 4] + dots[i * 8 + 6];
+                    const float pk = dots[i * 8 + 1] + dots[i * 8 + 3] + dots[i * 8 + 5] + dots[i * 8 + 7];
+                    dqv = rowv[i] * (dqn[r] * p.scale - qn[r] * inv_scale * pq);
+                    dkv = rowv[64 + i] * (dkn[r] - kn[r] * pk);
+                } else {
+                    dqv = dqn[r] * p.scale;
+                    dkv = dkn[r];
+                }
+                p.dq[o] = __float2bfloat16(dqv);
+                p.dk[o] = __float2bfloat16(dkv);
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) tmem_dealloc(tmem, 512);
+}
+
+}  // namespace tc
+
+int tc_intra_backward(const simt::Ws& w, const tc::TcWs& t, int tokens, const void* q, const void* k, const void* v,
+                      const void* g, const void* d_o, int gbf16, int l2norm, float scale, void* dq, void* dk, void* dv,
+                      void* dg, void* dbeta, cudaStream_t st) {
+    using namespace tc;
+    const uint64_t nch = (uint64_t)w.nslots * w.H;
+    const uint64_t cols = (uint64_t)w.H * 128;
+    CUtensorMap mq, mk, mv, mdO, mT, mH, mdH, mZT, mdZT;
+    int rc = 0;
+    rc |= make_map_bf16(&mq, q, (uint64_t)tokens, cols, 64, 64);
+    rc |= make_map_bf16(&mk, k, (uint64_t)tokens, cols, 64, 64);
+    rc |= make_map_bf16(&mv, v, (uint64_t)tokens, cols, 64, 64);
+    rc |= make_map_bf16(&mdO, d_o, (uint64_t)tokens, cols, 64, 64);
+    rc |= make_map_bf16(&mT, t.Tp, nch * 64, 64, 64, 64);
+    rc |= make_map_bf16(&mH, t.Hp, nch * 128, 128, 64, 128);
+    rc |= make_map_bf16(&mdH, t.dHp, nch * 128, 128, 64, 128);
+    rc |= make_map_bf16(&mZT, t.ZT, nch * 128, 64, 64, 128);
+    rc |= make_map_bf16(&mdZT, t.dZT, nch * 128, 64, 64, 128);
+    if (rc) return KDA_ERR_CUDA;
+    IntraBwdArgs a;
+    a.chunk_tok0 = w.chunk_tok0; a.chunk_len = w.chunk_len;
+    a.q = static_cast<const __nv_bfloat16*>(q); a.k = static_cast<const __nv_bfloat16*>(k);
+    a.v = static_cast<const __nv_bfloat16*>(v); a.g = g;
+    a.qinv = w.qinv; a.kinv = w.kinv; a.beta = w.beta; a.Mt = t.Mt;
+    a.dq = static_cast<__nv_bfloat16*>(dq); a.dk = static_cast<__nv_bfloat16*>(dk); a.dv = static_cast<__nv_bfloat16*>(dv);
+    a.dg = dg; a.dbeta = dbeta; a.gbf16 = gbf16; a.l2norm = l2norm; a.H = w.H; a.scale = scale; a.status = t.status;
+    if (cudaFuncSetAttribute(tc_intra_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kIntraBwdSmem) != cudaSuccess)
+        return launch_status();
+    KDA_LAUNCH("tc_intra_bwd_kernel", st,
+               tc_intra_bwd_kernel<<<dim3(w.nslots, w.H), 512, kIntraBwdSmem, st>>>(mq, mk, mv, mdO, mT, mH, mdH, mZT, mdZT, a));
+    return launch_status();
+}
+
+}  // namespace kda

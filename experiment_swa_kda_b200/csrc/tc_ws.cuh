@@ -14,6 +14,7 @@ struct TcWs {
     __nv_bfloat16* AT;          // [nch][64][64]    A transposed: [source s][target i]
     __nv_bfloat16* UT;          // [nch][128][64]   U transposed: [value][token]
     __nv_bfloat16* Tp;          // [nch][64][64]    T = (I + M)^-1, row-major
+    __nv_bfloat16* Mt;          // [nch][64][64]    M before the beta scaling, strictly lower, row-major
     __nv_bfloat16* Hp;          // [nch][128][128]  chunk-start state, V-first [value][key]
     __nv_bfloat16* ZT;          // [nch][128][64]   Z transposed: [value][token]
     __nv_bfloat16* dHp;         // [nch][128][128]  adjoint of each chunk's outgoing state, V-first
@@ -32,6 +33,7 @@ inline TcWs carve_tc(const KdaChunkShape& sh, void* mem, size_t* bytes = nullptr
     t.AT = c.take<__nv_bfloat16>(nch * 4096);
     t.UT = c.take<__nv_bfloat16>(nch * 8192);
     t.Tp = c.take<__nv_bfloat16>(nch * 4096);
+    t.Mt = c.take<__nv_bfloat16>(nch * 4096);
     t.Hp = c.take<__nv_bfloat16>(nch * 16384);
     t.ZT = c.take<__nv_bfloat16>(nch * 8192);
     t.dHp = c.take<__nv_bfloat16>(nch * 16384);
