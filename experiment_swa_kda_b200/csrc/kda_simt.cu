@@ -976,11 +976,8 @@ int simt_chunk_bwd(const KdaChunkShape* sh, const void* q, const void* k, const 
         if (w.nslots > 0) {
             int rc = tc_scan_backward(w, s, t, sh->n_seq, sh->tokens, d_o, d_final, dh0, st);
             if (rc) return rc;
-            if (!getenv("KDA_DEBUG_FP32_LOCAL_VJP")) {
-                rc = tc_intra_backward(w, t, sh->tokens, q, k, v, g, d_o, gbf16, sh->l2norm, sh->scale, dq, dk, dv, dg,
-                                       dbeta, st);
-                return rc ? rc : launch_status();
-            }
+            rc = tc_intra_backward(w, t, sh->tokens, q, k, v, g, d_o, gbf16, sh->l2norm, sh->scale, dq, dk, dv, dg, dbeta, st);
+            return rc ? rc : launch_status();
         } else if (dh0) {
             return KDA_ERR_UNSUPPORTED;
         }

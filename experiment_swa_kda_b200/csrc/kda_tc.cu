@@ -505,72 +505,6 @@ __global__ void __launch_bounds__(128, 1)
     if (warp == 0) tmem_dealloc(tmem, 256);
 }
 
-// ---------------------------------------------------------------------------------------------
-// interim glue between the float32 intra-chunk kernels and the tensor-core scan
-// ---------------------------------------------------------------------------------------------
-// float32 workspace -> bf16 operand panels W^T, R^T = (qn exp(G))^T, E = kn exp(G_end - G), A^T, U^T, exp(G_end)
-__global__ void __launch_bounds__(256) tc_pack_panels_kernel(simt::Ws w, TcWs t) {
-    const int slot = blockIdx.x, h = blockIdx.y;
-    if (w.chunk_len[slot] == 0) return;
-    const size_t ch = (size_t)slot * w.H + h;
-    const int tid = threadIdx.x;
-    const float* G = w.G + ch * 64 * 128;
-    const float* qn = w.qn + ch * 64 * 128;
-    const float* kn = w.kn + ch * 64 * 128;
-    const float* W = w.W + ch * 64 * 128;
-    for (int idx = tid; idx < 64 * 128; idx += 256) {
-        const int d = idx & 127;
-        const float g = G[idx], ge = G[63 * 128 + d];
-        const int i = idx >> 7;
-        t.WT[ch * 8192 + d * 64 + i] = __float2bfloat16(W[idx]);                      // [key][token]
-        t.RT[ch * 8192 + d * 64 + i] = __float2bfloat16(qn[idx] * expf(g));
-        t.E[ch * 8192 + idx] = __float2bfloat16(kn[idx] * expf(ge - g));
-    }
-    if (tid < 128) t.decay_end[ch * 128 + tid] = expf(G[63 * 128 + tid]);
-    const float* A = w.A + ch * 4096;
-    for (int idx = tid; idx < 4096; idx += 256) {
-        const int s = idx >> 6, i = idx & 63;
-        t.AT[ch * 4096 + idx] = __float2bfloat16(A[i * 64 + s]);      // [s][i]
-    }
-    const float* U = w.Z + ch * 64 * 128;
-    for (int idx = tid; idx < 8192; idx += 256) {
-        const int v = idx >> 6, i = idx & 63;
-        t.UT[ch * 8192 + idx] = __float2bfloat16(U[i * 128 + v]);     // [v][i]
-    }
-}
-
-// bf16 panels H [v][k], Z^T [v][i]  ->  float32 workspace Hc [k][v], Z [i][v]
-__global__ void __launch_bounds__(256) tc_unpack_state_kernel(simt::Ws w, TcWs t) {
-    const int slot = blockIdx.x, h = blockIdx.y;
-    if (w.chunk_len[slot] == 0) return;
-    const size_t ch = (size_t)slot * w.H + h;
-    const int tid = threadIdx.x;
-    for (int idx = tid; idx < 128 * 128; idx += 256) {
-        const int k = idx >> 7, v = idx & 127;
-        w.Hc[ch * 16384 + idx] = __bfloat162float(t.Hp[ch * 16384 + v * 128 + k]);
-    }
-    for (int idx = tid; idx < 64 * 128; idx += 256) {
-        const int i = idx >> 7, v = idx & 127;
-        w.Z[ch * 8192 + idx] = __bfloat162float(t.ZT[ch * 8192 + v * 64 + i]);
-    }
-}
-
-// bf16 panels dH' [v][k], dZ^T [v][i]  ->  float32 scratch dHn [k][v], dZ [i][v]
-__global__ void __launch_bounds__(256) tc_unpack_adjoint_kernel(simt::Ws w, simt::Scr s, TcWs t) {
-    const int slot = blockIdx.x, h = blockIdx.y;
-    if (w.chunk_len[slot] == 0) return;
-    const size_t ch = (size_t)slot * w.H + h;
-    const int tid = threadIdx.x;
-    for (int idx = tid; idx < 128 * 128; idx += 256) {
-        const int k = idx >> 7, v = idx & 127;
-        s.dHn[ch * 16384 + idx] = __bfloat162float(t.dHp[ch * 16384 + v * 128 + k]);
-    }
-    for (int idx = tid; idx < 64 * 128; idx += 256) {
-        const int i = idx >> 7, v = idx & 127;
-        s.dZ[ch * 8192 + idx] = __bfloat162float(t.dZT[ch * 8192 + v * 64 + i]);
-    }
-}
-
 }  // namespace tc
 
 // ---------------------------------------------------------------------------------------------
@@ -598,7 +532,6 @@ int tc_scan_forward(const simt::Ws& w, const tc::TcWs& t, int n_seq, const float
         return KDA_ERR_CUDA;
     KDA_LAUNCH("tc_scan_fwd_kernel", st,
                tc_scan_fwd_kernel<<<dim3(n_seq, w.H), 128, kScanFwdSmem, st>>>(mW, mR, mE, mAT, mUT, mH, mZT, a));
-    KDA_LAUNCH("tc_unpack_state_kernel", st, tc_unpack_state_kernel<<<dim3(w.nslots, w.H), 256, 0, st>>>(w, t));
     return launch_status();
 }
 
@@ -623,7 +556,6 @@ int tc_scan_backward(const simt::Ws& w, const simt::Scr& s, const tc::TcWs& t, i
         return KDA_ERR_CUDA;
     KDA_LAUNCH("tc_scan_bwd_kernel", st,
                tc_scan_bwd_kernel<<<dim3(n_seq, w.H), 128, kScanBwdSmem, st>>>(mW, mR, mE, mAT, mdO, mdH, mdZT, a));
-    KDA_LAUNCH("tc_unpack_adjoint_kernel", st, tc_unpack_adjoint_kernel<<<dim3(w.nslots, w.H), 256, 0, st>>>(w, s, t));
     return launch_status();
 }
 

@@ -125,7 +125,7 @@ struct IntraFwdArgs {
     int gbf16, l2norm, H;
     float scale;
     TcWs t;
-    simt::Ws w;                       // float32 copies kept for the float32 backward kernels
+    simt::Ws w;                       // per-row scalars (inverse norms, beta) kept for the backward
 };
 
 constexpr int kIntraFwdSmem = 98304 + 49152 + 1024 + 1024;
@@ -265,9 +265,6 @@ __global__ void __launch_bounds__(128, 1)
         if (i & 1) rt[i >> 1] = pack2(__uint_as_float(rt[i >> 1]), r_);
         else rt[i >> 1] = __float_as_uint(r_);
         p.t.E[ch * 8192 + i * 128 + d] = __float2bfloat16(kn * __expf(gend - gi));
-        p.w.qn[(ch * 64 + i) * 128 + d] = qn;
-        p.w.kn[(ch * 64 + i) * 128 + d] = kn;
-        p.w.G[(ch * 64 + i) * 128 + d] = gi;
         // decay-masked product operands: targets relative to their own 16-row block, sources to every later block
         const int I = i >> 4;
         const float cI = I == 0 ? c0 : (I == 1 ? c1 : (I == 2 ? c2 : c3));
@@ -364,9 +361,6 @@ __global__ void __launch_bounds__(128, 1)
                 *reinterpret_cast<uint4*>(Tbb + sw128_off(i, c16)) =
                     make_uint4(pack2(src[0] * bb[0], src[1] * bb[1]), pack2(src[2] * bb[2], src[3] * bb[3]),
                                pack2(src[4] * bb[4], src[5] * bb[5]), pack2(src[6] * bb[6], src[7] * bb[7]));
-                float4* wt = reinterpret_cast<float4*>(p.w.T + ch * 4096 + i * 64 + 8 * c16);
-                wt[0] = make_float4(src[0], src[1], src[2], src[3]);
-                wt[1] = make_float4(src[4], src[5], src[6], src[7]);
             }
         }
         fence_async_smem();
