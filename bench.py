@@ -47,7 +47,13 @@ def kda_kernel_flops(K, V, C=64):
     fwd_total = sum(fwd.values())
     bwd = {"scan_bwd_kernel": 3 * C * K * V + tri * V, "pullback_kernel": 2 * (tri + stri) * K}
     bwd["bwd_local_kernel"] = 2 * fwd_total - sum(bwd.values())
-    out = {k: 2.0 * v for k, v in {**fwd, **bwd}.items()}     # FLOP = 2 * MAC
+    tcl = {   # tensor-core lane kernels (same algorithmic work, different kernel boundaries)
+        "tc_intra_fwd_kernel": fwd["build_am_kernel"] + fwd["uw_kernel"],
+        "tc_scan_fwd_kernel": fwd["scan_fwd_kernel"] + fwd["out_kernel"],
+        "tc_scan_bwd_kernel": bwd["scan_bwd_kernel"],
+        "tc_intra_bwd_kernel": bwd["bwd_local_kernel"] + bwd["pullback_kernel"],
+    }
+    out = {k: 2.0 * v for k, v in {**fwd, **bwd, **tcl}.items()}     # FLOP = 2 * MAC
     out["_fwd_bwd_total"] = 2.0 * 3 * fwd_total
     return out
 
@@ -220,12 +226,18 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--workload", default="chain", choices=["chain", "varlen", "decode"],
+                    help="chain = config 1 (default, the driver's line); varlen = config 3; decode = config 4")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
     if args.impl == "reference":
         run_reference(args, rank, world)
+        return
+    if args.workload != "chain":
+        import bench_extra
+        bench_extra.run(args, rank, world, local)
         return
 
     import torch.distributed as dist

@@ -1,0 +1,194 @@
+"""Extra benchmark workloads, reached through `python bench.py --workload varlen|decode`.
+
+varlen (BASELINE config 3): packed KDA forward+backward, 65,536 tokens, H=16, Dk=Dv=128, seeded document
+lengths ~ U[256, 8192], per-sequence initial states ~ N(0, 0.02), bf16 I/O.  With N GPUs the heads are
+sharded (H/N per GPU, every GPU sees all sequences), no collective.
+decode (BASELINE config 4): recurrent decode, batch 256, H=16, Dk=Dv=128, fp32 state ~ N(0, 0.02), one token
+per step; the state (256 MiB) is read and rewritten every step.  With N GPUs the batch is sharded.
+Each prints one JSON line on rank 0 with the metric, the algorithmic roofline figure and the per-kernel times.
+"""
+
+from __future__ import annotations
+
+import json
+import os
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+FLOP_PER_TOKEN_HEAD = 423040.0      # chunked KDA fwd+bwd, C=64, K=V=128 (triangular products at triangular cost)
+
+
+def _peaks():
+    try:
+        return json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json"))), "measured"
+    except Exception:
+        return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}, "fallback"
+
+
+def _lengths(total, seed):
+    gen = torch.Generator().manual_seed(seed)
+    out, acc = [], 0
+    while acc < total:
+        n = int(torch.randint(256, 8193, (1,), generator=gen).item())
+        n = min(n, total - acc)
+        out.append(n)
+        acc += n
+    return out
+
+
+def run_varlen(args, rank, world, local, dist):
+    import experiment_swa_kda_b200 as m
+    from experiment_swa_kda_b200 import _lib
+    from bench import kda_kernel_flops
+    dev = torch.device(f"cuda:{local}")
+    total, H, D = 8 * 8192, 16, 128
+    Hl = H // world                                     # heads of this rank
+    lens = _lengths(total, 0)
+    cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32, device=dev)
+    gen = torch.Generator().manual_seed(100 + rank)
+    unit = lambda t: t / t.norm(dim=-1, keepdim=True)
+    bf = torch.bfloat16
+    x = {
+        "q": unit(torch.randn(1, total, Hl, D, generator=gen)).to(bf), "k": unit(torch.randn(1, total, Hl, D, generator=gen)).to(bf),
+        "v": torch.randn(1, total, Hl, D, generator=gen).to(bf),
+        "g": (-torch.nn.functional.softplus(torch.randn(1, total, Hl, D, generator=gen)) * 0.1).clamp(-5, 0).to(bf),
+        "beta": torch.sigmoid(torch.randn(1, total, Hl, generator=gen)).to(bf),
+    }
+    x = {n: t.to(dev).requires_grad_(True) for n, t in x.items()}
+    h0 = (torch.randn(len(lens), Hl, D, D, generator=gen) * 0.02).to(dev).requires_grad_(True)
+    probe = torch.randn(1, total, Hl, D, generator=gen).to(bf).to(dev)
+
+    def step():
+        o, fs = m.chunk_kda(x["q"], x["k"], x["v"], x["g"], x["beta"], initial_state=h0, output_final_state=True, cu_seqlens=cu)
+        return torch.autograd.grad(o, list(x.values()) + [h0], probe)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    barrier()
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    l0 = _lib.launch_count()
+    for a, b in ev:      # inputs (5 x 32 MiB per head-shard at N=1: 1.3 GB with panels) are far larger than L2
+        a.record()
+        step()
+        b.record()
+    barrier()
+    launches = _lib.launch_count() - l0
+    t = torch.tensor([sum(a.elapsed_time(b) for a, b in ev)], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item()) / args.steps
+    _lib.profile(True)
+    for _ in range(args.steps):
+        step()
+    torch.cuda.synchronize(dev)
+    rep = _lib.profile_report()
+    _lib.profile(False)
+    if rank != 0:
+        return
+    peaks, src = _peaks()
+    nch = sum((n + 63) // 64 for n in lens) * Hl
+    flops = kda_kernel_flops(D, D)
+    tot = sum(v[1] for v in rep.values()) or 1.0
+    kern = {}
+    for name, (n, tms) in rep.items():
+        row = {"launches_per_step": n / args.steps, "avg_us": tms / n * 1e3, "share": tms / tot}
+        if name in flops:
+            row["tflops"] = flops[name] * nch / (tms / n * 1e-3) / 1e12
+            row["frac_of_bf16_peak"] = row["tflops"] / peaks["bf16_tflops"]
+        kern[name] = row
+    top = max(rep, key=lambda k: rep[k][1])
+    line = {
+        "metric": "kda_varlen_fwd_bwd_token_heads_per_s", "value": total * H / (ms * 1e-3), "unit": "token-heads/s",
+        "tokens_per_s": total / (ms * 1e-3) if world == 1 else total / (ms * 1e-3), "n_gpus": world, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "dtype": "bf16",
+        "data": "synthetic",
+        "config": {"workload": f"config3 packed KDA fwd+bwd: {total} tokens, {len(lens)} sequences U[256,8192], H16 D128 chunk64, "
+                               f"heads sharded {Hl}/GPU, initial states N(0,0.02)", "l2": "inputs larger than L2"},
+        "tflops_algorithmic": FLOP_PER_TOKEN_HEAD * total * H / (ms * 1e-3) / 1e12,
+        "gpu_launches": int(launches),
+        "roofline": {"kernel": top, "bound": "tensor", "achieved": kern[top].get("tflops"), "peak": peaks["bf16_tflops"],
+                     "unit": "TFLOP/s", "frac": kern[top].get("frac_of_bf16_peak"), "traffic": None, "peak_source": src},
+        "kernels": kern,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def run_decode(args, rank, world, local, dist):
+    from experiment_swa_kda_b200 import _lib
+    lib = _lib.load()
+    dev = torch.device(f"cuda:{local}")
+    B, H, D = 256 // world, 16, 128
+    n_steps = 1024
+    gen = torch.Generator().manual_seed(7 + rank)
+    bf = torch.bfloat16
+    unit = lambda t: t / t.norm(dim=-1, keepdim=True)
+    NI = 16           # distinct per-step inputs, cycled (1 MiB each; the 256 MiB state dominates the traffic)
+    q = unit(torch.randn(NI, B, H, D, generator=gen)).to(bf).to(dev)
+    k = unit(torch.randn(NI, B, H, D, generator=gen)).to(bf).to(dev)
+    v = torch.randn(NI, B, H, D, generator=gen).to(bf).to(dev)
+    g = (-torch.nn.functional.softplus(torch.randn(NI, B, H, D, generator=gen)) * 0.1).clamp(-5, 0).to(bf).to(dev)
+    beta = torch.sigmoid(torch.randn(NI, B, H, generator=gen)).to(bf).to(dev)
+    s = [(torch.randn(B, H, D, D, generator=gen) * 0.02).to(dev), torch.empty(B, H, D, D, device=dev)]
+    o = torch.empty(B, H, D, dtype=bf, device=dev)
+    st = torch.cuda.current_stream(dev).cuda_stream
+    p = lambda t: t.data_ptr()
+
+    def run(n):
+        for i in range(n):
+            j = i % NI
+            rc = lib.kda_decode_step(B, H, D, D, 1, 1, 1, D ** -0.5, p(q[j]), p(k[j]), p(v[j]), p(g[j]), p(beta[j]),
+                                     p(s[i & 1]), p(s[(i + 1) & 1]), p(o), st)
+            if rc:
+                raise RuntimeError(f"kda_decode_step failed: {rc}")
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+
+    run(64)
+    barrier()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    run(n_steps)
+    b.record()
+    barrier()
+    t = torch.tensor([a.elapsed_time(b)], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item()) / n_steps
+    if rank != 0:
+        return
+    peaks, src = _peaks()
+    Bt = B * world
+    bytes_step = 2 * Bt * H * D * D * 4 + Bt * H * (3 * D + D) * 2 + Bt * H * 2 + Bt * H * D * 2
+    gbs = bytes_step / (ms * 1e-3) / 1e9
+    line = {
+        "metric": "kda_decode_state_GBps", "value": gbs, "unit": "GB/s", "n_gpus": world, "steps": n_steps, "warmup": 64,
+        "us_per_step": ms * 1e3, "tokens_per_s": Bt / (ms * 1e-3), "higher_is_better": True, "scaling": "strong",
+        "dtype": "f32 state, bf16 activations", "data": "synthetic",
+        "config": {"workload": f"config4 recurrent decode: batch {Bt} ({B}/GPU), H16, Dk=Dv=128, fp32 state read+written every step, "
+                               f"{n_steps} steps in one timed region", "l2": "state (256 MiB at N=1) larger than L2; at N=8 the 32 MiB "
+                               "per-GPU state can sit in L2, so the figure is effective bandwidth"},
+        "bytes_per_step": bytes_step,
+        "roofline": {"kernel": "decode_kernel", "bound": "hbm", "achieved": gbs / world, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                     "frac": gbs / world / peaks["hbm_gbs"], "traffic": None, "peak_source": src},
+    }
+    print(json.dumps(line), flush=True)
+
+
+def run(args, rank, world, local):
+    import torch.distributed as dist
+    dev = torch.device(f"cuda:{local}")
+    torch.cuda.set_device(dev)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    (run_varlen if args.workload == "varlen" else run_decode)(args, rank, world, local, dist)
+    if world > 1:
+        dist.destroy_process_group()

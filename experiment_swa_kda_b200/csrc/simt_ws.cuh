@@ -51,8 +51,11 @@ struct Carver {
     }
 };
 
+// The tensor-core lane keeps only the chunk table and the per-row scalars here (its operand panels live in
+// tc::TcWs); the large float32 arrays are carved with zero length for it.
 inline Ws carve_ws(const KdaChunkShape& sh, void* mem, size_t* bytes = nullptr) {
     Ws w;
+    const size_t big = sh.lane == KDA_LANE_TC ? 0 : 1;
     w.H = sh.heads; w.K = sh.key_dim; w.V = sh.value_dim;
     w.Kp = ceil_div(sh.key_dim, 64) * 64;
     w.Vp = ceil_div(sh.value_dim, 64) * 64;
@@ -63,14 +66,14 @@ inline Ws carve_ws(const KdaChunkShape& sh, void* mem, size_t* bytes = nullptr) 
     w.chunk_tok0 = c.take<int>(w.nslots + 1);
     w.chunk_len = c.take<int>(w.nslots + 1);
     w.seq_chunk0 = c.take<int>(sh.n_seq + 1);
-    w.qn = c.take<float>(nch * 64 * w.Kp);
-    w.kn = c.take<float>(nch * 64 * w.Kp);
-    w.G = c.take<float>(nch * 64 * w.Kp);
-    w.W = c.take<float>(nch * 64 * w.Kp);
-    w.Z = c.take<float>(nch * 64 * w.Vp);
-    w.A = c.take<float>(nch * 4096);
-    w.T = c.take<float>(nch * 4096);
-    w.Hc = c.take<float>(nch * w.Kp * w.Vp);
+    w.qn = c.take<float>(big * nch * 64 * w.Kp);
+    w.kn = c.take<float>(big * nch * 64 * w.Kp);
+    w.G = c.take<float>(big * nch * 64 * w.Kp);
+    w.W = c.take<float>(big * nch * 64 * w.Kp);
+    w.Z = c.take<float>(big * nch * 64 * w.Vp);
+    w.A = c.take<float>(big * nch * 4096);
+    w.T = c.take<float>(big * nch * 4096);
+    w.Hc = c.take<float>(big * nch * w.Kp * w.Vp);
     w.qinv = c.take<float>(nch * 64);
     w.kinv = c.take<float>(nch * 64);
     w.beta = c.take<float>(nch * 64);
@@ -81,7 +84,7 @@ inline Ws carve_ws(const KdaChunkShape& sh, void* mem, size_t* bytes = nullptr) 
 inline Scr carve_scr(const KdaChunkShape& sh, void* mem, size_t* bytes = nullptr) {
     Scr s;
     const int Kp = ceil_div(sh.key_dim, 64) * 64, Vp = ceil_div(sh.value_dim, 64) * 64;
-    const size_t nch = (size_t)slots_for(sh, false) * sh.heads;
+    const size_t nch = sh.lane == KDA_LANE_TC ? 0 : (size_t)slots_for(sh, false) * sh.heads;   // float32 lane only
     Carver c(mem);
     s.dZ = c.take<float>(nch * 64 * Vp);
     s.dHn = c.take<float>(nch * Kp * Vp);
