@@ -95,31 +95,61 @@ __global__ void gate_bwd_reduce_kernel(int nblk, int H, int K, const float* __re
 // warp owns a row at a time: a single coalesced read and a single coalesced write per row, two
 // shuffle reductions, and o_v = q.S'_v + beta r_v (q.k) so the row is never re-read.
 // =============================================================================================
-constexpr int kDecRows = 4;  // rows a warp keeps in flight
-
-template <bool VEC>
+// NV4 > 0: K % 4 == 0, lane owns NV4 float4 of a row (keys 128*j + 4*lane + 0..3); NV4 == 0: scalar layout,
+// lane owns keys lane + 32*e.  R rows are kept in flight per warp; every load is issued unconditionally
+// (addresses clamped, values masked) so the loads of a row group overlap.
+template <int NV4, int R>
 __global__ void __launch_bounds__(256) decode_kernel(int H, int K, int V, int bf16, int gbf16, int l2norm, float scale,
                                                      const void* __restrict__ q, const void* __restrict__ k,
                                                      const void* __restrict__ v, const void* __restrict__ g,
                                                      const void* __restrict__ beta, const float* s_in, float* s_out,
                                                      void* __restrict__ o, int rows_per_cta) {
-    const int bh = blockIdx.x;            // sequence * H + head
+    constexpr int NE = NV4 > 0 ? 4 * NV4 : 8;     // state elements per lane per row
+    const int bh = blockIdx.x;                    // sequence * H + head
     const int v_base = blockIdx.y * rows_per_cta;
+    const int v_end = min(V, v_base + rows_per_cta);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    // lane-owned key indices: VEC: kidx(e) = 128*(e/4) + 4*lane + e%4 ; scalar: kidx(e) = lane + 32*e
-    float qe[8], ke[8], dec[8];
+    auto key_of = [&](int e) { return NV4 > 0 ? (128 * (e >> 2) + 4 * lane + (e & 3)) : (lane + 32 * e); };
+    auto load_rows = [&](int r0, float (&s)[R][NE], float (&vv)[R]) {
+#pragma unroll
+        for (int j = 0; j < R; ++j) {
+            const int row = min(r0 + j, v_end - 1);
+            const float* src = s_in + ((size_t)bh * V + row) * K;
+            if (NV4 > 0) {
+#pragma unroll
+                for (int e4 = 0; e4 < NV4; ++e4) {
+                    const int kk = min(128 * e4 + 4 * lane, K - 4);
+                    const float4 x = __ldcs(reinterpret_cast<const float4*>(src + kk));
+                    s[j][4 * e4 + 0] = x.x; s[j][4 * e4 + 1] = x.y; s[j][4 * e4 + 2] = x.z; s[j][4 * e4 + 3] = x.w;
+                }
+            } else {
+#pragma unroll
+                for (int e = 0; e < NE; ++e) s[j][e] = src[min(lane + 32 * e, K - 1)];
+            }
+            vv[j] = ld_io(v, (size_t)bh * V + row, bf16);
+        }
+    };
+    // first row group goes out before the per-(sequence, head) scalars are needed
+    float s[R][NE], vv[R];
+    int r0 = v_base + warp * R;
+    if (r0 < v_end) load_rows(r0, s, vv);
+
+    float qe[NE], ke[NE], dec[NE];
+#pragma unroll
+    for (int e = 0; e < NE; ++e) {
+        const size_t i = (size_t)bh * K + min(key_of(e), K - 1);
+        qe[e] = ld_io(q, i, bf16);
+        ke[e] = ld_io(k, i, bf16);
+        dec[e] = ld_io(g, i, gbf16);
+    }
+    const float bt = ld_io(beta, bh, gbf16);
     float sq = 0.f, sk = 0.f;
 #pragma unroll
-    for (int e = 0; e < 8; ++e) {
-        const int kk = VEC ? (128 * (e >> 2) + 4 * lane + (e & 3)) : (lane + 32 * e);
-        if (kk < K) {
-            const size_t i = (size_t)bh * K + kk;
-            qe[e] = ld_io(q, i, bf16);
-            ke[e] = ld_io(k, i, bf16);
-            dec[e] = expf(ld_io(g, i, gbf16));
-        } else {
-            qe[e] = 0.f; ke[e] = 0.f; dec[e] = 0.f;
-        }
+    for (int e = 0; e < NE; ++e) {
+        const bool in = key_of(e) < K;
+        qe[e] = in ? qe[e] : 0.f;
+        ke[e] = in ? ke[e] : 0.f;
+        dec[e] = in ? expf(dec[e]) : 0.f;
         sq += qe[e] * qe[e];
         sk += ke[e] * ke[e];
     }
@@ -127,61 +157,46 @@ __global__ void __launch_bounds__(256) decode_kernel(int H, int K, int V, int bf
     sk = warp_sum(sk);
     const float qi = (l2norm ? 1.f / fmaxf(sqrtf(sq), 1e-12f) : 1.f) * scale;
     const float ki = l2norm ? 1.f / fmaxf(sqrtf(sk), 1e-12f) : 1.f;
-    const float bt = ld_io(beta, bh, gbf16);
     float qk = 0.f;
 #pragma unroll
-    for (int e = 0; e < 8; ++e) {
+    for (int e = 0; e < NE; ++e) {
         qe[e] *= qi;
         ke[e] *= ki;
         qk += qe[e] * ke[e];
     }
     qk = warp_sum(qk);
-    const int v_end = min(V, v_base + rows_per_cta);
-    for (int r0 = v_base + warp * kDecRows; r0 < v_end; r0 += 8 * kDecRows) {
-        float s[kDecRows][8];
+
+    for (; r0 < v_end; r0 += 8 * R) {
+        float a[R], b[R];
 #pragma unroll
-        for (int j = 0; j < kDecRows; ++j) {
-            const int row = r0 + j;
-            const float* src = s_in + ((size_t)bh * V + row) * K;
-            if (row < v_end) {
-                if (VEC) {
+        for (int j = 0; j < R; ++j) {
+            a[j] = 0.f;
+            b[j] = 0.f;
 #pragma unroll
-                    for (int e4 = 0; e4 < 2; ++e4) {
-                        const int kk = 128 * e4 + 4 * lane;
-                        float4 x = (kk < K) ? __ldcs(reinterpret_cast<const float4*>(src + kk)) : make_float4(0, 0, 0, 0);
-                        s[j][4 * e4 + 0] = x.x; s[j][4 * e4 + 1] = x.y; s[j][4 * e4 + 2] = x.z; s[j][4 * e4 + 3] = x.w;
-                    }
-                } else {
+            for (int e = 0; e < NE; ++e) {
+                s[j][e] *= dec[e];
+                a[j] += ke[e] * s[j][e];
+                b[j] += qe[e] * s[j][e];
+            }
+        }
+        // R independent reductions interleaved
 #pragma unroll
-                    for (int e = 0; e < 8; ++e) {
-                        const int kk = lane + 32 * e;
-                        s[j][e] = (kk < K) ? src[kk] : 0.f;
-                    }
-                }
-            } else {
+        for (int off = 16; off > 0; off >>= 1) {
 #pragma unroll
-                for (int e = 0; e < 8; ++e) s[j][e] = 0.f;
+            for (int j = 0; j < R; ++j) {
+                a[j] += __shfl_xor_sync(0xffffffffu, a[j], off);
+                b[j] += __shfl_xor_sync(0xffffffffu, b[j], off);
             }
         }
 #pragma unroll
-        for (int j = 0; j < kDecRows; ++j) {
+        for (int j = 0; j < R; ++j) {
             const int row = r0 + j;
-            float a = 0.f, b = 0.f;
-#pragma unroll
-            for (int e = 0; e < 8; ++e) {
-                s[j][e] *= dec[e];
-                a += ke[e] * s[j][e];
-                b += qe[e] * s[j][e];
-            }
-            a = warp_sum(a);
-            b = warp_sum(b);
             if (row < v_end) {
-                const float res = ld_io(v, (size_t)bh * V + row, bf16) - a;
-                const float br = bt * res;
+                const float br = bt * (vv[j] - a[j]);
                 float* dst = s_out + ((size_t)bh * V + row) * K;
-                if (VEC) {
+                if (NV4 > 0) {
 #pragma unroll
-                    for (int e4 = 0; e4 < 2; ++e4) {
+                    for (int e4 = 0; e4 < NV4; ++e4) {
                         const int kk = 128 * e4 + 4 * lane;
                         if (kk < K)
                             __stcs(reinterpret_cast<float4*>(dst + kk),
@@ -190,14 +205,15 @@ __global__ void __launch_bounds__(256) decode_kernel(int H, int K, int V, int bf
                     }
                 } else {
 #pragma unroll
-                    for (int e = 0; e < 8; ++e) {
+                    for (int e = 0; e < NE; ++e) {
                         const int kk = lane + 32 * e;
                         if (kk < K) dst[kk] = s[j][e] + br * ke[e];
                     }
                 }
-                if (lane == 0) st_io(o, (size_t)bh * V + row, bf16, b + br * qk);
+                if (lane == 0) st_io(o, (size_t)bh * V + row, bf16, b[j] + br * qk);
             }
         }
+        if (r0 + 8 * R < v_end) load_rows(r0 + 8 * R, s, vv);
     }
 }
 
@@ -791,15 +807,18 @@ extern "C" int kda_decode_step(int32_t n_seq, int32_t heads, int32_t key_dim, in
     if (!q || !k || !v || !g || !beta || !state_in || !state_out || !o) return KDA_ERR_NULL;
     const int bf16 = io_dtype == KDA_DTYPE_BF16, gbf16 = gate_dtype == KDA_DTYPE_BF16;
     // rows per CTA: 32 (8 warps x 4 rows); fewer CTAs per (sequence, head) once the grid is large enough
-    const int rows_per_cta = 32;
+    // one CTA per (sequence, head) once there are enough of them to fill the GPU; otherwise split the value rows
+    const int rows_per_cta = (n_seq * heads >= 148 * 4) ? value_dim : 32;
     dim3 grid(n_seq * heads, ceil_div(value_dim, rows_per_cta));
-    const bool vec = (key_dim % 4 == 0) && ((reinterpret_cast<uintptr_t>(state_in) | reinterpret_cast<uintptr_t>(state_out)) % 16 == 0);
-    if (vec)
-        KDA_LAUNCH("decode_kernel", (cudaStream_t)stream, pw::decode_kernel<true><<<grid, 256, 0, (cudaStream_t)stream>>>(heads, key_dim, value_dim, bf16, gbf16, l2norm, scale, q, k,
-                                                                         v, g, beta, state_in, state_out, o, rows_per_cta));
+    cudaStream_t st = (cudaStream_t)stream;
+    const bool vec = (key_dim % 4 == 0) &&
+                     ((reinterpret_cast<uintptr_t>(state_in) | reinterpret_cast<uintptr_t>(state_out)) % 16 == 0);
+    if (vec && key_dim <= 128)
+        KDA_LAUNCH("decode_kernel", st, pw::decode_kernel<1, 8><<<grid, 256, 0, st>>>(heads, key_dim, value_dim, bf16, gbf16, l2norm, scale, q, k, v, g, beta, state_in, state_out, o, rows_per_cta));
+    else if (vec)
+        KDA_LAUNCH("decode_kernel", st, pw::decode_kernel<2, 4><<<grid, 256, 0, st>>>(heads, key_dim, value_dim, bf16, gbf16, l2norm, scale, q, k, v, g, beta, state_in, state_out, o, rows_per_cta));
     else
-        KDA_LAUNCH("decode_kernel", (cudaStream_t)stream, pw::decode_kernel<false><<<grid, 256, 0, (cudaStream_t)stream>>>(heads, key_dim, value_dim, bf16, gbf16, l2norm, scale, q,
-                                                                          k, v, g, beta, state_in, state_out, o, rows_per_cta));
+        KDA_LAUNCH("decode_kernel", st, pw::decode_kernel<0, 4><<<grid, 256, 0, st>>>(heads, key_dim, value_dim, bf16, gbf16, l2norm, scale, q, k, v, g, beta, state_in, state_out, o, rows_per_cta));
     return launch_status();
 }
 

@@ -23,6 +23,12 @@
 namespace kda {
 namespace tc {
 
+#ifdef KDA_PHASE_TIMING
+#define KDA_TICKB(n) do { if (threadIdx.x == 0 && blockIdx.y == 0 && (blockIdx.x == 0 || blockIdx.x == 100)) tick[n] = clock64(); } while (0)
+#else
+#define KDA_TICKB(n) do { } while (0)
+#endif
+
 int make_map_bf16(CUtensorMap* m, const void* ptr, uint64_t rows, uint64_t cols, uint32_t box_cols, uint32_t box_rows);
 
 namespace {
@@ -112,11 +118,15 @@ __global__ void __launch_bounds__(512, 1)
     __shared__ uint64_t bar_in, bar_mma;
     __shared__ uint32_t tmem_slot;
 
+#ifdef KDA_PHASE_TIMING
+    long long tick[16];
+#endif
     const int slot = blockIdx.x, h = blockIdx.y, H = p.H;
     const int len = p.chunk_len[slot];
     if (len == 0) return;
     const int tok0 = p.chunk_tok0[slot];
     const int ch = slot * H + h;
+    KDA_TICKB(0);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int I = warp >> 2;             // row block of this thread
     const int d = tid & 127;             // channel (and TMEM lane) of this thread
@@ -174,9 +184,11 @@ __global__ void __launch_bounds__(512, 1)
         for (int r = 0; r < 16; ++r) G[r] += pre;
         cref[I * 128 + d] = G[0];
     }
+    KDA_TICKB(1);
     bool ok = mbar_wait(&bar_in, 0, p.status, 40);
     ok = __syncthreads_and(ok);          // also publishes cref
     const float egend = __expf(gend);
+    KDA_TICKB(2);
 
     // TMEM columns
     constexpr uint32_t cDa = 0, cDb = 64, cDc = 128, cDd = 192, cDg = 256, cDf = 320, cDe = 384;
@@ -239,10 +251,12 @@ __global__ void __launch_bounds__(512, 1)
             st16(Qp, eoff(i, d, 8192), __expf(G[r]) * kn[r]);
         }
     }
+    KDA_TICKB(3);
     ok = ok && mbar_wait(&bar_mma, 0, p.status, 41);
     ok = __syncthreads_and(ok);
     tc_fence_after();
 
+    KDA_TICKB(4);
     // ================================================================ phase 2a: first read-out
     float dqn[16], dkn[16], dG[16];
     float ge_part = 0.f;
@@ -296,10 +310,12 @@ __global__ void __launch_bounds__(512, 1)
                          umma_smem_desc_sw128(bT + k16 * 2048, 8192, 1024), id_k_mn, k16 > 0);
         umma_commit(&bar_mma);
     }
+    KDA_TICKB(5);
     ok = ok && mbar_wait(&bar_mma, 1, p.status, 42);
     ok = __syncthreads_and(ok);
     tc_fence_after();
 
+    KDA_TICKB(6);
     // ================================================================ phase 3: X, Y, dM
     // M = 64 accumulators keep row (16*w + l) in lane l < 16 of warp w < 4.  tcgen05.ld is warp-collective, so all 32
     // lanes of those warps run the loads; lanes >= 16 mirror a row and never store.
@@ -351,6 +367,7 @@ __global__ void __launch_bounds__(512, 1)
                          umma_smem_desc_sw128(smem_u32(XT) + k16 * 32, 16, 1024), id, k16 > 0);
         umma_commit(&bar_mma);
     }
+    KDA_TICKB(7);
     ok = ok && mbar_wait(&bar_mma, 0, p.status, 43);
     ok = __syncthreads_and(ok);
     tc_fence_after();
@@ -379,10 +396,12 @@ __global__ void __launch_bounds__(512, 1)
                          umma_smem_desc_sw128(smem_u32(Ts) + k16 * 32, 16, 1024), id, k16 > 0);
         umma_commit(&bar_mma);
     }
+    KDA_TICKB(8);
     ok = ok && mbar_wait(&bar_mma, 1, p.status, 44);
     ok = __syncthreads_and(ok);
     tc_fence_after();
 
+    KDA_TICKB(9);
     // ================================================================ phase 4: pull-back operands
     uint8_t* Sk = sm + kR1;           // k~_I panels: [I][2 blocks][64 rows s x 128 B]     MN-major A
     uint8_t* Xk = sm + kR3;           // target stacks: [I][2 blocks][32 rows x 128 B]     MN-major A
@@ -477,10 +496,12 @@ __global__ void __launch_bounds__(512, 1)
         }
         umma_commit(&bar_mma);
     }
+    KDA_TICKB(10);
     ok = ok && mbar_wait(&bar_mma, 0, p.status, 45);
     ok = __syncthreads_and(ok);
     tc_fence_after();
 
+    KDA_TICKB(11);
     // ================================================================ phase 5: assemble the gradients
     {
         float t[16];
@@ -570,6 +591,13 @@ __global__ void __launch_bounds__(512, 1)
             }
         }
     }
+    KDA_TICKB(12);
+#ifdef KDA_PHASE_TIMING
+    if (threadIdx.x == 0 && blockIdx.y == 0 && (blockIdx.x == 0 || blockIdx.x == 100))
+        printf("intra_bwd blk %d: setup+g %lld | tma wait %lld | issue1+dD/Q' %lld | mma1 wait %lld | readout2a %lld | mma2 wait %lld | X^T %lld | Y wait %lld | Ywrite+dM wait %lld | p4 operands %lld | mma pb wait %lld | assemble %lld | total %lld\n",
+               blockIdx.x, tick[1] - tick[0], tick[2] - tick[1], tick[3] - tick[2], tick[4] - tick[3], tick[5] - tick[4], tick[6] - tick[5],
+               tick[7] - tick[6], tick[8] - tick[7], tick[9] - tick[8], tick[10] - tick[9], tick[11] - tick[10], tick[12] - tick[11], tick[12] - tick[0]);
+#endif
     tc_fence_before();
     __syncthreads();
     if (warp == 0) tmem_dealloc(tmem, 512);
