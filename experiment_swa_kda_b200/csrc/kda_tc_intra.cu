@@ -43,12 +43,13 @@ __device__ __forceinline__ uint32_t el_off(int r, int d, uint32_t blk_bytes) {
 
 constexpr int kLDs = 68;
 
-// dst[S x S] = alpha * A[S x S] * B[S x S] (row-major fp32, leading dimension kLDs, 16-byte aligned rows) for
-// NB independent problems laid out by the callers' pointer functions; 128 threads, each owns a strip of
-// CW consecutive columns of one row so that B is read with 128-bit loads and every load is independent.
+constexpr int kNT = 512;   // threads per CTA: thread (I, d) = 16-token row block I (warp >> 2), channel d (tid & 127)
+
+// dst[S x S] = alpha * A[S x S] * B[S x S] (row-major fp32, leading dimension kLDs) for NB independent problems
+// addressed through the callers' pointer functions; kNT threads, each owning CW consecutive columns of one row.
 template <int S, int NB, class PA, class PB, class PD>
-__device__ __forceinline__ void block_mm128(PA pa, PB pb, PD pd, float alpha) {
-    constexpr int CW = S * S * NB / 128;          // columns per thread: 4 (S=16, NB=2) or 8 (S=32, NB=1)
+__device__ __forceinline__ void block_mm(PA pa, PB pb, PD pd, float alpha) {
+    constexpr int CW = S * S * NB / kNT;          // 1 (S=16, NB=2) or 2 (S=32, NB=1)
     constexpr int TPR = S / CW;                   // threads per row
     const int tid = threadIdx.x;
     const int prob = tid / (S * TPR), rem = tid - prob * (S * TPR);
@@ -62,24 +63,18 @@ __device__ __forceinline__ void block_mm128(PA pa, PB pb, PD pd, float alpha) {
     for (int t = 0; t < S; ++t) {
         const float a = A[t];
 #pragma unroll
-        for (int c4 = 0; c4 < CW / 4; ++c4) {
-            const float4 bv = *reinterpret_cast<const float4*>(B + t * kLDs + 4 * c4);
-            acc[4 * c4 + 0] += a * bv.x; acc[4 * c4 + 1] += a * bv.y;
-            acc[4 * c4 + 2] += a * bv.z; acc[4 * c4 + 3] += a * bv.w;
-        }
+        for (int c = 0; c < CW; ++c) acc[c] += a * B[t * kLDs + c];
     }
     float* D = pd(prob) + i * kLDs + j0;
 #pragma unroll
-    for (int c4 = 0; c4 < CW / 4; ++c4)
-        *reinterpret_cast<float4*>(D + 4 * c4) =
-            make_float4(alpha * acc[4 * c4], alpha * acc[4 * c4 + 1], alpha * acc[4 * c4 + 2], alpha * acc[4 * c4 + 3]);
+    for (int c = 0; c < CW; ++c) D[c] = alpha * acc[c];
 }
 
 // Ts = (I + Ms)^-1 for strictly lower-triangular Ms (64x64): 16x16 diagonal solves, then 32 and 64 merges
 //   inv([[A,0],[C,B]]) = [[Ai,0],[-Bi C Ai, Bi]].
-__device__ void unit_lower_inverse128(const float* Ms, float* Ts, float* tmp) {
+__device__ void unit_lower_inverse(const float* Ms, float* Ts, float* tmp) {
     const int tid = threadIdx.x;
-    for (int idx = tid; idx < 64 * kLDs; idx += 128) Ts[idx] = 0.f;
+    for (int idx = tid; idx < 64 * kLDs; idx += kNT) Ts[idx] = 0.f;
     __syncthreads();
     if (tid < 64) {
         const int b = tid >> 4, j = tid & 15;
@@ -100,19 +95,19 @@ __device__ void unit_lower_inverse128(const float* Ms, float* Ts, float* tmp) {
     }
     __syncthreads();
     // 32x32 merges, two independent pairs: tmp_p = C_p Ai_p ; T21_p = -Bi_p tmp_p
-    block_mm128<16, 2>([&](int p) { return Ms + (32 * p + 16) * kLDs + 32 * p; },
-                       [&](int p) { return Ts + (32 * p) * kLDs + 32 * p; },
-                       [&](int p) { return tmp + p * 16 * kLDs; }, 1.f);
+    block_mm<16, 2>([&](int p) { return Ms + (32 * p + 16) * kLDs + 32 * p; },
+                    [&](int p) { return Ts + (32 * p) * kLDs + 32 * p; },
+                    [&](int p) { return tmp + p * 16 * kLDs; }, 1.f);
     __syncthreads();
-    block_mm128<16, 2>([&](int p) { return Ts + (32 * p + 16) * kLDs + 32 * p + 16; },
-                       [&](int p) { return tmp + p * 16 * kLDs; },
-                       [&](int p) { return Ts + (32 * p + 16) * kLDs + 32 * p; }, -1.f);
+    block_mm<16, 2>([&](int p) { return Ts + (32 * p + 16) * kLDs + 32 * p + 16; },
+                    [&](int p) { return tmp + p * 16 * kLDs; },
+                    [&](int p) { return Ts + (32 * p + 16) * kLDs + 32 * p; }, -1.f);
     __syncthreads();
     // 64x64 merge
-    block_mm128<32, 1>([&](int) { return Ms + 32 * kLDs; }, [&](int) { return Ts; }, [&](int) { return tmp; }, 1.f);
+    block_mm<32, 1>([&](int) { return Ms + 32 * kLDs; }, [&](int) { return Ts; }, [&](int) { return tmp; }, 1.f);
     __syncthreads();
-    block_mm128<32, 1>([&](int) { return Ts + 32 * kLDs + 32; }, [&](int) { return tmp; },
-                       [&](int) { return Ts + 32 * kLDs; }, -1.f);
+    block_mm<32, 1>([&](int) { return Ts + 32 * kLDs + 32; }, [&](int) { return tmp; },
+                    [&](int) { return Ts + 32 * kLDs; }, -1.f);
     __syncthreads();
 }
 
@@ -128,35 +123,55 @@ struct IntraFwdArgs {
     simt::Ws w;                       // per-row scalars (inverse norms, beta) kept for the backward
 };
 
-constexpr int kIntraFwdSmem = 98304 + 49152 + 1024 + 1024;
+// shared-memory map (bytes from a 1024-aligned base)
+constexpr int kFS0 = 0;          // 32 KB  source stack, target blocks 0|1   -> later Ms, Ts, tmp (fp32)
+constexpr int kFX0 = 32768;      // 16 KB  target stack, blocks 0|1
+constexpr int kFS1 = 49152;      // 32 KB  source stack, target blocks 2|3
+constexpr int kFX1 = 81920;      // 16 KB  target stack, blocks 2|3          -> later T and T diag(beta) (bf16)
+constexpr int kFQ = 98304;       // 16 KB  Q = beta e^G k (MN-major A)
+constexpr int kFIn = 114688;     // 48 KB  q | k | v tiles (TMA)
+constexpr int kFSmall = 163840;  // floats: gsum[4][128] cref[4][128] qinv[64] kinv[64] beta[64]
+constexpr int kIntraFwdSmem = kFSmall + (2 * 512 + 3 * 64) * 4 + 1024;
 
-__global__ void __launch_bounds__(128, 1)
+__device__ __forceinline__ void tmem_ld16f(uint32_t taddr, float (&f)[16]) {
+    uint32_t r[16];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr)
+        : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int j = 0; j < 16; ++j) f[j] = __uint_as_float(r[j]);
+}
+
+__global__ void __launch_bounds__(kNT, 1)
     tc_intra_fwd_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant__ CUtensorMap mk,
                         const __grid_constant__ CUtensorMap mv, IntraFwdArgs p) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* sm = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-    // phase 1 view: operands of the A / M~ chains
-    uint8_t* S0 = sm;              // [2][128 rows x 128 B]
-    uint8_t* X0 = sm + 32768;      // [2][64 rows x 128 B]
-    uint8_t* S1 = sm + 49152;
-    uint8_t* X1 = sm + 81920;
-    // phase 2 view (after both chains have completed)
-    float* Ms = reinterpret_cast<float*>(sm);
+    uint8_t* S0 = sm + kFS0;
+    uint8_t* X0 = sm + kFX0;
+    uint8_t* S1 = sm + kFS1;
+    uint8_t* X1 = sm + kFX1;
+    float* Ms = reinterpret_cast<float*>(sm);      // phase-2 view of the source/target stacks
     float* Ts = Ms + 64 * kLDs;
     float* tmp = Ts + 64 * kLDs;
-    uint8_t* Qs = sm + 49152;      // [2 key blocks][64 rows x 128 B]     MN-major A
-    uint8_t* Tb = sm + 65536;      // [64 rows x 128 B]                   K-major B: T
-    uint8_t* Tbb = sm + 73728;     // [64 rows x 128 B]                   K-major B: T diag(beta)
-    // TMA-staged inputs, token-major rows of 128 B per 64-channel block (128-byte swizzle)
-    uint8_t* qs = sm + 98304;      // [2][64 x 128 B]
+    uint8_t* Tb = sm + kFX1;                       // [64 rows x 128 B] K-major B: T
+    uint8_t* Tbb = sm + kFX1 + 8192;               //                              T diag(beta)
+    uint8_t* Qs = sm + kFQ;
+    uint8_t* qs = sm + kFIn;
     uint8_t* ks = qs + 16384;
-    uint8_t* vs = ks + 16384;      // doubles as the MN-major A operand of U^T = v^T (T diag(beta))^T
-    float* qinv = reinterpret_cast<float*>(vs + 16384);
+    uint8_t* vs = ks + 16384;                      // doubles as the MN-major A operand of U^T = v^T (T diag(beta))^T
+    float* gsum = reinterpret_cast<float*>(sm + kFSmall);
+    float* cref = gsum + 512;
+    float* qinv = cref + 512;
     float* kinv = qinv + 64;
     float* bet = kinv + 64;
     __shared__ uint64_t bar_am, bar_uw, bar_in;
     __shared__ uint32_t tmem_slot;
-
 #ifdef KDA_PHASE_TIMING
     long long tick[12];
 #endif
@@ -165,7 +180,9 @@ __global__ void __launch_bounds__(128, 1)
     if (len == 0) return;
     const int tok0 = p.chunk_tok0[slot];
     const size_t ch = (size_t)slot * H + h;
-    const int tid = threadIdx.x, warp = tid >> 5;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int I = warp >> 2, d = tid & 127;
+    const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
     KDA_TICK(0);
 
     if (tid == 0) {
@@ -180,13 +197,36 @@ __global__ void __launch_bounds__(128, 1)
             tma_load_2d(vs + kb * 8192, &mv, &bar_in, h * 128 + kb * 64, tok0);
         }
     }
-    if (warp == 0) tmem_alloc(&tmem_slot, 256);
-    __syncthreads();                         // barrier initialisation visible to every waiter
+    if (warp == 1) tmem_alloc(&tmem_slot, 256);
+
+    // ---- cumulative log-decay of this thread's 16 rows (loads unconditional, row index clamped into the chunk)
+    const size_t rstride = (size_t)H * 128;
+    const size_t col = ((size_t)tok0 * H + h) * 128 + d;
+    float G[16];
+    {
+#pragma unroll
+        for (int r = 0; r < 16; ++r) G[r] = ld_io(p.g, col + (size_t)min(16 * I + r, len - 1) * rstride, p.gbf16);
+        float run = 0.f;
+#pragma unroll
+        for (int r = 0; r < 16; ++r) {
+            run += (16 * I + r < len) ? G[r] : 0.f;
+            G[r] = run;
+        }
+        gsum[I * 128 + d] = run;
+    }
+    if (tid < 64) {
+        const float b = tid < len ? ld_io(p.beta, (size_t)(tok0 + tid) * H + h, p.gbf16) : 0.f;
+        bet[tid] = b;
+        p.w.beta[ch * 64 + tid] = b;
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = tmem_slot;
     bool ok = mbar_wait(&bar_in, 0, p.t.status, 30);
     KDA_TICK(1);
-
-    // ---- phase A: one thread per row: inverse norms (q rows on threads 0..63, k rows on 64..127), beta
-    {
+    // ---- inverse norms: one thread per row (q rows on threads 0..63, k rows on 64..127)
+    if (tid < 128) {
         const int r = tid & 63;
         const uint8_t* tile = tid < 64 ? qs : ks;
         float ss = 0.f;
@@ -201,95 +241,79 @@ __global__ void __launch_bounds__(128, 1)
                     ss += f.x * f.x + f.y * f.y;
                 }
             }
-        } else {
+        } else if (tid < 64) {
             // rows past a ragged tail hold other tokens: blank the value rows that feed the U product
-            if (tid < 64) {
 #pragma unroll
-                for (int c = 0; c < 16; ++c)
-                    *reinterpret_cast<uint4*>(vs + (c >> 3) * 8192 + sw128_off(r, c & 7)) = make_uint4(0, 0, 0, 0);
-            }
+            for (int c = 0; c < 16; ++c)
+                *reinterpret_cast<uint4*>(vs + (c >> 3) * 8192 + sw128_off(r, c & 7)) = make_uint4(0, 0, 0, 0);
         }
         float inv = 0.f;
         if (r < len) inv = p.l2norm ? 1.0f / fmaxf(sqrtf(ss), 1e-12f) : 1.0f;
         if (tid < 64) {
             qinv[r] = inv;
             p.w.qinv[ch * 64 + r] = inv;
-            const float b = r < len ? ld_io(p.beta, (size_t)(tok0 + r) * H + h, p.gbf16) : 0.f;
-            bet[r] = b;
-            p.w.beta[ch * 64 + r] = b;
         } else {
             kinv[r] = inv;
             p.w.kinv[ch * 64 + r] = inv;
         }
     }
-    tc_fence_before();
-    __syncthreads();
-    tc_fence_after();
-    const uint32_t tmem = tmem_slot;
-    const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
-
-    KDA_TICK(2);
-    // ---- phase B: one thread per channel d
-    const int d = tid;
-    const size_t col = ((size_t)tok0 * H + h) * 128 + d;       // element (row 0, channel d) of q/k/v/g
-    const size_t rstride = (size_t)H * 128;
-    float G[64];
+    float gend;
     {
-        // unconditional loads (row index clamped into the chunk) so that all 64 are in flight together
+        const float s0 = gsum[d], s1 = gsum[128 + d], s2 = gsum[256 + d], s3 = gsum[384 + d];
+        const float pre = I == 0 ? 0.f : (I == 1 ? s0 : (I == 2 ? s0 + s1 : s0 + s1 + s2));
+        gend = s0 + s1 + s2 + s3;
 #pragma unroll
-        for (int i = 0; i < 64; ++i) G[i] = ld_io(p.g, col + (size_t)min(i, len - 1) * rstride, p.gbf16);
-        float run = 0.f;
+        for (int r = 0; r < 16; ++r) G[r] += pre;
+        cref[I * 128 + d] = G[0];
+        if (I == 0) p.t.decay_end[ch * 128 + d] = __expf(gend);
+    }
+    __syncthreads();
+    KDA_TICK(2);
+
+    // ---- operand panels for this thread's 16 rows of channel d
+    {
+        const float c0 = cref[d], c1 = cref[128 + d], c2 = cref[256 + d], c3 = cref[384 + d];
+        const float cI = I == 0 ? c0 : (I == 1 ? c1 : (I == 2 ? c2 : c3));
+        const float fb0 = __expf(c1 - c0), fb1 = __expf(c2 - c1), fb2 = __expf(c3 - c2);
+        uint8_t* X = (I < 2) ? X0 : X1;
+        uint32_t rt[8];
 #pragma unroll
-        for (int i = 0; i < 64; ++i) {
-            run += (i < len) ? G[i] : 0.f;
-            G[i] = run;
+        for (int r = 0; r < 16; ++r) {
+            const int i = 16 * I + r;
+            float qv = 0.f, kv = 0.f;
+            if (i < len) {
+                qv = __bfloat162float(*reinterpret_cast<const __nv_bfloat16*>(qs + el_off(i, d, 8192)));
+                kv = __bfloat162float(*reinterpret_cast<const __nv_bfloat16*>(ks + el_off(i, d, 8192)));
+            }
+            const float qn = qv * qinv[i] * p.scale, kn = kv * kinv[i];
+            const float gi = G[r];
+            const float eG = __expf(gi);
+            const float r_ = qn * eG;
+            if (r & 1) rt[r >> 1] = pack2(__uint_as_float(rt[r >> 1]), r_);
+            else rt[r >> 1] = __float_as_uint(r_);
+            p.t.E[ch * 8192 + i * 128 + d] = __float2bfloat16(kn * __expf(gend - gi));
+            st_bf16(Qs, el_off(i, d, 8192), bet[i] * eG * kn);
+            // decay-masked product operands: targets relative to their own 16-row block, sources to every later block
+            const float tq = __expf(gi - cI);
+            const int xr = (I & 1) * 32 + r;
+            st_bf16(X, el_off(xr, d, 8192), qn * tq);
+            st_bf16(X, el_off(xr + 16, d, 8192), kn * tq);
+            float f = kn * __expf(cI - gi);      // source row i scaled to its own block
+            float s0v = 0.f, s1v = 0.f, s2v = 0.f, s3v = 0.f;
+            if (I == 0) { s0v = f; f *= fb0; }
+            if (I <= 1) { s1v = f; f *= fb1; }
+            if (I <= 2) { s2v = f; f *= fb2; }
+            s3v = f;
+            st_bf16(S0, el_off(i, d, 16384), s0v);
+            st_bf16(S0, el_off(64 + i, d, 16384), s1v);
+            st_bf16(S1, el_off(i, d, 16384), s2v);
+            st_bf16(S1, el_off(64 + i, d, 16384), s3v);
         }
+        uint4* dst = reinterpret_cast<uint4*>(p.t.RT + ch * 8192 + (size_t)d * 64 + 16 * I);
+        dst[0] = make_uint4(rt[0], rt[1], rt[2], rt[3]);
+        dst[1] = make_uint4(rt[4], rt[5], rt[6], rt[7]);
     }
     KDA_TICK(3);
-    const float gend = G[63];
-    p.t.decay_end[ch * 128 + d] = __expf(gend);
-    const float c0 = G[0], c1 = G[16], c2 = G[32], c3 = G[48];
-    const float fb0 = __expf(c1 - c0), fb1 = __expf(c2 - c1), fb2 = __expf(c3 - c2);
-    uint32_t rt[32];
-#pragma unroll
-    for (int i = 0; i < 64; ++i) {
-        float qv = 0.f, kv = 0.f;
-        if (i < len) {
-            qv = __bfloat162float(*reinterpret_cast<const __nv_bfloat16*>(qs + el_off(i, d, 8192)));
-            kv = __bfloat162float(*reinterpret_cast<const __nv_bfloat16*>(ks + el_off(i, d, 8192)));
-        }
-        const float qn = qv * qinv[i] * p.scale, kn = kv * kinv[i];
-        const float gi = G[i];
-        const float eG = __expf(gi);
-        const float r_ = qn * eG;
-        if (i & 1) rt[i >> 1] = pack2(__uint_as_float(rt[i >> 1]), r_);
-        else rt[i >> 1] = __float_as_uint(r_);
-        p.t.E[ch * 8192 + i * 128 + d] = __float2bfloat16(kn * __expf(gend - gi));
-        // decay-masked product operands: targets relative to their own 16-row block, sources to every later block
-        const int I = i >> 4;
-        const float cI = I == 0 ? c0 : (I == 1 ? c1 : (I == 2 ? c2 : c3));
-        const float tq = __expf(gi - cI);
-        uint8_t* X = (I < 2) ? X0 : X1;
-        const int xr = (I & 1) * 32 + (i & 15);
-        st_bf16(X, el_off(xr, d, 8192), qn * tq);
-        st_bf16(X, el_off(xr + 16, d, 8192), kn * tq);
-        float f = kn * __expf(cI - gi);      // source row i scaled to its own block
-        float s0v = 0.f, s1v = 0.f, s2v = 0.f, s3v = 0.f;
-        if (I == 0) { s0v = f; f *= fb0; }
-        if (I <= 1) { s1v = f; f *= fb1; }
-        if (I <= 2) { s2v = f; f *= fb2; }
-        s3v = f;
-        st_bf16(S0, el_off(i, d, 16384), s0v);
-        st_bf16(S0, el_off(64 + i, d, 16384), s1v);
-        st_bf16(S1, el_off(i, d, 16384), s2v);
-        st_bf16(S1, el_off(64 + i, d, 16384), s3v);
-    }
-    {
-        uint4* dst = reinterpret_cast<uint4*>(p.t.RT + ch * 8192 + (size_t)d * 64);
-#pragma unroll
-        for (int c = 0; c < 8; ++c) dst[c] = make_uint4(rt[4 * c], rt[4 * c + 1], rt[4 * c + 2], rt[4 * c + 3]);
-    }
-    KDA_TICK(4);
     fence_async_smem();
     tc_fence_before();
     __syncthreads();
@@ -309,59 +333,53 @@ __global__ void __launch_bounds__(128, 1)
     ok = mbar_wait(&bar_am, 0, p.t.status, 31) && ok;
     ok = __syncthreads_and(ok);
     tc_fence_after();
-    KDA_TICK(5);
+    KDA_TICK(4);
     if (ok) {
-        // ---- A^T panel and beta*M~ (fp32) from the accumulators; lane = source row (two blocks per chain)
-        const int half = tid >> 6, s = tid & 63;
+        // ---- A^T panel, M~ panel and beta*M~ (fp32) from the two accumulators.  Lane = source row (two 64-row
+        // halves per chain); the four warp groups split chain x {A columns, M~ columns}.
+        {
+            const int m = (warp & 3) * 32 + lane;          // accumulator row
+            const int half = m >> 6, s = m & 63;
+            const int pr = I >> 1, sub = I & 1;            // chain, 0: A columns / 1: M~ columns
+            const int Ib = 2 * pr + half;                  // target block held in these columns
+            float t[16];
+            tmem_ld16f(tmem + lane_base + pr * 64 + 32 * half + 16 * sub, t);
+            if (sub == 0) {
+                uint32_t at[8];
 #pragma unroll
-        for (int pr = 0; pr < 2; ++pr) {
-            const int I = 2 * pr + half;
-            uint32_t r[32];
-            tmem_ld32(tmem + lane_base + pr * 64 + 32 * half, r);
-            tmem_ld_wait();
-            uint32_t at[8];
+                for (int c = 0; c < 16; ++c) {
+                    const float a = (s <= 16 * Ib + c) ? t[c] : 0.f;
+                    if (c & 1) at[c >> 1] = pack2(__uint_as_float(at[c >> 1]), a);
+                    else at[c >> 1] = __float_as_uint(a);
+                }
+                uint4* dst = reinterpret_cast<uint4*>(p.t.AT + ch * 4096 + s * 64 + 16 * Ib);
+                dst[0] = make_uint4(at[0], at[1], at[2], at[3]);
+                dst[1] = make_uint4(at[4], at[5], at[6], at[7]);
+            } else {
 #pragma unroll
-            for (int c = 0; c < 16; ++c) {
-                const int t = 16 * I + c;
-                const float a = (s <= t) ? __uint_as_float(r[c]) : 0.f;
-                const float mt = (s < t) ? __uint_as_float(r[16 + c]) : 0.f;
-                const float m = bet[t] * mt;
-                Ms[t * kLDs + s] = m;
-                p.t.Mt[ch * 4096 + t * 64 + s] = __float2bfloat16(mt);
-                if (c & 1) at[c >> 1] = pack2(__uint_as_float(at[c >> 1]), a);
-                else at[c >> 1] = __float_as_uint(a);
+                for (int c = 0; c < 16; ++c) {
+                    const int tt = 16 * Ib + c;
+                    const float mt = (s < tt) ? t[c] : 0.f;
+                    Ms[tt * kLDs + s] = bet[tt] * mt;
+                    p.t.Mt[ch * 4096 + tt * 64 + s] = __float2bfloat16(mt);
+                }
             }
-            uint4* dst = reinterpret_cast<uint4*>(p.t.AT + ch * 4096 + s * 64 + 16 * I);
-            dst[0] = make_uint4(at[0], at[1], at[2], at[3]);
-            dst[1] = make_uint4(at[4], at[5], at[6], at[7]);
-        }
-        KDA_TICK(6);
-        // ---- Q = beta e^G k as an MN-major A operand (rows = token, 64-channel blocks)
-#pragma unroll
-        for (int i = 0; i < 64; ++i) {
-            float kv = 0.f;
-            if (i < len) kv = __bfloat162float(*reinterpret_cast<const __nv_bfloat16*>(ks + el_off(i, d, 8192)));
-            st_bf16(Qs, el_off(i, d, 8192), bet[i] * __expf(G[i]) * kv * kinv[i]);
         }
         __syncthreads();
-        KDA_TICK(7);
-        unit_lower_inverse128(Ms, Ts, tmp);
-        KDA_TICK(8);
-        // ---- T: bf16 K-major B operand, bf16 panel and fp32 copy
+        KDA_TICK(5);
+        unit_lower_inverse(Ms, Ts, tmp);
+        KDA_TICK(6);
+        // ---- T: bf16 K-major B operands (plain and column-scaled by beta) and the bf16 panel; one 16-byte chunk each
         {
-            const int i = tid >> 1, hf = tid & 1;
-#pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                const int c16 = 4 * hf + c;
-                const float* src = Ts + i * kLDs + 8 * c16;
-                uint4 u = make_uint4(pack2(src[0], src[1]), pack2(src[2], src[3]), pack2(src[4], src[5]), pack2(src[6], src[7]));
-                *reinterpret_cast<uint4*>(Tb + sw128_off(i, c16)) = u;
-                *reinterpret_cast<uint4*>(p.t.Tp + ch * 4096 + i * 64 + 8 * c16) = u;
-                const float* bb = bet + 8 * c16;
-                *reinterpret_cast<uint4*>(Tbb + sw128_off(i, c16)) =
-                    make_uint4(pack2(src[0] * bb[0], src[1] * bb[1]), pack2(src[2] * bb[2], src[3] * bb[3]),
-                               pack2(src[4] * bb[4], src[5] * bb[5]), pack2(src[6] * bb[6], src[7] * bb[7]));
-            }
+            const int i = tid >> 3, c16 = tid & 7;
+            const float* src = Ts + i * kLDs + 8 * c16;
+            const float* bb = bet + 8 * c16;
+            uint4 u = make_uint4(pack2(src[0], src[1]), pack2(src[2], src[3]), pack2(src[4], src[5]), pack2(src[6], src[7]));
+            *reinterpret_cast<uint4*>(Tb + sw128_off(i, c16)) = u;
+            *reinterpret_cast<uint4*>(p.t.Tp + ch * 4096 + i * 64 + 8 * c16) = u;
+            *reinterpret_cast<uint4*>(Tbb + sw128_off(i, c16)) =
+                make_uint4(pack2(src[0] * bb[0], src[1] * bb[1]), pack2(src[2] * bb[2], src[3] * bb[3]),
+                           pack2(src[4] * bb[4], src[5] * bb[5]), pack2(src[6] * bb[6], src[7] * bb[7]));
         }
         fence_async_smem();
         tc_fence_before();
@@ -371,52 +389,46 @@ __global__ void __launch_bounds__(128, 1)
             const uint32_t idesc = umma_idesc_bf16(128, 64, kMajorMN, kMajorK);
             const uint32_t b0 = smem_u32(Tb), b1 = smem_u32(Tbb);
 #pragma unroll
-            for (int k16 = 0; k16 < 4; ++k16)
+            for (int k16 = 0; k16 < 4; ++k16)     // U^T = v^T (T diag(beta))^T
                 umma_bf16_ss(tmem + 128, umma_smem_desc_sw128(smem_u32(vs) + k16 * 2048, 8192, 1024),
                              umma_smem_desc_sw128(b1 + k16 * 32, 16, 1024), idesc, k16 > 0);
 #pragma unroll
-            for (int k16 = 0; k16 < 4; ++k16)
+            for (int k16 = 0; k16 < 4; ++k16)     // W^T = Q^T T^T
                 umma_bf16_ss(tmem + 192, umma_smem_desc_sw128(smem_u32(Qs) + k16 * 2048, 8192, 1024),
                              umma_smem_desc_sw128(b0 + k16 * 32, 16, 1024), idesc, k16 > 0);
             umma_commit(&bar_uw);
         }
-        KDA_TICK(9);
+        KDA_TICK(7);
         ok = mbar_wait(&bar_uw, 0, p.t.status, 32);
         ok = __syncthreads_and(ok);
         tc_fence_after();
-        KDA_TICK(10);
+        KDA_TICK(8);
         if (ok) {
-            // lane = value channel (U^T) / key channel (W^T); one 128-byte row each
+            // lane = value channel (U^T) / key channel (W^T); warp groups split {U, W} x {tokens 0..31, 32..63}
+            const int which = I >> 1, hb = I & 1;
+            __nv_bfloat16* base = (which ? p.t.WT : p.t.UT) + ch * 8192 + (size_t)d * 64 + hb * 32;
+            uint32_t r[32];
+            tmem_ld32(tmem + lane_base + 128 + which * 64 + hb * 32, r);
+            tmem_ld_wait();
+            uint4* dst = reinterpret_cast<uint4*>(base);
 #pragma unroll
-            for (int which = 0; which < 2; ++which) {
-                __nv_bfloat16* base = (which ? p.t.WT : p.t.UT) + ch * 8192 + (size_t)tid * 64;
-#pragma unroll
-                for (int hb = 0; hb < 2; ++hb) {
-                    uint32_t r[32];
-                    tmem_ld32(tmem + lane_base + 128 + which * 64 + hb * 32, r);
-                    tmem_ld_wait();
-                    uint4* dst = reinterpret_cast<uint4*>(base + hb * 32);
-#pragma unroll
-                    for (int c = 0; c < 4; ++c)
-                        dst[c] = make_uint4(pack2(__uint_as_float(r[8 * c]), __uint_as_float(r[8 * c + 1])),
-                                            pack2(__uint_as_float(r[8 * c + 2]), __uint_as_float(r[8 * c + 3])),
-                                            pack2(__uint_as_float(r[8 * c + 4]), __uint_as_float(r[8 * c + 5])),
-                                            pack2(__uint_as_float(r[8 * c + 6]), __uint_as_float(r[8 * c + 7])));
-                }
-            }
+            for (int c = 0; c < 4; ++c)
+                dst[c] = make_uint4(pack2(__uint_as_float(r[8 * c]), __uint_as_float(r[8 * c + 1])),
+                                    pack2(__uint_as_float(r[8 * c + 2]), __uint_as_float(r[8 * c + 3])),
+                                    pack2(__uint_as_float(r[8 * c + 4]), __uint_as_float(r[8 * c + 5])),
+                                    pack2(__uint_as_float(r[8 * c + 6]), __uint_as_float(r[8 * c + 7])));
         }
     }
-    KDA_TICK(11);
+    KDA_TICK(9);
 #ifdef KDA_PHASE_TIMING
     if (threadIdx.x == 0 && blockIdx.y == 0 && (blockIdx.x == 0 || blockIdx.x == 100))
-        printf("intra_fwd blk %d: tma %lld | norms %lld | gload %lld | loop1 %lld | mma_am %lld | tmem->Ms %lld | Qloop %lld | inverse %lld | Twrite %lld | mma_uw %lld | epilogue %lld | total %lld\n",
+        printf("intra_fwd blk %d: g+tma %lld | norms %lld | panels %lld | mma_am %lld | readout %lld | inverse %lld | T+issue %lld | mma_uw %lld | epilogue %lld | total %lld\n",
                blockIdx.x, tick[1] - tick[0], tick[2] - tick[1], tick[3] - tick[2], tick[4] - tick[3], tick[5] - tick[4],
-               tick[6] - tick[5], tick[7] - tick[6], tick[8] - tick[7], tick[9] - tick[8], tick[10] - tick[9],
-               tick[11] - tick[10], tick[11] - tick[0]);
+               tick[6] - tick[5], tick[7] - tick[6], tick[8] - tick[7], tick[9] - tick[8], tick[9] - tick[0]);
 #endif
     tc_fence_before();
     __syncthreads();
-    if (warp == 0) tmem_dealloc(tmem, 256);
+    if (warp == 1) tmem_dealloc(tmem, 256);
 }
 
 }  // namespace tc
@@ -437,7 +449,7 @@ int tc_intra_forward(const simt::Ws& w, const tc::TcWs& t, const void* q, const 
     if (cudaFuncSetAttribute(tc_intra_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kIntraFwdSmem) != cudaSuccess)
         return KDA_ERR_CUDA;
     KDA_LAUNCH("tc_intra_fwd_kernel", st,
-               tc_intra_fwd_kernel<<<dim3(w.nslots, w.H), 128, kIntraFwdSmem, st>>>(mq, mk, mv, a));
+               tc_intra_fwd_kernel<<<dim3(w.nslots, w.H), kNT, kIntraFwdSmem, st>>>(mq, mk, mv, a));
     return launch_status();
 }
 
