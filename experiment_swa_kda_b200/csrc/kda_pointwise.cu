@@ -10,6 +10,12 @@
 namespace kda {
 namespace pw {
 
+// sigmoid for the bf16 I/O paths: fast intrinsics are far inside bf16 rounding; float32 I/O keeps expf and a true divide
+template <bool FAST>
+__device__ __forceinline__ float sigmoid_t(float x) {
+    return FAST ? __fdividef(1.0f, 1.0f + __expf(-x)) : 1.0f / (1.0f + expf(-x));
+}
+
 // =============================================================================================
 // gate / beta activations
 // =============================================================================================
@@ -361,7 +367,7 @@ __global__ void __launch_bounds__(256) conv_fwd_kernel(int B, int T, int C, int 
                 float z = 0.f;
 #pragma unroll
                 for (int j = 0; j < W; ++j) z += wv[j][e] * xin[tt + j][e];
-                out[e] = silu ? z * sigmoidf_(z) : z;
+                out[e] = silu ? z * sigmoid_t<BF16>(z) : z;
             }
             st_vec<VEC, BF16>(y, ((size_t)b * T + t) * C + c0, out);
         }
@@ -377,7 +383,7 @@ __global__ void __launch_bounds__(256) conv_fwd_kernel(int B, int T, int C, int 
     }
 }
 
-// Backward.  blockDim = (32 channel groups, 8 time tiles).  Each thread recomputes the
+// Backward.  blockDim = (16 channel groups, 16 time tiles).  Each thread recomputes the
 // pre-activations of its tile plus W-1 following tokens, emits dx for its tile and a
 // register partial of dweight; the 8 tiles of a block are summed in shared memory and
 // written as one partial per block, reduced in fixed order by conv_dw_reduce_kernel.
@@ -389,10 +395,10 @@ __global__ void __launch_bounds__(256) conv_bwd_kernel(int B, int T, int C, int 
                                                        const void* __restrict__ dy, const void* __restrict__ dfin,
                                                        void* __restrict__ dx, void* __restrict__ dcache,
                                                        float* __restrict__ dw_part) {
-    __shared__ float red[8][32][W * VEC];
+    __shared__ float red[16][16][W * VEC];
     const int ncg = C / VEC, ntile = (T + kConvBT - 1) / kConvBT;
-    const int cg = blockIdx.x * 32 + threadIdx.x;
-    const int tile = blockIdx.y * 8 + threadIdx.y;
+    const int cg = blockIdx.x * 16 + threadIdx.x;
+    const int tile = blockIdx.y * 16 + threadIdx.y;
     const int b = blockIdx.z;
     const bool active = cg < ncg && tile < ntile;
     float dwv[W][VEC];
@@ -421,7 +427,7 @@ __global__ void __launch_bounds__(256) conv_bwd_kernel(int B, int T, int C, int 
 #pragma unroll
                     for (int m = 0; m < W; ++m) z += wv[m][e] * xin[j + m][e];
                     if (silu) {
-                        const float sg = sigmoidf_(z);
+                        const float sg = sigmoid_t<BF16>(z);
                         gy[j][e] *= sg * (1.f + z * (1.f - sg));
                     }
                 }
@@ -471,7 +477,7 @@ __global__ void __launch_bounds__(256) conv_bwd_kernel(int B, int T, int C, int 
 #pragma unroll
                     for (int j = 0; j < W; ++j) z += wv[j][e] * win[j][e];
                     if (silu) {
-                        const float sg = sigmoidf_(z);
+                        const float sg = sigmoid_t<BF16>(z);
                         g[e] *= sg * (1.f + z * (1.f - sg));
                     }
                     dzw[W - 1][e] = g[e];
@@ -524,7 +530,7 @@ __global__ void __launch_bounds__(256) conv_bwd_kernel(int B, int T, int C, int 
 #pragma unroll
                     for (int j = 0; j < W; ++j) z += wv[j][e] * w2[j][e];
                     if (silu) {
-                        const float sg = sigmoidf_(z);
+                        const float sg = sigmoid_t<BF16>(z);
                         g[e] *= sg * (1.f + z * (1.f - sg));
                     }
 #pragma unroll
@@ -560,7 +566,7 @@ __global__ void __launch_bounds__(256) conv_bwd_kernel(int B, int T, int C, int 
             for (int e = 0; e < VEC; ++e) {
                 float a = 0.f;
 #pragma unroll
-                for (int r = 0; r < 8; ++r) a += red[r][threadIdx.x][j * VEC + e];
+                for (int r = 0; r < 16; ++r) a += red[r][threadIdx.x][j * VEC + e];
                 dw_part[(pblk * C + cg * VEC + e) * W + j] = a;
             }
     }
@@ -647,12 +653,12 @@ __global__ void __launch_bounds__(256) rmsnorm_fwd_kernel(long long rows, int D,
                 const float4 ww = *reinterpret_cast<const float4*>(w + d);
                 const float wa[4] = {ww.x, ww.y, ww.z, ww.w};
 #pragma unroll
-                for (int e = 0; e < 4; ++e) out[e] = a[e] * inv * wa[e] * sigmoidf_(gt[e]);
+                for (int e = 0; e < 4; ++e) out[e] = a[e] * inv * wa[e] * sigmoid_t<BF16>(gt[e]);
                 st4<BF16>(y, base + d, out);
             }
         } else {
             for (int d = lane; d < D; d += 32)
-                st_io(y, base + d, BF16, ld_io(x, base + d, BF16) * inv * w[d] * sigmoidf_(ld_io(gate, base + d, BF16)));
+                st_io(y, base + d, BF16, ld_io(x, base + d, BF16) * inv * w[d] * sigmoid_t<BF16>(ld_io(gate, base + d, BF16)));
         }
     }
 }
@@ -686,11 +692,11 @@ __global__ void __launch_bounds__(256) rmsnorm_bwd_kernel(long long rows, int D,
                 const float4 ww = *reinterpret_cast<const float4*>(w + d);
                 const float wa[4] = {ww.x, ww.y, ww.z, ww.w};
 #pragma unroll
-                for (int e = 0; e < 4; ++e) dot += gy[e] * sigmoidf_(gt[e]) * wa[e] * a[e] * inv;
+                for (int e = 0; e < 4; ++e) dot += gy[e] * sigmoid_t<BF16>(gt[e]) * wa[e] * a[e] * inv;
             }
         } else {
             for (int d = lane; d < D; d += 32)
-                dot += ld_io(dy, base + d, BF16) * sigmoidf_(ld_io(gate, base + d, BF16)) * w[d] * ld_io(x, base + d, BF16) * inv;
+                dot += ld_io(dy, base + d, BF16) * sigmoid_t<BF16>(ld_io(gate, base + d, BF16)) * w[d] * ld_io(x, base + d, BF16) * inv;
         }
         dot = warp_sum(dot) / (float)D;
         if (VEC4) {
@@ -703,7 +709,7 @@ __global__ void __launch_bounds__(256) rmsnorm_bwd_kernel(long long rows, int D,
                 const float wa[4] = {ww.x, ww.y, ww.z, ww.w};
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
-                    const float n = a[e] * inv, s = sigmoidf_(gt[e]);
+                    const float n = a[e] * inv, s = sigmoid_t<BF16>(gt[e]);
                     const float du = gy[e] * s;
                     og[e] = gy[e] * n * wa[e] * s * (1.f - s);
                     ox[e] = inv * (du * wa[e] - n * dot);
@@ -714,7 +720,7 @@ __global__ void __launch_bounds__(256) rmsnorm_bwd_kernel(long long rows, int D,
             }
         } else {
             for (int d = lane; d < D; d += 32) {
-                const float n = ld_io(x, base + d, BF16) * inv, s = sigmoidf_(ld_io(gate, base + d, BF16));
+                const float n = ld_io(x, base + d, BF16) * inv, s = sigmoid_t<BF16>(ld_io(gate, base + d, BF16));
                 const float gyv = ld_io(dy, base + d, BF16);
                 const float du = gyv * s;
                 st_io(dgate, base + d, BF16, gyv * n * w[d] * s * (1.f - s));
@@ -841,14 +847,14 @@ int conv_fwd_w(int B, int T, int C, int bf16, int silu, const void* x, const voi
 }
 
 inline void conv_bwd_grid(int B, int T, int C, int vec, dim3& grid) {
-    grid = dim3(ceil_div(C / vec, 32), ceil_div(ceil_div(T, pw::kConvBT), 8), B);
+    grid = dim3(ceil_div(C / vec, 16), ceil_div(ceil_div(T, pw::kConvBT), 16), B);
 }
 
 template <int W>
 int conv_bwd_w(int B, int T, int C, int bf16, int silu, const void* x, const void* w, const void* cache, const void* dy,
                const void* dfin, void* dx, void* dcache, float* dwgt, float* part, cudaStream_t st) {
     const bool al16 = ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(dy) | reinterpret_cast<uintptr_t>(dx)) % 16) == 0;
-    dim3 grid, block(32, 8);
+    dim3 grid, block(16, 16);
     // the vector path keeps W*VEC partials per thread in shared memory; wide windows use the scalar path
     constexpr bool kVecOk = W <= 4;
     if (bf16) {
@@ -907,7 +913,7 @@ extern "C" int kda_conv_fwd(int32_t batch, int32_t seq_len, int32_t channels, in
 }
 
 extern "C" size_t kda_conv_bwd_scratch_bytes(int32_t batch, int32_t seq_len, int32_t channels, int32_t width) {
-    const size_t nblk = (size_t)ceil_div(ceil_div(seq_len > 0 ? seq_len : 1, pw::kConvBT), 8) * (batch > 0 ? batch : 1);
+    const size_t nblk = (size_t)ceil_div(ceil_div(seq_len > 0 ? seq_len : 1, pw::kConvBT), 16) * (batch > 0 ? batch : 1);
     return align_up(nblk * channels * width * sizeof(float), 256);
 }
 
