@@ -226,6 +226,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-graph", action="store_true", help="launch every step eagerly instead of replaying a CUDA graph")
     ap.add_argument("--workload", default="chain", choices=["chain", "varlen", "decode"],
                     help="chain = config 1 (default, the driver's line); varlen = config 3; decode = config 4")
     args = ap.parse_args()
@@ -256,9 +257,26 @@ def main():
         torch.cuda.synchronize(dev)
 
     # ---- device-resident arm -----------------------------------------------------------------
+    # The step (every kernel of the forward and backward chain, launched through the public API) is captured
+    # once into a CUDA graph and replayed: at this size the chain is ~30 short kernels and eager launching
+    # leaves the GPU idle between them.
     chain.upload()
     for _ in range(max(args.warmup, 3)):
         chain.step()
+    barrier()
+    graph = None
+    l0 = _lib.launch_count()
+    if not args.no_graph:
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            outs = chain.step()
+        run_step = graph.replay
+    else:
+        outs = None
+        run_step = chain.step
+    launches_per_step = _lib.launch_count() - l0
+    for _ in range(3):
+        run_step()
     barrier()
     sampler = ClockSampler(local)
     sampler.start()
@@ -268,10 +286,10 @@ def main():
     for a, b in ev:
         flush.zero_()
         a.record()
-        chain.step()
+        run_step()
         b.record()
     barrier()
-    launches = _lib.launch_count() - l0
+    launches = (_lib.launch_count() - l0) if graph is None else launches_per_step * args.steps
     clocks = sampler.stop()
     ms = sum(a.elapsed_time(b) for a, b in ev)
     t = torch.tensor([ms], dtype=torch.float64, device=dev)
@@ -282,17 +300,25 @@ def main():
     value = chain.tokens() * world / (ms_step * 1e-3)
 
     # ---- end-to-end arm: pinned host inputs -> device -> chain -> pinned host results ----------
+    def e2e_step():
+        if graph is None:
+            chain.upload()
+            return chain.download(*chain.step())
+        with torch.no_grad():
+            for n, hbuf in chain.host.items():
+                chain.x[n].copy_(hbuf, non_blocking=True)       # graph inputs live at fixed addresses
+        graph.replay()
+        return chain.download(*outs)
+
     d2h = 0
     for _ in range(3):
-        chain.upload()
-        d2h = chain.download(*chain.step())
+        d2h = e2e_step()
     barrier()
     ev2 = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
     for a, b in ev2:
         flush.zero_()
         a.record()
-        chain.upload()
-        d2h = chain.download(*chain.step())
+        d2h = e2e_step()
         b.record()
     barrier()
     t2 = torch.tensor([sum(a.elapsed_time(b) for a, b in ev2)], dtype=torch.float64, device=dev)
@@ -355,7 +381,8 @@ def main():
             "config": {"workload": "config1 chain: conv4+SiLU(q,k,v) -> chunked KDA fwd+bwd -> gated RMSNorm fwd+bwd; "
                                    "B2 T4096 H3 Dk=Dv=128 chunk64, bf16 I/O, fp32 state/accumulation",
                        "tokens_per_step_per_gpu": chain.tokens(), "l2": "flushed between steps (256 MiB write)",
-                       "lane": "tc scan (tcgen05) + fp32 cuda-core intra-chunk", "sharding": "replicated per-GPU batches, no collective"},
+                       "lane": "tcgen05 (intra-chunk products and state scans)",
+                       "launch": "eager" if args.no_graph else "CUDA graph replay of the captured step", "sharding": "replicated per-GPU batches, no collective"},
             "tflops_algorithmic": flops["_fwd_bwd_total"] * nch * world / (ms_step * 1e-3) / 1e12,
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": chain.h2d_bytes(), "d2h_bytes_per_step": d2h},
             "gpu_launches": int(launches), "clocks": clocks, "roofline": roof, "kernels": kern,
