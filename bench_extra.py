@@ -42,7 +42,7 @@ def run_varlen(args, rank, world, local, dist):
     from experiment_swa_kda_b200 import _lib
     from bench import kda_kernel_flops
     dev = torch.device(f"cuda:{local}")
-    total, H, D = 8 * 8192, 16, 128
+    total, H, D = args.tokens, 16, 128
     Hl = H // world                                     # heads of this rank
     lens = _lengths(total, 0)
     cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32, device=dev)
