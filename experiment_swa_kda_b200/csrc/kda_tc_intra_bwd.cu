@@ -87,7 +87,8 @@ constexpr int kR5 = 114688;    // 48 KB  q | k | v tiles
 constexpr int kR6 = 163840;    //  8 KB  T
 constexpr int kR7 = 172032;    // 16 KB  dW^T                      -> later: [dA_I ; beta dM_I] tiles (4 x 4 KB)
 constexpr int kR8 = 188416;    // 16 KB  Q' = e^G k
-constexpr int kSmall = 204800; // floats: gsum[4][128] cref[4][128] part[4][128] tot[4][128] dots[64][8] rowv[3][64]
+constexpr int kRM = 204800;    //  8 KB  M~ (before beta), row-major [target][source]
+constexpr int kSmall = 212992; // floats: gsum[4][128] cref[4][128] part[4][128] tot[4][128] dots[64][8] rowv[3][64]
 constexpr int kIntraBwdSmem = kSmall + (4 * 4 * 128 + 64 * 8 + 3 * 64) * 4 + 1024;
 
 __global__ void __launch_bounds__(512, 1)
@@ -95,7 +96,8 @@ __global__ void __launch_bounds__(512, 1)
                         const __grid_constant__ CUtensorMap mv, const __grid_constant__ CUtensorMap mdO,
                         const __grid_constant__ CUtensorMap mT, const __grid_constant__ CUtensorMap mH,
                         const __grid_constant__ CUtensorMap mdH, const __grid_constant__ CUtensorMap mZT,
-                        const __grid_constant__ CUtensorMap mdZT, IntraBwdArgs p) {
+                        const __grid_constant__ CUtensorMap mdZT, const __grid_constant__ CUtensorMap mMt,
+                        IntraBwdArgs p) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* sm = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     uint8_t* Hs = sm + kR1;
@@ -109,6 +111,7 @@ __global__ void __launch_bounds__(512, 1)
     uint8_t* Ts = sm + kR6;
     uint8_t* dWs = sm + kR7;
     uint8_t* Qp = sm + kR8;
+    uint8_t* Mts = sm + kRM;
     float* gsum = reinterpret_cast<float*>(sm + kSmall);   // [4][128] block sums of g
     float* cref = gsum + 512;                              // [4][128] G at the first row of each block
     float* part = cref + 512;                              // [4][128] scratch partials
@@ -136,7 +139,7 @@ __global__ void __launch_bounds__(512, 1)
         mbar_init(&bar_in, 1);
         mbar_init(&bar_mma, 1);
         mbar_fence_init();
-        mbar_expect_tx(&bar_in, 65536 + 16384 * 3 + 49152 + 8192);
+        mbar_expect_tx(&bar_in, 65536 + 16384 * 3 + 49152 + 8192 + 8192);
         for (int mb = 0; mb < 2; ++mb) {
             tma_load_2d(Hs + mb * 16384, &mH, &bar_in, mb * 64, ch * 128);
             tma_load_2d(dHs + mb * 16384, &mdH, &bar_in, mb * 64, ch * 128);
@@ -148,6 +151,7 @@ __global__ void __launch_bounds__(512, 1)
         tma_load_2d(ZTs, &mZT, &bar_in, 0, ch * 128);
         tma_load_2d(dZTs, &mdZT, &bar_in, 0, ch * 128);
         tma_load_2d(Ts, &mT, &bar_in, 0, ch * 64);
+        tma_load_2d(Mts, &mMt, &bar_in, 0, ch * 64);
     }
     if (warp == 0) tmem_alloc(&tmem_slot, 512);
 
@@ -318,31 +322,29 @@ __global__ void __launch_bounds__(512, 1)
     KDA_TICKB(6);
     // ================================================================ phase 3: X, Y, dM
     // M = 64 accumulators keep row (16*w + l) in lane l < 16 of warp w < 4.  tcgen05.ld is warp-collective, so all 32
-    // lanes of those warps run the loads; lanes >= 16 mirror a row and never store.
-    const bool rowwarp = warp < 4;
+    // lanes of those warps run the loads; lanes >= 16 mirror a row and never store.  All four warp groups see the same lanes, so each takes 16 of the 64 columns.
     const bool rowown = lane < 16;
     const int row = 16 * (warp & 3) + (lane & 15);
     uint8_t* XT = sm + kR2;           // [64 rows s][64 i]   K-major B
     uint8_t* Yt = sm + kR2 + 8192;    // [64 rows j][64 s]   K-major A
     float dbeta_acc = 0.f;
-    if (rowwarp) {
+    float* dbp = dots;                // [4][64] partial dbeta per column group (dots is not in use yet)
+    {
+        // every warp group takes 16 of the 64 columns of row `row`
         const float bs = rowv[128 + row];
+        float t[16];
+        tmem_ld16(tmem + lane_base + cDf + 16 * I, t);
+        uint32_t pkd[8];
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-            float t[16];
-            tmem_ld16(tmem + lane_base + cDf + 16 * c, t);
-            uint32_t pkd[8];
-#pragma unroll
-            for (int j = 0; j < 16; ++j) {
-                const int i = 16 * c + j;
-                dbeta_acc += ld16(Ts, sw128_off(i, row >> 3) + (row & 7) * 2) * t[j];     // T[i][s] * Xraw[i][s]
-                if (j & 1) pkd[j >> 1] = pk2(__uint_as_float(pkd[j >> 1]), bs * t[j]);
-                else pkd[j >> 1] = __float_as_uint(bs * t[j]);
-            }
-            if (rowown) {
-                *reinterpret_cast<uint4*>(XT + sw128_off(row, 2 * c)) = make_uint4(pkd[0], pkd[1], pkd[2], pkd[3]);
-                *reinterpret_cast<uint4*>(XT + sw128_off(row, 2 * c + 1)) = make_uint4(pkd[4], pkd[5], pkd[6], pkd[7]);
-            }
+        for (int j = 0; j < 16; ++j) {
+            const int i = 16 * I + j;
+            dbeta_acc += ld16(Ts, sw128_off(i, row >> 3) + (row & 7) * 2) * t[j];     // T[i][s] * Xraw[i][s]
+            if (j & 1) pkd[j >> 1] = pk2(__uint_as_float(pkd[j >> 1]), bs * t[j]);
+            else pkd[j >> 1] = __float_as_uint(bs * t[j]);
+        }
+        if (rowown) {
+            *reinterpret_cast<uint4*>(XT + sw128_off(row, 2 * I)) = make_uint4(pkd[0], pkd[1], pkd[2], pkd[3]);
+            *reinterpret_cast<uint4*>(XT + sw128_off(row, 2 * I + 1)) = make_uint4(pkd[4], pkd[5], pkd[6], pkd[7]);
         }
     }
     {   // dQ contributions (all threads)
@@ -371,17 +373,14 @@ __global__ void __launch_bounds__(512, 1)
     ok = ok && mbar_wait(&bar_mma, 0, p.status, 43);
     ok = __syncthreads_and(ok);
     tc_fence_after();
-    if (rowwarp) {
-#pragma unroll
-        for (int c = 0; c < 4; ++c) {
-            float t[16];
-            tmem_ld16(tmem + lane_base + cDb + 16 * c, t);
-            if (rowown) {
-                *reinterpret_cast<uint4*>(Yt + sw128_off(row, 2 * c)) =
-                    make_uint4(pk2(t[0], t[1]), pk2(t[2], t[3]), pk2(t[4], t[5]), pk2(t[6], t[7]));
-                *reinterpret_cast<uint4*>(Yt + sw128_off(row, 2 * c + 1)) =
-                    make_uint4(pk2(t[8], t[9]), pk2(t[10], t[11]), pk2(t[12], t[13]), pk2(t[14], t[15]));
-            }
+    {
+        float t[16];
+        tmem_ld16(tmem + lane_base + cDb + 16 * I, t);
+        if (rowown) {
+            *reinterpret_cast<uint4*>(Yt + sw128_off(row, 2 * I)) =
+                make_uint4(pk2(t[0], t[1]), pk2(t[2], t[3]), pk2(t[4], t[5]), pk2(t[6], t[7]));
+            *reinterpret_cast<uint4*>(Yt + sw128_off(row, 2 * I + 1)) =
+                make_uint4(pk2(t[8], t[9]), pk2(t[10], t[11]), pk2(t[12], t[13]), pk2(t[14], t[15]));
         }
     }
     fence_async_smem();
@@ -406,46 +405,43 @@ __global__ void __launch_bounds__(512, 1)
     uint8_t* Sk = sm + kR1;           // k~_I panels: [I][2 blocks][64 rows s x 128 B]     MN-major A
     uint8_t* Xk = sm + kR3;           // target stacks: [I][2 blocks][32 rows x 128 B]     MN-major A
     uint8_t* DAt = sm + kR7;          // [I][32 rows: 16 dA rows, 16 beta*dM rows][64 s]   K-major / MN-major B
-    if (rowwarp) {
-        // row j of dM = -stril(Y T^T) and of dA = tril(dO Z^T); dbeta gets sum_l dM[j][l] M~[j][l]
+    {
+        // row j of dM = -stril(Y T^T) and of dA = tril(dO Z^T), 16 source columns per warp group;
+        // dbeta gets sum_l dM[j][l] M~[j][l]
         const int j = row, Ib = j >> 4, rr = j & 15;
         const float bj = rowv[128 + j];
-        const __nv_bfloat16* mt = p.Mt + (size_t)ch * 4096 + j * 64;
+        float tm[16], ta[16], mv16[16];
+        tmem_ld16(tmem + lane_base + cDc + 16 * I, tm);
+        tmem_ld16(tmem + lane_base + cDg + 16 * I, ta);
+        {
+            const uint4 m0 = *reinterpret_cast<const uint4*>(Mts + sw128_off(j, 2 * I));
+            const uint4 m1 = *reinterpret_cast<const uint4*>(Mts + sw128_off(j, 2 * I + 1));
+            const __nv_bfloat162* hh = reinterpret_cast<const __nv_bfloat162*>(&m0);
+            const __nv_bfloat162* hg = reinterpret_cast<const __nv_bfloat162*>(&m1);
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-            float tm[16], ta[16];
-            tmem_ld16(tmem + lane_base + cDc + 16 * c, tm);
-            tmem_ld16(tmem + lane_base + cDg + 16 * c, ta);
-            uint4 m0 = *reinterpret_cast<const uint4*>(mt + 16 * c), m1 = *reinterpret_cast<const uint4*>(mt + 16 * c + 8);
-            float mv16[16];
-            {
-                const __nv_bfloat162* hh = reinterpret_cast<const __nv_bfloat162*>(&m0);
-                const __nv_bfloat162* hg = reinterpret_cast<const __nv_bfloat162*>(&m1);
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    float2 f0 = __bfloat1622float2(hh[e]), f1 = __bfloat1622float2(hg[e]);
-                    mv16[2 * e] = f0.x; mv16[2 * e + 1] = f0.y; mv16[8 + 2 * e] = f1.x; mv16[8 + 2 * e + 1] = f1.y;
-                }
-            }
-            uint32_t pa[8], pm[8];
-#pragma unroll
-            for (int e = 0; e < 16; ++e) {
-                const int l = 16 * c + e;
-                const float dm = (l < j) ? -tm[e] : 0.f;
-                const float da = (l <= j) ? ta[e] : 0.f;
-                dbeta_acc += dm * mv16[e];
-                if (e & 1) { pa[e >> 1] = pk2(__uint_as_float(pa[e >> 1]), da); pm[e >> 1] = pk2(__uint_as_float(pm[e >> 1]), bj * dm); }
-                else { pa[e >> 1] = __float_as_uint(da); pm[e >> 1] = __float_as_uint(bj * dm); }
-            }
-            uint8_t* tile = DAt + Ib * 4096;
-            if (rowown) {
-                *reinterpret_cast<uint4*>(tile + sw128_off(rr, 2 * c)) = make_uint4(pa[0], pa[1], pa[2], pa[3]);
-                *reinterpret_cast<uint4*>(tile + sw128_off(rr, 2 * c + 1)) = make_uint4(pa[4], pa[5], pa[6], pa[7]);
-                *reinterpret_cast<uint4*>(tile + sw128_off(16 + rr, 2 * c)) = make_uint4(pm[0], pm[1], pm[2], pm[3]);
-                *reinterpret_cast<uint4*>(tile + sw128_off(16 + rr, 2 * c + 1)) = make_uint4(pm[4], pm[5], pm[6], pm[7]);
+            for (int e = 0; e < 4; ++e) {
+                float2 f0 = __bfloat1622float2(hh[e]), f1 = __bfloat1622float2(hg[e]);
+                mv16[2 * e] = f0.x; mv16[2 * e + 1] = f0.y; mv16[8 + 2 * e] = f1.x; mv16[8 + 2 * e + 1] = f1.y;
             }
         }
-        if (rowown && j < len) st_io(p.dbeta, (size_t)(tok0 + j) * H + h, p.gbf16, dbeta_acc);
+        uint32_t pa[8], pm[8];
+#pragma unroll
+        for (int e = 0; e < 16; ++e) {
+            const int l = 16 * I + e;
+            const float dm = (l < j) ? -tm[e] : 0.f;
+            const float da = (l <= j) ? ta[e] : 0.f;
+            dbeta_acc += dm * mv16[e];
+            if (e & 1) { pa[e >> 1] = pk2(__uint_as_float(pa[e >> 1]), da); pm[e >> 1] = pk2(__uint_as_float(pm[e >> 1]), bj * dm); }
+            else { pa[e >> 1] = __float_as_uint(da); pm[e >> 1] = __float_as_uint(bj * dm); }
+        }
+        if (rowown) {
+            uint8_t* tile = DAt + Ib * 4096;
+            *reinterpret_cast<uint4*>(tile + sw128_off(rr, 2 * I)) = make_uint4(pa[0], pa[1], pa[2], pa[3]);
+            *reinterpret_cast<uint4*>(tile + sw128_off(rr, 2 * I + 1)) = make_uint4(pa[4], pa[5], pa[6], pa[7]);
+            *reinterpret_cast<uint4*>(tile + sw128_off(16 + rr, 2 * I)) = make_uint4(pm[0], pm[1], pm[2], pm[3]);
+            *reinterpret_cast<uint4*>(tile + sw128_off(16 + rr, 2 * I + 1)) = make_uint4(pm[4], pm[5], pm[6], pm[7]);
+            dbp[I * 64 + j] = dbeta_acc;
+        }
     }
     {
         const float c0 = cref[d], c1 = cref[128 + d], c2 = cref[256 + d], c3 = cref[384 + d];
@@ -475,6 +471,8 @@ __global__ void __launch_bounds__(512, 1)
     fence_async_smem();
     tc_fence_before();
     __syncthreads();
+    if (tid < 64 && tid < len)
+        st_io(p.dbeta, (size_t)(tok0 + tid) * H + h, p.gbf16, dbp[tid] + dbp[64 + tid] + dbp[128 + tid] + dbp[192 + tid]);
     // accumulator columns of the pull-back: RP_I (32 columns each) and CP_I (64 columns each)
     constexpr uint32_t cRP = 192;
     const uint32_t cCP[4] = {0, 64, 128, 320};
@@ -611,7 +609,7 @@ int tc_intra_backward(const simt::Ws& w, const tc::TcWs& t, int tokens, const vo
     using namespace tc;
     const uint64_t nch = (uint64_t)w.nslots * w.H;
     const uint64_t cols = (uint64_t)w.H * 128;
-    CUtensorMap mq, mk, mv, mdO, mT, mH, mdH, mZT, mdZT;
+    CUtensorMap mq, mk, mv, mdO, mT, mH, mdH, mZT, mdZT, mMt;
     int rc = 0;
     rc |= make_map_bf16(&mq, q, (uint64_t)tokens, cols, 64, 64);
     rc |= make_map_bf16(&mk, k, (uint64_t)tokens, cols, 64, 64);
@@ -622,6 +620,7 @@ int tc_intra_backward(const simt::Ws& w, const tc::TcWs& t, int tokens, const vo
     rc |= make_map_bf16(&mdH, t.dHp, nch * 128, 128, 64, 128);
     rc |= make_map_bf16(&mZT, t.ZT, nch * 128, 64, 64, 128);
     rc |= make_map_bf16(&mdZT, t.dZT, nch * 128, 64, 64, 128);
+    rc |= make_map_bf16(&mMt, t.Mt, nch * 64, 64, 64, 64);
     if (rc) return KDA_ERR_CUDA;
     IntraBwdArgs a;
     a.chunk_tok0 = w.chunk_tok0; a.chunk_len = w.chunk_len;
@@ -633,7 +632,7 @@ int tc_intra_backward(const simt::Ws& w, const tc::TcWs& t, int tokens, const vo
     if (cudaFuncSetAttribute(tc_intra_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kIntraBwdSmem) != cudaSuccess)
         return launch_status();
     KDA_LAUNCH("tc_intra_bwd_kernel", st,
-               tc_intra_bwd_kernel<<<dim3(w.nslots, w.H), 512, kIntraBwdSmem, st>>>(mq, mk, mv, mdO, mT, mH, mdH, mZT, mdZT, a));
+               tc_intra_bwd_kernel<<<dim3(w.nslots, w.H), 512, kIntraBwdSmem, st>>>(mq, mk, mv, mdO, mT, mH, mdH, mZT, mdZT, mMt, a));
     return launch_status();
 }
 
