@@ -72,3 +72,19 @@ def test_host_validation_matches_reference_contract():
     prov = m.kda_backend_provenance()
     assert prov["components"]["chunk_forward"]["torch_operator"] == "nanochat_kda::chunk_forward"
     assert all(c["owner"] == "project" for c in prov["components"].values())
+
+
+def test_nanochat_kda_namespace_registers_the_reference_schemas():
+    from experiment_swa_kda_b200 import nanochat_ops
+    nanochat_ops.register()
+    nanochat_ops.register()        # idempotent
+    for name in ("chunk_forward", "chunk_backward", "recurrent_decode", "causal_convolution_forward",
+                 "causal_convolution_backward", "rmsnorm_gate_forward", "rmsnorm_gate_backward"):
+        op = getattr(torch.ops.nanochat_kda, name)
+        assert op is not None
+    schema = str(torch.ops.nanochat_kda.chunk_forward.default._schema)
+    assert "Tensor? initial_state" in schema and "float lower_bound, float scale" in schema
+    # no CPU kernel is registered: a CPU call fails closed instead of falling back
+    x = torch.randn(1, 4, 8)
+    with pytest.raises((RuntimeError, NotImplementedError)):
+        torch.ops.nanochat_kda.causal_convolution_forward(x, torch.randn(8, 4), None, False)
