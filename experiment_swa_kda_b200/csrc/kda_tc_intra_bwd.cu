@@ -122,7 +122,7 @@ __global__ void __launch_bounds__(512, 1)
     __shared__ uint32_t tmem_slot;
 
 #ifdef KDA_PHASE_TIMING
-    long long tick[16];
+    long long tick[20];
 #endif
     const int slot = blockIdx.x, h = blockIdx.y, H = p.H;
     const int len = p.chunk_len[slot];
@@ -443,6 +443,7 @@ __global__ void __launch_bounds__(512, 1)
             dbp[I * 64 + j] = dbeta_acc;
         }
     }
+    KDA_TICKB(13);
     {
         const float c0 = cref[d], c1 = cref[128 + d], c2 = cref[256 + d], c3 = cref[384 + d];
         const float cI = I == 0 ? c0 : (I == 1 ? c1 : (I == 2 ? c2 : c3));
@@ -534,6 +535,7 @@ __global__ void __launch_bounds__(512, 1)
             }
         }
     }
+    KDA_TICKB(14);
     // chunk-end term and reverse cumulative sum of dG over the 64 rows of this channel
     float suffix = 0.f;
     {
@@ -552,6 +554,7 @@ __global__ void __launch_bounds__(512, 1)
         for (int Ib = 3; Ib > 0; --Ib)
             if (Ib > I) suffix += tot[Ib * 128 + d];
     }
+    KDA_TICKB(15);
     // L2-normalisation VJP needs per-row dots over the channels: unit k is kn, unit q is qn / scale
     const float inv_scale = p.scale != 0.f ? 1.0f / p.scale : 0.f;
 #pragma unroll
@@ -564,7 +567,9 @@ __global__ void __launch_bounds__(512, 1)
             dots[i * 8 + (warp & 3) * 2 + 1] = pk;
         }
     }
+    KDA_TICKB(16);
     __syncthreads();
+    KDA_TICKB(17);
     if (ok) {
         float run = suffix;
 #pragma unroll
@@ -595,6 +600,10 @@ __global__ void __launch_bounds__(512, 1)
         printf("intra_bwd blk %d: setup+g %lld | tma wait %lld | issue1+dD/Q' %lld | mma1 wait %lld | readout2a %lld | mma2 wait %lld | X^T %lld | Y wait %lld | Ywrite+dM wait %lld | p4 operands %lld | mma pb wait %lld | assemble %lld | total %lld\n",
                blockIdx.x, tick[1] - tick[0], tick[2] - tick[1], tick[3] - tick[2], tick[4] - tick[3], tick[5] - tick[4], tick[6] - tick[5],
                tick[7] - tick[6], tick[8] - tick[7], tick[9] - tick[8], tick[10] - tick[9], tick[11] - tick[10], tick[12] - tick[11], tick[12] - tick[0]);
+    if (threadIdx.x == 0 && blockIdx.y == 0 && blockIdx.x == 100)
+        printf("   detail: p4 rows %lld | p4 panels %lld || RP/CP reads %lld | sums+sync %lld | shuffles %lld | sync %lld | stores %lld\n",
+               tick[13] - tick[9], tick[10] - tick[13], tick[14] - tick[11], tick[15] - tick[14], tick[16] - tick[15],
+               tick[17] - tick[16], tick[12] - tick[17]);
 #endif
     tc_fence_before();
     __syncthreads();

@@ -53,7 +53,12 @@ def test_chunk_ops_forward_backward_match_oracle(T, D):
     want = torch.autograd.grad((eo, es), e, (co.float(), cs))
     assert O.rel_l2(o.float(), eo) <= 1e-2 and O.rel_l2(s, es) <= 1e-2
     for name, a, b in zip(("q", "k", "v", "raw_gate", "beta_logits", "A_log", "dt_bias", "initial_state"), got, want):
-        assert O.rel_l2(a.float(), b) <= 1e-2, name
+        if name in ("A_log", "dt_bias"):
+            # parameter gradients are sums over all tokens of bf16-level terms that largely cancel: the reference's own
+            # element-wise bar for them (configs/research/kda_cuda_ownership.toml:44-47) is the meaningful one
+            torch.testing.assert_close(a.float().cpu(), b, atol=2e-2, rtol=2e-2)
+        else:
+            assert O.rel_l2(a.float(), b) <= 1e-2, name
 
 
 def test_decode_conv_and_norm_ops():
