@@ -47,10 +47,14 @@ def kda_kernel_flops(K, V, C=64):
     fwd_total = sum(fwd.values())
     bwd = {"scan_bwd_kernel": 3 * C * K * V + tri * V, "pullback_kernel": 2 * (tri + stri) * K}
     bwd["bwd_local_kernel"] = 2 * fwd_total - sum(bwd.values())
-    tcl = {   # tensor-core lane kernels (same algorithmic work, different kernel boundaries)
+    tcl = {   # tensor-core lane kernels: the multiply-adds each one actually performs (different kernel boundaries and
+        # a regrouped recurrence, so the parts do not add up to the reference-algorithm total below)
         "tc_intra_fwd_kernel": fwd["build_am_kernel"] + fwd["uw_kernel"],
-        "tc_scan_fwd_kernel": fwd["scan_fwd_kernel"] + fwd["out_kernel"],
-        "tc_scan_bwd_kernel": bwd["scan_bwd_kernel"],
+        "tc_transition_kernel": C * K * K + C * C * K,
+        "tc_affine_scan_fwd_kernel": K * K * V + C * K * V,
+        "tc_chunk_out_kernel": 2 * C * K * V + C * C * V,
+        "tc_affine_scan_bwd_kernel": K * K * V + C * K * V,
+        "tc_chunk_dz_kernel": C * C * V + C * K * V,
         "tc_intra_bwd_kernel": bwd["bwd_local_kernel"] + bwd["pullback_kernel"],
     }
     out = {k: 2.0 * v for k, v in {**fwd, **bwd, **tcl}.items()}     # FLOP = 2 * MAC
@@ -425,7 +429,7 @@ def main():
             "config": {"workload": "config1 chain: conv4+SiLU(q,k,v) -> chunked KDA fwd+bwd -> gated RMSNorm fwd+bwd; "
                                    "B2 T4096 H3 Dk=Dv=128 chunk64, bf16 I/O, fp32 state/accumulation",
                        "tokens_per_step_per_gpu": chain.tokens(), "l2": "flushed between steps (256 MiB write)",
-                       "lane": "tcgen05 (intra-chunk products and state scans)",
+                       "lane": "tcgen05 (intra-chunk products, chunk transitions and affine state scans)",
                        "launch": "eager" if args.no_graph else "CUDA graph replay of the captured step", "sharding": "replicated per-GPU batches, no collective"},
             "tflops_algorithmic": flops["_fwd_bwd_total"] * nch * world / (ms_step * 1e-3) / 1e12,
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": chain.h2d_bytes(), "d2h_bytes_per_step": d2h,

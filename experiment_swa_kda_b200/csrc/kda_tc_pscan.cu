@@ -1,0 +1,669 @@
+// Tensor-core lane (K = V = 128): the state recurrences as affine scans.
+//
+// With Z = U - W H substituted, one chunk maps its incoming state H to
+//     H' = exp(G_end) . H  -  (W^T E)^T-contracted H  +  E^T U          i.e.  H'^T = dec . H^T - H^T Pn + U^T E
+// and the adjoint recurrence of the backward is its transpose,
+//     dH^T = dec . dH'^T - dH'^T Pn^T + dO^T (R - A W).
+// Pn = W^T E and Rm = R - A W do not depend on the state, so they are computed for all chunks in parallel
+// (transition kernel) and the sequential part of a chunk step shrinks to ONE UMMA chain between two register passes:
+//     pack state -> bf16 A operand | D = state-independent term (issued a step early) - state x Pn | state = dec . state + D
+// Everything else that used to sit inside the scans runs chunk-parallel on all SMs afterwards:
+//     forward   Z^T = U^T - (W H)^T,  O^T = (R H)^T + (A Z)^T      from the chunk-start states the scan stored
+//     backward  dZ^T = dO^T A + dH'^T E^T                          from the state adjoints the scan stored
+// All products are written transposed so that M = 128 (value index = TMEM lane) for every UMMA.
+// Restates reference chunk_wy_forward.cu:940-1275 (state scan), 1498-1588 (output) and
+// chunk_wy_backward.cu:2445-2562 (adjoint scan); the algebraic regrouping is this implementation's.
+
+#include "common.cuh"
+#include "simt_ws.cuh"
+#include "tc_common.cuh"
+#include "tc_ws.cuh"
+
+namespace kda {
+namespace tc {
+
+int make_map_bf16(CUtensorMap* m, const void* ptr, uint64_t rows, uint64_t cols, uint32_t box_cols, uint32_t box_rows);
+
+// ---------------------------------------------------------------------------------------------
+// transition kernel: Pn = W^T E  [k][k'],  RmT = R^T - W^T A^T  [k][i]      one CTA per chunk-head
+// ---------------------------------------------------------------------------------------------
+struct TransArgs {
+    const int* chunk_len;
+    const __nv_bfloat16* RT;
+    __nv_bfloat16 *Pn, *RmT;
+    int H;
+    int* status;
+};
+
+constexpr int kTransSmem = 16384 + 16384 + 8192 + 1024;   // W^T | E | A^T
+
+__global__ void __launch_bounds__(256, 1)
+    tc_transition_kernel(const __grid_constant__ CUtensorMap mW, const __grid_constant__ CUtensorMap mE,
+                         const __grid_constant__ CUtensorMap mAT, TransArgs p) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* sm = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    __shared__ uint64_t bar_in, bar_mma;
+    __shared__ uint32_t tmem_slot;
+    const int slot = blockIdx.x, h = blockIdx.y;
+    if (p.chunk_len[slot] == 0) return;
+    const int ch = slot * p.H + h;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int g = warp >> 2;                       // column half handled by this warpgroup
+    const int k = (warp & 3) * 32 + lane;          // key row = TMEM lane
+    if (tid == 0) {
+        mbar_init(&bar_in, 1);
+        mbar_init(&bar_mma, 1);
+        mbar_fence_init();
+        mbar_expect_tx(&bar_in, 16384 + 16384 + 8192);
+        tma_load_2d(sm, &mW, &bar_in, 0, ch * 128);                                    // W^T [key][token]
+        for (int nb = 0; nb < 2; ++nb) tma_load_2d(sm + 16384 + nb * 8192, &mE, &bar_in, nb * 64, ch * 64);
+        tma_load_2d(sm + 32768, &mAT, &bar_in, 0, ch * 64);
+    }
+    if (warp == 1) tmem_alloc(&tmem_slot, 256);
+    // this thread's part of R^T while the tiles fly: row k, tokens 32g .. 32g+31
+    uint4 rt[4];
+    {
+        const uint4* src = reinterpret_cast<const uint4*>(p.RT + (size_t)ch * 8192 + (size_t)k * 64 + 32 * g);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) rt[j] = src[j];
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = tmem_slot;
+    const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
+    bool ok = true;
+    if (tid == 0) {
+        ok = mbar_wait(&bar_in, 0, p.status, 40);
+        if (ok) {
+            tc_fence_after();
+            const uint32_t a0 = smem_u32(sm), bE = smem_u32(sm + 16384), bA = smem_u32(sm + 32768);
+            const uint32_t id128 = umma_idesc_bf16(128, 128, kMajorK, kMajorMN);
+            const uint32_t id64 = umma_idesc_bf16(128, 64, kMajorK, kMajorMN);
+#pragma unroll
+            for (int k16 = 0; k16 < 4; ++k16)     // Pn = W^T E
+                umma_bf16_ss(tmem, umma_smem_desc_sw128(a0 + k16 * 32, 16, 1024),
+                             umma_smem_desc_sw128(bE + k16 * 2048, 8192, 1024), id128, k16 > 0);
+#pragma unroll
+            for (int k16 = 0; k16 < 4; ++k16)     // (A W)^T = W^T A^T
+                umma_bf16_ss(tmem + 128, umma_smem_desc_sw128(a0 + k16 * 32, 16, 1024),
+                             umma_smem_desc_sw128(bA + k16 * 2048, 8192, 1024), id64, k16 > 0);
+            umma_commit(&bar_mma);
+        }
+    }
+    ok = mbar_wait(&bar_mma, 0, p.status, 41) && ok;
+    ok = __syncthreads_and(ok);
+    tc_fence_after();
+    if (ok) {
+        uint4* dp = reinterpret_cast<uint4*>(p.Pn + (size_t)ch * 16384 + (size_t)k * 128 + 64 * g);
+#pragma unroll
+        for (int b = 0; b < 2; ++b) {
+            uint32_t r[32];
+            tmem_ld32(tmem + lane_base + 64 * g + 32 * b, r);
+            tmem_ld_wait();
+#pragma unroll
+            for (int c = 0; c < 4; ++c)
+                dp[4 * b + c] = make_uint4(pack_bf16(__uint_as_float(r[8 * c]), __uint_as_float(r[8 * c + 1])),
+                                           pack_bf16(__uint_as_float(r[8 * c + 2]), __uint_as_float(r[8 * c + 3])),
+                                           pack_bf16(__uint_as_float(r[8 * c + 4]), __uint_as_float(r[8 * c + 5])),
+                                           pack_bf16(__uint_as_float(r[8 * c + 6]), __uint_as_float(r[8 * c + 7])));
+        }
+        uint32_t r[32];
+        tmem_ld32(tmem + lane_base + 128 + 32 * g, r);
+        tmem_ld_wait();
+        uint4* dr = reinterpret_cast<uint4*>(p.RmT + (size_t)ch * 8192 + (size_t)k * 64 + 32 * g);
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            float f[8];
+            unpack_bf16x8(rt[c], f);
+            dr[c] = make_uint4(pack_bf16(f[0] - __uint_as_float(r[8 * c]), f[1] - __uint_as_float(r[8 * c + 1])),
+                               pack_bf16(f[2] - __uint_as_float(r[8 * c + 2]), f[3] - __uint_as_float(r[8 * c + 3])),
+                               pack_bf16(f[4] - __uint_as_float(r[8 * c + 4]), f[5] - __uint_as_float(r[8 * c + 5])),
+                               pack_bf16(f[6] - __uint_as_float(r[8 * c + 6]), f[7] - __uint_as_float(r[8 * c + 7])));
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tmem, 256);
+}
+
+// ---------------------------------------------------------------------------------------------
+// affine scan: one CTA per (sequence, head) walks the chunks in order (forward) or in reverse (backward)
+//     forward    S = H^T   [v][k]:   S' = dec . S - S Pn   + U^T E           stores S (chunk-start state) per chunk
+//     backward   S = dH'^T [v][k]:   S' = dec . S - S Pn^T + dO^T Rm         stores S (adjoint of the chunk's outgoing state)
+// 320 threads, specialised by warp; they meet only through mbarriers:
+//   warps 0-7  state: thread (kh, v) owns S[v][64*kh .. 64*kh+63] in registers
+//   warp 8     one lane issues the TMA loads, two chunks ahead
+//   warp 9     one lane issues every UMMA and the TMA stores of the state panels
+// TMEM: the accumulator is double-buffered (columns 0 / 128) so that the state-independent product of step c+1 is
+// issued while the state threads still read the accumulator of step c.  The bf16 state panel in shared memory is
+// double-buffered too, so the TMA store of panel c has a whole step to read it before it is packed again.
+// ---------------------------------------------------------------------------------------------
+struct AffineScanArgs {
+    const int* seq_chunk0;
+    const int* chunk_tok0;
+    const float* decay_end;   // [nch][128] exp(G_end)
+    const float* s_in;        // V-first initial state (forward: h0, backward: cotangent of the final state), or null
+    float* s_out;             // V-first final state of the scan (forward: final state, backward: dh0), or null
+    int H;
+    int* status;
+};
+
+constexpr int kPStage = 65536;                              // Pn 32 KB | X 16 KB (U^T or Rm^T) | Y 16 KB (E or dO)
+constexpr int kPStageBytes = kPStage + 512;                 // + exp(G_end), which lands in a ring of its own
+constexpr int kAffineScanSmem = 2 * kPStage + 2 * 32768 + 1024;
+constexpr int kAffineScanThreads = 320;
+
+#ifdef KDA_PHASE_TIMING
+#define KDA_TICKP(n) do { if (tid == 0) { long long t_ = clock64(); acc[n] += t_ - tlast; tlast = t_; } } while (0)
+#else
+#define KDA_TICKP(n) do { } while (0)
+#endif
+
+template <bool kBwd>
+__global__ void __launch_bounds__(kAffineScanThreads, 1)
+    tc_affine_scan_kernel(const __grid_constant__ CUtensorMap mP, const __grid_constant__ CUtensorMap mX,
+                          const __grid_constant__ CUtensorMap mY, const __grid_constant__ CUtensorMap mS, AffineScanArgs p) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* sm = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint8_t* Sop = sm + 2 * kPStage;               // 2 x [2 k-blocks][128 rows x 128 B]: bf16 state panel of step c in c % 2
+    __shared__ __align__(16) float dec_ring[4][128];   // exp(G_end) of step c in slot c % 4
+    // full: a stage has landed.  free: every product that reads a stage is complete (one per stage, so that the load
+    // thread can never miss a phase).  sop: all state threads have packed the state panel.  mma: the step's
+    // accumulator is complete.
+    __shared__ uint64_t bar_full[2], bar_free[2], bar_sop, bar_mma;
+    __shared__ uint32_t tmem_slot;
+    __shared__ volatile int abort_flag;
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int v = (warp & 3) * 32 + lane;          // value row = TMEM lane
+    const int seq = blockIdx.x, h = blockIdx.y, H = p.H;
+    const int c_begin = p.seq_chunk0[seq], c_end = p.seq_chunk0[seq + 1];
+    const int n = c_end - c_begin;
+    auto slot_of = [&](int c) { return kBwd ? c_end - 1 - c : c_begin + c; };   // chunk slot of step c
+
+    if (tid == 0) {
+        mbar_init(&bar_full[0], 1);
+        mbar_init(&bar_full[1], 1);
+        mbar_init(&bar_free[0], 1);
+        mbar_init(&bar_free[1], 1);
+        mbar_init(&bar_sop, 256);
+        mbar_init(&bar_mma, 1);
+        mbar_fence_init();
+        abort_flag = 0;
+    }
+    if (warp == 1) tmem_alloc(&tmem_slot, 256);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = tmem_slot;
+    const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
+
+    if (warp == 8) {
+        // ------------------------------------------------------------------ load warp
+        if (lane == 0) {
+            auto issue_loads = [&](int c) {
+                const int st = c & 1;
+                const int slot = slot_of(c);
+                const int ch = slot * H + h;
+                uint8_t* b = sm + st * kPStage;
+                mbar_expect_tx(&bar_full[st], kPStageBytes);
+                bulk_load_1d(dec_ring[c & 3], p.decay_end + (size_t)ch * 128, 512, &bar_full[st]);
+                for (int nb = 0; nb < 2; ++nb) tma_load_2d(b + nb * 16384, &mP, &bar_full[st], nb * 64, ch * 128);
+                tma_load_2d(b + 32768, &mX, &bar_full[st], 0, ch * 128);                  // U^T / Rm^T: [128][64]
+                if (!kBwd) {
+                    for (int nb = 0; nb < 2; ++nb) tma_load_2d(b + 49152 + nb * 8192, &mY, &bar_full[st], nb * 64, ch * 64);
+                } else {
+                    const int tok0 = p.chunk_tok0[slot];
+                    for (int nb = 0; nb < 2; ++nb) tma_load_2d(b + 49152 + nb * 8192, &mY, &bar_full[st], h * 128 + nb * 64, tok0);
+                }
+            };
+            int issued = 0;
+            for (; issued < 2 && issued < n; ++issued) issue_loads(issued);
+            bool ok = true;
+            for (int c = 0; c + 2 < n && ok; ++c) {     // stage c % 2 is free once every product of step c is complete
+                ok = mbar_wait(&bar_free[c & 1], (c >> 1) & 1, p.status, 50);
+                if (ok) { issue_loads(c + 2); issued = c + 3; }
+                else abort_flag = 1;
+            }
+            if (!ok)   // unwinding: the copies in flight must land before the block may exit
+                for (int c = issued > 2 ? issued - 2 : 0; c < issued; ++c) mbar_wait(&bar_full[c & 1], (c >> 1) & 1, nullptr, 0);
+        }
+    } else if (warp == 9) {
+        // ------------------------------------------------------------------ UMMA / panel-store thread
+        if (lane == 0 && n > 0) {
+            // state-independent product:  forward U^T E (A K-major, B MN-major), backward dO^T Rm (A MN-major, B K-major)
+            const uint32_t id_ind = kBwd ? umma_idesc_bf16(128, 128, kMajorMN, kMajorK) : umma_idesc_bf16(128, 128, kMajorK, kMajorMN);
+            // state product, negated:  forward -S Pn (B MN-major: rows of Pn are the contraction index),
+            //                          backward -S Pn^T (B K-major: rows of Pn are the output index)
+            const uint32_t id_st = umma_idesc_bf16(128, 128, kMajorK, kBwd ? kMajorK : kMajorMN, 1);
+            auto issue_independent = [&](int c) {
+                const uint32_t s0 = smem_u32(sm + (c & 1) * kPStage);
+                const uint32_t d = tmem + 128 * (c & 1);
+#pragma unroll
+                for (int k16 = 0; k16 < 4; ++k16) {
+                    if (!kBwd)
+                        umma_bf16_ss(d, umma_smem_desc_sw128(s0 + 32768 + k16 * 32, 16, 1024),
+                                     umma_smem_desc_sw128(s0 + 49152 + k16 * 2048, 8192, 1024), id_ind, k16 > 0);
+                    else
+                        umma_bf16_ss(d, umma_smem_desc_sw128(s0 + 49152 + k16 * 2048, 8192, 1024),
+                                     umma_smem_desc_sw128(s0 + 32768 + k16 * 32, 16, 1024), id_ind, k16 > 0);
+                }
+            };
+            bool ok = mbar_wait(&bar_full[0], 0, p.status, 51);
+            if (ok) {
+                tc_fence_after();
+                issue_independent(0);
+            } else abort_flag = 1;
+            for (int c = 0; c < n && ok; ++c) {
+                const int st = c & 1;
+                const int ch = slot_of(c) * H + h;
+                const uint32_t s0 = smem_u32(sm + st * kPStage);
+                const uint32_t a_s = smem_u32(Sop + st * 32768);
+                if (!mbar_wait(&bar_sop, c & 1, p.status, 52)) { abort_flag = 1; break; }
+                tc_fence_after();
+#pragma unroll
+                for (int k16 = 0; k16 < 8; ++k16) {
+                    const uint64_t ad = umma_smem_desc_sw128(a_s + (k16 >> 2) * 16384 + (k16 & 3) * 32, 16, 1024);
+                    const uint64_t bd = kBwd ? umma_smem_desc_sw128(s0 + (k16 >> 2) * 16384 + (k16 & 3) * 32, 16, 1024)
+                                             : umma_smem_desc_sw128(s0 + k16 * 2048, 16384, 1024);
+                    umma_bf16_ss(tmem + 128 * st, ad, bd, id_st, 1);
+                }
+                // The store of panel c-1 has read its buffer before this commit lets the state threads pack panel c+1
+                // into it.
+                tma_store_wait_read();
+                umma_commit(&bar_mma);
+                umma_commit(&bar_free[st]);
+                tma_store_2d(&mS, Sop + st * 32768, 0, ch * 128);
+                tma_store_2d(&mS, Sop + st * 32768 + 16384, 64, ch * 128);
+                tma_store_commit();
+                if (c + 1 < n) {
+                    // accumulator (c+1) % 2 was last read by the state threads in step c-1, before they packed panel c
+                    if (!mbar_wait(&bar_full[(c + 1) & 1], ((c + 1) >> 1) & 1, p.status, 51)) { abort_flag = 1; break; }
+                    tc_fence_after();
+                    issue_independent(c + 1);
+                }
+            }
+            tma_store_wait_all();
+        }
+    } else {
+        // ------------------------------------------------------------------ state warpgroups
+        const int kh = warp >> 2;                  // key half of this thread
+        float s[64];
+        if (p.s_in) {
+            const float4* src = reinterpret_cast<const float4*>(p.s_in + (((size_t)seq * H + h) * 128 + v) * 128 + 64 * kh);
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+                float4 x = src[j];
+                s[4 * j] = x.x; s[4 * j + 1] = x.y; s[4 * j + 2] = x.z; s[4 * j + 3] = x.w;
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 64; ++j) s[j] = 0.f;
+        }
+        // this thread's half of the state row -> bf16 A operand (K-major, 128-byte swizzle)
+        auto pack_state = [&](int c) {
+            uint8_t* dst = Sop + (c & 1) * 32768 + kh * 16384;
+#pragma unroll
+            for (int c16 = 0; c16 < 8; ++c16) {
+                uint4 u;
+                u.x = pack_bf16(s[8 * c16 + 0], s[8 * c16 + 1]);
+                u.y = pack_bf16(s[8 * c16 + 2], s[8 * c16 + 3]);
+                u.z = pack_bf16(s[8 * c16 + 4], s[8 * c16 + 5]);
+                u.w = pack_bf16(s[8 * c16 + 6], s[8 * c16 + 7]);
+                *reinterpret_cast<uint4*>(dst + sw128_off(v, c16)) = u;
+            }
+            fence_async_smem();
+            tc_fence_before();
+            mbar_arrive(&bar_sop);
+        };
+#ifdef KDA_PHASE_TIMING
+        long long acc[4] = {0, 0, 0, 0}, tlast = clock64();
+#endif
+        bool ok = true;
+        if (n > 0) pack_state(0);
+        for (int c = 0; c < n; ++c) {
+            KDA_TICKP(0);
+            if (!mbar_wait(&bar_mma, c & 1, p.status, 53) || !mbar_wait(&bar_full[c & 1], (c >> 1) & 1, p.status, 54)) {
+                abort_flag = 1; ok = false;
+                break;
+            }
+            tc_fence_after();
+            KDA_TICKP(1);
+            const float* dc = dec_ring[c & 3] + 64 * kh;
+            {
+                uint32_t r0[32], r1[32];     // both halves in flight before the wait
+                tmem_ld32(tmem + lane_base + 128 * (c & 1) + 64 * kh, r0);
+                tmem_ld32(tmem + lane_base + 128 * (c & 1) + 64 * kh + 32, r1);
+                tmem_ld_wait();
+#pragma unroll
+                for (int j4 = 0; j4 < 8; ++j4) {
+                    const float4 dv = *reinterpret_cast<const float4*>(dc + 4 * j4);
+                    s[4 * j4 + 0] = dv.x * s[4 * j4 + 0] + __uint_as_float(r0[4 * j4 + 0]);
+                    s[4 * j4 + 1] = dv.y * s[4 * j4 + 1] + __uint_as_float(r0[4 * j4 + 1]);
+                    s[4 * j4 + 2] = dv.z * s[4 * j4 + 2] + __uint_as_float(r0[4 * j4 + 2]);
+                    s[4 * j4 + 3] = dv.w * s[4 * j4 + 3] + __uint_as_float(r0[4 * j4 + 3]);
+                }
+#pragma unroll
+                for (int j4 = 0; j4 < 8; ++j4) {
+                    const float4 dv = *reinterpret_cast<const float4*>(dc + 32 + 4 * j4);
+                    s[32 + 4 * j4 + 0] = dv.x * s[32 + 4 * j4 + 0] + __uint_as_float(r1[4 * j4 + 0]);
+                    s[32 + 4 * j4 + 1] = dv.y * s[32 + 4 * j4 + 1] + __uint_as_float(r1[4 * j4 + 1]);
+                    s[32 + 4 * j4 + 2] = dv.z * s[32 + 4 * j4 + 2] + __uint_as_float(r1[4 * j4 + 2]);
+                    s[32 + 4 * j4 + 3] = dv.w * s[32 + 4 * j4 + 3] + __uint_as_float(r1[4 * j4 + 3]);
+                }
+            }
+            tc_fence_before();
+            KDA_TICKP(2);
+            if (c + 1 < n) pack_state(c + 1);
+            KDA_TICKP(3);
+        }
+#ifdef KDA_PHASE_TIMING
+        if (tid == 0 && blockIdx.x == 0 && blockIdx.y == 0 && n > 0)
+            printf("affine scan %s per step: loop %lld | wait %lld | update %lld | pack %lld\n", kBwd ? "bwd" : "fwd", acc[0] / n,
+                   acc[1] / n, acc[2] / n, acc[3] / n);
+#endif
+        if (ok && abort_flag == 0 && p.s_out) {
+            float4* dst = reinterpret_cast<float4*>(p.s_out + (((size_t)seq * H + h) * 128 + v) * 128 + 64 * kh);
+#pragma unroll
+            for (int j = 0; j < 16; ++j) dst[j] = make_float4(s[4 * j], s[4 * j + 1], s[4 * j + 2], s[4 * j + 3]);
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tmem, 256);
+}
+
+// ---------------------------------------------------------------------------------------------
+// chunk output (forward), one CTA per chunk-head, from the chunk-start state the scan stored:
+//     [ (W H)^T | (R H)^T ] = H^T [ W^T | R^T ]      M=128, N=128, K=128
+//     Z^T = U^T - (W H)^T                             registers -> bf16 panel (kept for the backward) and A operand
+//     (A Z)^T = Z^T A^T                               M=128, N=64,  K=64
+//     O^T = (R H)^T + (A Z)^T                         transposed through shared memory into o[token][head][value]
+// 256 threads: thread (g, v) handles value row v, tokens 32g .. 32g+31.
+// ---------------------------------------------------------------------------------------------
+struct ChunkOutArgs {
+    const int* chunk_tok0;
+    const int* chunk_len;
+    __nv_bfloat16* ZT;
+    __nv_bfloat16* o;          // [tokens][H][128]
+    int H;
+    int* status;
+};
+
+constexpr int kOutH = 0, kOutWR = 32768, kOutU = 65536, kOutA = 81920, kOutZ = 90112, kOutO = 106496;
+constexpr int kChunkOutSmem = kOutO + 16384 + 1024;
+
+__global__ void __launch_bounds__(256, 1)
+    tc_chunk_out_kernel(const __grid_constant__ CUtensorMap mH, const __grid_constant__ CUtensorMap mW,
+                        const __grid_constant__ CUtensorMap mR, const __grid_constant__ CUtensorMap mUT,
+                        const __grid_constant__ CUtensorMap mAT, ChunkOutArgs p) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* sm = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint8_t* Zop = sm + kOutZ;                     // [128 rows x 128 B] K-major A operand
+    __nv_bfloat16* Ot = reinterpret_cast<__nv_bfloat16*>(sm + kOutO);   // [64 tokens][128 values]
+    __shared__ uint64_t bar_in, bar_mma1, bar_mma2;
+    __shared__ uint32_t tmem_slot;
+    const int slot = blockIdx.x, h = blockIdx.y, H = p.H;
+    const int len = p.chunk_len[slot];
+    if (len == 0) return;
+    const int tok0 = p.chunk_tok0[slot];
+    const int ch = slot * H + h;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int g = warp >> 2;
+    const int v = (warp & 3) * 32 + lane;
+    if (tid == 0) {
+        mbar_init(&bar_in, 1);
+        mbar_init(&bar_mma1, 1);
+        mbar_init(&bar_mma2, 1);
+        mbar_fence_init();
+        mbar_expect_tx(&bar_in, 32768 + 32768 + 16384 + 8192);
+        for (int kb = 0; kb < 2; ++kb) tma_load_2d(sm + kOutH + kb * 16384, &mH, &bar_in, kb * 64, ch * 128);
+        tma_load_2d(sm + kOutWR, &mW, &bar_in, 0, ch * 128);
+        tma_load_2d(sm + kOutWR + 16384, &mR, &bar_in, 0, ch * 128);
+        tma_load_2d(sm + kOutU, &mUT, &bar_in, 0, ch * 128);
+        tma_load_2d(sm + kOutA, &mAT, &bar_in, 0, ch * 64);
+    }
+    if (warp == 1) tmem_alloc(&tmem_slot, 256);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = tmem_slot;
+    const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
+    bool ok = true;
+    if (tid == 0) {
+        ok = mbar_wait(&bar_in, 0, p.status, 60);
+        if (ok) {
+            tc_fence_after();
+            const uint32_t a0 = smem_u32(sm + kOutH), b0 = smem_u32(sm + kOutWR);
+            const uint32_t idesc = umma_idesc_bf16(128, 128, kMajorK, kMajorMN);
+#pragma unroll
+            for (int k16 = 0; k16 < 8; ++k16)
+                umma_bf16_ss(tmem, umma_smem_desc_sw128(a0 + (k16 >> 2) * 16384 + (k16 & 3) * 32, 16, 1024),
+                             umma_smem_desc_sw128(b0 + k16 * 2048, 16384, 1024), idesc, k16 > 0);
+            umma_commit(&bar_mma1);
+        }
+    }
+    ok = mbar_wait(&bar_mma1, 0, p.status, 61) && ok;
+    // the U^T tile was written by TMA: every reader observes the barrier it completed on
+    ok = mbar_wait(&bar_in, 0, p.status, 60) && ok;
+    tc_fence_after();
+    {   // Z^T for tokens 32g .. 32g+31 of row v
+        const uint8_t* UTs = sm + kOutU;
+        uint32_t r[32];
+        tmem_ld32(tmem + lane_base + 32 * g, r);
+        tmem_ld_wait();
+        uint4* zdst = reinterpret_cast<uint4*>(p.ZT + (size_t)ch * 8192 + (size_t)v * 64 + 32 * g);
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) {
+            const int c16 = g * 4 + q4;
+            float u[8];
+            unpack_bf16x8(*reinterpret_cast<const uint4*>(UTs + sw128_off(v, c16)), u);
+            uint4 z;
+            z.x = pack_bf16(u[0] - __uint_as_float(r[8 * q4 + 0]), u[1] - __uint_as_float(r[8 * q4 + 1]));
+            z.y = pack_bf16(u[2] - __uint_as_float(r[8 * q4 + 2]), u[3] - __uint_as_float(r[8 * q4 + 3]));
+            z.z = pack_bf16(u[4] - __uint_as_float(r[8 * q4 + 4]), u[5] - __uint_as_float(r[8 * q4 + 5]));
+            z.w = pack_bf16(u[6] - __uint_as_float(r[8 * q4 + 6]), u[7] - __uint_as_float(r[8 * q4 + 7]));
+            *reinterpret_cast<uint4*>(Zop + sw128_off(v, c16)) = z;
+            if (ok) zdst[q4] = z;
+        }
+    }
+    fence_async_smem();
+    tc_fence_before();
+    ok = __syncthreads_and(ok);
+    if (tid == 0 && ok) {
+        tc_fence_after();
+        const uint32_t a0 = smem_u32(Zop), b0 = smem_u32(sm + kOutA);
+        const uint32_t idesc = umma_idesc_bf16(128, 64, kMajorK, kMajorMN);
+#pragma unroll
+        for (int k16 = 0; k16 < 4; ++k16)
+            umma_bf16_ss(tmem + 128, umma_smem_desc_sw128(a0 + k16 * 32, 16, 1024),
+                         umma_smem_desc_sw128(b0 + k16 * 2048, 8192, 1024), idesc, k16 > 0);
+        umma_commit(&bar_mma2);
+    }
+    if (ok) ok = mbar_wait(&bar_mma2, 0, p.status, 62);
+    tc_fence_after();
+    if (ok) {
+        uint32_t r1[32], r2[32];
+        tmem_ld32(tmem + lane_base + 64 + 32 * g, r1);
+        tmem_ld32(tmem + lane_base + 128 + 32 * g, r2);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 32; ++j) Ot[(32 * g + j) * 128 + v] = __float2bfloat16(__uint_as_float(r1[j]) + __uint_as_float(r2[j]));
+    }
+    ok = __syncthreads_and(ok);
+    if (ok) {
+        // 64 token rows of 256 bytes: 16 threads per row, 16 rows per pass
+        const int c = tid & 15;
+#pragma unroll
+        for (int pass = 0; pass < 4; ++pass) {
+            const int i = pass * 16 + (tid >> 4);
+            if (i < len)
+                *reinterpret_cast<uint4*>(p.o + ((size_t)(tok0 + i) * H + h) * 128 + 8 * c) =
+                    *reinterpret_cast<const uint4*>(Ot + i * 128 + 8 * c);
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tmem, 256);
+}
+
+// ---------------------------------------------------------------------------------------------
+// dZ (backward), one CTA per chunk-head, from the state adjoint the scan stored:
+//     dZ^T = dO^T A + dH'^T E^T          M=128, N=64: K=64 (MN-major A) then K=128
+// ---------------------------------------------------------------------------------------------
+struct ChunkDzArgs {
+    const int* chunk_tok0;
+    const int* chunk_len;
+    __nv_bfloat16* dZT;
+    int H;
+    int* status;
+};
+
+constexpr int kDzH = 0, kDzE = 32768, kDzO = 49152, kDzA = 65536;
+constexpr int kChunkDzSmem = kDzA + 8192 + 1024;
+
+__global__ void __launch_bounds__(256, 1)
+    tc_chunk_dz_kernel(const __grid_constant__ CUtensorMap mdH, const __grid_constant__ CUtensorMap mE,
+                       const __grid_constant__ CUtensorMap mdO, const __grid_constant__ CUtensorMap mAT, ChunkDzArgs p) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* sm = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    __shared__ uint64_t bar_in, bar_mma;
+    __shared__ uint32_t tmem_slot;
+    const int slot = blockIdx.x, h = blockIdx.y, H = p.H;
+    if (p.chunk_len[slot] == 0) return;
+    const int tok0 = p.chunk_tok0[slot];
+    const int ch = slot * H + h;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int g = warp >> 2;
+    const int v = (warp & 3) * 32 + lane;
+    if (tid == 0) {
+        mbar_init(&bar_in, 1);
+        mbar_init(&bar_mma, 1);
+        mbar_fence_init();
+        mbar_expect_tx(&bar_in, 32768 + 16384 + 16384 + 8192);
+        for (int kb = 0; kb < 2; ++kb) {
+            tma_load_2d(sm + kDzH + kb * 16384, &mdH, &bar_in, kb * 64, ch * 128);
+            tma_load_2d(sm + kDzE + kb * 8192, &mE, &bar_in, kb * 64, ch * 64);
+            tma_load_2d(sm + kDzO + kb * 8192, &mdO, &bar_in, h * 128 + kb * 64, tok0);
+        }
+        tma_load_2d(sm + kDzA, &mAT, &bar_in, 0, ch * 64);
+    }
+    if (warp == 1) tmem_alloc(&tmem_slot, 64);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = tmem_slot;
+    const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
+    bool ok = true;
+    if (tid == 0) {
+        ok = mbar_wait(&bar_in, 0, p.status, 70);
+        if (ok) {
+            tc_fence_after();
+            const uint32_t s0 = smem_u32(sm);
+            const uint32_t ida = umma_idesc_bf16(128, 64, kMajorMN, kMajorK);
+            const uint32_t idb = umma_idesc_bf16(128, 64, kMajorK, kMajorK);
+#pragma unroll
+            for (int k16 = 0; k16 < 4; ++k16)     // dO^T A
+                umma_bf16_ss(tmem, umma_smem_desc_sw128(s0 + kDzO + k16 * 2048, 8192, 1024),
+                             umma_smem_desc_sw128(s0 + kDzA + k16 * 32, 16, 1024), ida, k16 > 0);
+#pragma unroll
+            for (int k16 = 0; k16 < 8; ++k16)     // + dH'^T E^T
+                umma_bf16_ss(tmem, umma_smem_desc_sw128(s0 + kDzH + (k16 >> 2) * 16384 + (k16 & 3) * 32, 16, 1024),
+                             umma_smem_desc_sw128(s0 + kDzE + (k16 >> 2) * 8192 + (k16 & 3) * 32, 16, 1024), idb, 1);
+            umma_commit(&bar_mma);
+        }
+    }
+    ok = mbar_wait(&bar_mma, 0, p.status, 71) && ok;
+    ok = __syncthreads_and(ok);
+    tc_fence_after();
+    if (ok) {
+        uint32_t r[32];
+        tmem_ld32(tmem + lane_base + 32 * g, r);
+        tmem_ld_wait();
+        uint4* dst = reinterpret_cast<uint4*>(p.dZT + (size_t)ch * 8192 + (size_t)v * 64 + 32 * g);
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+            dst[c] = make_uint4(pack_bf16(__uint_as_float(r[8 * c]), __uint_as_float(r[8 * c + 1])),
+                                pack_bf16(__uint_as_float(r[8 * c + 2]), __uint_as_float(r[8 * c + 3])),
+                                pack_bf16(__uint_as_float(r[8 * c + 4]), __uint_as_float(r[8 * c + 5])),
+                                pack_bf16(__uint_as_float(r[8 * c + 6]), __uint_as_float(r[8 * c + 7])));
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tmem, 64);
+}
+
+}  // namespace tc
+
+// ---------------------------------------------------------------------------------------------
+// host entries used by the chunk forward / backward when the tensor-core lane is selected
+// ---------------------------------------------------------------------------------------------
+int tc_scan_forward(const simt::Ws& w, const tc::TcWs& t, int n_seq, const float* h0, float* final_state, void* o,
+                    cudaStream_t st) {
+    using namespace tc;
+    const uint64_t nch = (uint64_t)w.nslots * w.H;
+    CUtensorMap mW, mR, mE, mAT, mUT, mH, mP;
+    int rc = 0;
+    rc |= make_map_bf16(&mW, t.WT, nch * 128, 64, 64, 128);
+    rc |= make_map_bf16(&mR, t.RT, nch * 128, 64, 64, 128);
+    rc |= make_map_bf16(&mE, t.E, nch * 64, 128, 64, 64);
+    rc |= make_map_bf16(&mAT, t.AT, nch * 64, 64, 64, 64);
+    rc |= make_map_bf16(&mUT, t.UT, nch * 128, 64, 64, 128);
+    rc |= make_map_bf16(&mH, t.Hp, nch * 128, 128, 64, 128);
+    rc |= make_map_bf16(&mP, t.Pn, nch * 128, 128, 64, 128);
+    if (rc) return KDA_ERR_CUDA;
+    if (cudaFuncSetAttribute(tc_transition_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kTransSmem) != cudaSuccess ||
+        cudaFuncSetAttribute(tc_affine_scan_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kAffineScanSmem) != cudaSuccess ||
+        cudaFuncSetAttribute(tc_chunk_out_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kChunkOutSmem) != cudaSuccess)
+        return KDA_ERR_CUDA;
+    TransArgs ta;
+    ta.chunk_len = w.chunk_len; ta.RT = t.RT; ta.Pn = t.Pn; ta.RmT = t.RmT; ta.H = w.H; ta.status = t.status;
+    KDA_LAUNCH("tc_transition_kernel", st,
+               tc_transition_kernel<<<dim3(w.nslots, w.H), 256, kTransSmem, st>>>(mW, mE, mAT, ta));
+    if (int e = launch_status()) return e;
+    AffineScanArgs a;
+    a.seq_chunk0 = w.seq_chunk0; a.chunk_tok0 = w.chunk_tok0; a.decay_end = t.decay_end; a.s_in = h0; a.s_out = final_state;
+    a.H = w.H; a.status = t.status;
+    KDA_LAUNCH("tc_affine_scan_fwd_kernel", st,
+               tc_affine_scan_kernel<false><<<dim3(n_seq, w.H), kAffineScanThreads, kAffineScanSmem, st>>>(mP, mUT, mE, mH, a));
+    if (int e = launch_status()) return e;
+    ChunkOutArgs oa;
+    oa.chunk_tok0 = w.chunk_tok0; oa.chunk_len = w.chunk_len; oa.ZT = t.ZT; oa.o = static_cast<__nv_bfloat16*>(o); oa.H = w.H;
+    oa.status = t.status;
+    KDA_LAUNCH("tc_chunk_out_kernel", st,
+               tc_chunk_out_kernel<<<dim3(w.nslots, w.H), 256, kChunkOutSmem, st>>>(mH, mW, mR, mUT, mAT, oa));
+    return launch_status();
+}
+
+int tc_scan_backward(const simt::Ws& w, const simt::Scr& s, const tc::TcWs& t, int n_seq, int tokens, const void* d_o,
+                     const float* d_final, float* dh0, cudaStream_t st) {
+    using namespace tc;
+    (void)s;
+    const uint64_t nch = (uint64_t)w.nslots * w.H;
+    CUtensorMap mE, mAT, mdO, mdH, mP, mRm;
+    int rc = 0;
+    rc |= make_map_bf16(&mE, t.E, nch * 64, 128, 64, 64);
+    rc |= make_map_bf16(&mAT, t.AT, nch * 64, 64, 64, 64);
+    rc |= make_map_bf16(&mdO, d_o, (uint64_t)tokens, (uint64_t)w.H * 128, 64, 64);
+    rc |= make_map_bf16(&mdH, t.dHp, nch * 128, 128, 64, 128);
+    rc |= make_map_bf16(&mP, t.Pn, nch * 128, 128, 64, 128);
+    rc |= make_map_bf16(&mRm, t.RmT, nch * 128, 64, 64, 128);
+    if (rc) return KDA_ERR_CUDA;
+    if (cudaFuncSetAttribute(tc_affine_scan_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kAffineScanSmem) != cudaSuccess ||
+        cudaFuncSetAttribute(tc_chunk_dz_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kChunkDzSmem) != cudaSuccess)
+        return KDA_ERR_CUDA;
+    AffineScanArgs a;
+    a.seq_chunk0 = w.seq_chunk0; a.chunk_tok0 = w.chunk_tok0; a.decay_end = t.decay_end; a.s_in = d_final; a.s_out = dh0;
+    a.H = w.H; a.status = t.status;
+    KDA_LAUNCH("tc_affine_scan_bwd_kernel", st,
+               tc_affine_scan_kernel<true><<<dim3(n_seq, w.H), kAffineScanThreads, kAffineScanSmem, st>>>(mP, mRm, mdO, mdH, a));
+    if (int e = launch_status()) return e;
+    ChunkDzArgs da;
+    da.chunk_tok0 = w.chunk_tok0; da.chunk_len = w.chunk_len; da.dZT = t.dZT; da.H = w.H; da.status = t.status;
+    KDA_LAUNCH("tc_chunk_dz_kernel", st,
+               tc_chunk_dz_kernel<<<dim3(w.nslots, w.H), 256, kChunkDzSmem, st>>>(mdH, mE, mdO, mAT, da));
+    return launch_status();
+}
+
+}  // namespace kda

@@ -19,6 +19,8 @@ struct TcWs {
     __nv_bfloat16* ZT;          // [nch][128][64]   Z transposed: [value][token]
     __nv_bfloat16* dHp;         // [nch][128][128]  adjoint of each chunk's outgoing state, V-first
     __nv_bfloat16* dZT;         // [nch][128][64]   dZ transposed
+    __nv_bfloat16* Pn;          // [nch][128][128]  W^T E: [key k][key k'], the state-to-state part of the chunk transition
+    __nv_bfloat16* RmT;         // [nch][128][64]   (R - A W)^T: [key][token]
     float* decay_end;           // [nch][128]       exp(G_end)
     int* status;                // device status word (0 = ok)
 };
@@ -38,6 +40,8 @@ inline TcWs carve_tc(const KdaChunkShape& sh, void* mem, size_t* bytes = nullptr
     t.ZT = c.take<__nv_bfloat16>(nch * 8192);
     t.dHp = c.take<__nv_bfloat16>(nch * 16384);
     t.dZT = c.take<__nv_bfloat16>(nch * 8192);
+    t.Pn = c.take<__nv_bfloat16>(nch * 16384);
+    t.RmT = c.take<__nv_bfloat16>(nch * 8192);
     t.decay_end = c.take<float>(nch * 128);
     t.status = c.take<int>(64);
     if (bytes) *bytes = align_up(c.off, 256);
