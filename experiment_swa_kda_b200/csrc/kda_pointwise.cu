@@ -383,6 +383,63 @@ __global__ void __launch_bounds__(256) conv_fwd_kernel(int B, int T, int C, int 
     }
 }
 
+// Forward without a carried-in window and without a final-state output (the training path).  Lane = channel pair, so
+// every global access of a warp is one contiguous 128-byte (bf16) row segment; each thread slides the window over 8
+// consecutive tokens with all of its loads issued up front.
+template <bool BF16>
+__device__ __forceinline__ float2 ld_pair(const void* p, size_t i) {
+    if (BF16) return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(reinterpret_cast<const __nv_bfloat16*>(p) + i));
+    return *reinterpret_cast<const float2*>(reinterpret_cast<const float*>(p) + i);
+}
+template <bool BF16>
+__device__ __forceinline__ void st_pair(void* p, size_t i, float a, float b) {
+    if (BF16) *reinterpret_cast<__nv_bfloat162*>(reinterpret_cast<__nv_bfloat16*>(p) + i) = __floats2bfloat162_rn(a, b);
+    else *reinterpret_cast<float2*>(reinterpret_cast<float*>(p) + i) = make_float2(a, b);
+}
+
+constexpr int kConvPairT = 8;    // tokens per thread
+
+template <int W, bool BF16>
+__global__ void __launch_bounds__(256) conv_fwd_pair_kernel(int T, int C, int silu, const void* __restrict__ x,
+                                                            const void* __restrict__ wgt, void* __restrict__ y) {
+    const int p = threadIdx.x & 31, g = threadIdx.x >> 5;
+    const int c = blockIdx.x * 64 + 2 * p;
+    const int t0 = (blockIdx.y * 8 + g) * kConvPairT, b = blockIdx.z;
+    if (t0 >= T) return;
+    const bool cok = c < C;
+    const int cl = cok ? c : 0;
+    float w0[W], w1[W];
+#pragma unroll
+    for (int m = 0; m < W; ++m) {
+        w0[m] = ld_io(wgt, (size_t)cl * W + m, BF16);
+        w1[m] = ld_io(wgt, (size_t)(cl + 1) * W + m, BF16);
+    }
+    const size_t rowbase = (size_t)b * T;
+    float2 xin[kConvPairT + W - 1];
+#pragma unroll
+    for (int j = 0; j < kConvPairT + W - 1; ++j) {
+        const int t = t0 - (W - 1) + j;
+        const int tc = min(max(t, 0), T - 1);
+        float2 v = ld_pair<BF16>(x, (rowbase + tc) * C + cl);
+        if (t < 0 || t >= T) v = make_float2(0.f, 0.f);
+        xin[j] = v;
+    }
+#pragma unroll
+    for (int tt = 0; tt < kConvPairT; ++tt) {
+        float z0 = 0.f, z1 = 0.f;
+#pragma unroll
+        for (int m = 0; m < W; ++m) {
+            z0 += w0[m] * xin[tt + m].x;
+            z1 += w1[m] * xin[tt + m].y;
+        }
+        if (silu) {
+            z0 *= sigmoid_t<BF16>(z0);
+            z1 *= sigmoid_t<BF16>(z1);
+        }
+        if (t0 + tt < T && cok) st_pair<BF16>(y, (rowbase + t0 + tt) * C + c, z0, z1);
+    }
+}
+
 // Backward.  blockDim = (16 channel groups, 16 time tiles).  Each thread recomputes the
 // pre-activations of its tile plus W-1 following tokens, emits dx for its tile and a
 // register partial of dweight; the 8 tiles of a block are summed in shared memory and
@@ -569,6 +626,111 @@ __global__ void __launch_bounds__(256) conv_bwd_kernel(int B, int T, int C, int 
                 for (int r = 0; r < 16; ++r) a += red[r][threadIdx.x][j * VEC + e];
                 dw_part[(pblk * C + cg * VEC + e) * W + j] = a;
             }
+    }
+}
+
+// Backward without a carried-in window (no initial state, no final-state cotangent: the training path).  One block
+// owns 64 tokens x 64 channels.  It stages x (with a W-1 halo on both sides) and dy (W-1 halo after) in shared memory
+// as float pairs, turns dy into dz in place (each pre-activation is recomputed once, not once per window position),
+// then forms dx from the dz window and the block's dweight partial.  Lane = channel pair, so every global access of a
+// warp is one contiguous row segment; warp = row group.
+constexpr int kConvTileT = 64, kConvTileC = 64;
+
+template <int W, bool BF16>
+__global__ void __launch_bounds__(256) conv_bwd_tile_kernel(int T, int C, int silu, const void* __restrict__ x,
+                                                            const void* __restrict__ wgt, const void* __restrict__ dy,
+                                                            void* __restrict__ dx, float* __restrict__ dw_part) {
+    constexpr int XR = kConvTileT + 2 * (W - 1);   // x rows  t0-(W-1) .. t0+63+(W-1)
+    constexpr int GR = kConvTileT + W - 1;         // dy rows t0 .. t0+63+(W-1)
+    __shared__ float2 xs[XR][32];
+    __shared__ float2 gs[GR][32];
+    __shared__ float red[8][W][kConvTileC];
+    const int p = threadIdx.x & 31, g = threadIdx.x >> 5;
+    const int cb = blockIdx.x * kConvTileC;
+    const int c = cb + 2 * p;
+    const int t0 = blockIdx.y * kConvTileT, b = blockIdx.z;
+    const bool cok = c < C;
+    const int cl = cok ? c : 0;                    // loads stay unconditional: out-of-range lanes read column 0 and are masked
+    float w0[W], w1[W];
+#pragma unroll
+    for (int m = 0; m < W; ++m) {
+        w0[m] = ld_io(wgt, (size_t)cl * W + m, BF16);
+        w1[m] = ld_io(wgt, (size_t)(cl + 1) * W + m, BF16);
+    }
+    const size_t rowbase = (size_t)b * T;
+#pragma unroll
+    for (int r = g; r < XR; r += 8) {
+        const int t = t0 - (W - 1) + r;
+        const int tc = min(max(t, 0), T - 1);
+        float2 v = ld_pair<BF16>(x, (rowbase + tc) * C + cl);
+        if (t < 0 || t >= T || !cok) v = make_float2(0.f, 0.f);
+        xs[r][p] = v;
+    }
+#pragma unroll
+    for (int r = g; r < GR; r += 8) {
+        const int t = t0 + r;
+        const int tc = min(t, T - 1);
+        float2 v = ld_pair<BF16>(dy, (rowbase + tc) * C + cl);
+        if (t >= T || !cok) v = make_float2(0.f, 0.f);
+        gs[r][p] = v;
+    }
+    __syncthreads();
+    float dw0[W], dw1[W];
+#pragma unroll
+    for (int m = 0; m < W; ++m) dw0[m] = dw1[m] = 0.f;
+#pragma unroll
+    for (int r = g; r < GR; r += 8) {
+        float2 gy = gs[r][p];
+        float2 xv[W];
+        float z0 = 0.f, z1 = 0.f;
+#pragma unroll
+        for (int m = 0; m < W; ++m) {
+            xv[m] = xs[r + m][p];
+            z0 += w0[m] * xv[m].x;
+            z1 += w1[m] * xv[m].y;
+        }
+        if (silu) {
+            const float s0 = sigmoid_t<BF16>(z0), s1 = sigmoid_t<BF16>(z1);
+            gy.x *= s0 * (1.f + z0 * (1.f - s0));
+            gy.y *= s1 * (1.f + z1 * (1.f - s1));
+        }
+        gs[r][p] = gy;                             // dz; element (r, p) is touched by this thread only
+        if (r < kConvTileT) {                      // rows of the halo belong to the next block's dweight
+#pragma unroll
+            for (int m = 0; m < W; ++m) {
+                dw0[m] += gy.x * xv[m].x;
+                dw1[m] += gy.y * xv[m].y;
+            }
+        }
+    }
+#pragma unroll
+    for (int m = 0; m < W; ++m) {
+        red[g][m][2 * p] = dw0[m];
+        red[g][m][2 * p + 1] = dw1[m];
+    }
+    __syncthreads();
+    // dx[t] = sum_m w[m] dz[t + W-1-m]
+#pragma unroll
+    for (int r = g; r < kConvTileT; r += 8) {
+        const int t = t0 + r;
+        float a0 = 0.f, a1 = 0.f;
+#pragma unroll
+        for (int m = 0; m < W; ++m) {
+            const float2 d = gs[r + W - 1 - m][p];
+            a0 += w0[m] * d.x;
+            a1 += w1[m] * d.y;
+        }
+        if (t < T && cok) st_pair<BF16>(dx, (rowbase + t) * C + c, a0, a1);
+    }
+    if (threadIdx.x < kConvTileC && cb + threadIdx.x < C) {
+        const size_t pblk = (size_t)blockIdx.z * gridDim.y + blockIdx.y;
+#pragma unroll
+        for (int m = 0; m < W; ++m) {
+            float a = 0.f;
+#pragma unroll
+            for (int r = 0; r < 8; ++r) a += red[r][m][threadIdx.x];
+            dw_part[(pblk * C + cb + threadIdx.x) * W + m] = a;
+        }
     }
 }
 
@@ -836,6 +998,12 @@ int conv_fwd_w(int B, int T, int C, int bf16, int silu, const void* x, const voi
     const int ntile = ceil_div(T, pw::kConvTT);
     auto blocks = [&](int vec) { return (unsigned)(((size_t)B * ntile * (C / vec) + 255) / 256); };
     const bool al16 = ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y)) % 16) == 0;
+    if (!cache && !fin && C % 2 == 0 && al16) {
+        const dim3 grid(ceil_div(C, 64), ceil_div(T, 8 * pw::kConvPairT), B);
+        if (bf16) KDA_LAUNCH("conv_fwd_kernel", st, pw::conv_fwd_pair_kernel<W, true><<<grid, 256, 0, st>>>(T, C, silu, x, w, y));
+        else KDA_LAUNCH("conv_fwd_kernel", st, pw::conv_fwd_pair_kernel<W, false><<<grid, 256, 0, st>>>(T, C, silu, x, w, y));
+        return launch_status();
+    }
     if (bf16) {
         if (C % 8 == 0 && al16) KDA_LAUNCH("conv_fwd_kernel", st, pw::conv_fwd_kernel<W, 8, true><<<blocks(8), 256, 0, st>>>(B, T, C, silu, x, w, cache, y, fin));
         else KDA_LAUNCH("conv_fwd_kernel", st, pw::conv_fwd_kernel<W, 1, true><<<blocks(1), 256, 0, st>>>(B, T, C, silu, x, w, cache, y, fin));
@@ -855,6 +1023,18 @@ int conv_bwd_w(int B, int T, int C, int bf16, int silu, const void* x, const voi
                const void* dfin, void* dx, void* dcache, float* dwgt, float* part, cudaStream_t st) {
     const bool al16 = ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(dy) | reinterpret_cast<uintptr_t>(dx)) % 16) == 0;
     dim3 grid, block(16, 16);
+    if constexpr (W <= 4) {
+        // no carried-in window and no final-state cotangent: the tiled kernel (same partial layout: one row of
+        // partials per 64-token tile and batch entry)
+        if (!cache && !dfin && !dcache && C % 2 == 0 && al16) {
+            grid = dim3(ceil_div(C, pw::kConvTileC), ceil_div(T, pw::kConvTileT), B);
+            if (bf16) KDA_LAUNCH("conv_bwd_kernel", st, pw::conv_bwd_tile_kernel<W, true><<<grid, 256, 0, st>>>(T, C, silu, x, w, dy, dx, part));
+            else KDA_LAUNCH("conv_bwd_kernel", st, pw::conv_bwd_tile_kernel<W, false><<<grid, 256, 0, st>>>(T, C, silu, x, w, dy, dx, part));
+            const int nblk = grid.y * grid.z;
+            KDA_LAUNCH("conv_dw_reduce_kernel", st, pw::conv_dw_reduce_kernel<<<ceil_div(C * W, 32), 256, 0, st>>>(nblk, C * W, part, dwgt));
+            return launch_status();
+        }
+    }
     // the vector path keeps W*VEC partials per thread in shared memory; wide windows use the scalar path
     constexpr bool kVecOk = W <= 4;
     if (bf16) {

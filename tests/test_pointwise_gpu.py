@@ -68,6 +68,29 @@ def test_conv_bf16_matches_oracle(B, T, C, state):
         assert O.rel_l2(got[2].float(), want[2]) <= 1e-2
 
 
+@pytest.mark.parametrize("B,T,C,dtype", [(2, 4096, 384, torch.bfloat16), (1, 100, 20, torch.bfloat16), (2, 67, 384, torch.float32),
+                                         (3, 1, 64, torch.float32), (1, 5, 130, torch.bfloat16), (2, 129, 72, torch.float32)])
+def test_conv_training_path_matches_oracle(B, T, C, dtype):
+    """No carried-in window, no final state: the tiled forward / backward kernels (ragged T and C tails included)."""
+    gen = torch.Generator().manual_seed(T * 7 + C)
+    x = torch.randn(B, T, C, generator=gen).to(dtype)
+    w = (torch.rand(C, 4, generator=gen) * 2 - 1) * (3 ** 0.5) * C ** -0.5
+    mod = _conv_mod(C, 4, w.to(D0))
+    xd = x.to(D0).requires_grad_(True)
+    y, fs = mod(xd)
+    assert fs is None
+    xe = x.float().requires_grad_(True)
+    we = (w.to(dtype).float() if dtype == torch.bfloat16 else w.clone()).requires_grad_(True)
+    ye, _ = O.causal_conv(xe, we)
+    cy = torch.randn(ye.shape, generator=gen).to(dtype)
+    got = torch.autograd.grad(y, [xd, mod.weight], cy.to(D0))
+    want = torch.autograd.grad(ye, [xe, we], cy.float())
+    tol = 1e-2 if dtype == torch.bfloat16 else 1e-5
+    assert O.rel_l2(y.float(), ye) <= tol
+    assert O.rel_l2(got[0].float(), want[0]) <= tol
+    assert O.rel_l2(got[1].squeeze(1).float(), want[1]) <= tol
+
+
 def test_conv_full_sequence_equals_token_decode():
     gen = torch.Generator().manual_seed(99)
     x = torch.randn(2, 9, 8, generator=gen).to(D0)
