@@ -443,7 +443,7 @@ __global__ void __launch_bounds__(256) conv_fwd_pair_kernel(int T, int C, int si
 // Backward.  blockDim = (16 channel groups, 16 time tiles).  Each thread recomputes the
 // pre-activations of its tile plus W-1 following tokens, emits dx for its tile and a
 // register partial of dweight; the 8 tiles of a block are summed in shared memory and
-// written as one partial per block, reduced in fixed order by conv_dw_reduce_kernel.
+// written as one partial per block, reduced in fixed order by column_sum_kernel.
 constexpr int kConvBT = 4;   // tokens per thread in the backward
 
 template <int W, int VEC, bool BF16>
@@ -734,24 +734,6 @@ __global__ void __launch_bounds__(256) conv_bwd_tile_kernel(int T, int C, int si
     }
 }
 
-// 32 columns per block; 8 warps each sum every 8th partial row, then a fixed-order combine
-__global__ void __launch_bounds__(256) conv_dw_reduce_kernel(int nblk, int CW, const float* __restrict__ part,
-                                                             float* __restrict__ dw) {
-    __shared__ float red[8][32];
-    const int lane = threadIdx.x & 31, seg = threadIdx.x >> 5;
-    const int i = blockIdx.x * 32 + lane;
-    float a = 0.f;
-    if (i < CW)
-        for (int b = seg; b < nblk; b += 8) a += part[(size_t)b * CW + i];
-    red[seg][lane] = a;
-    __syncthreads();
-    if (seg == 0 && i < CW) {
-        float t = 0.f;
-#pragma unroll
-        for (int r = 0; r < 8; ++r) t += red[r][lane];
-        dw[i] = t;
-    }
-}
 
 // =============================================================================================
 // gated RMSNorm:  y = x * inv * w * sigmoid(gate),  inv = rsqrt(mean(x^2) + eps).  One warp per row.
@@ -900,24 +882,135 @@ __global__ void __launch_bounds__(256) rmsnorm_bwd_kernel(long long rows, int D,
     }
 }
 
-// 32 columns per block; 8 warps each sum every 8th partial row, then a fixed-order combine
-__global__ void __launch_bounds__(256) rmsnorm_dw_reduce_kernel(int nblk, int D, const float* __restrict__ part,
-                                                                float* __restrict__ dw) {
-    __shared__ float red[8][32];
-    const int lane = threadIdx.x & 31, seg = threadIdx.x >> 5;
-    const int d = blockIdx.x * 32 + lane;
-    float a = 0.f;
-    if (d < D)
-        for (int b = seg; b < nblk; b += 8) a += part[(size_t)b * D + d];
-    red[seg][lane] = a;
-    __syncthreads();
-    if (seg == 0 && d < D) {
-        float t = 0.f;
+// Rows of exactly 128 elements (the head width of the tensor-core lane): the row lives in registers, and a warp works on
+// four rows at a time with all of their loads issued before the first reduction, so that a thread has 8-12 independent
+// 8-byte (bf16) loads in flight instead of one row's worth.
+constexpr int kRmsRows = 4;
+
+template <bool BF16>
+__global__ void __launch_bounds__(256) rmsnorm_fwd128_kernel(long long rows, float eps, const void* __restrict__ x,
+                                                             const void* __restrict__ gate, const float* __restrict__ w,
+                                                             void* __restrict__ y, float* __restrict__ inv_rms) {
+    const int lane = threadIdx.x & 31;
+    const long long warp0 = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+    const long long nwarp = (long long)gridDim.x * 8;
+    const float4 ww = *reinterpret_cast<const float4*>(w + 4 * lane);
+    const float wa[4] = {ww.x, ww.y, ww.z, ww.w};
+    for (long long row0 = warp0 * kRmsRows; row0 < rows; row0 += nwarp * kRmsRows) {
+        float a[kRmsRows][4], gt[kRmsRows][4], ss[kRmsRows];
 #pragma unroll
-        for (int r = 0; r < 8; ++r) t += red[r][lane];
-        dw[d] = t;
+        for (int r = 0; r < kRmsRows; ++r) {
+            const size_t base = (size_t)min(row0 + r, rows - 1) * 128 + 4 * lane;
+            ld4<BF16>(a[r], x, base);
+            ld4<BF16>(gt[r], gate, base);
+        }
+#pragma unroll
+        for (int r = 0; r < kRmsRows; ++r) ss[r] = a[r][0] * a[r][0] + a[r][1] * a[r][1] + a[r][2] * a[r][2] + a[r][3] * a[r][3];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+            for (int r = 0; r < kRmsRows; ++r) ss[r] += __shfl_xor_sync(0xffffffffu, ss[r], o);
+#pragma unroll
+        for (int r = 0; r < kRmsRows; ++r) {
+            if (row0 + r < rows) {
+                const float inv = rsqrtf(ss[r] * (1.0f / 128.0f) + eps);
+                if (lane == 0) inv_rms[row0 + r] = inv;
+                float out[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) out[e] = a[r][e] * inv * wa[e] * sigmoid_t<BF16>(gt[r][e]);
+                st4<BF16>(y, (size_t)(row0 + r) * 128 + 4 * lane, out);
+            }
+        }
     }
 }
+
+template <bool BF16>
+__global__ void __launch_bounds__(256) rmsnorm_bwd128_kernel(long long rows, const void* __restrict__ x,
+                                                             const void* __restrict__ gate, const float* __restrict__ w,
+                                                             const float* __restrict__ inv_rms, const void* __restrict__ dy,
+                                                             void* __restrict__ dx, void* __restrict__ dgate,
+                                                             float* __restrict__ dw_part) {
+    __shared__ float dws[8][128];
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    const long long warp0 = (long long)blockIdx.x * 8 + wid;
+    const long long nwarp = (long long)gridDim.x * 8;
+    const float4 ww = *reinterpret_cast<const float4*>(w + 4 * lane);
+    const float wa[4] = {ww.x, ww.y, ww.z, ww.w};
+    float dwa[4] = {0.f, 0.f, 0.f, 0.f};
+    for (long long row0 = warp0 * kRmsRows; row0 < rows; row0 += nwarp * kRmsRows) {
+        float a[kRmsRows][4], gt[kRmsRows][4], gy[kRmsRows][4], inv[kRmsRows], dot[kRmsRows];
+#pragma unroll
+        for (int r = 0; r < kRmsRows; ++r) {
+            const long long rr = min(row0 + r, rows - 1);
+            const size_t base = (size_t)rr * 128 + 4 * lane;
+            ld4<BF16>(a[r], x, base);
+            ld4<BF16>(gt[r], gate, base);
+            ld4<BF16>(gy[r], dy, base);
+            inv[r] = inv_rms[rr];
+        }
+#pragma unroll
+        for (int r = 0; r < kRmsRows; ++r) {
+            dot[r] = 0.f;
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                gt[r][e] = sigmoid_t<BF16>(gt[r][e]);          // s
+                a[r][e] *= inv[r];                             // n
+                dot[r] += gy[r][e] * gt[r][e] * wa[e] * a[r][e];
+            }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+            for (int r = 0; r < kRmsRows; ++r) dot[r] += __shfl_xor_sync(0xffffffffu, dot[r], o);
+#pragma unroll
+        for (int r = 0; r < kRmsRows; ++r) {
+            if (row0 + r < rows) {
+                const float mean = dot[r] * (1.0f / 128.0f);
+                float ox[4], og[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float n = a[r][e], sg = gt[r][e];
+                    const float du = gy[r][e] * sg;
+                    og[e] = gy[r][e] * n * wa[e] * sg * (1.f - sg);
+                    ox[e] = inv[r] * (du * wa[e] - n * mean);
+                    dwa[e] += du * n;
+                }
+                const size_t base = (size_t)(row0 + r) * 128 + 4 * lane;
+                st4<BF16>(dx, base, ox);
+                st4<BF16>(dgate, base, og);
+            }
+        }
+    }
+#pragma unroll
+    for (int e = 0; e < 4; ++e) dws[wid][4 * lane + e] = dwa[e];
+    __syncthreads();
+    if (threadIdx.x < 128) {
+        float t = 0.f;
+#pragma unroll
+        for (int r = 0; r < 8; ++r) t += dws[r][threadIdx.x];
+        dw_part[(size_t)blockIdx.x * 128 + threadIdx.x] = t;
+    }
+}
+
+// out[i] = sum over b of part[b][i]: 32 columns per block, 32 row segments summed in a fixed order
+__global__ void __launch_bounds__(1024) column_sum_kernel(int nblk, int N, const float* __restrict__ part,
+                                                          float* __restrict__ out) {
+    __shared__ float red[32][33];
+    const int lane = threadIdx.x & 31, seg = threadIdx.x >> 5;
+    const int i = blockIdx.x * 32 + lane;
+    float a = 0.f;
+    if (i < N)
+        for (int b = seg; b < nblk; b += 32) a += part[(size_t)b * N + i];
+    red[seg][lane] = a;
+    __syncthreads();
+    if (seg == 0 && i < N) {
+        float t = 0.f;
+#pragma unroll
+        for (int r = 0; r < 32; ++r) t += red[r][lane];
+        out[i] = t;
+    }
+}
+
 
 }  // namespace pw
 }  // namespace kda
@@ -1031,7 +1124,7 @@ int conv_bwd_w(int B, int T, int C, int bf16, int silu, const void* x, const voi
             if (bf16) KDA_LAUNCH("conv_bwd_kernel", st, pw::conv_bwd_tile_kernel<W, true><<<grid, 256, 0, st>>>(T, C, silu, x, w, dy, dx, part));
             else KDA_LAUNCH("conv_bwd_kernel", st, pw::conv_bwd_tile_kernel<W, false><<<grid, 256, 0, st>>>(T, C, silu, x, w, dy, dx, part));
             const int nblk = grid.y * grid.z;
-            KDA_LAUNCH("conv_dw_reduce_kernel", st, pw::conv_dw_reduce_kernel<<<ceil_div(C * W, 32), 256, 0, st>>>(nblk, C * W, part, dwgt));
+            KDA_LAUNCH("conv_dw_reduce_kernel", st, pw::column_sum_kernel<<<ceil_div(C * W, 32), 1024, 0, st>>>(nblk, C * W, part, dwgt));
             return launch_status();
         }
     }
@@ -1061,7 +1154,7 @@ int conv_bwd_w(int B, int T, int C, int bf16, int silu, const void* x, const voi
         }
     }
     const int nblk = grid.y * grid.z;
-    KDA_LAUNCH("conv_dw_reduce_kernel", st, pw::conv_dw_reduce_kernel<<<ceil_div(C * W, 32), 256, 0, st>>>(nblk, C * W, part, dwgt));
+    KDA_LAUNCH("conv_dw_reduce_kernel", st, pw::column_sum_kernel<<<ceil_div(C * W, 32), 1024, 0, st>>>(nblk, C * W, part, dwgt));
     return launch_status();
 }
 
@@ -1127,6 +1220,12 @@ extern "C" int kda_rmsnorm_gate_fwd(int64_t rows, int32_t dim, int32_t io_dtype,
     const bool vec = dim % 128 == 0 &&
                      ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(gate) | reinterpret_cast<uintptr_t>(y) |
                        reinterpret_cast<uintptr_t>(weight)) % 16) == 0;
+    if (vec && dim == 128) {
+        const int nb4 = (int)std::min<long long>((rows + 8 * pw::kRmsRows - 1) / (8 * pw::kRmsRows), 148LL * 8);
+        if (io_dtype == KDA_DTYPE_BF16) KDA_LAUNCH("rmsnorm_fwd_kernel", st, pw::rmsnorm_fwd128_kernel<true><<<nb4, 256, 0, st>>>(rows, eps, x, gate, weight, y, inv_rms));
+        else KDA_LAUNCH("rmsnorm_fwd_kernel", st, pw::rmsnorm_fwd128_kernel<false><<<nb4, 256, 0, st>>>(rows, eps, x, gate, weight, y, inv_rms));
+        return launch_status();
+    }
     if (io_dtype == KDA_DTYPE_BF16) {
         if (vec) KDA_LAUNCH("rmsnorm_fwd_kernel", st, pw::rmsnorm_fwd_kernel<true, true><<<nb, 256, 0, st>>>(rows, dim, eps, x, gate, weight, y, inv_rms));
         else KDA_LAUNCH("rmsnorm_fwd_kernel", st, pw::rmsnorm_fwd_kernel<true, false><<<nb, 256, 0, st>>>(rows, dim, eps, x, gate, weight, y, inv_rms));
@@ -1155,7 +1254,10 @@ extern "C" int kda_rmsnorm_gate_bwd(int64_t rows, int32_t dim, int32_t io_dtype,
     const bool vec = dim % 128 == 0 &&
                      ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(gate) | reinterpret_cast<uintptr_t>(d_y) |
                        reinterpret_cast<uintptr_t>(dx) | reinterpret_cast<uintptr_t>(dgate) | reinterpret_cast<uintptr_t>(weight)) % 16) == 0;
-    if (nb > 0) {
+    if (nb > 0 && vec && dim == 128) {
+        if (io_dtype == KDA_DTYPE_BF16) KDA_LAUNCH("rmsnorm_bwd_kernel", st, pw::rmsnorm_bwd128_kernel<true><<<nb, 256, 0, st>>>(rows, x, gate, weight, inv_rms, d_y, dx, dgate, part));
+        else KDA_LAUNCH("rmsnorm_bwd_kernel", st, pw::rmsnorm_bwd128_kernel<false><<<nb, 256, 0, st>>>(rows, x, gate, weight, inv_rms, d_y, dx, dgate, part));
+    } else if (nb > 0) {
         if (io_dtype == KDA_DTYPE_BF16) {
             if (vec) KDA_LAUNCH("rmsnorm_bwd_kernel", st, pw::rmsnorm_bwd_kernel<true, true><<<nb, 256, smem, st>>>(rows, dim, x, gate, weight, inv_rms, d_y, dx, dgate, part));
             else KDA_LAUNCH("rmsnorm_bwd_kernel", st, pw::rmsnorm_bwd_kernel<true, false><<<nb, 256, smem, st>>>(rows, dim, x, gate, weight, inv_rms, d_y, dx, dgate, part));
@@ -1164,7 +1266,7 @@ extern "C" int kda_rmsnorm_gate_bwd(int64_t rows, int32_t dim, int32_t io_dtype,
             else KDA_LAUNCH("rmsnorm_bwd_kernel", st, pw::rmsnorm_bwd_kernel<false, false><<<nb, 256, smem, st>>>(rows, dim, x, gate, weight, inv_rms, d_y, dx, dgate, part));
         }
     }
-    KDA_LAUNCH("rmsnorm_dw_reduce_kernel", st, pw::rmsnorm_dw_reduce_kernel<<<ceil_div(dim, 32), 256, 0, st>>>(nb, dim, part, dweight));
+    KDA_LAUNCH("rmsnorm_dw_reduce_kernel", st, pw::column_sum_kernel<<<ceil_div(dim, 32), 1024, 0, st>>>(nb, dim, part, dweight));
     return launch_status();
 }
 
