@@ -281,13 +281,26 @@ __device__ __forceinline__ void st_vec(void* p, size_t i, const float (&src)[VEC
 }
 
 
+// one weight; float32 weights next to bf16 activations are rounded to bf16 first, which is what a cast of the
+// weight tensor to the activation dtype would have produced
+__device__ __forceinline__ float ld_w(const void* w, size_t i, bool bf16, int wf32) {
+    if (wf32) {
+        const float f = reinterpret_cast<const float*>(w)[i];
+        return bf16 ? __bfloat162float(__float2bfloat16(f)) : f;
+    }
+    return ld_io(w, i, bf16);
+}
+
 // weights of VEC adjacent channels: W*VEC contiguous elements starting at c0*W
 template <int W, int VEC, bool BF16>
-__device__ __forceinline__ void ld_weights(float (&wv)[W][VEC], const void* wgt, int c0) {
+__device__ __forceinline__ void ld_weights(float (&wv)[W][VEC], const void* wgt, int c0, int wf32) {
     float flat[W * VEC];
     constexpr int N = W * VEC;
     const size_t base = (size_t)c0 * W;
-    if (BF16 && N % 8 == 0 && (base % 8) == 0) {
+    if (wf32) {
+#pragma unroll
+        for (int j = 0; j < N; ++j) flat[j] = ld_w(wgt, base + j, BF16, 1);
+    } else if (BF16 && N % 8 == 0 && (base % 8) == 0) {
 #pragma unroll
         for (int j = 0; j < N / 8; ++j) {
             float t[8];
@@ -329,7 +342,7 @@ __device__ __forceinline__ void ld_xx(float (&dst)[VEC], const void* x, const vo
 }
 
 template <int W, int VEC, bool BF16>
-__global__ void __launch_bounds__(256) conv_fwd_kernel(int B, int T, int C, int silu, const void* __restrict__ x,
+__global__ void __launch_bounds__(256) conv_fwd_kernel(int B, int T, int C, int silu, int wf32, const void* __restrict__ x,
                                                        const void* __restrict__ wgt, const void* __restrict__ cache,
                                                        void* __restrict__ y, void* __restrict__ fin) {
     const int ncg = C / VEC, ntile = (T + kConvTT - 1) / kConvTT;
@@ -338,7 +351,7 @@ __global__ void __launch_bounds__(256) conv_fwd_kernel(int B, int T, int C, int 
     const int cg = (int)(gid % ncg), tile = (int)((gid / ncg) % ntile), b = (int)(gid / ((size_t)ncg * ntile));
     const int c0 = cg * VEC, t0 = tile * kConvTT, t1 = min(T, t0 + kConvTT);
     float wv[W][VEC];
-    ld_weights<W, VEC, BF16>(wv, wgt, c0);
+    ld_weights<W, VEC, BF16>(wv, wgt, c0, wf32);
     // inputs at times t0-(W-1) .. t0+kConvTT-1.  Interior tiles issue every load unconditionally (so they
     // overlap); only the first and last tile of a sequence take the guarded path.
     float xin[kConvTT + W - 1][VEC];
@@ -400,7 +413,7 @@ __device__ __forceinline__ void st_pair(void* p, size_t i, float a, float b) {
 constexpr int kConvPairT = 8;    // tokens per thread
 
 template <int W, bool BF16>
-__global__ void __launch_bounds__(256) conv_fwd_pair_kernel(int T, int C, int silu, const void* __restrict__ x,
+__global__ void __launch_bounds__(256) conv_fwd_pair_kernel(int T, int C, int silu, int wf32, const void* __restrict__ x,
                                                             const void* __restrict__ wgt, void* __restrict__ y) {
     const int p = threadIdx.x & 31, g = threadIdx.x >> 5;
     const int c = blockIdx.x * 64 + 2 * p;
@@ -411,8 +424,8 @@ __global__ void __launch_bounds__(256) conv_fwd_pair_kernel(int T, int C, int si
     float w0[W], w1[W];
 #pragma unroll
     for (int m = 0; m < W; ++m) {
-        w0[m] = ld_io(wgt, (size_t)cl * W + m, BF16);
-        w1[m] = ld_io(wgt, (size_t)(cl + 1) * W + m, BF16);
+        w0[m] = ld_w(wgt, (size_t)cl * W + m, BF16, wf32);
+        w1[m] = ld_w(wgt, (size_t)(cl + 1) * W + m, BF16, wf32);
     }
     const size_t rowbase = (size_t)b * T;
     float2 xin[kConvPairT + W - 1];
@@ -447,7 +460,7 @@ __global__ void __launch_bounds__(256) conv_fwd_pair_kernel(int T, int C, int si
 constexpr int kConvBT = 4;   // tokens per thread in the backward
 
 template <int W, int VEC, bool BF16>
-__global__ void __launch_bounds__(256) conv_bwd_kernel(int B, int T, int C, int silu, const void* __restrict__ x,
+__global__ void __launch_bounds__(256) conv_bwd_kernel(int B, int T, int C, int silu, int wf32, const void* __restrict__ x,
                                                        const void* __restrict__ wgt, const void* __restrict__ cache,
                                                        const void* __restrict__ dy, const void* __restrict__ dfin,
                                                        void* __restrict__ dx, void* __restrict__ dcache,
@@ -466,7 +479,7 @@ __global__ void __launch_bounds__(256) conv_bwd_kernel(int B, int T, int C, int 
     if (active) {
         const int c0 = cg * VEC, t0 = tile * kConvBT, t1 = min(T, t0 + kConvBT);
         float wv[W][VEC];
-        ld_weights<W, VEC, BF16>(wv, wgt, c0);
+        ld_weights<W, VEC, BF16>(wv, wgt, c0, wf32);
         if (t0 >= W - 1 && t0 + kConvBT + W <= T) {
             // interior tile: every load is unconditional and independent, then pure register arithmetic
             float xin[kConvBT + 2 * (W - 1)][VEC];   // x at t0-(W-1) .. t0+kConvBT+W-2
@@ -637,7 +650,7 @@ __global__ void __launch_bounds__(256) conv_bwd_kernel(int B, int T, int C, int 
 constexpr int kConvTileT = 64, kConvTileC = 64;
 
 template <int W, bool BF16>
-__global__ void __launch_bounds__(256) conv_bwd_tile_kernel(int T, int C, int silu, const void* __restrict__ x,
+__global__ void __launch_bounds__(256) conv_bwd_tile_kernel(int T, int C, int silu, int wf32, const void* __restrict__ x,
                                                             const void* __restrict__ wgt, const void* __restrict__ dy,
                                                             void* __restrict__ dx, float* __restrict__ dw_part) {
     constexpr int XR = kConvTileT + 2 * (W - 1);   // x rows  t0-(W-1) .. t0+63+(W-1)
@@ -654,8 +667,8 @@ __global__ void __launch_bounds__(256) conv_bwd_tile_kernel(int T, int C, int si
     float w0[W], w1[W];
 #pragma unroll
     for (int m = 0; m < W; ++m) {
-        w0[m] = ld_io(wgt, (size_t)cl * W + m, BF16);
-        w1[m] = ld_io(wgt, (size_t)(cl + 1) * W + m, BF16);
+        w0[m] = ld_w(wgt, (size_t)cl * W + m, BF16, wf32);
+        w1[m] = ld_w(wgt, (size_t)(cl + 1) * W + m, BF16, wf32);
     }
     const size_t rowbase = (size_t)b * T;
 #pragma unroll
@@ -1086,23 +1099,23 @@ extern "C" int kda_decode_step(int32_t n_seq, int32_t heads, int32_t key_dim, in
 namespace {
 
 template <int W>
-int conv_fwd_w(int B, int T, int C, int bf16, int silu, const void* x, const void* w, const void* cache, void* y,
+int conv_fwd_w(int B, int T, int C, int bf16, int wf32, int silu, const void* x, const void* w, const void* cache, void* y,
                void* fin, cudaStream_t st) {
     const int ntile = ceil_div(T, pw::kConvTT);
     auto blocks = [&](int vec) { return (unsigned)(((size_t)B * ntile * (C / vec) + 255) / 256); };
     const bool al16 = ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y)) % 16) == 0;
     if (!cache && !fin && C % 2 == 0 && al16) {
         const dim3 grid(ceil_div(C, 64), ceil_div(T, 8 * pw::kConvPairT), B);
-        if (bf16) KDA_LAUNCH("conv_fwd_kernel", st, pw::conv_fwd_pair_kernel<W, true><<<grid, 256, 0, st>>>(T, C, silu, x, w, y));
-        else KDA_LAUNCH("conv_fwd_kernel", st, pw::conv_fwd_pair_kernel<W, false><<<grid, 256, 0, st>>>(T, C, silu, x, w, y));
+        if (bf16) KDA_LAUNCH("conv_fwd_kernel", st, pw::conv_fwd_pair_kernel<W, true><<<grid, 256, 0, st>>>(T, C, silu, wf32, x, w, y));
+        else KDA_LAUNCH("conv_fwd_kernel", st, pw::conv_fwd_pair_kernel<W, false><<<grid, 256, 0, st>>>(T, C, silu, wf32, x, w, y));
         return launch_status();
     }
     if (bf16) {
-        if (C % 8 == 0 && al16) KDA_LAUNCH("conv_fwd_kernel", st, pw::conv_fwd_kernel<W, 8, true><<<blocks(8), 256, 0, st>>>(B, T, C, silu, x, w, cache, y, fin));
-        else KDA_LAUNCH("conv_fwd_kernel", st, pw::conv_fwd_kernel<W, 1, true><<<blocks(1), 256, 0, st>>>(B, T, C, silu, x, w, cache, y, fin));
+        if (C % 8 == 0 && al16) KDA_LAUNCH("conv_fwd_kernel", st, pw::conv_fwd_kernel<W, 8, true><<<blocks(8), 256, 0, st>>>(B, T, C, silu, wf32, x, w, cache, y, fin));
+        else KDA_LAUNCH("conv_fwd_kernel", st, pw::conv_fwd_kernel<W, 1, true><<<blocks(1), 256, 0, st>>>(B, T, C, silu, wf32, x, w, cache, y, fin));
     } else {
-        if (C % 4 == 0 && al16) KDA_LAUNCH("conv_fwd_kernel", st, pw::conv_fwd_kernel<W, 4, false><<<blocks(4), 256, 0, st>>>(B, T, C, silu, x, w, cache, y, fin));
-        else KDA_LAUNCH("conv_fwd_kernel", st, pw::conv_fwd_kernel<W, 1, false><<<blocks(1), 256, 0, st>>>(B, T, C, silu, x, w, cache, y, fin));
+        if (C % 4 == 0 && al16) KDA_LAUNCH("conv_fwd_kernel", st, pw::conv_fwd_kernel<W, 4, false><<<blocks(4), 256, 0, st>>>(B, T, C, silu, wf32, x, w, cache, y, fin));
+        else KDA_LAUNCH("conv_fwd_kernel", st, pw::conv_fwd_kernel<W, 1, false><<<blocks(1), 256, 0, st>>>(B, T, C, silu, wf32, x, w, cache, y, fin));
     }
     return launch_status();
 }
@@ -1112,7 +1125,7 @@ inline void conv_bwd_grid(int B, int T, int C, int vec, dim3& grid) {
 }
 
 template <int W>
-int conv_bwd_w(int B, int T, int C, int bf16, int silu, const void* x, const void* w, const void* cache, const void* dy,
+int conv_bwd_w(int B, int T, int C, int bf16, int wf32, int silu, const void* x, const void* w, const void* cache, const void* dy,
                const void* dfin, void* dx, void* dcache, float* dwgt, float* part, cudaStream_t st) {
     const bool al16 = ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(dy) | reinterpret_cast<uintptr_t>(dx)) % 16) == 0;
     dim3 grid, block(16, 16);
@@ -1121,8 +1134,8 @@ int conv_bwd_w(int B, int T, int C, int bf16, int silu, const void* x, const voi
         // partials per 64-token tile and batch entry)
         if (!cache && !dfin && !dcache && C % 2 == 0 && al16) {
             grid = dim3(ceil_div(C, pw::kConvTileC), ceil_div(T, pw::kConvTileT), B);
-            if (bf16) KDA_LAUNCH("conv_bwd_kernel", st, pw::conv_bwd_tile_kernel<W, true><<<grid, 256, 0, st>>>(T, C, silu, x, w, dy, dx, part));
-            else KDA_LAUNCH("conv_bwd_kernel", st, pw::conv_bwd_tile_kernel<W, false><<<grid, 256, 0, st>>>(T, C, silu, x, w, dy, dx, part));
+            if (bf16) KDA_LAUNCH("conv_bwd_kernel", st, pw::conv_bwd_tile_kernel<W, true><<<grid, 256, 0, st>>>(T, C, silu, wf32, x, w, dy, dx, part));
+            else KDA_LAUNCH("conv_bwd_kernel", st, pw::conv_bwd_tile_kernel<W, false><<<grid, 256, 0, st>>>(T, C, silu, wf32, x, w, dy, dx, part));
             const int nblk = grid.y * grid.z;
             KDA_LAUNCH("conv_dw_reduce_kernel", st, pw::column_sum_kernel<<<ceil_div(C * W, 32), 1024, 0, st>>>(nblk, C * W, part, dwgt));
             return launch_status();
@@ -1134,23 +1147,23 @@ int conv_bwd_w(int B, int T, int C, int bf16, int silu, const void* x, const voi
         if constexpr (kVecOk) {
             if (C % 8 == 0 && al16) {
                 conv_bwd_grid(B, T, C, 8, grid);
-                KDA_LAUNCH("conv_bwd_kernel", st, pw::conv_bwd_kernel<W, 8, true><<<grid, block, 0, st>>>(B, T, C, silu, x, w, cache, dy, dfin, dx, dcache, part));
+                KDA_LAUNCH("conv_bwd_kernel", st, pw::conv_bwd_kernel<W, 8, true><<<grid, block, 0, st>>>(B, T, C, silu, wf32, x, w, cache, dy, dfin, dx, dcache, part));
             }
         }
         if (!(kVecOk && C % 8 == 0 && al16)) {
             conv_bwd_grid(B, T, C, 1, grid);
-            KDA_LAUNCH("conv_bwd_kernel", st, pw::conv_bwd_kernel<W, 1, true><<<grid, block, 0, st>>>(B, T, C, silu, x, w, cache, dy, dfin, dx, dcache, part));
+            KDA_LAUNCH("conv_bwd_kernel", st, pw::conv_bwd_kernel<W, 1, true><<<grid, block, 0, st>>>(B, T, C, silu, wf32, x, w, cache, dy, dfin, dx, dcache, part));
         }
     } else {
         if constexpr (kVecOk) {
             if (C % 4 == 0 && al16) {
                 conv_bwd_grid(B, T, C, 4, grid);
-                KDA_LAUNCH("conv_bwd_kernel", st, pw::conv_bwd_kernel<W, 4, false><<<grid, block, 0, st>>>(B, T, C, silu, x, w, cache, dy, dfin, dx, dcache, part));
+                KDA_LAUNCH("conv_bwd_kernel", st, pw::conv_bwd_kernel<W, 4, false><<<grid, block, 0, st>>>(B, T, C, silu, wf32, x, w, cache, dy, dfin, dx, dcache, part));
             }
         }
         if (!(kVecOk && C % 4 == 0 && al16)) {
             conv_bwd_grid(B, T, C, 1, grid);
-            KDA_LAUNCH("conv_bwd_kernel", st, pw::conv_bwd_kernel<W, 1, false><<<grid, block, 0, st>>>(B, T, C, silu, x, w, cache, dy, dfin, dx, dcache, part));
+            KDA_LAUNCH("conv_bwd_kernel", st, pw::conv_bwd_kernel<W, 1, false><<<grid, block, 0, st>>>(B, T, C, silu, wf32, x, w, cache, dy, dfin, dx, dcache, part));
         }
     }
     const int nblk = grid.y * grid.z;
@@ -1178,9 +1191,10 @@ extern "C" int kda_conv_fwd(int32_t batch, int32_t seq_len, int32_t channels, in
                             void* final_state, void* stream) {
     if (batch <= 0 || seq_len <= 0 || channels <= 0 || width <= 0) return KDA_ERR_BAD_SHAPE;
     if (!x || !weight || !y) return KDA_ERR_NULL;
-    const int bf16 = io_dtype == KDA_DTYPE_BF16;
+    const int wf32 = (io_dtype & KDA_WEIGHT_F32) != 0;
+    const int bf16 = (io_dtype & 0xff) == KDA_DTYPE_BF16;
     cudaStream_t st = (cudaStream_t)stream;
-#define CALL(WW) conv_fwd_w<WW>(batch, seq_len, channels, bf16, silu, x, weight, initial_state, y, final_state, st)
+#define CALL(WW) conv_fwd_w<WW>(batch, seq_len, channels, bf16, wf32, silu, x, weight, initial_state, y, final_state, st)
     KDA_CONV_SWITCH(CALL)
 #undef CALL
 }
@@ -1197,10 +1211,11 @@ extern "C" int kda_conv_bwd(int32_t batch, int32_t seq_len, int32_t channels, in
     if (batch <= 0 || seq_len <= 0 || channels <= 0 || width <= 0) return KDA_ERR_BAD_SHAPE;
     if (!x || !weight || !d_y || !dx || !dweight) return KDA_ERR_NULL;
     if (!scratch || scratch_bytes < kda_conv_bwd_scratch_bytes(batch, seq_len, channels, width)) return KDA_ERR_WORKSPACE;
-    const int bf16 = io_dtype == KDA_DTYPE_BF16;
+    const int wf32 = (io_dtype & KDA_WEIGHT_F32) != 0;
+    const int bf16 = (io_dtype & 0xff) == KDA_DTYPE_BF16;
     cudaStream_t st = (cudaStream_t)stream;
 #define CALL(WW)                                                                                                  \
-    conv_bwd_w<WW>(batch, seq_len, channels, bf16, silu, x, weight, initial_state, d_y, d_final_state, dx,        \
+    conv_bwd_w<WW>(batch, seq_len, channels, bf16, wf32, silu, x, weight, initial_state, d_y, d_final_state, dx,  \
                    d_initial_state, dweight, static_cast<float*>(scratch), st)
     KDA_CONV_SWITCH(CALL)
 #undef CALL

@@ -131,10 +131,10 @@ __global__ void __launch_bounds__(256, 1)
 // affine scan: one CTA per (sequence, head) walks the chunks in order (forward) or in reverse (backward)
 //     forward    S = H^T   [v][k]:   S' = dec . S - S Pn   + U^T E           stores S (chunk-start state) per chunk
 //     backward   S = dH'^T [v][k]:   S' = dec . S - S Pn^T + dO^T Rm         stores S (adjoint of the chunk's outgoing state)
-// 320 threads, specialised by warp; they meet only through mbarriers:
-//   warps 0-7  state: thread (kh, v) owns S[v][64*kh .. 64*kh+63] in registers
-//   warp 8     one lane issues the TMA loads, two chunks ahead
-//   warp 9     one lane issues every UMMA and the TMA stores of the state panels
+// Threads are specialised by warp; they meet only through mbarriers:
+//   state warpgroups (kScanGroups of them): thread (g, v) owns S[v][g*kScanCols .. (g+1)*kScanCols) in registers
+//   next warp   one lane issues the TMA loads, two chunks ahead
+//   last warp   one lane issues every UMMA and the TMA stores of the state panels
 // TMEM: the accumulator is double-buffered (columns 0 / 128) so that the state-independent product of step c+1 is
 // issued while the state threads still read the accumulator of step c.  The bf16 state panel in shared memory is
 // double-buffered too, so the TMA store of panel c has a whole step to read it before it is packed again.
@@ -152,7 +152,12 @@ struct AffineScanArgs {
 constexpr int kPStage = 65536;                              // Pn 32 KB | X 16 KB (U^T or Rm^T) | Y 16 KB (E or dO)
 constexpr int kPStageBytes = kPStage + 512;                 // + exp(G_end), which lands in a ring of its own
 constexpr int kAffineScanSmem = 2 * kPStage + 2 * 32768 + 1024;
-constexpr int kAffineScanThreads = 320;
+#ifndef KDA_SCAN_GROUPS
+#define KDA_SCAN_GROUPS 2
+#endif
+constexpr int kScanGroups = KDA_SCAN_GROUPS;                // state warpgroups: each thread owns 128 / kScanGroups columns of a row
+constexpr int kScanCols = 128 / kScanGroups;
+constexpr int kAffineScanThreads = (4 * kScanGroups + 2) * 32;
 
 #ifdef KDA_PHASE_TIMING
 #define KDA_TICKP(n) do { if (tid == 0) { long long t_ = clock64(); acc[n] += t_ - tlast; tlast = t_; } } while (0)
@@ -187,7 +192,7 @@ __global__ void __launch_bounds__(kAffineScanThreads, 1)
         mbar_init(&bar_full[1], 1);
         mbar_init(&bar_free[0], 1);
         mbar_init(&bar_free[1], 1);
-        mbar_init(&bar_sop, 256);
+        mbar_init(&bar_sop, 128 * kScanGroups);
         mbar_init(&bar_mma, 1);
         mbar_fence_init();
         abort_flag = 0;
@@ -199,7 +204,7 @@ __global__ void __launch_bounds__(kAffineScanThreads, 1)
     const uint32_t tmem = tmem_slot;
     const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
 
-    if (warp == 8) {
+    if (warp == 4 * kScanGroups) {
         // ------------------------------------------------------------------ load warp
         if (lane == 0) {
             auto issue_loads = [&](int c) {
@@ -229,7 +234,7 @@ __global__ void __launch_bounds__(kAffineScanThreads, 1)
             if (!ok)   // unwinding: the copies in flight must land before the block may exit
                 for (int c = issued > 2 ? issued - 2 : 0; c < issued; ++c) mbar_wait(&bar_full[c & 1], (c >> 1) & 1, nullptr, 0);
         }
-    } else if (warp == 9) {
+    } else if (warp == 4 * kScanGroups + 1) {
         // ------------------------------------------------------------------ UMMA / panel-store thread
         if (lane == 0 && n > 0) {
             // state-independent product:  forward U^T E (A K-major, B MN-major), backward dO^T Rm (A MN-major, B K-major)
@@ -288,30 +293,31 @@ __global__ void __launch_bounds__(kAffineScanThreads, 1)
         }
     } else {
         // ------------------------------------------------------------------ state warpgroups
-        const int kh = warp >> 2;                  // key half of this thread
-        float s[64];
+        const int col0 = (warp >> 2) * kScanCols;  // first key column of this thread
+        float s[kScanCols];
         if (p.s_in) {
-            const float4* src = reinterpret_cast<const float4*>(p.s_in + (((size_t)seq * H + h) * 128 + v) * 128 + 64 * kh);
+            const float4* src = reinterpret_cast<const float4*>(p.s_in + (((size_t)seq * H + h) * 128 + v) * 128 + col0);
 #pragma unroll
-            for (int j = 0; j < 16; ++j) {
+            for (int j = 0; j < kScanCols / 4; ++j) {
                 float4 x = src[j];
                 s[4 * j] = x.x; s[4 * j + 1] = x.y; s[4 * j + 2] = x.z; s[4 * j + 3] = x.w;
             }
         } else {
 #pragma unroll
-            for (int j = 0; j < 64; ++j) s[j] = 0.f;
+            for (int j = 0; j < kScanCols; ++j) s[j] = 0.f;
         }
-        // this thread's half of the state row -> bf16 A operand (K-major, 128-byte swizzle)
+        // this thread's part of the state row -> bf16 A operand (K-major, 128-byte swizzle, two 64-key blocks)
         auto pack_state = [&](int c) {
-            uint8_t* dst = Sop + (c & 1) * 32768 + kh * 16384;
+            uint8_t* dst = Sop + (c & 1) * 32768;
 #pragma unroll
-            for (int c16 = 0; c16 < 8; ++c16) {
+            for (int q = 0; q < kScanCols / 8; ++q) {
+                const int gc = col0 / 8 + q;       // 16-byte chunk index along the 128 keys
                 uint4 u;
-                u.x = pack_bf16(s[8 * c16 + 0], s[8 * c16 + 1]);
-                u.y = pack_bf16(s[8 * c16 + 2], s[8 * c16 + 3]);
-                u.z = pack_bf16(s[8 * c16 + 4], s[8 * c16 + 5]);
-                u.w = pack_bf16(s[8 * c16 + 6], s[8 * c16 + 7]);
-                *reinterpret_cast<uint4*>(dst + sw128_off(v, c16)) = u;
+                u.x = pack_bf16(s[8 * q + 0], s[8 * q + 1]);
+                u.y = pack_bf16(s[8 * q + 2], s[8 * q + 3]);
+                u.z = pack_bf16(s[8 * q + 4], s[8 * q + 5]);
+                u.w = pack_bf16(s[8 * q + 6], s[8 * q + 7]);
+                *reinterpret_cast<uint4*>(dst + (gc >> 3) * 16384 + sw128_off(v, gc & 7)) = u;
             }
             fence_async_smem();
             tc_fence_before();
@@ -330,28 +336,22 @@ __global__ void __launch_bounds__(kAffineScanThreads, 1)
             }
             tc_fence_after();
             KDA_TICKP(1);
-            const float* dc = dec_ring[c & 3] + 64 * kh;
+            const float* dc = dec_ring[c & 3] + col0;
             {
-                uint32_t r0[32], r1[32];     // both halves in flight before the wait
-                tmem_ld32(tmem + lane_base + 128 * (c & 1) + 64 * kh, r0);
-                tmem_ld32(tmem + lane_base + 128 * (c & 1) + 64 * kh + 32, r1);
+                uint32_t r[kScanCols / 32][32];    // every part in flight before the wait
+#pragma unroll
+                for (int b = 0; b < kScanCols / 32; ++b) tmem_ld32(tmem + lane_base + 128 * (c & 1) + col0 + 32 * b, r[b]);
                 tmem_ld_wait();
 #pragma unroll
-                for (int j4 = 0; j4 < 8; ++j4) {
-                    const float4 dv = *reinterpret_cast<const float4*>(dc + 4 * j4);
-                    s[4 * j4 + 0] = dv.x * s[4 * j4 + 0] + __uint_as_float(r0[4 * j4 + 0]);
-                    s[4 * j4 + 1] = dv.y * s[4 * j4 + 1] + __uint_as_float(r0[4 * j4 + 1]);
-                    s[4 * j4 + 2] = dv.z * s[4 * j4 + 2] + __uint_as_float(r0[4 * j4 + 2]);
-                    s[4 * j4 + 3] = dv.w * s[4 * j4 + 3] + __uint_as_float(r0[4 * j4 + 3]);
-                }
+                for (int b = 0; b < kScanCols / 32; ++b)
 #pragma unroll
-                for (int j4 = 0; j4 < 8; ++j4) {
-                    const float4 dv = *reinterpret_cast<const float4*>(dc + 32 + 4 * j4);
-                    s[32 + 4 * j4 + 0] = dv.x * s[32 + 4 * j4 + 0] + __uint_as_float(r1[4 * j4 + 0]);
-                    s[32 + 4 * j4 + 1] = dv.y * s[32 + 4 * j4 + 1] + __uint_as_float(r1[4 * j4 + 1]);
-                    s[32 + 4 * j4 + 2] = dv.z * s[32 + 4 * j4 + 2] + __uint_as_float(r1[4 * j4 + 2]);
-                    s[32 + 4 * j4 + 3] = dv.w * s[32 + 4 * j4 + 3] + __uint_as_float(r1[4 * j4 + 3]);
-                }
+                    for (int j4 = 0; j4 < 8; ++j4) {
+                        const float4 dv = *reinterpret_cast<const float4*>(dc + 32 * b + 4 * j4);
+                        s[32 * b + 4 * j4 + 0] = dv.x * s[32 * b + 4 * j4 + 0] + __uint_as_float(r[b][4 * j4 + 0]);
+                        s[32 * b + 4 * j4 + 1] = dv.y * s[32 * b + 4 * j4 + 1] + __uint_as_float(r[b][4 * j4 + 1]);
+                        s[32 * b + 4 * j4 + 2] = dv.z * s[32 * b + 4 * j4 + 2] + __uint_as_float(r[b][4 * j4 + 2]);
+                        s[32 * b + 4 * j4 + 3] = dv.w * s[32 * b + 4 * j4 + 3] + __uint_as_float(r[b][4 * j4 + 3]);
+                    }
             }
             tc_fence_before();
             KDA_TICKP(2);
@@ -364,9 +364,9 @@ __global__ void __launch_bounds__(kAffineScanThreads, 1)
                    acc[1] / n, acc[2] / n, acc[3] / n);
 #endif
         if (ok && abort_flag == 0 && p.s_out) {
-            float4* dst = reinterpret_cast<float4*>(p.s_out + (((size_t)seq * H + h) * 128 + v) * 128 + 64 * kh);
+            float4* dst = reinterpret_cast<float4*>(p.s_out + (((size_t)seq * H + h) * 128 + v) * 128 + col0);
 #pragma unroll
-            for (int j = 0; j < 16; ++j) dst[j] = make_float4(s[4 * j], s[4 * j + 1], s[4 * j + 2], s[4 * j + 3]);
+            for (int j = 0; j < kScanCols / 4; ++j) dst[j] = make_float4(s[4 * j], s[4 * j + 1], s[4 * j + 2], s[4 * j + 3]);
         }
     }
     tc_fence_before();

@@ -211,6 +211,14 @@ def decode_step(q, k, v, g, beta, state, scale, l2norm=True, out_state: Optional
 # short convolution
 # --------------------------------------------------------------------------------------------
 
+KDA_WEIGHT_F32 = 0x100
+
+
+def _wflag(x, weight):
+    """float32 weights next to lower-precision activations are read as they are (rounded on load by the kernel)."""
+    return KDA_WEIGHT_F32 if (weight.dtype == torch.float32 and x.dtype != torch.float32) else 0
+
+
 def conv_fwd(x, weight, initial_state, want_final, silu=True):
     lib = _lib.load()
     dev = _need_cuda(x, weight, initial_state)
@@ -219,7 +227,7 @@ def conv_fwd(x, weight, initial_state, want_final, silu=True):
     y = torch.empty_like(x)
     fin = torch.empty(B, Cc, W, dtype=x.dtype, device=dev) if want_final else None
     with torch.cuda.device(dev):
-        rc = lib.kda_conv_fwd(B, T, Cc, W, _dt(x), 1 if silu else 0, _ptr(x), _ptr(weight), _ptr(initial_state), _ptr(y),
+        rc = lib.kda_conv_fwd(B, T, Cc, W, _dt(x) | _wflag(x, weight), 1 if silu else 0, _ptr(x), _ptr(weight), _ptr(initial_state), _ptr(y),
                               _ptr(fin), _stream(dev))
     _lib.check(rc, "kda_conv_fwd")
     return y, fin
@@ -235,7 +243,7 @@ def conv_bwd(x, weight, initial_state, dy, dfin, silu=True):
     dinit = torch.empty_like(initial_state) if initial_state is not None else None
     scr = _bytes(lib.kda_conv_bwd_scratch_bytes(B, T, Cc, W), dev)
     with torch.cuda.device(dev):
-        rc = lib.kda_conv_bwd(B, T, Cc, W, _dt(x), 1 if silu else 0, _ptr(x), _ptr(weight), _ptr(initial_state), _ptr(dy),
+        rc = lib.kda_conv_bwd(B, T, Cc, W, _dt(x) | _wflag(x, weight), 1 if silu else 0, _ptr(x), _ptr(weight), _ptr(initial_state), _ptr(dy),
                               _ptr(dfin), _ptr(dx), _ptr(dw), _ptr(dinit), _ptr(scr), scr.numel(), _stream(dev))
     _lib.check(rc, "kda_conv_bwd")
     return dx, dw, dinit
@@ -248,7 +256,9 @@ class ConvFunction(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, weight, initial_state, output_final_state, silu):
         x = x.contiguous()
-        w = weight.contiguous().to(x.dtype)
+        w = weight.contiguous()
+        if w.dtype != torch.float32:
+            w = w.to(x.dtype)
         s0 = None if initial_state is None else initial_state.contiguous().to(x.dtype)
         y, fin = conv_fwd(x, w, s0, output_final_state, silu)
         ctx.save_for_backward(x, w, s0)

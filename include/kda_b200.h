@@ -35,6 +35,10 @@ extern "C" {
 
 #define KDA_DTYPE_F32 0
 #define KDA_DTYPE_BF16 1
+/* kda_conv_fwd / kda_conv_bwd only: OR this into io_dtype when `weight` is float32 although the activations are
+ * not; each weight is then rounded to the activation dtype as it is loaded (the result a cast of the weight tensor
+ * would give) and no converted copy of the weights is needed. */
+#define KDA_WEIGHT_F32 0x100
 
 #define KDA_LANE_FP32 0 /* CUDA-core float32 arithmetic, any K, V <= 256 */
 #define KDA_LANE_TC 1   /* tcgen05 BF16 tensor-core tiles, float32 accumulation and state */
