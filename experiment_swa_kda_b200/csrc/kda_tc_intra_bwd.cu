@@ -557,17 +557,38 @@ __global__ void __launch_bounds__(512, 1)
     KDA_TICKB(15);
     // L2-normalisation VJP needs per-row dots over the channels: unit k is kn, unit q is qn / scale
     const float inv_scale = p.scale != 0.f ? 1.0f / p.scale : 0.f;
+    {
+        // 32 per-row products (q and k of 16 rows) summed over the 32 channels of this warp with 31 shuffles: each
+        // step halves the values a lane carries, so lane L ends with the warp's total of value L.
+        float vals[16];
+        {
+            const bool up = (lane & 16) != 0;      // first step straight from the operands: value j pairs with value j + 16
 #pragma unroll
-    for (int r = 0; r < 16; ++r) {
-        const int i = 16 * I + r;
-        const float pq = warp_sum(qn[r] * inv_scale * dqn[r] * p.scale);
-        const float pk = warp_sum(kn[r] * dkn[r]);
-        if (lane == 0) {
-            dots[i * 8 + (warp & 3) * 2] = pq;
-            dots[i * 8 + (warp & 3) * 2 + 1] = pk;
+            for (int j = 0; j < 16; ++j) {
+                const float a = (j & 1) ? kn[j >> 1] * dkn[j >> 1] : qn[j >> 1] * dqn[j >> 1];                  // value j
+                const float b = (j & 1) ? kn[8 + (j >> 1)] * dkn[8 + (j >> 1)] : qn[8 + (j >> 1)] * dqn[8 + (j >> 1)];   // j + 16
+                vals[j] = (up ? b : a) + __shfl_xor_sync(0xffffffffu, up ? a : b, 16);
+            }
         }
+#pragma unroll
+        for (int o = 8; o >= 1; o >>= 1) {
+            const bool up = (lane & o) != 0;
+#pragma unroll
+            for (int j = 0; j < o; ++j) {
+                const float send = up ? vals[j] : vals[j + o];
+                const float keep = up ? vals[j + o] : vals[j];
+                vals[j] = keep + __shfl_xor_sync(0xffffffffu, send, o);
+            }
+        }
+        // lane L holds value L = (row L/2, q or k): quadrant partial
+        dots[(16 * I + (lane >> 1)) * 8 + (warp & 3) * 2 + (lane & 1)] = vals[0];
     }
     KDA_TICKB(16);
+    __syncthreads();
+    if (tid < 128) {          // the four quadrant partials of (row, q|k) -> one number, in place
+        const int i = tid >> 1, w = tid & 1;
+        dots[i * 8 + w] = dots[i * 8 + w] + dots[i * 8 + 2 + w] + dots[i * 8 + 4 + w] + dots[i * 8 + 6 + w];
+    }
     __syncthreads();
     KDA_TICKB(17);
     if (ok) {
@@ -581,8 +602,8 @@ __global__ void __launch_bounds__(512, 1)
                 st_io(p.dg, o, p.gbf16, run);
                 float dqv, dkv;
                 if (p.l2norm) {
-                    const float pq = dots[i * 8] + dots[i * 8 + 2] + dots[i * 8 + 4] + dots[i * 8 + 6];
-                    const float pk = dots[i * 8 + 1] + dots[i * 8 + 3] + dots[i * 8 + 5] + dots[i * 8 + 7];
+                    const float2 pp = *reinterpret_cast<const float2*>(dots + i * 8);
+                    const float pq = pp.x, pk = pp.y;
                     dqv = rowv[i] * (dqn[r] * p.scale - qn[r] * inv_scale * pq);
                     dkv = rowv[64 + i] * (dkn[r] - kn[r] * pk);
                 } else {
