@@ -232,8 +232,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-graph", action="store_true", help="launch every step eagerly instead of replaying a CUDA graph")
     ap.add_argument("--tokens", type=int, default=8 * 8192, help="packed tokens of the varlen workload")
-    ap.add_argument("--workload", default="chain", choices=["chain", "varlen", "decode"],
-                    help="chain = config 1 (default, the driver's line); varlen = config 3; decode = config 4")
+    ap.add_argument("--workload", default="chain", choices=["chain", "varlen", "decode", "pointwise"],
+                    help="chain = config 1 (default, the driver's line); varlen = config 3; decode = config 4; pointwise = conv / gated RMSNorm at 256 MiB tensors")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

@@ -5,6 +5,9 @@ lengths ~ U[256, 8192], per-sequence initial states ~ N(0, 0.02), bf16 I/O.  Wit
 sharded (H/N per GPU, every GPU sees all sequences), no collective.
 decode (BASELINE config 4): recurrent decode, batch 256, H=16, Dk=Dv=128, fp32 state ~ N(0, 0.02), one token
 per step; the state (256 MiB) is read and rewritten every step.  With N GPUs the batch is sharded.
+pointwise: the HBM-bound kernels either side of the KDA operator at a size that cannot sit in L2: short convolution
+(W=4, SiLU) and gated RMSNorm, forward and backward, on 65,536 tokens x 2,048 channels (256 MiB bf16 per tensor).
+Each kernel is timed alone with CUDA events; the figure is algorithmic bytes / time against the measured HBM peak.
 Each prints one JSON line on rank 0 with the metric, the algorithmic roofline figure and the per-kernel times.
 """
 
@@ -183,12 +186,63 @@ def run_decode(args, rank, world, local, dist):
     print(json.dumps(line), flush=True)
 
 
+def run_pointwise(args, rank, world, local, dist):
+    from experiment_swa_kda_b200 import ops
+    dev = torch.device(f"cuda:{local}")
+    T, C, D, W = 65536, 2048, 128, 4
+    bf = torch.bfloat16
+    gen = torch.Generator(device=dev).manual_seed(11 + rank)
+    rnd = lambda *sh: torch.randn(*sh, generator=gen, device=dev, dtype=torch.float32).to(bf)
+    x, dy = rnd(1, T, C), rnd(1, T, C)
+    w = ((torch.rand(C, W, generator=gen, device=dev) * 2 - 1) * (3 ** 0.5) * C ** -0.5)
+    xr, gate, dyr = x.view(T * C // D, D), rnd(T * C // D, D), dy.view(T * C // D, D)
+    nw = torch.ones(D, device=dev)
+    _, inv = ops.rmsnorm_gate_fwd(xr, gate, nw, 1e-6)
+    n = T * C * 2                                       # bytes of one bf16 tensor
+    cases = {
+        "conv_fwd": (lambda: ops.conv_fwd(x, w, None, False, True), 2 * n),
+        "conv_bwd": (lambda: ops.conv_bwd(x, w, None, dy, None, True), 3 * n),
+        "rmsnorm_gate_fwd": (lambda: ops.rmsnorm_gate_fwd(xr, gate, nw, 1e-6), 3 * n),
+        "rmsnorm_gate_bwd": (lambda: ops.rmsnorm_gate_bwd(xr, gate, nw, inv, dyr), 5 * n),
+    }
+    peaks, src = _peaks()
+    out = {}
+    for name, (fn, nbytes) in cases.items():
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize(dev)
+        evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(max(args.steps, 5))]
+        for a, b in evs:
+            a.record()
+            fn()
+            b.record()
+        torch.cuda.synchronize(dev)
+        ts = sorted(a.elapsed_time(b) for a, b in evs)
+        ms = ts[len(ts) // 2]
+        gbs = nbytes / (ms * 1e-3) / 1e9
+        out[name] = {"us": ms * 1e3, "algorithmic_bytes": nbytes, "gbs": gbs, "frac_of_hbm_peak": gbs / peaks["hbm_gbs"]}
+    if rank != 0:
+        return
+    worst = min(out, key=lambda k: out[k]["frac_of_hbm_peak"])
+    line = {
+        "metric": "pointwise_hbm_GBps_min", "value": out[worst]["gbs"], "unit": "GB/s", "n_gpus": world, "steps": max(args.steps, 5),
+        "warmup": 3, "higher_is_better": True, "scaling": "weak", "dtype": "bf16 I/O, f32 math", "data": "synthetic",
+        "config": {"workload": f"short convolution (W=4, SiLU) and gated RMSNorm fwd/bwd on {T} tokens x {C} channels "
+                               f"(256 MiB per tensor, larger than L2), each kernel timed alone, median",
+                   "timing": "includes the weight-gradient partial reduction launch for the two backward calls"},
+        "kernels": out,
+        "roofline": {"kernel": worst, "bound": "hbm", "achieved": out[worst]["gbs"], "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                     "frac": out[worst]["frac_of_hbm_peak"], "traffic": None, "peak_source": src},
+    }
+    print(json.dumps(line), flush=True)
+
+
 def run(args, rank, world, local):
     import torch.distributed as dist
     dev = torch.device(f"cuda:{local}")
     torch.cuda.set_device(dev)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
-    (run_varlen if args.workload == "varlen" else run_decode)(args, rank, world, local, dist)
+    {"varlen": run_varlen, "decode": run_decode, "pointwise": run_pointwise}[args.workload](args, rank, world, local, dist)
     if world > 1:
         dist.destroy_process_group()

@@ -5,6 +5,8 @@
 
 #include <algorithm>
 
+#include <type_traits>
+
 #include "common.cuh"
 
 namespace kda {
@@ -410,46 +412,116 @@ __device__ __forceinline__ void st_pair(void* p, size_t i, float a, float b) {
     else *reinterpret_cast<float2*>(reinterpret_cast<float*>(p) + i) = make_float2(a, b);
 }
 
+// N consecutive weights starting at element `base` (the W taps of N / W adjacent channels), with 16-byte loads when the
+// run is 16-byte aligned: a warp then reads one contiguous span instead of 32 scattered words per tap.
+template <int N, bool BF16>
+__device__ __forceinline__ void ld_wrun(float (&flat)[N], const void* wgt, size_t base, int wf32) {
+    const bool f32 = wf32 || !BF16;
+    if (f32 && N % 4 == 0 && base % 4 == 0) {
+#pragma unroll
+        for (int j = 0; j < N / 4; ++j) {
+            const float4 f = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(wgt) + base + 4 * j);
+            flat[4 * j] = f.x; flat[4 * j + 1] = f.y; flat[4 * j + 2] = f.z; flat[4 * j + 3] = f.w;
+        }
+        if (BF16) {
+#pragma unroll
+            for (int j = 0; j < N; ++j) flat[j] = __bfloat162float(__float2bfloat16(flat[j]));
+        }
+    } else if (!f32 && N % 8 == 0 && base % 8 == 0) {
+#pragma unroll
+        for (int j = 0; j < N / 8; ++j) {
+            float t[8];
+            ld_vec<8, true>(t, wgt, base + 8 * j);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) flat[8 * j + e] = t[e];
+        }
+    } else {
+#pragma unroll
+        for (int j = 0; j < N; ++j) flat[j] = ld_w(wgt, base + j, BF16, wf32);
+    }
+}
+
 constexpr int kConvPairT = 8;    // tokens per thread
 
-template <int W, bool BF16>
+// VEC adjacent channels (2 or 4) as floats
+template <int VEC, bool BF16>
+__device__ __forceinline__ void ld_cvec(float (&d)[VEC], const void* p, size_t i) {
+    if (VEC == 2) {
+        const float2 v = ld_pair<BF16>(p, i);
+        d[0] = v.x; d[1] = v.y;
+    } else if (BF16) {
+        const uint2 u = *reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(p) + i);
+        const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.x));
+        const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.y));
+        d[0] = a.x; d[1] = a.y; d[2] = b.x; d[3] = b.y;
+    } else {
+        const float4 f = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p) + i);
+        d[0] = f.x; d[1] = f.y; d[2] = f.z; d[3] = f.w;
+    }
+}
+template <int VEC, bool BF16>
+__device__ __forceinline__ void st_cvec(void* p, size_t i, const float (&s)[VEC]) {
+    if (VEC == 2) {
+        st_pair<BF16>(p, i, s[0], s[1]);
+    } else if (BF16) {
+        uint2 u;
+        *reinterpret_cast<__nv_bfloat162*>(&u.x) = __floats2bfloat162_rn(s[0], s[1]);
+        *reinterpret_cast<__nv_bfloat162*>(&u.y) = __floats2bfloat162_rn(s[2], s[3]);
+        *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(p) + i) = u;
+    } else {
+        *reinterpret_cast<float4*>(reinterpret_cast<float*>(p) + i) = make_float4(s[0], s[1], s[2], s[3]);
+    }
+}
+
+// grid: x = channel blocks of 32*VEC, y = blocks of 8 time groups x kConvPairT tokens, z = batch
+template <int W, int VEC, bool BF16>
 __global__ void __launch_bounds__(256) conv_fwd_pair_kernel(int T, int C, int silu, int wf32, const void* __restrict__ x,
                                                             const void* __restrict__ wgt, void* __restrict__ y) {
     const int p = threadIdx.x & 31, g = threadIdx.x >> 5;
-    const int c = blockIdx.x * 64 + 2 * p;
+    const int c = (blockIdx.x * 32 + p) * VEC;
     const int t0 = (blockIdx.y * 8 + g) * kConvPairT, b = blockIdx.z;
     if (t0 >= T) return;
     const bool cok = c < C;
     const int cl = cok ? c : 0;
-    float w0[W], w1[W];
+    float wv[W][VEC];
+    {
+        float flat[W * VEC];
+        ld_wrun<W * VEC, BF16>(flat, wgt, (size_t)cl * W, wf32);
 #pragma unroll
-    for (int m = 0; m < W; ++m) {
-        w0[m] = ld_w(wgt, (size_t)cl * W + m, BF16, wf32);
-        w1[m] = ld_w(wgt, (size_t)(cl + 1) * W + m, BF16, wf32);
+        for (int e = 0; e < VEC; ++e)
+#pragma unroll
+            for (int m = 0; m < W; ++m) wv[m][e] = flat[e * W + m];
     }
     const size_t rowbase = (size_t)b * T;
-    float2 xin[kConvPairT + W - 1];
+    float xin[kConvPairT + W - 1][VEC];
+    if (t0 >= W - 1 && t0 + kConvPairT <= T) {
+        // interior: plain address arithmetic, every load independent
+        const size_t base = (rowbase + t0 - (W - 1)) * C + cl;
 #pragma unroll
-    for (int j = 0; j < kConvPairT + W - 1; ++j) {
-        const int t = t0 - (W - 1) + j;
-        const int tc = min(max(t, 0), T - 1);
-        float2 v = ld_pair<BF16>(x, (rowbase + tc) * C + cl);
-        if (t < 0 || t >= T) v = make_float2(0.f, 0.f);
-        xin[j] = v;
+        for (int j = 0; j < kConvPairT + W - 1; ++j) ld_cvec<VEC, BF16>(xin[j], x, base + (size_t)j * C);
+    } else {
+#pragma unroll
+        for (int j = 0; j < kConvPairT + W - 1; ++j) {
+            const int t = t0 - (W - 1) + j;
+            const int tc = min(max(t, 0), T - 1);
+            ld_cvec<VEC, BF16>(xin[j], x, (rowbase + tc) * C + cl);
+            if (t < 0 || t >= T) {
+#pragma unroll
+                for (int e = 0; e < VEC; ++e) xin[j][e] = 0.f;
+            }
+        }
     }
 #pragma unroll
     for (int tt = 0; tt < kConvPairT; ++tt) {
-        float z0 = 0.f, z1 = 0.f;
+        float out[VEC];
 #pragma unroll
-        for (int m = 0; m < W; ++m) {
-            z0 += w0[m] * xin[tt + m].x;
-            z1 += w1[m] * xin[tt + m].y;
+        for (int e = 0; e < VEC; ++e) {
+            float z = 0.f;
+#pragma unroll
+            for (int m = 0; m < W; ++m) z += wv[m][e] * xin[tt + m][e];
+            out[e] = silu ? z * sigmoid_t<BF16>(z) : z;
         }
-        if (silu) {
-            z0 *= sigmoid_t<BF16>(z0);
-            z1 *= sigmoid_t<BF16>(z1);
-        }
-        if (t0 + tt < T && cok) st_pair<BF16>(y, (rowbase + t0 + tt) * C + c, z0, z1);
+        if (t0 + tt < T && cok) st_cvec<VEC, BF16>(y, (rowbase + t0 + tt) * C + c, out);
     }
 }
 
@@ -655,7 +727,10 @@ __global__ void __launch_bounds__(256) conv_bwd_tile_kernel(int T, int C, int si
                                                             void* __restrict__ dx, float* __restrict__ dw_part) {
     constexpr int XR = kConvTileT + 2 * (W - 1);   // x rows  t0-(W-1) .. t0+63+(W-1)
     constexpr int GR = kConvTileT + W - 1;         // dy rows t0 .. t0+63+(W-1)
-    __shared__ float2 xs[XR][32];
+    constexpr int RPW = kConvTileT / 8;            // consecutive rows per warp
+    // x stays in its storage type (a bf16 pair is one 32-bit word); dy is widened because dz replaces it in place
+    typedef typename std::conditional<BF16, __nv_bfloat162, float2>::type xpair_t;
+    __shared__ xpair_t xs[XR][32];
     __shared__ float2 gs[GR][32];
     __shared__ float red[8][W][kConvTileC];
     const int p = threadIdx.x & 31, g = threadIdx.x >> 5;
@@ -665,25 +740,35 @@ __global__ void __launch_bounds__(256) conv_bwd_tile_kernel(int T, int C, int si
     const bool cok = c < C;
     const int cl = cok ? c : 0;                    // loads stay unconditional: out-of-range lanes read column 0 and are masked
     float w0[W], w1[W];
+    {
+        float flat[2 * W];
+        ld_wrun<2 * W, BF16>(flat, wgt, (size_t)cl * W, wf32);
 #pragma unroll
-    for (int m = 0; m < W; ++m) {
-        w0[m] = ld_w(wgt, (size_t)cl * W + m, BF16, wf32);
-        w1[m] = ld_w(wgt, (size_t)(cl + 1) * W + m, BF16, wf32);
+        for (int m = 0; m < W; ++m) {
+            w0[m] = flat[m];
+            w1[m] = flat[W + m];
+        }
     }
     const size_t rowbase = (size_t)b * T;
+    auto xload = [&](int tc) -> xpair_t {
+        if constexpr (BF16) return *reinterpret_cast<const __nv_bfloat162*>(reinterpret_cast<const __nv_bfloat16*>(x) + (rowbase + tc) * C + cl);
+        else return *reinterpret_cast<const float2*>(reinterpret_cast<const float*>(x) + (rowbase + tc) * C + cl);
+    };
+    auto xwide = [](const xpair_t& v) -> float2 {
+        if constexpr (BF16) return __bfloat1622float2(v);
+        else return v;
+    };
 #pragma unroll
     for (int r = g; r < XR; r += 8) {
         const int t = t0 - (W - 1) + r;
-        const int tc = min(max(t, 0), T - 1);
-        float2 v = ld_pair<BF16>(x, (rowbase + tc) * C + cl);
-        if (t < 0 || t >= T || !cok) v = make_float2(0.f, 0.f);
+        xpair_t v = xload(min(max(t, 0), T - 1));
+        if (t < 0 || t >= T || !cok) v = xpair_t();
         xs[r][p] = v;
     }
 #pragma unroll
     for (int r = g; r < GR; r += 8) {
         const int t = t0 + r;
-        const int tc = min(t, T - 1);
-        float2 v = ld_pair<BF16>(dy, (rowbase + tc) * C + cl);
+        float2 v = ld_pair<BF16>(dy, (rowbase + min(t, T - 1)) * C + cl);
         if (t >= T || !cok) v = make_float2(0.f, 0.f);
         gs[r][p] = v;
     }
@@ -691,49 +776,69 @@ __global__ void __launch_bounds__(256) conv_bwd_tile_kernel(int T, int C, int si
     float dw0[W], dw1[W];
 #pragma unroll
     for (int m = 0; m < W; ++m) dw0[m] = dw1[m] = 0.f;
+    // dz for rows r0 .. r0+n-1, walking down with the x window in registers; dweight only from the tile's own rows
+    auto dz_rows = [&](int r0, int n, bool own) {
+        float2 xw[W];
 #pragma unroll
-    for (int r = g; r < GR; r += 8) {
-        float2 gy = gs[r][p];
-        float2 xv[W];
-        float z0 = 0.f, z1 = 0.f;
+        for (int m = 0; m < W - 1; ++m) xw[m] = xwide(xs[r0 + m][p]);
 #pragma unroll
-        for (int m = 0; m < W; ++m) {
-            xv[m] = xs[r + m][p];
-            z0 += w0[m] * xv[m].x;
-            z1 += w1[m] * xv[m].y;
-        }
-        if (silu) {
-            const float s0 = sigmoid_t<BF16>(z0), s1 = sigmoid_t<BF16>(z1);
-            gy.x *= s0 * (1.f + z0 * (1.f - s0));
-            gy.y *= s1 * (1.f + z1 * (1.f - s1));
-        }
-        gs[r][p] = gy;                             // dz; element (r, p) is touched by this thread only
-        if (r < kConvTileT) {                      // rows of the halo belong to the next block's dweight
+        for (int i = 0; i < RPW; ++i) {
+            if (i < n) {
+                const int r = r0 + i;
+                xw[W - 1] = xwide(xs[r + W - 1][p]);
+                float2 gy = gs[r][p];
+                float z0 = 0.f, z1 = 0.f;
 #pragma unroll
-            for (int m = 0; m < W; ++m) {
-                dw0[m] += gy.x * xv[m].x;
-                dw1[m] += gy.y * xv[m].y;
+                for (int m = 0; m < W; ++m) {
+                    z0 += w0[m] * xw[m].x;
+                    z1 += w1[m] * xw[m].y;
+                }
+                if (silu) {
+                    const float s0 = sigmoid_t<BF16>(z0), s1 = sigmoid_t<BF16>(z1);
+                    gy.x *= s0 * (1.f + z0 * (1.f - s0));
+                    gy.y *= s1 * (1.f + z1 * (1.f - s1));
+                }
+                gs[r][p] = gy;                     // dz; element (r, p) is touched by this thread only
+                if (own) {
+#pragma unroll
+                    for (int m = 0; m < W; ++m) {
+                        dw0[m] += gy.x * xw[m].x;
+                        dw1[m] += gy.y * xw[m].y;
+                    }
+                }
+#pragma unroll
+                for (int m = 0; m < W - 1; ++m) xw[m] = xw[m + 1];
             }
         }
-    }
+    };
+    dz_rows(g * RPW, RPW, true);
+    if (g < W - 1) dz_rows(kConvTileT + g, 1, false);   // halo rows: their dweight belongs to the next block
 #pragma unroll
     for (int m = 0; m < W; ++m) {
         red[g][m][2 * p] = dw0[m];
         red[g][m][2 * p + 1] = dw1[m];
     }
     __syncthreads();
-    // dx[t] = sum_m w[m] dz[t + W-1-m]
+    // dx[t] = sum_m w[m] dz[t + W-1-m], again with a register window over this warp's consecutive rows
+    {
+        const int r0 = g * RPW;
+        float2 dw_[W];
 #pragma unroll
-    for (int r = g; r < kConvTileT; r += 8) {
-        const int t = t0 + r;
-        float a0 = 0.f, a1 = 0.f;
+        for (int m = 0; m < W - 1; ++m) dw_[m] = gs[r0 + m][p];
 #pragma unroll
-        for (int m = 0; m < W; ++m) {
-            const float2 d = gs[r + W - 1 - m][p];
-            a0 += w0[m] * d.x;
-            a1 += w1[m] * d.y;
+        for (int i = 0; i < RPW; ++i) {
+            const int r = r0 + i, t = t0 + r;
+            dw_[W - 1] = gs[r + W - 1][p];
+            float a0 = 0.f, a1 = 0.f;
+#pragma unroll
+            for (int m = 0; m < W; ++m) {
+                a0 += w0[m] * dw_[W - 1 - m].x;
+                a1 += w1[m] * dw_[W - 1 - m].y;
+            }
+            if (t < T && cok) st_pair<BF16>(dx, (rowbase + t) * C + c, a0, a1);
+#pragma unroll
+            for (int m = 0; m < W - 1; ++m) dw_[m] = dw_[m + 1];
         }
-        if (t < T && cok) st_pair<BF16>(dx, (rowbase + t) * C + c, a0, a1);
     }
     if (threadIdx.x < kConvTileC && cb + threadIdx.x < C) {
         const size_t pblk = (size_t)blockIdx.z * gridDim.y + blockIdx.y;
@@ -746,7 +851,6 @@ __global__ void __launch_bounds__(256) conv_bwd_tile_kernel(int T, int C, int si
         }
     }
 }
-
 
 // =============================================================================================
 // gated RMSNorm:  y = x * inv * w * sigmoid(gate),  inv = rsqrt(mean(x^2) + eps).  One warp per row.
@@ -1105,9 +1209,15 @@ int conv_fwd_w(int B, int T, int C, int bf16, int wf32, int silu, const void* x,
     auto blocks = [&](int vec) { return (unsigned)(((size_t)B * ntile * (C / vec) + 255) / 256); };
     const bool al16 = ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y)) % 16) == 0;
     if (!cache && !fin && C % 2 == 0 && al16) {
-        const dim3 grid(ceil_div(C, 64), ceil_div(T, 8 * pw::kConvPairT), B);
-        if (bf16) KDA_LAUNCH("conv_fwd_kernel", st, pw::conv_fwd_pair_kernel<W, true><<<grid, 256, 0, st>>>(T, C, silu, wf32, x, w, y));
-        else KDA_LAUNCH("conv_fwd_kernel", st, pw::conv_fwd_pair_kernel<W, false><<<grid, 256, 0, st>>>(T, C, silu, wf32, x, w, y));
+        const int vec = C % 128 == 0 ? 4 : 2;         // channels per thread
+        const dim3 grid(ceil_div(C, 32 * vec), ceil_div(T, 8 * pw::kConvPairT), B);
+        if (vec == 4) {
+            if (bf16) KDA_LAUNCH("conv_fwd_kernel", st, pw::conv_fwd_pair_kernel<W, 4, true><<<grid, 256, 0, st>>>(T, C, silu, wf32, x, w, y));
+            else KDA_LAUNCH("conv_fwd_kernel", st, pw::conv_fwd_pair_kernel<W, 4, false><<<grid, 256, 0, st>>>(T, C, silu, wf32, x, w, y));
+        } else {
+            if (bf16) KDA_LAUNCH("conv_fwd_kernel", st, pw::conv_fwd_pair_kernel<W, 2, true><<<grid, 256, 0, st>>>(T, C, silu, wf32, x, w, y));
+            else KDA_LAUNCH("conv_fwd_kernel", st, pw::conv_fwd_pair_kernel<W, 2, false><<<grid, 256, 0, st>>>(T, C, silu, wf32, x, w, y));
+        }
         return launch_status();
     }
     if (bf16) {
