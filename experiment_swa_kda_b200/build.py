@@ -67,5 +67,43 @@ def build(force: bool = False, verbose: bool = False) -> str:
     return LIB
 
 
+# ----------------------------------------------------------------------------------------------
+# the operator library: TORCH_LIBRARY(nanochat_kda) over the C ABI, compiled by the host compiler against the
+# installed PyTorch (the role of torch.utils.cpp_extension.load(is_python_module=False) in the reference loader)
+# ----------------------------------------------------------------------------------------------
+SHIM_SRC = os.path.join(PKG, "torch_shim", "nanochat_kda_ops.cpp")
+SHIM_LIB = os.path.join(LIBDIR, "libkda_b200_torch.so")
+
+
+def torch_ops_stale() -> bool:
+    if not os.path.exists(SHIM_LIB):
+        return True
+    t = os.path.getmtime(SHIM_LIB)
+    inc = os.path.join(os.path.dirname(PKG), "include", "kda_b200.h")
+    return os.path.getmtime(SHIM_SRC) > t or os.path.getmtime(inc) > t or os.path.getmtime(LIB) > t
+
+
+def build_torch_ops(force: bool = False) -> str:
+    build()
+    if not force and not torch_ops_stale():
+        return SHIM_LIB
+    import torch
+    from torch.utils import cpp_extension as ce
+    cxx = shutil.which("g++") or shutil.which("c++")
+    if not cxx:
+        raise RuntimeError("no C++ compiler found: cannot build libkda_b200_torch.so")
+    tlib = os.path.join(os.path.dirname(torch.__file__), "lib")
+    cuda_inc = os.path.join(os.path.dirname(os.path.dirname(nvcc_path())), "include")
+    cmd = [cxx, "-O2", "-std=c++17", "-shared", "-fPIC", f"-D_GLIBCXX_USE_CXX11_ABI={int(torch.compiled_with_cxx11_abi())}",
+           "-I" + os.path.join(os.path.dirname(PKG), "include"), "-I" + cuda_inc, *["-I" + i for i in ce.include_paths()],
+           SHIM_SRC, "-o", SHIM_LIB, "-L" + tlib, "-ltorch", "-ltorch_cpu", "-ltorch_cuda", "-lc10", "-lc10_cuda",
+           "-L" + LIBDIR, "-lkda_b200", "-Wl,-rpath,$ORIGIN", "-Wl,-rpath," + tlib]
+    proc = subprocess.run(cmd, capture_output=True, text=True)
+    if proc.returncode != 0:
+        raise RuntimeError("building libkda_b200_torch.so failed:\n" + proc.stdout + proc.stderr)
+    return SHIM_LIB
+
+
 if __name__ == "__main__":
     print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))
+    print(build_torch_ops(force="--force" in sys.argv))
