@@ -136,8 +136,9 @@ __global__ void __launch_bounds__(256, 1)
 //   next warp   one lane issues the TMA loads, two chunks ahead
 //   last warp   one lane issues every UMMA and the TMA stores of the state panels
 // TMEM: the accumulator is double-buffered (columns 0 / 128) so that the state-independent product of step c+1 is
-// issued while the state threads still read the accumulator of step c.  The bf16 state panel in shared memory is
-// double-buffered too, so the TMA store of panel c has a whole step to read it before it is packed again.
+// issued while the state threads still read the accumulator of step c; the bf16 state panel the state product reads as
+// its A operand sits at column 256.  Its shared-memory copy (for the TMA store) is double-buffered, so the store of
+// panel c has a whole step to read it before it is written again.
 // ---------------------------------------------------------------------------------------------
 struct AffineScanArgs {
     const int* seq_chunk0;
@@ -152,11 +153,9 @@ struct AffineScanArgs {
 constexpr int kPStage = 65536;                              // Pn 32 KB | X 16 KB (U^T or Rm^T) | Y 16 KB (E or dO)
 constexpr int kPStageBytes = kPStage + 512;                 // + exp(G_end), which lands in a ring of its own
 constexpr int kAffineScanSmem = 2 * kPStage + 2 * 32768 + 1024;
-#ifndef KDA_SCAN_GROUPS
-#define KDA_SCAN_GROUPS 2
-#endif
-constexpr int kScanGroups = KDA_SCAN_GROUPS;                // state warpgroups: each thread owns 128 / kScanGroups columns of a row
+constexpr int kScanGroups = 2;                              // state warpgroups: each thread owns 128 / kScanGroups columns of a row
 constexpr int kScanCols = 128 / kScanGroups;
+constexpr uint32_t kScanPanelCol = 256;                     // TMEM column of the bf16 state panel (64 columns: 128 keys as pairs)
 constexpr int kAffineScanThreads = (4 * kScanGroups + 2) * 32;
 
 #ifdef KDA_PHASE_TIMING
@@ -176,7 +175,7 @@ __global__ void __launch_bounds__(kAffineScanThreads, 1)
     // full: a stage has landed.  free: every product that reads a stage is complete (one per stage, so that the load
     // thread can never miss a phase).  sop: all state threads have packed the state panel.  mma: the step's
     // accumulator is complete.
-    __shared__ uint64_t bar_full[2], bar_free[2], bar_sop, bar_mma;
+    __shared__ uint64_t bar_full[2], bar_free[2], bar_sop, bar_pan, bar_mma;
     __shared__ uint32_t tmem_slot;
     __shared__ volatile int abort_flag;
 
@@ -193,11 +192,12 @@ __global__ void __launch_bounds__(kAffineScanThreads, 1)
         mbar_init(&bar_free[0], 1);
         mbar_init(&bar_free[1], 1);
         mbar_init(&bar_sop, 128 * kScanGroups);
+        mbar_init(&bar_pan, 128 * kScanGroups);
         mbar_init(&bar_mma, 1);
         mbar_fence_init();
         abort_flag = 0;
     }
-    if (warp == 1) tmem_alloc(&tmem_slot, 256);
+    if (warp == 1) tmem_alloc(&tmem_slot, 512);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -264,21 +264,21 @@ __global__ void __launch_bounds__(kAffineScanThreads, 1)
                 const int st = c & 1;
                 const int ch = slot_of(c) * H + h;
                 const uint32_t s0 = smem_u32(sm + st * kPStage);
-                const uint32_t a_s = smem_u32(Sop + st * 32768);
                 if (!mbar_wait(&bar_sop, c & 1, p.status, 52)) { abort_flag = 1; break; }
                 tc_fence_after();
 #pragma unroll
-                for (int k16 = 0; k16 < 8; ++k16) {
-                    const uint64_t ad = umma_smem_desc_sw128(a_s + (k16 >> 2) * 16384 + (k16 & 3) * 32, 16, 1024);
+                for (int k16 = 0; k16 < 8; ++k16) {   // A = the packed state in tensor memory, 8 columns per K = 16
                     const uint64_t bd = kBwd ? umma_smem_desc_sw128(s0 + (k16 >> 2) * 16384 + (k16 & 3) * 32, 16, 1024)
                                              : umma_smem_desc_sw128(s0 + k16 * 2048, 16384, 1024);
-                    umma_bf16_ss(tmem + 128 * st, ad, bd, id_st, 1);
+                    umma_bf16_ts(tmem + 128 * st, tmem + kScanPanelCol + 8 * k16, bd, id_st, 1);
                 }
-                // The store of panel c-1 has read its buffer before this commit lets the state threads pack panel c+1
+                // The store of panel c-1 has read its buffer before this commit lets the state threads write panel c+1
                 // into it.
                 tma_store_wait_read();
                 umma_commit(&bar_mma);
                 umma_commit(&bar_free[st]);
+                // the copy of the panel in shared memory (written after the tensor-memory one, off the critical path)
+                if (!mbar_wait(&bar_pan, c & 1, p.status, 55)) { abort_flag = 1; break; }
                 tma_store_2d(&mS, Sop + st * 32768, 0, ch * 128);
                 tma_store_2d(&mS, Sop + st * 32768 + 16384, 64, ch * 128);
                 tma_store_commit();
@@ -306,22 +306,25 @@ __global__ void __launch_bounds__(kAffineScanThreads, 1)
 #pragma unroll
             for (int j = 0; j < kScanCols; ++j) s[j] = 0.f;
         }
-        // this thread's part of the state row -> bf16 A operand (K-major, 128-byte swizzle, two 64-key blocks)
+        // This thread's half of the state row as bf16 pairs: first into tensor memory, where the state product reads its
+        // A operand (lane = value row, 32 columns per key half), then - after the arrival that releases the UMMA
+        // thread - into the shared-memory panel that the TMA store sends to the chunk-parallel kernels.
+        static_assert(kScanCols == 64, "the tensor-memory panel is written with one 32-column store per thread");
+        const int kh = col0 / 64;
         auto pack_state = [&](int c) {
-            uint8_t* dst = Sop + (c & 1) * 32768;
+            uint32_t w[32];
 #pragma unroll
-            for (int q = 0; q < kScanCols / 8; ++q) {
-                const int gc = col0 / 8 + q;       // 16-byte chunk index along the 128 keys
-                uint4 u;
-                u.x = pack_bf16(s[8 * q + 0], s[8 * q + 1]);
-                u.y = pack_bf16(s[8 * q + 2], s[8 * q + 3]);
-                u.z = pack_bf16(s[8 * q + 4], s[8 * q + 5]);
-                u.w = pack_bf16(s[8 * q + 6], s[8 * q + 7]);
-                *reinterpret_cast<uint4*>(dst + (gc >> 3) * 16384 + sw128_off(v, gc & 7)) = u;
-            }
-            fence_async_smem();
+            for (int j = 0; j < 32; ++j) w[j] = pack_bf16(s[2 * j], s[2 * j + 1]);
+            tmem_st32(tmem + lane_base + kScanPanelCol + 32 * kh, w);
+            tmem_st_wait();
             tc_fence_before();
             mbar_arrive(&bar_sop);
+            uint8_t* dst = Sop + (c & 1) * 32768 + kh * 16384;
+#pragma unroll
+            for (int q = 0; q < 8; ++q)
+                *reinterpret_cast<uint4*>(dst + sw128_off(v, q)) = make_uint4(w[4 * q], w[4 * q + 1], w[4 * q + 2], w[4 * q + 3]);
+            fence_async_smem();
+            mbar_arrive(&bar_pan);
         };
 #ifdef KDA_PHASE_TIMING
         long long acc[4] = {0, 0, 0, 0}, tlast = clock64();
@@ -371,7 +374,7 @@ __global__ void __launch_bounds__(kAffineScanThreads, 1)
     }
     tc_fence_before();
     __syncthreads();
-    if (warp == 1) tmem_dealloc(tmem, 256);
+    if (warp == 1) tmem_dealloc(tmem, 512);
 }
 
 // ---------------------------------------------------------------------------------------------
