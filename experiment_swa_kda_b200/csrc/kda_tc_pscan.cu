@@ -37,7 +37,7 @@ struct TransArgs {
 
 constexpr int kTransSmem = 16384 + 16384 + 8192 + 1024;   // W^T | E | A^T
 
-__global__ void __launch_bounds__(256, 1)
+__global__ void __launch_bounds__(256, 2)
     tc_transition_kernel(const __grid_constant__ CUtensorMap mW, const __grid_constant__ CUtensorMap mE,
                          const __grid_constant__ CUtensorMap mAT, TransArgs p) {
     extern __shared__ uint8_t smem_raw[];
@@ -191,8 +191,8 @@ __global__ void __launch_bounds__(kAffineScanThreads, 1)
         mbar_init(&bar_full[1], 1);
         mbar_init(&bar_free[0], 1);
         mbar_init(&bar_free[1], 1);
-        mbar_init(&bar_sop, 128 * kScanGroups);
-        mbar_init(&bar_pan, 128 * kScanGroups);
+        mbar_init(&bar_sop, 4 * kScanGroups);      // one arrival per state warp
+        mbar_init(&bar_pan, 4 * kScanGroups);
         mbar_init(&bar_mma, 1);
         mbar_fence_init();
         abort_flag = 0;
@@ -318,13 +318,13 @@ __global__ void __launch_bounds__(kAffineScanThreads, 1)
             tmem_st32(tmem + lane_base + kScanPanelCol + 32 * kh, w);
             tmem_st_wait();
             tc_fence_before();
-            mbar_arrive(&bar_sop);
+            warp_arrive(&bar_sop, lane);
             uint8_t* dst = Sop + (c & 1) * 32768 + kh * 16384;
 #pragma unroll
             for (int q = 0; q < 8; ++q)
                 *reinterpret_cast<uint4*>(dst + sw128_off(v, q)) = make_uint4(w[4 * q], w[4 * q + 1], w[4 * q + 2], w[4 * q + 3]);
             fence_async_smem();
-            mbar_arrive(&bar_pan);
+            warp_arrive(&bar_pan, lane);
         };
 #ifdef KDA_PHASE_TIMING
         long long acc[4] = {0, 0, 0, 0}, tlast = clock64();
@@ -394,10 +394,12 @@ struct ChunkOutArgs {
     int* status;
 };
 
-constexpr int kOutH = 0, kOutWR = 32768, kOutU = 65536, kOutA = 81920, kOutZ = 90112, kOutO = 106496;
-constexpr int kChunkOutSmem = kOutO + 16384 + 1024;
+// Z^T reuses the [W^T|R^T] tile and the output tile reuses the state tile: both are dead once the first UMMA chain has
+// completed, and the smaller footprint lets two CTAs share an SM.
+constexpr int kOutH = 0, kOutWR = 32768, kOutU = 65536, kOutA = 81920, kOutZ = kOutWR, kOutO = kOutH;
+constexpr int kChunkOutSmem = kOutA + 8192 + 1024;
 
-__global__ void __launch_bounds__(256, 1)
+__global__ void __launch_bounds__(256, 2)
     tc_chunk_out_kernel(const __grid_constant__ CUtensorMap mH, const __grid_constant__ CUtensorMap mW,
                         const __grid_constant__ CUtensorMap mR, const __grid_constant__ CUtensorMap mUT,
                         const __grid_constant__ CUtensorMap mAT, ChunkOutArgs p) {
@@ -526,7 +528,7 @@ struct ChunkDzArgs {
 constexpr int kDzH = 0, kDzE = 32768, kDzO = 49152, kDzA = 65536;
 constexpr int kChunkDzSmem = kDzA + 8192 + 1024;
 
-__global__ void __launch_bounds__(256, 1)
+__global__ void __launch_bounds__(256, 3)
     tc_chunk_dz_kernel(const __grid_constant__ CUtensorMap mdH, const __grid_constant__ CUtensorMap mE,
                        const __grid_constant__ CUtensorMap mdO, const __grid_constant__ CUtensorMap mAT, ChunkDzArgs p) {
     extern __shared__ uint8_t smem_raw[];
