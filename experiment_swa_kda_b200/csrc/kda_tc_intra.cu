@@ -45,55 +45,83 @@ constexpr int kLDs = 68;
 
 constexpr int kNT = 512;   // threads per CTA: thread (I, d) = 16-token row block I (warp >> 2), channel d (tid & 127)
 
-// dst[S x S] = alpha * A[S x S] * B[S x S] (row-major fp32, leading dimension kLDs) for NB independent problems
-// addressed through the callers' pointer functions; kNT threads, each owning CW consecutive columns of one row.
+// dst[S x S] = alpha * A[S x S] * B[S x S] (row-major fp32, leading dimension kLDs, 16-byte aligned columns) for NB
+// independent problems addressed through the callers' pointer functions.  Each of the first S*S*NB/8 threads owns a
+// 2 x 4 tile of one product, so a step of the contraction costs a warp three shared-memory wavefronts (two broadcast
+// words of A, one 16-byte row piece of B) for eight multiply-adds per thread.
 template <int S, int NB, class PA, class PB, class PD>
 __device__ __forceinline__ void block_mm(PA pa, PB pb, PD pd, float alpha) {
-    constexpr int CW = S * S * NB / kNT;          // 1 (S=16, NB=2) or 2 (S=32, NB=1)
-    constexpr int TPR = S / CW;                   // threads per row
+    constexpr int TPP = S * S / 8;                // threads per problem
     const int tid = threadIdx.x;
-    const int prob = tid / (S * TPR), rem = tid - prob * (S * TPR);
-    const int i = rem / TPR, j0 = (rem - i * TPR) * CW;
-    const float* A = pa(prob) + i * kLDs;
+    if (tid >= TPP * NB) return;
+    const int prob = tid / TPP, rem = tid - prob * TPP;
+    const int i0 = (rem / (S / 4)) * 2, j0 = (rem % (S / 4)) * 4;
+    const float* A0 = pa(prob) + i0 * kLDs;
     const float* B = pb(prob) + j0;
-    float acc[CW];
+    float acc[2][4];
 #pragma unroll
-    for (int c = 0; c < CW; ++c) acc[c] = 0.f;
+    for (int r = 0; r < 2; ++r)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) acc[r][c] = 0.f;
 #pragma unroll
     for (int t = 0; t < S; ++t) {
-        const float a = A[t];
-#pragma unroll
-        for (int c = 0; c < CW; ++c) acc[c] += a * B[t * kLDs + c];
+        const float a0 = A0[t], a1 = A0[kLDs + t];
+        const float4 bv = *reinterpret_cast<const float4*>(B + t * kLDs);
+        acc[0][0] += a0 * bv.x; acc[0][1] += a0 * bv.y; acc[0][2] += a0 * bv.z; acc[0][3] += a0 * bv.w;
+        acc[1][0] += a1 * bv.x; acc[1][1] += a1 * bv.y; acc[1][2] += a1 * bv.z; acc[1][3] += a1 * bv.w;
     }
-    float* D = pd(prob) + i * kLDs + j0;
+    float* D = pd(prob) + i0 * kLDs + j0;
 #pragma unroll
-    for (int c = 0; c < CW; ++c) D[c] = alpha * acc[c];
+    for (int r = 0; r < 2; ++r)
+        *reinterpret_cast<float4*>(D + r * kLDs) = make_float4(alpha * acc[r][0], alpha * acc[r][1], alpha * acc[r][2], alpha * acc[r][3]);
 }
 
-// Ts = (I + Ms)^-1 for strictly lower-triangular Ms (64x64): 16x16 diagonal solves, then 32 and 64 merges
-//   inv([[A,0],[C,B]]) = [[Ai,0],[-Bi C Ai, Bi]].
+// Ts = (I + Ms)^-1 for strictly lower-triangular Ms (64x64): 8x8 diagonal solves (a short dependent chain per thread),
+// then merges to 16, 32 and 64 with   inv([[A,0],[C,B]]) = [[Ai,0],[-Bi C Ai, Bi]].
 __device__ void unit_lower_inverse(const float* Ms, float* Ts, float* tmp) {
     const int tid = threadIdx.x;
-    for (int idx = tid; idx < 64 * kLDs; idx += kNT) Ts[idx] = 0.f;
+    for (int idx = tid; idx < 64 * kLDs / 4; idx += kNT) reinterpret_cast<float4*>(Ts)[idx] = make_float4(0.f, 0.f, 0.f, 0.f);
     __syncthreads();
     if (tid < 64) {
-        const int b = tid >> 4, j = tid & 15;
-        const float* Lb = Ms + (16 * b) * kLDs + 16 * b;
-        float x[16];
+        const int b = tid >> 3, j = tid & 7;          // diagonal block, column of the inverse
+        const float* Lb = Ms + (8 * b) * kLDs + 8 * b;
+        float x[8];
 #pragma unroll
-        for (int i = 0; i < 16; ++i) x[i] = (i == j) ? 1.f : 0.f;
+        for (int i = 0; i < 8; ++i) x[i] = (i == j) ? 1.f : 0.f;
 #pragma unroll
-        for (int i = 1; i < 16; ++i) {
+        for (int i = 1; i < 8; ++i) {
             float s = 0.f;
 #pragma unroll
             for (int t = 0; t < i; ++t) s += Lb[i * kLDs + t] * x[t];
             x[i] = (i > j) ? -s : x[i];
         }
-        float* Tb = Ts + (16 * b) * kLDs + 16 * b;
+        float* Tb = Ts + (8 * b) * kLDs + 8 * b;
 #pragma unroll
-        for (int i = 0; i < 16; ++i) Tb[i * kLDs + j] = x[i];
+        for (int i = 0; i < 8; ++i) Tb[i * kLDs + j] = x[i];
     }
     __syncthreads();
+    // 16x16 merges, four independent pairs of 8x8 blocks: tmp_p = C_p Ai_p ; T21_p = -Bi_p tmp_p
+    {
+        const int p = tid >> 6, i = (tid >> 3) & 7, j = tid & 7;
+        if (tid < 256) {
+            const float* C = Ms + (16 * p + 8 + i) * kLDs + 16 * p;
+            const float* Ai = Ts + (16 * p) * kLDs + 16 * p + j;
+            float a = 0.f;
+#pragma unroll
+            for (int t = 0; t < 8; ++t) a += C[t] * Ai[t * kLDs];
+            tmp[(p * 8 + i) * kLDs + j] = a;
+        }
+        __syncthreads();
+            if (tid < 256) {
+            const float* Bi = Ts + (16 * p + 8 + i) * kLDs + 16 * p + 8;
+            const float* Tm = tmp + (p * 8) * kLDs + j;
+            float a = 0.f;
+#pragma unroll
+            for (int t = 0; t < 8; ++t) a += Bi[t] * Tm[t * kLDs];
+            Ts[(16 * p + 8 + i) * kLDs + 16 * p + j] = -a;
+        }
+        __syncthreads();
+        }
     // 32x32 merges, two independent pairs: tmp_p = C_p Ai_p ; T21_p = -Bi_p tmp_p
     block_mm<16, 2>([&](int p) { return Ms + (32 * p + 16) * kLDs + 32 * p; },
                     [&](int p) { return Ts + (32 * p) * kLDs + 32 * p; },
