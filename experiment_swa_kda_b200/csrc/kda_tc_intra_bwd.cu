@@ -506,29 +506,37 @@ __global__ void __launch_bounds__(512, 1)
         float t[16];
         const float c0 = cref[d], c1 = cref[128 + d], c2 = cref[256 + d], c3 = cref[384 + d];
         const float cOwn = I == 0 ? c0 : (I == 1 ? c1 : (I == 2 ? c2 : c3));
+        // decay factors of this thread's rows relative to its own block reference: e1 = e^{G - c_own} (<= 1) for the
+        // row parts, e2 = e^{c_own - G} for the column parts (a later block I' contributes e^{c_I' - c_own} e2)
+        float e1[16];
+#pragma unroll
+        for (int r = 0; r < 16; ++r) e1[r] = __expf(G[r] - cOwn);
         tmem_ld16(tmem + lane_base + cRP + 32 * I, t);          // row part through dA
 #pragma unroll
         for (int r = 0; r < 16; ++r) {
-            const float x = __expf(G[r] - cOwn) * t[r];
+            const float x = e1[r] * t[r];
             dqn[r] += x;
             dG[r] += qn[r] * x;
         }
         tmem_ld16(tmem + lane_base + cRP + 32 * I + 16, t);     // row part through beta*dM
 #pragma unroll
         for (int r = 0; r < 16; ++r) {
-            const float x = __expf(G[r] - cOwn) * t[r];
+            const float x = e1[r] * t[r];
             dkn[r] += x;
             dG[r] += kn[r] * x;
         }
+#pragma unroll
+        for (int r = 0; r < 16; ++r) e1[r] = __expf(cOwn - G[r]);   // now e2
         // column part: sources of block I receive from target blocks I' >= I, each with its own decay reference
 #pragma unroll
         for (int Ib = 0; Ib < 4; ++Ib) {
             if (Ib >= I) {
                 const float cI = Ib == 0 ? c0 : (Ib == 1 ? c1 : (Ib == 2 ? c2 : c3));
+                const float fI = __expf(cI - cOwn);
                 tmem_ld16(tmem + lane_base + cCP[Ib] + 16 * I, t);
 #pragma unroll
                 for (int r = 0; r < 16; ++r) {
-                    const float x = __expf(cI - G[r]) * t[r];
+                    const float x = fI * e1[r] * t[r];
                     dkn[r] += x;
                     dG[r] -= kn[r] * x;
                 }
@@ -591,27 +599,52 @@ __global__ void __launch_bounds__(512, 1)
     }
     __syncthreads();
     KDA_TICKB(17);
-    if (ok) {
+    {
+        // The gradients of this thread's 16 rows go through shared memory (the source-panel region is free now), so
+        // that they leave as 16-byte row segments instead of one 2-byte store per row, tensor and thread.
+        __nv_bfloat16* tq = reinterpret_cast<__nv_bfloat16*>(sm + kR1);            // [64][128] dq
+        __nv_bfloat16* tk = tq + 64 * 128;                                          // [64][128] dk
+        __nv_bfloat16* tgb = tk + 64 * 128;                                         // [64][128] dg when the gate dtype is bf16
+        float* tgf = reinterpret_cast<float*>(sm + kR1 + 32768);                    // [64][128] dg when it is float32
         float run = suffix;
 #pragma unroll
         for (int r = 15; r >= 0; --r) {
             const int i = 16 * I + r;
             run += dG[r];
-            if (i < len) {
-                const size_t o = col + (size_t)i * rstride;
-                st_io(p.dg, o, p.gbf16, run);
-                float dqv, dkv;
-                if (p.l2norm) {
-                    const float2 pp = *reinterpret_cast<const float2*>(dots + i * 8);
-                    const float pq = pp.x, pk = pp.y;
-                    dqv = rowv[i] * (dqn[r] * p.scale - qn[r] * inv_scale * pq);
-                    dkv = rowv[64 + i] * (dkn[r] - kn[r] * pk);
-                } else {
-                    dqv = dqn[r] * p.scale;
-                    dkv = dkn[r];
+            float dqv, dkv;
+            if (p.l2norm) {
+                const float2 pp = *reinterpret_cast<const float2*>(dots + i * 8);
+                const float pq = pp.x, pk = pp.y;
+                dqv = rowv[i] * (dqn[r] * p.scale - qn[r] * inv_scale * pq);
+                dkv = rowv[64 + i] * (dkn[r] - kn[r] * pk);
+            } else {
+                dqv = dqn[r] * p.scale;
+                dkv = dkn[r];
+            }
+            tq[i * 128 + d] = __float2bfloat16(dqv);
+            tk[i * 128 + d] = __float2bfloat16(dkv);
+            if (p.gbf16) tgb[i * 128 + d] = __float2bfloat16(run);
+            else tgf[i * 128 + d] = run;
+        }
+        __syncthreads();
+        if (ok) {
+            const int c = tid & 15;
+#pragma unroll
+            for (int pass = 0; pass < 2; ++pass) {
+                const int i = pass * 32 + (tid >> 4);
+                if (i < len) {
+                    const size_t o = ((size_t)(tok0 + i) * H + h) * 128;
+                    *reinterpret_cast<uint4*>(p.dq + o + 8 * c) = *reinterpret_cast<const uint4*>(tq + i * 128 + 8 * c);
+                    *reinterpret_cast<uint4*>(p.dk + o + 8 * c) = *reinterpret_cast<const uint4*>(tk + i * 128 + 8 * c);
+                    if (p.gbf16) {
+                        *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.dg) + o + 8 * c) =
+                            *reinterpret_cast<const uint4*>(tgb + i * 128 + 8 * c);
+                    } else {
+                        float* dgp = reinterpret_cast<float*>(p.dg) + o;
+                        *reinterpret_cast<uint4*>(dgp + 4 * c) = *reinterpret_cast<const uint4*>(tgf + i * 128 + 4 * c);
+                        *reinterpret_cast<uint4*>(dgp + 64 + 4 * c) = *reinterpret_cast<const uint4*>(tgf + i * 128 + 64 + 4 * c);
+                    }
                 }
-                p.dq[o] = __float2bfloat16(dqv);
-                p.dk[o] = __float2bfloat16(dkv);
             }
         }
     }
