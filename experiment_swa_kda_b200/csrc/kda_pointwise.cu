@@ -1184,7 +1184,8 @@ extern "C" int kda_decode_step(int32_t n_seq, int32_t heads, int32_t key_dim, in
     if (n_seq == 0) return KDA_OK;
     if (!q || !k || !v || !g || !beta || !state_in || !state_out || !o) return KDA_ERR_NULL;
     const int bf16 = io_dtype == KDA_DTYPE_BF16, gbf16 = gate_dtype == KDA_DTYPE_BF16;
-    // rows per CTA: 32 (8 warps x 4 rows); fewer CTAs per (sequence, head) once the grid is large enough
+    // four rows in flight per warp: at ~70 registers three to four CTAs share an SM, so one CTA's prologue (norms, decay) hides
+    // under the others' streaming; eight rows per warp measured 20 % slower
     // one CTA per (sequence, head) once there are enough of them to fill the GPU; otherwise split the value rows
     const int rows_per_cta = (n_seq * heads >= 148 * 4) ? value_dim : 32;
     dim3 grid(n_seq * heads, ceil_div(value_dim, rows_per_cta));
@@ -1192,7 +1193,7 @@ extern "C" int kda_decode_step(int32_t n_seq, int32_t heads, int32_t key_dim, in
     const bool vec = (key_dim % 4 == 0) &&
                      ((reinterpret_cast<uintptr_t>(state_in) | reinterpret_cast<uintptr_t>(state_out)) % 16 == 0);
     if (vec && key_dim <= 128)
-        KDA_LAUNCH("decode_kernel", st, pw::decode_kernel<1, 8><<<grid, 256, 0, st>>>(heads, key_dim, value_dim, bf16, gbf16, l2norm, scale, q, k, v, g, beta, state_in, state_out, o, rows_per_cta));
+        KDA_LAUNCH("decode_kernel", st, pw::decode_kernel<1, 4><<<grid, 256, 0, st>>>(heads, key_dim, value_dim, bf16, gbf16, l2norm, scale, q, k, v, g, beta, state_in, state_out, o, rows_per_cta));
     else if (vec)
         KDA_LAUNCH("decode_kernel", st, pw::decode_kernel<2, 4><<<grid, 256, 0, st>>>(heads, key_dim, value_dim, bf16, gbf16, l2norm, scale, q, k, v, g, beta, state_in, state_out, o, rows_per_cta));
     else
