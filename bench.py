@@ -158,9 +158,7 @@ class Chain:
     def step(self):
         x, cfg = self.x, self.cfg
         sh = (cfg["B"], cfg["T"], cfg["H"], cfg["D"])
-        q = self.convs[0](x["xq"])[0].view(sh)
-        k = self.convs[1](x["xk"])[0].view(sh)
-        v = self.convs[2](x["xv"])[0].view(sh)
+        q, k, v = (t.view(sh) for t in self.m.short_convolutions(self.convs, (x["xq"], x["xk"], x["xv"])))
         o, _ = self.m.chunk_kda(q, k, v, x["g"], x["beta"])
         y = self.norm(o, x["gate"])
         leaves = [x[n] for n in self.leaf_names] + [c.weight for c in self.convs] + [self.norm.weight]
@@ -325,9 +323,28 @@ def main():
         main = torch.cuda.current_stream(dev)
         s_in, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
         flat = [outs[0]] + list(outs[1])
-        st_in = [{n: torch.empty_like(t) for n, t in chain.x.items()} for _ in range(2)]
-        st_out = [[torch.empty_like(t) for t in flat] for _ in range(2)]
-        h_out = [[torch.empty(t.shape, dtype=t.dtype).pin_memory() for t in flat] for _ in range(2)]
+
+        def carve(buf, like):          # 256-byte aligned views of one flat byte buffer, shaped like the tensors
+            views, off = [], 0
+            for t in like:
+                n = t.numel() * t.element_size()
+                views.append(buf[off:off + n].view(t.dtype).view(t.shape))
+                off += (n + 255) // 256 * 256
+            return views
+
+        size = lambda like: sum((t.numel() * t.element_size() + 255) // 256 * 256 for t in like)
+        names = list(chain.host)
+        ins = [chain.host[n] for n in names]
+        # one pinned buffer and one copy per direction and step: the step's inputs sit back to back in pinned host
+        # memory, the results land back to back in another pinned buffer
+        h_in = torch.empty(size(ins), dtype=torch.uint8).pin_memory()
+        for v, t in zip(carve(h_in, ins), ins):
+            v.copy_(t)
+        d_in = [torch.empty(size(ins), dtype=torch.uint8, device=dev) for _ in range(2)]
+        d_in_views = [carve(b, ins) for b in d_in]
+        d_out = [torch.empty(size(flat), dtype=torch.uint8, device=dev) for _ in range(2)]
+        d_out_views = [carve(b, flat) for b in d_out]
+        h_out = [torch.empty(size(flat), dtype=torch.uint8).pin_memory() for _ in range(2)]
         ev = {k: [torch.cuda.Event() for _ in range(2)] for k in ("in_ready", "in_free", "out_ready", "out_free")}
         t_begin, t_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         barrier()
@@ -340,29 +357,27 @@ def main():
                 with torch.cuda.stream(s_in):
                     if i >= 2:
                         s_in.wait_event(ev["in_free"][b])
-                    for n, hbuf in chain.host.items():
-                        st_in[b][n].copy_(hbuf, non_blocking=True)
+                    d_in[b].copy_(h_in, non_blocking=True)
                     ev["in_ready"][b].record(s_in)
                 main.wait_event(ev["in_ready"][b])
                 flush.zero_()
-                for n in chain.host:
-                    chain.x[n].copy_(st_in[b][n])                   # graph inputs live at fixed addresses
+                for n, v in zip(names, d_in_views[b]):
+                    chain.x[n].copy_(v)                              # graph inputs live at fixed addresses
                 ev["in_free"][b].record(main)
                 graph.replay()
                 if i >= 2:
                     main.wait_event(ev["out_free"][b])
-                for dst, src in zip(st_out[b], flat):
+                for dst, src in zip(d_out_views[b], flat):
                     dst.copy_(src)
                 ev["out_ready"][b].record(main)
                 with torch.cuda.stream(s_out):
                     s_out.wait_event(ev["out_ready"][b])
-                    for dst, src in zip(h_out[b], st_out[b]):
-                        dst.copy_(src, non_blocking=True)
+                    h_out[b].copy_(d_out[b], non_blocking=True)
                     ev["out_free"][b].record(s_out)
         t_end.record(s_out)
         s_out.synchronize()
         barrier()
-        return t_begin.elapsed_time(t_end), sum(h.numel() * h.element_size() for h in h_out[0])
+        return t_begin.elapsed_time(t_end), sum(t.numel() * t.element_size() for t in flat)
 
     e2e_run = e2e_serial if graph is None else e2e_pipelined
     e2e_run(3)

@@ -2,7 +2,7 @@
 (include/kda_b200.h) and a host-side mirror of the reference mixer interface."""
 
 from .kda import (KDAState, KimiDeltaAttention, RMSNormGated, ShortConvolution, chunk_kda, k3_decay_gate, kda,
-                  kda_backend_provenance, prepare_kda_backend, recurrent_kda_step)
+                  kda_backend_provenance, prepare_kda_backend, recurrent_kda_step, short_convolutions)
 
 __all__ = ["KDAState", "KimiDeltaAttention", "RMSNormGated", "ShortConvolution", "chunk_kda", "k3_decay_gate", "kda",
-           "kda_backend_provenance", "prepare_kda_backend", "recurrent_kda_step"]
+           "kda_backend_provenance", "prepare_kda_backend", "recurrent_kda_step", "short_convolutions"]

@@ -12,6 +12,7 @@ import os
 from . import build as _build
 
 OK = 0
+ERR_UNSUPPORTED = -2      # KDA_ERR_UNSUPPORTED
 DTYPE_F32, DTYPE_BF16 = 0, 1
 LANE_FP32, LANE_TC = 0, 1
 
@@ -37,6 +38,9 @@ _SIGNATURES = {
     "kda_conv_fwd": (C.c_int, [C.c_int32] * 6 + [_P] * 6),
     "kda_conv_bwd_scratch_bytes": (C.c_size_t, [C.c_int32] * 4),
     "kda_conv_bwd": (C.c_int, [C.c_int32] * 6 + [_P] * 9 + [C.c_size_t, _P]),
+    "kda_conv_fwd_multi": (C.c_int, [C.c_int32] * 7 + [_P] * 4),
+    "kda_conv_bwd_multi_scratch_bytes": (C.c_size_t, [C.c_int32] * 5),
+    "kda_conv_bwd_multi": (C.c_int, [C.c_int32] * 7 + [_P] * 6 + [C.c_size_t, _P]),
     "kda_rmsnorm_gate_fwd": (C.c_int, [C.c_int64, C.c_int32, C.c_int32, C.c_float] + [_P] * 6),
     "kda_rmsnorm_gate_bwd_scratch_bytes": (C.c_size_t, [C.c_int64, C.c_int32]),
     "kda_rmsnorm_gate_bwd": (C.c_int, [C.c_int64, C.c_int32, C.c_int32] + [_P] * 9 + [C.c_size_t, _P]),

@@ -480,14 +480,35 @@ __device__ __forceinline__ void st_cvec(void* p, size_t i, const float (&s)[VEC]
     }
 }
 
-// grid: x = channel blocks of 32*VEC, y = blocks of 8 time groups x kConvPairT tokens, z = batch
+// Up to kConvItems same-shaped convolutions (the q, k and v branches of a layer) share one launch: blockIdx.z runs over
+// item x batch.
+constexpr int kConvItems = 4;
+struct ConvFwdItems {
+    const void* x[kConvItems];
+    const void* w[kConvItems];
+    void* y[kConvItems];
+};
+struct ConvBwdItems {
+    const void* x[kConvItems];
+    const void* w[kConvItems];
+    const void* dy[kConvItems];
+    void* dx[kConvItems];
+};
+struct ColumnSumItems {
+    float* out[kConvItems];
+};
+
+// grid: x = channel blocks of 32*VEC, y = blocks of 8 time groups x kConvPairT tokens, z = item * B + batch
 template <int W, int VEC, bool BF16>
-__global__ void __launch_bounds__(256) conv_fwd_pair_kernel(int T, int C, int silu, int wf32, const void* __restrict__ x,
-                                                            const void* __restrict__ wgt, void* __restrict__ y) {
+__global__ void __launch_bounds__(256) conv_fwd_pair_kernel(int B, int T, int C, int silu, int wf32, ConvFwdItems items) {
     const int p = threadIdx.x & 31, g = threadIdx.x >> 5;
     const int c = (blockIdx.x * 32 + p) * VEC;
-    const int t0 = (blockIdx.y * 8 + g) * kConvPairT, b = blockIdx.z;
+    const int item = blockIdx.z / B;
+    const int t0 = (blockIdx.y * 8 + g) * kConvPairT, b = blockIdx.z - item * B;
     if (t0 >= T) return;
+    const void* __restrict__ x = items.x[item];
+    const void* __restrict__ wgt = items.w[item];
+    void* __restrict__ y = items.y[item];
     const bool cok = c < C;
     const int cl = cok ? c : 0;
     float wv[W][VEC];
@@ -729,9 +750,8 @@ __global__ void __launch_bounds__(256) conv_bwd_kernel(int B, int T, int C, int 
 constexpr int kConvTileT = 64, kConvTileC = 64;
 
 template <int W, bool BF16>
-__global__ void __launch_bounds__(256) conv_bwd_tile_kernel(int T, int C, int silu, int wf32, const void* __restrict__ x,
-                                                            const void* __restrict__ wgt, const void* __restrict__ dy,
-                                                            void* __restrict__ dx, float* __restrict__ dw_part) {
+__global__ void __launch_bounds__(256) conv_bwd_tile_kernel(int B, int T, int C, int silu, int wf32, ConvBwdItems items,
+                                                            float* __restrict__ dw_part) {
     constexpr int XR = kConvTileT + 2 * (W - 1);   // x rows  t0-(W-1) .. t0+63+(W-1)
     constexpr int GR = kConvTileT + W - 1;         // dy rows t0 .. t0+63+(W-1)
     constexpr int RPW = kConvTileT / 8;            // consecutive rows per warp
@@ -743,7 +763,12 @@ __global__ void __launch_bounds__(256) conv_bwd_tile_kernel(int T, int C, int si
     const int p = threadIdx.x & 31, g = threadIdx.x >> 5;
     const int cb = blockIdx.x * kConvTileC;
     const int c = cb + 2 * p;
-    const int t0 = blockIdx.y * kConvTileT, b = blockIdx.z;
+    const int item = blockIdx.z / B;
+    const int t0 = blockIdx.y * kConvTileT, b = blockIdx.z - item * B;
+    const void* __restrict__ x = items.x[item];
+    const void* __restrict__ wgt = items.w[item];
+    const void* __restrict__ dy = items.dy[item];
+    void* __restrict__ dx = items.dx[item];
     const bool cok = c < C;
     const int cl = cok ? c : 0;                    // loads stay unconditional: out-of-range lanes read column 0 and are masked
     float w0[W], w1[W];
@@ -1117,9 +1142,11 @@ __global__ void __launch_bounds__(256) rmsnorm_bwd128_kernel(long long rows, con
 }
 
 // out[i] = sum over b of part[b][i]: 32 columns per block, 32 row segments summed in a fixed order
-__global__ void __launch_bounds__(1024) column_sum_kernel(int nblk, int N, const float* __restrict__ part,
-                                                          float* __restrict__ out) {
+__global__ void __launch_bounds__(1024) column_sum_kernel(int nblk, int N, const float* __restrict__ part_all,
+                                                          ColumnSumItems outs) {
     __shared__ float red[32][33];
+    const float* __restrict__ part = part_all + (size_t)blockIdx.y * nblk * N;     // blockIdx.y = item
+    float* __restrict__ out = outs.out[blockIdx.y];
     const int lane = threadIdx.x & 31, seg = threadIdx.x >> 5;
     const int i = blockIdx.x * 32 + lane;
     float a = 0.f;
@@ -1210,6 +1237,34 @@ extern "C" int kda_decode_step(int32_t n_seq, int32_t heads, int32_t key_dim, in
 
 namespace {
 
+// training path (no carried-in window, no final state) for n same-shaped convolutions in one launch
+template <int W>
+int conv_fwd_fast(int n, int B, int T, int C, int bf16, int wf32, int silu, const pw::ConvFwdItems& it, cudaStream_t st) {
+    const int vec = C % 128 == 0 ? 4 : 2;         // channels per thread
+    const dim3 grid(ceil_div(C, 32 * vec), ceil_div(T, 8 * pw::kConvPairT), B * n);
+    if (vec == 4) {
+        if (bf16) KDA_LAUNCH("conv_fwd_kernel", st, pw::conv_fwd_pair_kernel<W, 4, true><<<grid, 256, 0, st>>>(B, T, C, silu, wf32, it));
+        else KDA_LAUNCH("conv_fwd_kernel", st, pw::conv_fwd_pair_kernel<W, 4, false><<<grid, 256, 0, st>>>(B, T, C, silu, wf32, it));
+    } else {
+        if (bf16) KDA_LAUNCH("conv_fwd_kernel", st, pw::conv_fwd_pair_kernel<W, 2, true><<<grid, 256, 0, st>>>(B, T, C, silu, wf32, it));
+        else KDA_LAUNCH("conv_fwd_kernel", st, pw::conv_fwd_pair_kernel<W, 2, false><<<grid, 256, 0, st>>>(B, T, C, silu, wf32, it));
+    }
+    return launch_status();
+}
+
+template <int W>
+int conv_bwd_fast(int n, int B, int T, int C, int bf16, int wf32, int silu, const pw::ConvBwdItems& it, float* const* dwgt,
+                  float* part, cudaStream_t st) {
+    const dim3 grid(ceil_div(C, pw::kConvTileC), ceil_div(T, pw::kConvTileT), B * n);
+    if (bf16) KDA_LAUNCH("conv_bwd_kernel", st, pw::conv_bwd_tile_kernel<W, true><<<grid, 256, 0, st>>>(B, T, C, silu, wf32, it, part));
+    else KDA_LAUNCH("conv_bwd_kernel", st, pw::conv_bwd_tile_kernel<W, false><<<grid, 256, 0, st>>>(B, T, C, silu, wf32, it, part));
+    const int nblk = grid.y * B;                  // partial rows per item
+    pw::ColumnSumItems outs = {};
+    for (int i = 0; i < n; ++i) outs.out[i] = dwgt[i];
+    KDA_LAUNCH("conv_dw_reduce_kernel", st, pw::column_sum_kernel<<<dim3(ceil_div(C * W, 32), n), 1024, 0, st>>>(nblk, C * W, part, outs));
+    return launch_status();
+}
+
 template <int W>
 int conv_fwd_w(int B, int T, int C, int bf16, int wf32, int silu, const void* x, const void* w, const void* cache, void* y,
                void* fin, cudaStream_t st) {
@@ -1217,16 +1272,9 @@ int conv_fwd_w(int B, int T, int C, int bf16, int wf32, int silu, const void* x,
     auto blocks = [&](int vec) { return (unsigned)(((size_t)B * ntile * (C / vec) + 255) / 256); };
     const bool al16 = ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y)) % 16) == 0;
     if (!cache && !fin && C % 2 == 0 && al16) {
-        const int vec = C % 128 == 0 ? 4 : 2;         // channels per thread
-        const dim3 grid(ceil_div(C, 32 * vec), ceil_div(T, 8 * pw::kConvPairT), B);
-        if (vec == 4) {
-            if (bf16) KDA_LAUNCH("conv_fwd_kernel", st, pw::conv_fwd_pair_kernel<W, 4, true><<<grid, 256, 0, st>>>(T, C, silu, wf32, x, w, y));
-            else KDA_LAUNCH("conv_fwd_kernel", st, pw::conv_fwd_pair_kernel<W, 4, false><<<grid, 256, 0, st>>>(T, C, silu, wf32, x, w, y));
-        } else {
-            if (bf16) KDA_LAUNCH("conv_fwd_kernel", st, pw::conv_fwd_pair_kernel<W, 2, true><<<grid, 256, 0, st>>>(T, C, silu, wf32, x, w, y));
-            else KDA_LAUNCH("conv_fwd_kernel", st, pw::conv_fwd_pair_kernel<W, 2, false><<<grid, 256, 0, st>>>(T, C, silu, wf32, x, w, y));
-        }
-        return launch_status();
+        pw::ConvFwdItems it = {};
+        it.x[0] = x; it.w[0] = w; it.y[0] = y;
+        return conv_fwd_fast<W>(1, B, T, C, bf16, wf32, silu, it, st);
     }
     if (bf16) {
         if (C % 8 == 0 && al16) KDA_LAUNCH("conv_fwd_kernel", st, pw::conv_fwd_kernel<W, 8, true><<<blocks(8), 256, 0, st>>>(B, T, C, silu, wf32, x, w, cache, y, fin));
@@ -1251,12 +1299,9 @@ int conv_bwd_w(int B, int T, int C, int bf16, int wf32, int silu, const void* x,
         // no carried-in window and no final-state cotangent: the tiled kernel (same partial layout: one row of
         // partials per 64-token tile and batch entry)
         if (!cache && !dfin && !dcache && C % 2 == 0 && al16) {
-            grid = dim3(ceil_div(C, pw::kConvTileC), ceil_div(T, pw::kConvTileT), B);
-            if (bf16) KDA_LAUNCH("conv_bwd_kernel", st, pw::conv_bwd_tile_kernel<W, true><<<grid, 256, 0, st>>>(T, C, silu, wf32, x, w, dy, dx, part));
-            else KDA_LAUNCH("conv_bwd_kernel", st, pw::conv_bwd_tile_kernel<W, false><<<grid, 256, 0, st>>>(T, C, silu, wf32, x, w, dy, dx, part));
-            const int nblk = grid.y * grid.z;
-            KDA_LAUNCH("conv_dw_reduce_kernel", st, pw::column_sum_kernel<<<ceil_div(C * W, 32), 1024, 0, st>>>(nblk, C * W, part, dwgt));
-            return launch_status();
+            pw::ConvBwdItems it = {};
+            it.x[0] = x; it.w[0] = w; it.dy[0] = dy; it.dx[0] = dx;
+            return conv_bwd_fast<W>(1, B, T, C, bf16, wf32, silu, it, &dwgt, part, st);
         }
     }
     // the vector path keeps W*VEC partials per thread in shared memory; wide windows use the scalar path
@@ -1285,7 +1330,9 @@ int conv_bwd_w(int B, int T, int C, int bf16, int wf32, int silu, const void* x,
         }
     }
     const int nblk = grid.y * grid.z;
-    KDA_LAUNCH("conv_dw_reduce_kernel", st, pw::column_sum_kernel<<<ceil_div(C * W, 32), 1024, 0, st>>>(nblk, C * W, part, dwgt));
+    pw::ColumnSumItems outs = {};
+    outs.out[0] = dwgt;
+    KDA_LAUNCH("conv_dw_reduce_kernel", st, pw::column_sum_kernel<<<ceil_div(C * W, 32), 1024, 0, st>>>(nblk, C * W, part, outs));
     return launch_status();
 }
 
@@ -1337,6 +1384,71 @@ extern "C" int kda_conv_bwd(int32_t batch, int32_t seq_len, int32_t channels, in
                    d_initial_state, dweight, static_cast<float*>(scratch), st)
     KDA_CONV_SWITCH(CALL)
 #undef CALL
+}
+
+// n same-shaped convolutions (the q, k and v branches of a layer) in one launch each way: training path only (no
+// carried-in window, no final state), width <= 4, even channel count, 16-byte aligned tensors; anything else returns
+// KDA_ERR_UNSUPPORTED and the caller issues the per-tensor calls.
+namespace {
+bool conv_multi_ok(int n, int channels, int width, const void* const* a, const void* const* b, const void* const* c) {
+    if (n < 1 || n > pw::kConvItems || width > 4 || channels % 2 != 0) return false;
+    for (int i = 0; i < n; ++i) {
+        if (!a[i] || !b[i] || (c && !c[i])) return false;
+        if ((reinterpret_cast<uintptr_t>(a[i]) | reinterpret_cast<uintptr_t>(b[i]) | (c ? reinterpret_cast<uintptr_t>(c[i]) : 0)) % 16) return false;
+    }
+    return true;
+}
+}  // namespace
+
+extern "C" int kda_conv_fwd_multi(int32_t n_items, int32_t batch, int32_t seq_len, int32_t channels, int32_t width,
+                                  int32_t io_dtype, int32_t silu, const void* const* x, const void* const* weight,
+                                  void* const* y, void* stream) {
+    if (batch <= 0 || seq_len <= 0 || channels <= 0 || width <= 0) return KDA_ERR_BAD_SHAPE;
+    if (!x || !weight || !y) return KDA_ERR_NULL;
+    if (!conv_multi_ok(n_items, channels, width, x, const_cast<const void* const*>(y), nullptr)) return KDA_ERR_UNSUPPORTED;
+    const int wf32 = (io_dtype & KDA_WEIGHT_F32) != 0;
+    const int bf16 = (io_dtype & 0xff) == KDA_DTYPE_BF16;
+    pw::ConvFwdItems it = {};
+    for (int i = 0; i < n_items; ++i) {
+        if (!weight[i]) return KDA_ERR_NULL;
+        it.x[i] = x[i]; it.w[i] = weight[i]; it.y[i] = y[i];
+    }
+    cudaStream_t st = (cudaStream_t)stream;
+    switch (width) {
+        case 1: return conv_fwd_fast<1>(n_items, batch, seq_len, channels, bf16, wf32, silu, it, st);
+        case 2: return conv_fwd_fast<2>(n_items, batch, seq_len, channels, bf16, wf32, silu, it, st);
+        case 3: return conv_fwd_fast<3>(n_items, batch, seq_len, channels, bf16, wf32, silu, it, st);
+        default: return conv_fwd_fast<4>(n_items, batch, seq_len, channels, bf16, wf32, silu, it, st);
+    }
+}
+
+extern "C" size_t kda_conv_bwd_multi_scratch_bytes(int32_t n_items, int32_t batch, int32_t seq_len, int32_t channels, int32_t width) {
+    return (size_t)(n_items > 0 ? n_items : 1) * kda_conv_bwd_scratch_bytes(batch, seq_len, channels, width);
+}
+
+extern "C" int kda_conv_bwd_multi(int32_t n_items, int32_t batch, int32_t seq_len, int32_t channels, int32_t width,
+                                  int32_t io_dtype, int32_t silu, const void* const* x, const void* const* weight,
+                                  const void* const* d_y, void* const* dx, float* const* dweight, void* scratch,
+                                  size_t scratch_bytes, void* stream) {
+    if (batch <= 0 || seq_len <= 0 || channels <= 0 || width <= 0) return KDA_ERR_BAD_SHAPE;
+    if (!x || !weight || !d_y || !dx || !dweight) return KDA_ERR_NULL;
+    if (!conv_multi_ok(n_items, channels, width, x, d_y, const_cast<const void* const*>(dx))) return KDA_ERR_UNSUPPORTED;
+    if (!scratch || scratch_bytes < kda_conv_bwd_multi_scratch_bytes(n_items, batch, seq_len, channels, width)) return KDA_ERR_WORKSPACE;
+    const int wf32 = (io_dtype & KDA_WEIGHT_F32) != 0;
+    const int bf16 = (io_dtype & 0xff) == KDA_DTYPE_BF16;
+    pw::ConvBwdItems it = {};
+    for (int i = 0; i < n_items; ++i) {
+        if (!weight[i] || !dweight[i]) return KDA_ERR_NULL;
+        it.x[i] = x[i]; it.w[i] = weight[i]; it.dy[i] = d_y[i]; it.dx[i] = dx[i];
+    }
+    cudaStream_t st = (cudaStream_t)stream;
+    float* part = static_cast<float*>(scratch);
+    switch (width) {
+        case 1: return conv_bwd_fast<1>(n_items, batch, seq_len, channels, bf16, wf32, silu, it, dweight, part, st);
+        case 2: return conv_bwd_fast<2>(n_items, batch, seq_len, channels, bf16, wf32, silu, it, dweight, part, st);
+        case 3: return conv_bwd_fast<3>(n_items, batch, seq_len, channels, bf16, wf32, silu, it, dweight, part, st);
+        default: return conv_bwd_fast<4>(n_items, batch, seq_len, channels, bf16, wf32, silu, it, dweight, part, st);
+    }
 }
 
 namespace {
@@ -1399,7 +1511,9 @@ extern "C" int kda_rmsnorm_gate_bwd(int64_t rows, int32_t dim, int32_t io_dtype,
             else KDA_LAUNCH("rmsnorm_bwd_kernel", st, pw::rmsnorm_bwd_kernel<false, false><<<nb, 256, smem, st>>>(rows, dim, x, gate, weight, inv_rms, d_y, dx, dgate, part));
         }
     }
-    KDA_LAUNCH("rmsnorm_dw_reduce_kernel", st, pw::column_sum_kernel<<<ceil_div(dim, 32), 1024, 0, st>>>(nb, dim, part, dweight));
+    pw::ColumnSumItems outs = {};
+    outs.out[0] = dweight;
+    KDA_LAUNCH("rmsnorm_dw_reduce_kernel", st, pw::column_sum_kernel<<<ceil_div(dim, 32), 1024, 0, st>>>(nb, dim, part, outs));
     return launch_status();
 }
 

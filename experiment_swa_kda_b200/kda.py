@@ -281,6 +281,24 @@ class ShortConvolution(nn.Conv1d):
         return ops.ConvFunction.apply(x, self.weight.squeeze(1), state, output_final_state, True)
 
 
+def short_convolutions(convs, xs):
+    """Run several same-shaped `ShortConvolution`s (the q, k and v branches of a layer) as one launch each way.
+
+    Training path only: no cache in, no final state out.  Returns the list of outputs; results are identical to calling
+    the modules one by one (the same kernel runs over an extra grid dimension)."""
+    convs, xs = list(convs), list(xs)
+    if len(convs) != len(xs) or not convs:
+        raise ValueError("short_convolutions needs one input per convolution")
+    for conv, x in zip(convs, xs):
+        if x.ndim != 3 or x.shape[-1] != conv.in_channels:
+            raise ValueError(f"x must have shape [B,T,{conv.in_channels}]")
+        if not x.is_cuda:
+            raise RuntimeError("project CUDA causal convolution cannot fall back on CPU")
+    if len(convs) > 4 or xs[0].shape[1] == 0:
+        return [conv(x)[0] for conv, x in zip(convs, xs)]
+    return list(ops.ConvMultiFunction.apply(True, len(convs), *xs, *[c.weight.squeeze(1) for c in convs]))
+
+
 class KimiDeltaAttention(nn.Module):
     """K3-compatible KDA mixer: q/k/v projections -> short conv -> KDA -> gated RMSNorm -> o_proj."""
 
@@ -321,9 +339,15 @@ class KimiDeltaAttention(nn.Module):
         k_state = None if state is None else state.k_conv
         v_state = None if state is None else state.v_conv
         memory = None if state is None else state.memory
-        q, q_final = self.q_conv1d(self.q_proj(hidden_states), q_state, output_final_state=want_state)
-        k, k_final = self.k_conv1d(self.k_proj(hidden_states), k_state, output_final_state=want_state)
-        v, v_final = self.v_conv1d(self.v_proj(hidden_states), v_state, output_final_state=want_state)
+        if state is None and not want_state and length > 0:
+            # training path: the three branches share one launch each way
+            q, k, v = short_convolutions((self.q_conv1d, self.k_conv1d, self.v_conv1d),
+                                         (self.q_proj(hidden_states), self.k_proj(hidden_states), self.v_proj(hidden_states)))
+            q_final = k_final = v_final = None
+        else:
+            q, q_final = self.q_conv1d(self.q_proj(hidden_states), q_state, output_final_state=want_state)
+            k, k_final = self.k_conv1d(self.k_proj(hidden_states), k_state, output_final_state=want_state)
+            v, v_final = self.v_conv1d(self.v_proj(hidden_states), v_state, output_final_state=want_state)
         shape4 = (batch, length, self.num_heads, self.head_dim)
         q, k, v = q.reshape(shape4), k.reshape(shape4), v.reshape(shape4)
         raw_gate = self.f_b_proj(self.f_a_proj(hidden_states)).reshape(shape4)
@@ -338,4 +362,4 @@ class KimiDeltaAttention(nn.Module):
 
 
 __all__ = ["KDAState", "KimiDeltaAttention", "RMSNormGated", "ShortConvolution", "chunk_kda", "k3_decay_gate", "kda",
-           "kda_backend_provenance", "prepare_kda_backend", "recurrent_kda_step"]
+           "kda_backend_provenance", "prepare_kda_backend", "recurrent_kda_step", "short_convolutions"]

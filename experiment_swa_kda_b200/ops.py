@@ -276,6 +276,75 @@ class ConvFunction(torch.autograd.Function):
         return dx, dw.to(ctx.wdtype), dinit, None, None
 
 
+def _ptr_array(ts):
+    import ctypes as C
+    arr = (C.c_void_p * len(ts))(*[t.data_ptr() for t in ts])
+    return arr
+
+
+class ConvMultiFunction(torch.autograd.Function):
+    """n same-shaped causal convolutions + SiLU (the q, k and v branches of a layer) in one launch each way.
+    Training path only (no cache, no final state); falls back to the per-tensor operator when the library declines."""
+
+    @staticmethod
+    def forward(ctx, silu, n, *tensors):
+        import ctypes as C
+        xs = [t.contiguous() for t in tensors[:n]]
+        ws = []
+        for w in tensors[n:]:
+            w = w.contiguous()
+            ws.append(w if w.dtype == torch.float32 else w.to(xs[0].dtype))
+        lib = _lib.load()
+        dev = _need_cuda(*xs, *ws)
+        B, T, Cc = xs[0].shape
+        W = ws[0].shape[-1]
+        same = all(x.shape == xs[0].shape and x.dtype == xs[0].dtype for x in xs) and \
+            all(w.shape == ws[0].shape and w.dtype == ws[0].dtype for w in ws)
+        ys = [torch.empty_like(x) for x in xs]
+        rc = _lib.ERR_UNSUPPORTED
+        if same:
+            with torch.cuda.device(dev):
+                rc = lib.kda_conv_fwd_multi(n, B, T, Cc, W, _dt(xs[0]) | _wflag(xs[0], ws[0]), 1 if silu else 0,
+                                            C.cast(_ptr_array(xs), C.c_void_p), C.cast(_ptr_array(ws), C.c_void_p),
+                                            C.cast(_ptr_array(ys), C.c_void_p), _stream(dev))
+        if rc == _lib.ERR_UNSUPPORTED:
+            ys = [conv_fwd(x, w, None, False, silu)[0] for x, w in zip(xs, ws)]
+        else:
+            _lib.check(rc, "kda_conv_fwd_multi")
+        ctx.save_for_backward(*xs, *ws)
+        ctx.n, ctx.silu, ctx.same = n, silu, same
+        ctx.wdtypes = [w.dtype for w in tensors[n:]]
+        return tuple(ys)
+
+    @staticmethod
+    def backward(ctx, *dys):
+        import ctypes as C
+        n = ctx.n
+        saved = ctx.saved_tensors
+        xs, ws = list(saved[:n]), list(saved[n:])
+        dys = [(torch.zeros_like(x) if d is None else d.contiguous().to(x.dtype)) for d, x in zip(dys, xs)]
+        lib = _lib.load()
+        dev = xs[0].device
+        B, T, Cc = xs[0].shape
+        W = ws[0].shape[-1]
+        dxs = [torch.empty_like(x) for x in xs]
+        dws = [torch.empty(Cc, W, dtype=torch.float32, device=dev) for _ in xs]
+        rc = _lib.ERR_UNSUPPORTED
+        if ctx.same:
+            scr = _bytes(lib.kda_conv_bwd_multi_scratch_bytes(n, B, T, Cc, W), dev)
+            with torch.cuda.device(dev):
+                rc = lib.kda_conv_bwd_multi(n, B, T, Cc, W, _dt(xs[0]) | _wflag(xs[0], ws[0]), 1 if ctx.silu else 0,
+                                            C.cast(_ptr_array(xs), C.c_void_p), C.cast(_ptr_array(ws), C.c_void_p),
+                                            C.cast(_ptr_array(dys), C.c_void_p), C.cast(_ptr_array(dxs), C.c_void_p),
+                                            C.cast(_ptr_array(dws), C.c_void_p), _ptr(scr), scr.numel(), _stream(dev))
+        if rc == _lib.ERR_UNSUPPORTED:
+            res = [conv_bwd(x, w, None, d, None, ctx.silu) for x, w, d in zip(xs, ws, dys)]
+            dxs, dws = [r[0] for r in res], [r[1] for r in res]
+        else:
+            _lib.check(rc, "kda_conv_bwd_multi")
+        return (None, None, *dxs, *[dw.to(dt) for dw, dt in zip(dws, ctx.wdtypes)])
+
+
 # --------------------------------------------------------------------------------------------
 # gated RMSNorm
 # --------------------------------------------------------------------------------------------

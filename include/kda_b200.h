@@ -138,6 +138,19 @@ int kda_conv_bwd(int32_t batch, int32_t seq_len, int32_t channels, int32_t width
  * x, gate, y [rows, dim] in io_dtype; weight float32 [dim]; inv_rms float32 [rows].
  * Stands in for nanochat_kda::rmsnorm_gate_forward / _backward (reference rmsnorm_gate.cu:31-273).
  */
+/* n_items (1..4) same-shaped convolutions in ONE launch each way - the q, k and v branches of a layer (the reference
+ * issues three separate operator calls, nanochat/mixers/kda.py:758-766; there is no batched counterpart there).
+ * Training path only: no carried-in window, no final state, width <= 4, even channel count, 16-byte aligned tensors;
+ * any other case returns KDA_ERR_UNSUPPORTED and the caller issues the per-tensor calls.  x, weight, y, d_y, dx, dweight
+ * are HOST arrays of n_items device pointers; io_dtype may carry KDA_WEIGHT_F32.  scratch:
+ * kda_conv_bwd_multi_scratch_bytes. */
+int kda_conv_fwd_multi(int32_t n_items, int32_t batch, int32_t seq_len, int32_t channels, int32_t width, int32_t io_dtype,
+                       int32_t silu, const void* const* x, const void* const* weight, void* const* y, void* stream);
+size_t kda_conv_bwd_multi_scratch_bytes(int32_t n_items, int32_t batch, int32_t seq_len, int32_t channels, int32_t width);
+int kda_conv_bwd_multi(int32_t n_items, int32_t batch, int32_t seq_len, int32_t channels, int32_t width, int32_t io_dtype,
+                       int32_t silu, const void* const* x, const void* const* weight, const void* const* d_y,
+                       void* const* dx, float* const* dweight, void* scratch, size_t scratch_bytes, void* stream);
+
 int kda_rmsnorm_gate_fwd(int64_t rows, int32_t dim, int32_t io_dtype, float eps, const void* x, const void* gate,
                          const float* weight, void* y, float* inv_rms, void* stream);
 size_t kda_rmsnorm_gate_bwd_scratch_bytes(int64_t rows, int32_t dim);

@@ -91,6 +91,24 @@ def test_conv_training_path_matches_oracle(B, T, C, dtype):
     assert O.rel_l2(got[1].squeeze(1).float(), want[1]) <= tol
 
 
+@pytest.mark.parametrize("B,T,C,dtype", [(2, 300, 384, torch.bfloat16), (1, 67, 20, torch.float32)])
+def test_short_convolutions_one_launch_equals_per_tensor_calls(B, T, C, dtype):
+    """The batched q/k/v convolution entry points give bit-identical outputs and gradients to three separate calls."""
+    gen = torch.Generator().manual_seed(T + C)
+    mods = [_conv_mod(C, 4, ((torch.rand(C, 4, generator=gen) * 2 - 1) * 0.1).to(D0)) for _ in range(3)]
+    xs = [torch.randn(B, T, C, generator=gen).to(dtype).to(D0).requires_grad_(True) for _ in range(3)]
+    cys = [torch.randn(B, T, C, generator=gen).to(dtype).to(D0) for _ in range(3)]
+    import experiment_swa_kda_b200 as M
+    ys = M.short_convolutions(mods, xs)
+    got = torch.autograd.grad(ys, xs + [m.weight for m in mods], cys)
+    ys1 = [m(x)[0] for m, x in zip(mods, xs)]
+    want = torch.autograd.grad(ys1, xs + [m.weight for m in mods], cys)
+    for a, b in zip(ys, ys1):
+        assert torch.equal(a, b)
+    for a, b in zip(got, want):
+        assert torch.equal(a, b)
+
+
 def test_conv_full_sequence_equals_token_decode():
     gen = torch.Generator().manual_seed(99)
     x = torch.randn(2, 9, 8, generator=gen).to(D0)
