@@ -230,6 +230,20 @@ def test_decode_step_activated_surface(K, V, dtype):
     assert O.rel_l2(o.float(), eo) <= tol and O.rel_l2(s, es) <= (FP32_TOL if dtype == torch.float32 else 1e-4)
 
 
+@pytest.mark.parametrize("K,V", [(128, 128), (256, 64), (20, 12)])
+def test_decode_step_in_place_state_equals_out_of_place(K, V):
+    """state_out may alias state_in (a serving loop that keeps one state buffer per layer): every row is read in full
+    before it is written, so the in-place update is bit-identical to the non-mutating one."""
+    from experiment_swa_kda_b200 import ops
+    d = O.make_inputs(5, 1, 3, K, V, seed=K * V, with_state=True)
+    x = to_dev(d, torch.bfloat16 if K >= 128 else torch.float32)
+    o_ref, s_ref = ops.decode_step(x["q"], x["k"], x["v"], x["g"], x["beta"], x["h0"], K ** -0.5, True)
+    state = x["h0"].clone()
+    o, s = ops.decode_step(x["q"], x["k"], x["v"], x["g"], x["beta"], state, K ** -0.5, True, out_state=state)
+    assert s.data_ptr() == state.data_ptr()
+    assert torch.equal(o, o_ref) and torch.equal(state, s_ref)
+
+
 # ---------------------------------------------------------------------------------- contracts
 def test_contract_errors_and_fail_closed():
     m = kda_mod()
