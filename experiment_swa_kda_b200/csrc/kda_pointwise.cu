@@ -497,6 +497,16 @@ struct ConvBwdItems {
 struct ColumnSumItems {
     float* out[kConvItems];
 };
+// Entry i of a kernel-parameter array by compile-time indices only: a run-time subscript would make every thread copy the
+// whole array to local memory first.
+template <class T>
+__device__ __forceinline__ T pick_item(T const (&a)[kConvItems], int i) {
+    T r = a[0];
+    if (i == 1) r = a[1];
+    if (i == 2) r = a[2];
+    if (i == 3) r = a[3];
+    return r;
+}
 
 // grid: x = channel blocks of 32*VEC, y = blocks of 8 time groups x kConvPairT tokens, z = item * B + batch
 template <int W, int VEC, bool BF16>
@@ -506,9 +516,9 @@ __global__ void __launch_bounds__(256) conv_fwd_pair_kernel(int B, int T, int C,
     const int item = blockIdx.z / B;
     const int t0 = (blockIdx.y * 8 + g) * kConvPairT, b = blockIdx.z - item * B;
     if (t0 >= T) return;
-    const void* __restrict__ x = items.x[item];
-    const void* __restrict__ wgt = items.w[item];
-    void* __restrict__ y = items.y[item];
+    const void* __restrict__ x = pick_item(items.x, item);
+    const void* __restrict__ wgt = pick_item(items.w, item);
+    void* __restrict__ y = pick_item(items.y, item);
     const bool cok = c < C;
     const int cl = cok ? c : 0;
     float wv[W][VEC];
@@ -765,10 +775,10 @@ __global__ void __launch_bounds__(256) conv_bwd_tile_kernel(int B, int T, int C,
     const int c = cb + 2 * p;
     const int item = blockIdx.z / B;
     const int t0 = blockIdx.y * kConvTileT, b = blockIdx.z - item * B;
-    const void* __restrict__ x = items.x[item];
-    const void* __restrict__ wgt = items.w[item];
-    const void* __restrict__ dy = items.dy[item];
-    void* __restrict__ dx = items.dx[item];
+    const void* __restrict__ x = pick_item(items.x, item);
+    const void* __restrict__ wgt = pick_item(items.w, item);
+    const void* __restrict__ dy = pick_item(items.dy, item);
+    void* __restrict__ dx = pick_item(items.dx, item);
     const bool cok = c < C;
     const int cl = cok ? c : 0;                    // loads stay unconditional: out-of-range lanes read column 0 and are masked
     float w0[W], w1[W];
@@ -1146,7 +1156,7 @@ __global__ void __launch_bounds__(1024) column_sum_kernel(int nblk, int N, const
                                                           ColumnSumItems outs) {
     __shared__ float red[32][33];
     const float* __restrict__ part = part_all + (size_t)blockIdx.y * nblk * N;     // blockIdx.y = item
-    float* __restrict__ out = outs.out[blockIdx.y];
+    float* __restrict__ out = pick_item(outs.out, (int)blockIdx.y);
     const int lane = threadIdx.x & 31, seg = threadIdx.x >> 5;
     const int i = blockIdx.x * 32 + lane;
     float a = 0.f;

@@ -120,6 +120,21 @@ def test_varlen_bf16_d128():
     run_case(1, 400, 2, 128, 128, dtype=torch.bfloat16, seed=12, tol=BF16_TOL, cu=cu, n_states=3)
 
 
+def test_varlen_many_short_sequences_bf16_d128():
+    """Tensor-core lane on a packed batch of mostly sub-chunk sequences with an empty one: one- and two-step scans,
+    ragged tails everywhere, more sequences than chunks per sequence."""
+    lens = [1, 63, 64, 65, 2, 0, 128, 129, 7, 191, 64, 33]
+    cu = [0]
+    for n in lens:
+        cu.append(cu[-1] + n)
+    run_case(1, cu[-1], 3, 128, 128, dtype=torch.bfloat16, seed=21, tol=BF16_TOL, cu=cu, n_states=len(lens))
+
+
+def test_long_chain_bf16_d128_single_head():
+    """160 dependent chunk steps of one (sequence, head): error growth of the bf16 tensor-core scans stays inside the bar."""
+    run_case(1, 160 * 64 - 17, 1, 128, 128, dtype=torch.bfloat16, seed=22, tol=BF16_TOL)
+
+
 # ---------------------------------------------------------------------------------- raw surface vs the reference's vectors
 NAMES = ("q", "k", "v", "raw_gate", "beta_logits", "A_log", "dt_bias", "initial_state")
 
