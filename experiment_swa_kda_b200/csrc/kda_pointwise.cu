@@ -410,8 +410,12 @@ __global__ void __launch_bounds__(256) conv_fwd_kernel(int B, int T, int C, int 
 // consecutive tokens with all of its loads issued up front.
 template <bool BF16>
 __device__ __forceinline__ float2 ld_pair(const void* p, size_t i) {
-    if (BF16) return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(reinterpret_cast<const __nv_bfloat16*>(p) + i));
-    return *reinterpret_cast<const float2*>(reinterpret_cast<const float*>(p) + i);
+    // read-only path: the inputs are never written by the kernel that reads them
+    if (BF16) {
+        const unsigned u = __ldg(reinterpret_cast<const unsigned*>(reinterpret_cast<const __nv_bfloat16*>(p) + i));
+        return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u));
+    }
+    return __ldg(reinterpret_cast<const float2*>(reinterpret_cast<const float*>(p) + i));
 }
 template <bool BF16>
 __device__ __forceinline__ void st_pair(void* p, size_t i, float a, float b) {
@@ -457,12 +461,12 @@ __device__ __forceinline__ void ld_cvec(float (&d)[VEC], const void* p, size_t i
         const float2 v = ld_pair<BF16>(p, i);
         d[0] = v.x; d[1] = v.y;
     } else if (BF16) {
-        const uint2 u = *reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(p) + i);
+        const uint2 u = __ldg(reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(p) + i));
         const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.x));
         const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.y));
         d[0] = a.x; d[1] = a.y; d[2] = b.x; d[3] = b.y;
     } else {
-        const float4 f = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p) + i);
+        const float4 f = __ldg(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p) + i));
         d[0] = f.x; d[1] = f.y; d[2] = f.z; d[3] = f.w;
     }
 }
@@ -793,8 +797,12 @@ __global__ void __launch_bounds__(256) conv_bwd_tile_kernel(int B, int T, int C,
     }
     const size_t rowbase = (size_t)b * T;
     auto xload = [&](int tc) -> xpair_t {
-        if constexpr (BF16) return *reinterpret_cast<const __nv_bfloat162*>(reinterpret_cast<const __nv_bfloat16*>(x) + (rowbase + tc) * C + cl);
-        else return *reinterpret_cast<const float2*>(reinterpret_cast<const float*>(x) + (rowbase + tc) * C + cl);
+        if constexpr (BF16) {
+            const unsigned u = __ldg(reinterpret_cast<const unsigned*>(reinterpret_cast<const __nv_bfloat16*>(x) + (rowbase + tc) * C + cl));
+            return *reinterpret_cast<const __nv_bfloat162*>(&u);
+        } else {
+            return __ldg(reinterpret_cast<const float2*>(reinterpret_cast<const float*>(x) + (rowbase + tc) * C + cl));
+        }
     };
     auto xwide = [](const xpair_t& v) -> float2 {
         if constexpr (BF16) return __bfloat1622float2(v);
