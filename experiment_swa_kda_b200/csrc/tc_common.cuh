@@ -47,21 +47,13 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* s
     return false;
 }
 
-// Warp-level forms: one lane touches the barrier for the whole (converged) warp.  Arrivals on one barrier word are
-// serialised atomics, so a barrier that hundreds of threads arrive on costs hundreds of cycles; counted per warp it
-// costs a few.  The barrier's expected count must then be the number of WARPS.
+// Warp-level arrival: one lane touches the barrier for the whole (converged) warp, so the number of serialised
+// arrivals on the barrier word is the number of warps, not of threads.  The barrier's expected count must then be the
+// number of WARPS.
 __device__ __forceinline__ void warp_arrive(uint64_t* bar, int lane) {
     __syncwarp();
     if (lane == 0) mbar_arrive(bar);
 }
-__device__ __forceinline__ bool warp_wait(uint64_t* bar, uint32_t parity, int* status, int code, int lane) {
-    int ok = 1;
-    if (lane == 0) ok = mbar_wait(bar, parity, status, code) ? 1 : 0;
-    ok = __shfl_sync(0xffffffffu, ok, 0);
-    __syncwarp();
-    return ok != 0;
-}
-
 // ------------------------------------------------------------------------------------- proxies / fences
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
