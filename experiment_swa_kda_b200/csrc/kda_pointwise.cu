@@ -771,8 +771,8 @@ __global__ void __launch_bounds__(256) conv_bwd_tile_kernel(int B, int T, int C,
     constexpr int RPW = kConvTileT / 8;            // consecutive rows per warp
     // x stays in its storage type (a bf16 pair is one 32-bit word); dy is widened because dz replaces it in place
     typedef typename std::conditional<BF16, __nv_bfloat162, float2>::type xpair_t;
-    __shared__ xpair_t xs[XR][32];
-    __shared__ float2 gs[GR][32];
+    __shared__ __align__(16) xpair_t xs[XR][32];
+    __shared__ __align__(16) float2 gs[GR][32];
     __shared__ float red[8][W][kConvTileC];
     const int p = threadIdx.x & 31, g = threadIdx.x >> 5;
     const int cb = blockIdx.x * kConvTileC;
@@ -808,19 +808,57 @@ __global__ void __launch_bounds__(256) conv_bwd_tile_kernel(int B, int T, int C,
         if constexpr (BF16) return __bfloat1622float2(v);
         else return v;
     };
+    if (t0 >= W - 1 && t0 + GR <= T && cb + kConvTileC <= C && (C & 3) == 0) {
+        // interior tile: no clamping, four channels per thread (sixteen threads cover a 64-channel row, a warp two rows),
+        // addresses advance by a constant stride
+        const int q = threadIdx.x & 15, rg = threadIdx.x >> 4;
+        const size_t e0 = (rowbase + t0 - (W - 1) + rg) * C + cb + 4 * q;       // x row rg of the tile, this thread's channels
+        const size_t step = (size_t)16 * C;
 #pragma unroll
-    for (int r = g; r < XR; r += 8) {
-        const int t = t0 - (W - 1) + r;
-        xpair_t v = xload(min(max(t, 0), T - 1));
-        if (t < 0 || t >= T || !cok) v = xpair_t();
-        xs[r][p] = v;
-    }
+        for (int it = 0; it < (XR + 15) / 16; ++it) {
+            const int r = rg + 16 * it;
+            if (r < XR) {
+                if constexpr (BF16) {
+                    const uint2 u = __ldg(reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(x) + e0 + it * step));
+                    *reinterpret_cast<uint2*>(&xs[r][2 * q]) = u;
+                } else {
+                    const float4 f = __ldg(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(x) + e0 + it * step));
+                    *reinterpret_cast<float4*>(&xs[r][2 * q]) = f;
+                }
+            }
+        }
+        const size_t g0 = (rowbase + t0 + rg) * C + cb + 4 * q;
 #pragma unroll
-    for (int r = g; r < GR; r += 8) {
-        const int t = t0 + r;
-        float2 v = ld_pair<BF16>(dy, (rowbase + min(t, T - 1)) * C + cl);
-        if (t >= T || !cok) v = make_float2(0.f, 0.f);
-        gs[r][p] = v;
+        for (int it = 0; it < (GR + 15) / 16; ++it) {
+            const int r = rg + 16 * it;
+            if (r < GR) {
+                float4 f;
+                if constexpr (BF16) {
+                    const uint2 u = __ldg(reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(dy) + g0 + it * step));
+                    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.x));
+                    const float2 b2 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.y));
+                    f = make_float4(a.x, a.y, b2.x, b2.y);
+                } else {
+                    f = __ldg(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(dy) + g0 + it * step));
+                }
+                *reinterpret_cast<float4*>(&gs[r][2 * q]) = f;
+            }
+        }
+    } else {
+#pragma unroll
+        for (int r = g; r < XR; r += 8) {
+            const int t = t0 - (W - 1) + r;
+            xpair_t v = xload(min(max(t, 0), T - 1));
+            if (t < 0 || t >= T || !cok) v = xpair_t();
+            xs[r][p] = v;
+        }
+#pragma unroll
+        for (int r = g; r < GR; r += 8) {
+            const int t = t0 + r;
+            float2 v = ld_pair<BF16>(dy, (rowbase + min(t, T - 1)) * C + cl);
+            if (t >= T || !cok) v = make_float2(0.f, 0.f);
+            gs[r][p] = v;
+        }
     }
     __syncthreads();
     float dw0[W], dw1[W];
