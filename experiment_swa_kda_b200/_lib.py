@@ -31,6 +31,7 @@ _SIGNATURES = {
     "kda_chunk_bwd_scratch_bytes": (C.c_size_t, [C.POINTER(ChunkShape)]),
     "kda_chunk_fwd": (C.c_int, [C.POINTER(ChunkShape)] + [_P] * 10 + [C.c_size_t, _P]),
     "kda_chunk_bwd": (C.c_int, [C.POINTER(ChunkShape)] + [_P] * 9 + [C.c_size_t, _P, C.c_size_t] + [_P] * 7),
+    "kda_chunk_status": (C.c_int, [C.POINTER(ChunkShape), _P, _P]),
     "kda_gate_fwd": (C.c_int, [C.c_int32] * 4 + [_P] * 4 + [C.c_float] + [_P] * 3),
     "kda_gate_bwd_scratch_bytes": (C.c_size_t, [C.c_int32] * 3),
     "kda_gate_bwd": (C.c_int, [C.c_int32] * 4 + [_P] * 4 + [C.c_float] + [_P] * 7 + [C.c_size_t, _P]),

@@ -14,6 +14,7 @@
 namespace kda {
 int simt_chunk_fwd(const KdaChunkShape* sh, const void* q, const void* k, const void* v, const void* g, const void* beta,
                    const float* h0, const int32_t* cu, void* o, float* final_state, void* workspace, cudaStream_t st);
+int chunk_status(const KdaChunkShape* sh, const void* workspace, cudaStream_t st);
 int simt_chunk_bwd(const KdaChunkShape* sh, const void* q, const void* k, const void* v, const void* g, const void* beta,
                    const int32_t* cu, const void* d_o, const float* d_final, const void* workspace, void* scratch,
                    void* dq, void* dk, void* dv, void* dg, void* dbeta, float* dh0, cudaStream_t st);
@@ -135,6 +136,11 @@ void end(cudaStream_t st) {
 }
 }  // namespace prof
 }  // namespace kda
+
+extern "C" int kda_chunk_status(const KdaChunkShape* shape, const void* workspace, void* stream) {
+    if (!shape || !workspace) return KDA_ERR_NULL;
+    return chunk_status(shape, workspace, (cudaStream_t)stream);
+}
 
 extern "C" unsigned long long kda_launch_count(void) {
     std::lock_guard<std::mutex> lk(kda::prof::mu);

@@ -105,9 +105,10 @@ __device__ __forceinline__ void st_acc_g(float* dst, size_t ld, const float (&ac
 // ---------------------------------------------------------------------------------------------
 // chunk table: which tokens each 64-token chunk slot covers
 // ---------------------------------------------------------------------------------------------
-__global__ void chunk_table_kernel(Ws w, const int32_t* __restrict__ cu, int n_seq, int seq_len) {
+__global__ void chunk_table_kernel(Ws w, const int32_t* __restrict__ cu, int n_seq, int seq_len, int* status) {
     __shared__ int total;
     if (threadIdx.x == 0) {
+        if (status) *status = 0;      // the tensor-core lane's device status word starts every forward clean
         int acc = 0;
         for (int s = 0; s < n_seq; ++s) {
             w.seq_chunk0[s] = acc;
@@ -925,13 +926,12 @@ int simt_chunk_fwd(const KdaChunkShape* sh, const void* q, const void* k, const 
     Ws w = simt::carve_ws(*sh, workspace);
     const int bf16 = sh->io_dtype == KDA_DTYPE_BF16, gbf16 = sh->gate_dtype == KDA_DTYPE_BF16;
     const int KT = w.Kp / 64, VT = w.Vp / 64;
-    KDA_LAUNCH("chunk_table_kernel", st, simt::chunk_table_kernel<<<1, 256, 0, st>>>(w, cu, sh->n_seq, sh->seq_len));
     if (sh->lane == KDA_LANE_TC) {
-        // chunk-parallel operand panels on tcgen05, then the tensor-core scan with the chunk output fused in
+        // chunk-parallel operand panels and transitions on tcgen05, the affine state scan, then the chunk outputs
         size_t ws_bytes = 0;
         simt::carve_ws(*sh, nullptr, &ws_bytes);
         tc::TcWs t = tc::carve_tc(*sh, static_cast<char*>(workspace) + ws_bytes);
-        if (cudaMemsetAsync(t.status, 0, sizeof(int), st) != cudaSuccess) return KDA_ERR_CUDA;
+        KDA_LAUNCH("chunk_table_kernel", st, simt::chunk_table_kernel<<<1, 256, 0, st>>>(w, cu, sh->n_seq, sh->seq_len, t.status));
         if (w.nslots > 0) {
             int rc = tc_intra_forward(w, t, q, k, v, g, beta, gbf16, sh->l2norm, sh->scale, sh->tokens, st);
             if (rc) return rc;
@@ -940,6 +940,7 @@ int simt_chunk_fwd(const KdaChunkShape* sh, const void* q, const void* k, const 
         }
         return launch_status();
     }
+    KDA_LAUNCH("chunk_table_kernel", st, simt::chunk_table_kernel<<<1, 256, 0, st>>>(w, cu, sh->n_seq, sh->seq_len, nullptr));
     if (w.nslots > 0) {
         dim3 gch(w.nslots, w.H);
         KDA_LAUNCH("prep_kernel", st, simt::prep_kernel<<<gch, 256, 0, st>>>(w, q, k, g, beta, bf16, gbf16, sh->l2norm, sh->scale));
@@ -959,6 +960,20 @@ int simt_chunk_fwd(const KdaChunkShape* sh, const void* q, const void* k, const 
         KDA_LAUNCH("out_kernel", st, simt::out_kernel<<<dim3(w.nslots, w.H, VT), 256, sm_out, st>>>(w, o, bf16));
     }
     return launch_status();
+}
+
+// Device status word of a forward / backward pair that used `workspace`: 0 unless a bounded wait of the tensor-core
+// lane expired.  Reads it back over the stream, i.e. synchronises the stream - for tests and post-mortems, not for the
+// hot path (and not under stream capture).
+int chunk_status(const KdaChunkShape* sh, const void* workspace, cudaStream_t st) {
+    if (sh->lane != KDA_LANE_TC) return KDA_OK;
+    size_t ws_bytes = 0;
+    simt::carve_ws(*sh, nullptr, &ws_bytes);
+    tc::TcWs t = tc::carve_tc(*sh, static_cast<char*>(const_cast<void*>(workspace)) + ws_bytes);
+    int v = 0;
+    if (cudaMemcpyAsync(&v, t.status, sizeof(int), cudaMemcpyDeviceToHost, st) != cudaSuccess) return KDA_ERR_CUDA;
+    if (cudaStreamSynchronize(st) != cudaSuccess) return KDA_ERR_CUDA;
+    return v ? KDA_ERR_DEVICE_STATUS : KDA_OK;
 }
 
 int simt_chunk_bwd(const KdaChunkShape* sh, const void* q, const void* k, const void* v, const void* g, const void* beta,

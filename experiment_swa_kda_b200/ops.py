@@ -99,6 +99,14 @@ def chunk_kda_bwd(q, k, v, g, beta, cu_seqlens, do, dfs, saved, want_dh0):
     return dq, dk, dv, dg, db, dh0
 
 
+def chunk_status(saved, dev) -> None:
+    """Raise if a bounded device-side wait expired in the kernels that used this workspace (synchronises the stream)."""
+    sh, ws = saved
+    with torch.cuda.device(dev):
+        rc = _lib.load().kda_chunk_status(sh, _ptr(ws), _stream(dev))
+    _lib.check(rc, "kda_chunk_status")
+
+
 class ChunkKDAFunction(torch.autograd.Function):
     """Autograd boundary of the chunked operator on activated inputs.
 

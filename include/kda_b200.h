@@ -95,6 +95,12 @@ int kda_chunk_bwd(const KdaChunkShape* shape, const void* q, const void* k, cons
  * (reference chunk.cu:98-132, chunk_wy_forward.cu:188-264; oracle tests/kda_oracle.py:31-47).
  * g_out and beta_out are float32 regardless of io_dtype.
  */
+/* Device status word of the forward / backward that used `workspace`: KDA_OK, or KDA_ERR_DEVICE_STATUS when a bounded
+ * wait inside a tensor-core-lane kernel expired (its results are then undefined).  Copies one word back over `stream`
+ * and SYNCHRONISES it: for tests and post-mortems, not for the hot path, and not under stream capture.  No reference
+ * counterpart (the reference's kernels have no device-side waits to bound). */
+int kda_chunk_status(const KdaChunkShape* shape, const void* workspace, void* stream);
+
 int kda_gate_fwd(int32_t tokens, int32_t heads, int32_t key_dim, int32_t io_dtype, const void* raw_gate,
                  const void* beta_logits, const float* A_log, const float* dt_bias, float lower_bound, float* g_out,
                  float* beta_out, void* stream);

@@ -259,6 +259,15 @@ def test_decode_step_in_place_state_equals_out_of_place(K, V):
     assert torch.equal(o, o_ref) and torch.equal(state, s_ref)
 
 
+def test_device_status_word_is_clean_after_tensor_core_forward_backward():
+    from experiment_swa_kda_b200 import _lib, ops
+    d = O.make_inputs(2, 200, 2, 128, 128, seed=5, with_state=True)
+    x = to_dev(d, torch.bfloat16)
+    o, fs, saved = ops.chunk_kda_fwd(x["q"], x["k"], x["v"], x["g"], x["beta"], x["h0"], None, 128 ** -0.5, True, True, _lib.LANE_TC)
+    ops.chunk_kda_bwd(x["q"], x["k"], x["v"], x["g"], x["beta"], None, torch.ones_like(o), None, saved, True)
+    ops.chunk_status(saved, o.device)      # raises on a non-zero status
+
+
 # ---------------------------------------------------------------------------------- contracts
 def test_contract_errors_and_fail_closed():
     m = kda_mod()
