@@ -20,7 +20,7 @@ LANE_FP32, LANE_TC = 0, 1
 class ChunkShape(C.Structure):
     _fields_ = [("n_seq", C.c_int32), ("seq_len", C.c_int32), ("tokens", C.c_int32), ("heads", C.c_int32),
                 ("key_dim", C.c_int32), ("value_dim", C.c_int32), ("io_dtype", C.c_int32), ("gate_dtype", C.c_int32),
-                ("lane", C.c_int32), ("l2norm", C.c_int32), ("scale", C.c_float)]
+                ("lane", C.c_int32), ("l2norm", C.c_int32), ("scale", C.c_float), ("forward_only", C.c_int32)]
 
 
 _P = C.c_void_p
@@ -32,6 +32,9 @@ _SIGNATURES = {
     "kda_chunk_fwd": (C.c_int, [C.POINTER(ChunkShape)] + [_P] * 10 + [C.c_size_t, _P]),
     "kda_chunk_bwd": (C.c_int, [C.POINTER(ChunkShape)] + [_P] * 9 + [C.c_size_t, _P, C.c_size_t] + [_P] * 7),
     "kda_chunk_status": (C.c_int, [C.POINTER(ChunkShape), _P, _P]),
+    "kda_chunk_status_async": (C.c_int, [C.POINTER(ChunkShape), _P, _P, _P]),
+    "kda_status_word_code": (C.c_int, [C.c_int32]),
+    "kda_selftest_bounded_wait": (C.c_int, [_P, C.c_uint32, _P]),
     "kda_gate_fwd": (C.c_int, [C.c_int32] * 4 + [_P] * 4 + [C.c_float] + [_P] * 3),
     "kda_gate_bwd_scratch_bytes": (C.c_size_t, [C.c_int32] * 3),
     "kda_gate_bwd": (C.c_int, [C.c_int32] * 4 + [_P] * 4 + [C.c_float] + [_P] * 7 + [C.c_size_t, _P]),

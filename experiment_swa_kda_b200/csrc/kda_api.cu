@@ -15,6 +15,8 @@ namespace kda {
 int simt_chunk_fwd(const KdaChunkShape* sh, const void* q, const void* k, const void* v, const void* g, const void* beta,
                    const float* h0, const int32_t* cu, void* o, float* final_state, void* workspace, cudaStream_t st);
 int chunk_status(const KdaChunkShape* sh, const void* workspace, cudaStream_t st);
+int chunk_status_async(const KdaChunkShape* sh, const void* workspace, int32_t* host_word, cudaStream_t st);
+int status_word_to_code(int v);
 int simt_chunk_bwd(const KdaChunkShape* sh, const void* q, const void* k, const void* v, const void* g, const void* beta,
                    const int32_t* cu, const void* d_o, const float* d_final, const void* workspace, void* scratch,
                    void* dq, void* dk, void* dv, void* dg, void* dbeta, float* dh0, cudaStream_t st);
@@ -29,6 +31,7 @@ static int check_shape(const KdaChunkShape* s, const int32_t* cu) {
     if (s->key_dim > KDA_MAX_DIM || s->value_dim > KDA_MAX_DIM) return KDA_ERR_BAD_SHAPE;
     if (s->io_dtype != KDA_DTYPE_F32 && s->io_dtype != KDA_DTYPE_BF16) return KDA_ERR_UNSUPPORTED;
     if (s->gate_dtype != KDA_DTYPE_F32 && s->gate_dtype != KDA_DTYPE_BF16) return KDA_ERR_UNSUPPORTED;
+    if (s->forward_only != 0 && s->forward_only != 1) return KDA_ERR_BAD_SHAPE;
     if (cu) {
         if (s->seq_len != 0) return KDA_ERR_BAD_SHAPE;   // packed batches describe lengths through cu_seqlens only
     } else {
@@ -52,6 +55,7 @@ extern "C" const char* kda_error_string(int code) {
         case KDA_ERR_CUDA: return "CUDA runtime reported an error at launch";
         case KDA_ERR_NULL: return "required pointer is null";
         case KDA_ERR_DEVICE_STATUS: return "kernel reported a device-side status (bounded wait expired)";
+        case KDA_ERR_CU_SEQLENS: return "cu_seqlens is inconsistent: not starting at 0, not ending at the token count, decreasing, or describing more chunks than the workspace holds";
         default: return "unknown error";
     }
 }
@@ -91,6 +95,7 @@ extern "C" int kda_chunk_bwd(const KdaChunkShape* shape, const void* q, const vo
                              void* dq, void* dk, void* dv, void* dg, void* dbeta, float* dh0, void* stream) {
     int rc = check_shape(shape, cu_seqlens);
     if (rc) return rc;
+    if (shape->forward_only) return KDA_ERR_UNSUPPORTED;      // that forward kept nothing for a backward
     if (shape->tokens > 0 && (!q || !k || !v || !g || !beta || !d_o || !dq || !dk || !dv || !dg || !dbeta))
         return KDA_ERR_NULL;
     if (!workspace || (reinterpret_cast<uintptr_t>(workspace) % 256) != 0 ||
@@ -141,6 +146,13 @@ extern "C" int kda_chunk_status(const KdaChunkShape* shape, const void* workspac
     if (!shape || !workspace) return KDA_ERR_NULL;
     return chunk_status(shape, workspace, (cudaStream_t)stream);
 }
+
+extern "C" int kda_chunk_status_async(const KdaChunkShape* shape, const void* workspace, int32_t* host_word, void* stream) {
+    if (!shape || !workspace || !host_word) return KDA_ERR_NULL;
+    return chunk_status_async(shape, workspace, host_word, (cudaStream_t)stream);
+}
+
+extern "C" int kda_status_word_code(int32_t word) { return status_word_to_code(word); }
 
 extern "C" unsigned long long kda_launch_count(void) {
     std::lock_guard<std::mutex> lk(kda::prof::mu);

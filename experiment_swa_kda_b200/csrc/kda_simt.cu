@@ -105,26 +105,42 @@ __device__ __forceinline__ void st_acc_g(float* dst, size_t ld, const float (&ac
 // ---------------------------------------------------------------------------------------------
 // chunk table: which tokens each 64-token chunk slot covers
 // ---------------------------------------------------------------------------------------------
-__global__ void chunk_table_kernel(Ws w, const int32_t* __restrict__ cu, int n_seq, int seq_len, int* status) {
+// A packed batch is described by cu_seqlens, which the caller controls: every segment is checked against the token
+// count and the slot budget before it enters the tables, so that no later kernel can be steered outside the tensors.
+// A segment that starts before the previous one ends, has a negative length or reaches past `tokens` is treated as
+// empty; chunks beyond the slot budget are dropped; either raises the status word (kStatusBadCuSeqlens), as does a
+// table that does not start at 0 or does not end at `tokens`.
+constexpr int kStatusBadCuSeqlens = 10;
+
+__global__ void chunk_table_kernel(Ws w, const int32_t* __restrict__ cu, int n_seq, int seq_len, int tokens, int* status) {
     __shared__ int total;
     if (threadIdx.x == 0) {
-        if (status) *status = 0;      // the tensor-core lane's device status word starts every forward clean
-        int acc = 0;
+        int flag = 0;
+        int acc = 0, prev_end = 0;
         for (int s = 0; s < n_seq; ++s) {
             w.seq_chunk0[s] = acc;
-            int len = cu ? (cu[s + 1] - cu[s]) : seq_len;
-            if (len < 0) len = 0;
-            acc += (len + kChunk - 1) / kChunk;
+            int len = seq_len;
+            if (cu) {
+                const int t0 = cu[s], t1 = cu[s + 1];
+                len = t1 - t0;
+                if (t0 < prev_end || len < 0 || t1 > tokens) { len = 0; flag = 1; }
+                else prev_end = t1;
+            }
+            int nc = (len + kChunk - 1) / kChunk;
+            if (acc + nc > w.nslots) { nc = w.nslots - acc; flag = 1; }
+            acc += nc;
         }
+        if (cu && (cu[0] != 0 || prev_end != tokens)) flag = 1;
         w.seq_chunk0[n_seq] = acc;
         total = acc;
+        *status = flag ? kStatusBadCuSeqlens : 0;      // every forward starts with a clean status word
     }
     __syncthreads();
     for (int s = threadIdx.x; s < n_seq; s += blockDim.x) {
-        int t0 = cu ? cu[s] : s * seq_len;
-        int len = cu ? (cu[s + 1] - cu[s]) : seq_len;
-        int c0 = w.seq_chunk0[s];
-        for (int j = 0; j * kChunk < len; ++j) {
+        const int c0 = w.seq_chunk0[s], nc = w.seq_chunk0[s + 1] - c0;
+        const int t0 = cu ? cu[s] : s * seq_len;
+        const int len = cu ? (cu[s + 1] - cu[s]) : seq_len;
+        for (int j = 0; j < nc; ++j) {
             w.chunk_seq[c0 + j] = s;
             w.chunk_tok0[c0 + j] = t0 + j * kChunk;
             w.chunk_len[c0 + j] = min(kChunk, len - j * kChunk);
@@ -931,7 +947,8 @@ int simt_chunk_fwd(const KdaChunkShape* sh, const void* q, const void* k, const 
         size_t ws_bytes = 0;
         simt::carve_ws(*sh, nullptr, &ws_bytes);
         tc::TcWs t = tc::carve_tc(*sh, static_cast<char*>(workspace) + ws_bytes);
-        KDA_LAUNCH("chunk_table_kernel", st, simt::chunk_table_kernel<<<1, 256, 0, st>>>(w, cu, sh->n_seq, sh->seq_len, t.status));
+        t.status = w.status;      // one status word per workspace, shared by both lanes
+        KDA_LAUNCH("chunk_table_kernel", st, simt::chunk_table_kernel<<<1, 256, 0, st>>>(w, cu, sh->n_seq, sh->seq_len, sh->tokens, w.status));
         if (w.nslots > 0) {
             int rc = tc_intra_forward(w, t, q, k, v, g, beta, gbf16, sh->l2norm, sh->scale, sh->tokens, st);
             if (rc) return rc;
@@ -940,7 +957,7 @@ int simt_chunk_fwd(const KdaChunkShape* sh, const void* q, const void* k, const 
         }
         return launch_status();
     }
-    KDA_LAUNCH("chunk_table_kernel", st, simt::chunk_table_kernel<<<1, 256, 0, st>>>(w, cu, sh->n_seq, sh->seq_len, nullptr));
+    KDA_LAUNCH("chunk_table_kernel", st, simt::chunk_table_kernel<<<1, 256, 0, st>>>(w, cu, sh->n_seq, sh->seq_len, sh->tokens, w.status));
     if (w.nslots > 0) {
         dim3 gch(w.nslots, w.H);
         KDA_LAUNCH("prep_kernel", st, simt::prep_kernel<<<gch, 256, 0, st>>>(w, q, k, g, beta, bf16, gbf16, sh->l2norm, sh->scale));
@@ -962,19 +979,29 @@ int simt_chunk_fwd(const KdaChunkShape* sh, const void* q, const void* k, const 
     return launch_status();
 }
 
-// Device status word of a forward / backward pair that used `workspace`: 0 unless a bounded wait of the tensor-core
-// lane expired.  Reads it back over the stream, i.e. synchronises the stream - for tests and post-mortems, not for the
-// hot path (and not under stream capture).
-int chunk_status(const KdaChunkShape* sh, const void* workspace, cudaStream_t st) {
-    if (sh->lane != KDA_LANE_TC) return KDA_OK;
-    size_t ws_bytes = 0;
-    simt::carve_ws(*sh, nullptr, &ws_bytes);
-    tc::TcWs t = tc::carve_tc(*sh, static_cast<char*>(const_cast<void*>(workspace)) + ws_bytes);
-    int v = 0;
-    if (cudaMemcpyAsync(&v, t.status, sizeof(int), cudaMemcpyDeviceToHost, st) != cudaSuccess) return KDA_ERR_CUDA;
-    if (cudaStreamSynchronize(st) != cudaSuccess) return KDA_ERR_CUDA;
-    return v ? KDA_ERR_DEVICE_STATUS : KDA_OK;
+// Device status word of a forward / backward pair that used `workspace`: 0, kStatusBadCuSeqlens, or the code of the
+// bounded wait that expired in the tensor-core lane.
+static int status_code(int v) {
+    return v == 0 ? KDA_OK : (v == simt::kStatusBadCuSeqlens ? KDA_ERR_CU_SEQLENS : KDA_ERR_DEVICE_STATUS);
 }
+
+// Reads the word back over the stream, i.e. synchronises the stream - for tests and post-mortems, not for the hot
+// path (and not under stream capture).
+int chunk_status(const KdaChunkShape* sh, const void* workspace, cudaStream_t st) {
+    Ws w = simt::carve_ws(*sh, const_cast<void*>(workspace));
+    int v = 0;
+    if (cudaMemcpyAsync(&v, w.status, sizeof(int), cudaMemcpyDeviceToHost, st) != cudaSuccess) return KDA_ERR_CUDA;
+    if (cudaStreamSynchronize(st) != cudaSuccess) return KDA_ERR_CUDA;
+    return status_code(v);
+}
+
+// Queues a copy of the word into caller-owned page-locked host memory; nothing waits.
+int chunk_status_async(const KdaChunkShape* sh, const void* workspace, int32_t* host_word, cudaStream_t st) {
+    Ws w = simt::carve_ws(*sh, const_cast<void*>(workspace));
+    return cudaMemcpyAsync(host_word, w.status, sizeof(int), cudaMemcpyDeviceToHost, st) == cudaSuccess ? KDA_OK : KDA_ERR_CUDA;
+}
+
+int status_word_to_code(int v) { return status_code(v); }
 
 int simt_chunk_bwd(const KdaChunkShape* sh, const void* q, const void* k, const void* v, const void* g, const void* beta,
                    const int32_t* cu, const void* d_o, const float* d_final, const void* workspace, void* scratch,
@@ -988,6 +1015,7 @@ int simt_chunk_bwd(const KdaChunkShape* sh, const void* q, const void* k, const 
         size_t ws_bytes = 0;
         simt::carve_ws(*sh, nullptr, &ws_bytes);
         tc::TcWs t = tc::carve_tc(*sh, static_cast<char*>(const_cast<void*>(workspace)) + ws_bytes);
+        t.status = w.status;
         if (w.nslots > 0) {
             int rc = tc_scan_backward(w, s, t, sh->n_seq, sh->tokens, d_o, d_final, dh0, st);
             if (rc) return rc;

@@ -55,5 +55,33 @@ int make_map_bf16(CUtensorMap* m, const void* ptr, uint64_t rows, uint64_t cols,
     return r == CUDA_SUCCESS ? KDA_OK : KDA_ERR_CUDA;
 }
 
+// ---------------------------------------------------------------------------------------------
+// self-test of the bounded wait every tensor-core-lane kernel relies on: one warp waits, with a short limit, on a
+// barrier that nothing ever arrives at.  The wait must give up, record its code in the status word and let the kernel
+// return normally (no trap, no unbounded spin), which is how a lost TMA completion or UMMA commit would surface.
+// ---------------------------------------------------------------------------------------------
+constexpr int kSelftestWaitCode = 99;
+
+__global__ void bounded_wait_selftest_kernel(int* status, uint32_t limit, int* returned) {
+    __shared__ uint64_t bar;
+    if (threadIdx.x == 0) {
+        mbar_init(&bar, 1);
+        mbar_fence_init();
+    }
+    __syncthreads();
+    const bool ok = mbar_wait(&bar, 0, status, kSelftestWaitCode, limit);
+    if (threadIdx.x == 0) *returned = ok ? 1 : 2;      // 2: the wait ran out and the thread carried on
+}
+
 }  // namespace tc
 }  // namespace kda
+
+extern "C" int kda_selftest_bounded_wait(int32_t* device_words, uint32_t poll_limit, void* stream) {
+    if (!device_words) return KDA_ERR_NULL;
+    if (poll_limit == 0 || poll_limit > 1000000u) return KDA_ERR_BAD_SHAPE;      // keep the self-test short
+    cudaStream_t st = (cudaStream_t)stream;
+    if (cudaMemsetAsync(device_words, 0, 2 * sizeof(int32_t), st) != cudaSuccess) return KDA_ERR_CUDA;
+    KDA_LAUNCH("bounded_wait_selftest_kernel", st,
+               kda::tc::bounded_wait_selftest_kernel<<<1, 32, 0, st>>>(device_words, poll_limit, device_words + 1));
+    return kda::launch_status();
+}

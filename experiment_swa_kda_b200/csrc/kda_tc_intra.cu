@@ -389,7 +389,7 @@ __global__ void __launch_bounds__(kNT, 1)
                     const int tt = 16 * Ib + c;
                     const float mt = (s < tt) ? t[c] : 0.f;
                     Ms[tt * kLDs + s] = bet[tt] * mt;
-                    p.t.Mt[ch * 4096 + tt * 64 + s] = __float2bfloat16(mt);
+                    if (!p.t.fwd_only) p.t.Mt[ch * 4096 + tt * 64 + s] = __float2bfloat16(mt);
                 }
             }
         }
@@ -404,7 +404,7 @@ __global__ void __launch_bounds__(kNT, 1)
             const float* bb = bet + 8 * c16;
             uint4 u = make_uint4(pack2(src[0], src[1]), pack2(src[2], src[3]), pack2(src[4], src[5]), pack2(src[6], src[7]));
             *reinterpret_cast<uint4*>(Tb + sw128_off(i, c16)) = u;
-            *reinterpret_cast<uint4*>(p.t.Tp + ch * 4096 + i * 64 + 8 * c16) = u;
+            if (!p.t.fwd_only) *reinterpret_cast<uint4*>(p.t.Tp + ch * 4096 + i * 64 + 8 * c16) = u;
             *reinterpret_cast<uint4*>(Tbb + sw128_off(i, c16)) =
                 make_uint4(pack2(src[0] * bb[0], src[1] * bb[1]), pack2(src[2] * bb[2], src[3] * bb[3]),
                            pack2(src[4] * bb[4], src[5] * bb[5]), pack2(src[6] * bb[6], src[7] * bb[7]));

@@ -84,10 +84,12 @@ __global__ void __launch_bounds__(256, 2)
             for (int k16 = 0; k16 < 4; ++k16)     // Pn = W^T E
                 umma_bf16_ss(tmem, umma_smem_desc_sw128(a0 + k16 * 32, 16, 1024),
                              umma_smem_desc_sw128(bE + k16 * 2048, 8192, 1024), id128, k16 > 0);
+            if (p.RmT != nullptr) {
 #pragma unroll
-            for (int k16 = 0; k16 < 4; ++k16)     // (A W)^T = W^T A^T
-                umma_bf16_ss(tmem + 128, umma_smem_desc_sw128(a0 + k16 * 32, 16, 1024),
-                             umma_smem_desc_sw128(bA + k16 * 2048, 8192, 1024), id64, k16 > 0);
+                for (int k16 = 0; k16 < 4; ++k16)     // (A W)^T = W^T A^T
+                    umma_bf16_ss(tmem + 128, umma_smem_desc_sw128(a0 + k16 * 32, 16, 1024),
+                                 umma_smem_desc_sw128(bA + k16 * 2048, 8192, 1024), id64, k16 > 0);
+            }
             umma_commit(&bar_mma);
         }
     }
@@ -108,18 +110,20 @@ __global__ void __launch_bounds__(256, 2)
                                            pack_bf16(__uint_as_float(r[8 * c + 4]), __uint_as_float(r[8 * c + 5])),
                                            pack_bf16(__uint_as_float(r[8 * c + 6]), __uint_as_float(r[8 * c + 7])));
         }
-        uint32_t r[32];
-        tmem_ld32(tmem + lane_base + 128 + 32 * g, r);
-        tmem_ld_wait();
-        uint4* dr = reinterpret_cast<uint4*>(p.RmT + (size_t)ch * 8192 + (size_t)k * 64 + 32 * g);
+        if (p.RmT != nullptr) {      // null in a forward-only call: the adjoint scan's operand is not needed
+            uint32_t r[32];
+            tmem_ld32(tmem + lane_base + 128 + 32 * g, r);
+            tmem_ld_wait();
+            uint4* dr = reinterpret_cast<uint4*>(p.RmT + (size_t)ch * 8192 + (size_t)k * 64 + 32 * g);
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-            float f[8];
-            unpack_bf16x8(rt[c], f);
-            dr[c] = make_uint4(pack_bf16(f[0] - __uint_as_float(r[8 * c]), f[1] - __uint_as_float(r[8 * c + 1])),
-                               pack_bf16(f[2] - __uint_as_float(r[8 * c + 2]), f[3] - __uint_as_float(r[8 * c + 3])),
-                               pack_bf16(f[4] - __uint_as_float(r[8 * c + 4]), f[5] - __uint_as_float(r[8 * c + 5])),
-                               pack_bf16(f[6] - __uint_as_float(r[8 * c + 6]), f[7] - __uint_as_float(r[8 * c + 7])));
+            for (int c = 0; c < 4; ++c) {
+                float f[8];
+                unpack_bf16x8(rt[c], f);
+                dr[c] = make_uint4(pack_bf16(f[0] - __uint_as_float(r[8 * c]), f[1] - __uint_as_float(r[8 * c + 1])),
+                                   pack_bf16(f[2] - __uint_as_float(r[8 * c + 2]), f[3] - __uint_as_float(r[8 * c + 3])),
+                                   pack_bf16(f[4] - __uint_as_float(r[8 * c + 4]), f[5] - __uint_as_float(r[8 * c + 5])),
+                                   pack_bf16(f[6] - __uint_as_float(r[8 * c + 6]), f[7] - __uint_as_float(r[8 * c + 7])));
+            }
         }
     }
     tc_fence_before();
@@ -157,12 +161,6 @@ constexpr int kScanGroups = 2;                              // state warpgroups:
 constexpr int kScanCols = 128 / kScanGroups;
 constexpr uint32_t kScanPanelCol = 256;                     // TMEM column of the bf16 state panel (64 columns: 128 keys as pairs)
 constexpr int kAffineScanThreads = (4 * kScanGroups + 2) * 32;
-
-#ifdef KDA_PHASE_TIMING
-#define KDA_TICKP(n) do { if (tid == 0) { long long t_ = clock64(); acc[n] += t_ - tlast; tlast = t_; } } while (0)
-#else
-#define KDA_TICKP(n) do { } while (0)
-#endif
 
 template <bool kBwd>
 __global__ void __launch_bounds__(kAffineScanThreads, 1)
@@ -311,7 +309,11 @@ __global__ void __launch_bounds__(kAffineScanThreads, 1)
         // thread - into the shared-memory panel that the TMA store sends to the chunk-parallel kernels.
         static_assert(kScanCols == 64, "the tensor-memory panel is written with one 32-column store per thread");
         const int kh = col0 / 64;
-        auto pack_state = [&](int c) {
+        // The stage of step c is observed HERE, before the arrival that lets the UMMA thread run step c: the commit of
+        // step c frees the stage for the loads of step c + 2, so a state warp that looked at the stage barrier only
+        // after that commit could find it two phases on and read the parity as "not yet complete".
+        auto pack_state = [&](int c) -> bool {
+            if (!mbar_wait(&bar_full[c & 1], (c >> 1) & 1, p.status, 54)) return false;
             uint32_t w[32];
 #pragma unroll
             for (int j = 0; j < 32; ++j) w[j] = pack_bf16(s[2 * j], s[2 * j + 1]);
@@ -325,20 +327,16 @@ __global__ void __launch_bounds__(kAffineScanThreads, 1)
                 *reinterpret_cast<uint4*>(dst + sw128_off(v, q)) = make_uint4(w[4 * q], w[4 * q + 1], w[4 * q + 2], w[4 * q + 3]);
             fence_async_smem();
             warp_arrive(&bar_pan, lane);
+            return true;
         };
-#ifdef KDA_PHASE_TIMING
-        long long acc[4] = {0, 0, 0, 0}, tlast = clock64();
-#endif
         bool ok = true;
-        if (n > 0) pack_state(0);
-        for (int c = 0; c < n; ++c) {
-            KDA_TICKP(0);
-            if (!mbar_wait(&bar_mma, c & 1, p.status, 53) || !mbar_wait(&bar_full[c & 1], (c >> 1) & 1, p.status, 54)) {
+        if (n > 0 && !pack_state(0)) { abort_flag = 1; ok = false; }
+        for (int c = 0; c < n && ok; ++c) {
+            if (!mbar_wait(&bar_mma, c & 1, p.status, 53)) {
                 abort_flag = 1; ok = false;
                 break;
             }
             tc_fence_after();
-            KDA_TICKP(1);
             const float* dc = dec_ring[c & 3] + col0;
             {
                 uint32_t r[kScanCols / 32][32];    // every part in flight before the wait
@@ -357,15 +355,8 @@ __global__ void __launch_bounds__(kAffineScanThreads, 1)
                     }
             }
             tc_fence_before();
-            KDA_TICKP(2);
-            if (c + 1 < n) pack_state(c + 1);
-            KDA_TICKP(3);
+            if (c + 1 < n && !pack_state(c + 1)) { abort_flag = 1; ok = false; }
         }
-#ifdef KDA_PHASE_TIMING
-        if (tid == 0 && blockIdx.x == 0 && blockIdx.y == 0 && n > 0)
-            printf("affine scan %s per step: loop %lld | wait %lld | update %lld | pack %lld\n", kBwd ? "bwd" : "fwd", acc[0] / n,
-                   acc[1] / n, acc[2] / n, acc[3] / n);
-#endif
         if (ok && abort_flag == 0 && p.s_out) {
             float4* dst = reinterpret_cast<float4*>(p.s_out + (((size_t)seq * H + h) * 128 + v) * 128 + col0);
 #pragma unroll
@@ -470,7 +461,7 @@ __global__ void __launch_bounds__(256, 2)
             z.z = pack_bf16(u[4] - __uint_as_float(r[8 * q4 + 4]), u[5] - __uint_as_float(r[8 * q4 + 5]));
             z.w = pack_bf16(u[6] - __uint_as_float(r[8 * q4 + 6]), u[7] - __uint_as_float(r[8 * q4 + 7]));
             *reinterpret_cast<uint4*>(Zop + sw128_off(v, c16)) = z;
-            if (ok) zdst[q4] = z;
+            if (ok && p.ZT != nullptr) zdst[q4] = z;      // kept for the backward only
         }
     }
     fence_async_smem();
@@ -623,7 +614,7 @@ int tc_scan_forward(const simt::Ws& w, const tc::TcWs& t, int n_seq, const float
         cudaFuncSetAttribute(tc_chunk_out_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kChunkOutSmem) != cudaSuccess)
         return KDA_ERR_CUDA;
     TransArgs ta;
-    ta.chunk_len = w.chunk_len; ta.RT = t.RT; ta.Pn = t.Pn; ta.RmT = t.RmT; ta.H = w.H; ta.status = t.status;
+    ta.chunk_len = w.chunk_len; ta.RT = t.RT; ta.Pn = t.Pn; ta.RmT = t.fwd_only ? nullptr : t.RmT; ta.H = w.H; ta.status = t.status;
     KDA_LAUNCH("tc_transition_kernel", st,
                tc_transition_kernel<<<dim3(w.nslots, w.H), 256, kTransSmem, st>>>(mW, mE, mAT, ta));
     if (int e = launch_status()) return e;
@@ -634,7 +625,7 @@ int tc_scan_forward(const simt::Ws& w, const tc::TcWs& t, int n_seq, const float
                tc_affine_scan_kernel<false><<<dim3(n_seq, w.H), kAffineScanThreads, kAffineScanSmem, st>>>(mP, mUT, mE, mH, a));
     if (int e = launch_status()) return e;
     ChunkOutArgs oa;
-    oa.chunk_tok0 = w.chunk_tok0; oa.chunk_len = w.chunk_len; oa.ZT = t.ZT; oa.o = static_cast<__nv_bfloat16*>(o); oa.H = w.H;
+    oa.chunk_tok0 = w.chunk_tok0; oa.chunk_len = w.chunk_len; oa.ZT = t.fwd_only ? nullptr : t.ZT; oa.o = static_cast<__nv_bfloat16*>(o); oa.H = w.H;
     oa.status = t.status;
     KDA_LAUNCH("tc_chunk_out_kernel", st,
                tc_chunk_out_kernel<<<dim3(w.nslots, w.H), 256, kChunkOutSmem, st>>>(mH, mW, mR, mUT, mAT, oa));

@@ -15,6 +15,7 @@ struct Ws {
     float *A, *T;               // [nch][64][64]
     float* Hc;                  // [nch][Kp][Vp]   state at the start of each chunk
     float *qinv, *kinv, *beta;  // [nch][64]
+    int* status;                // device status word of the forward / backward pair that owns this workspace (0 = ok)
     int nslots, H, K, V, Kp, Vp;
 };
 
@@ -77,6 +78,7 @@ inline Ws carve_ws(const KdaChunkShape& sh, void* mem, size_t* bytes = nullptr) 
     w.qinv = c.take<float>(nch * 64);
     w.kinv = c.take<float>(nch * 64);
     w.beta = c.take<float>(nch * 64);
+    w.status = c.take<int>(64);
     if (bytes) *bytes = align_up(c.off, 256);
     return w;
 }

@@ -22,28 +22,31 @@ struct TcWs {
     __nv_bfloat16* Pn;          // [nch][128][128]  W^T E: [key k][key k'], the state-to-state part of the chunk transition
     __nv_bfloat16* RmT;         // [nch][128][64]   (R - A W)^T: [key][token]
     float* decay_end;           // [nch][128]       exp(G_end)
-    int* status;                // device status word (0 = ok)
+    int* status;                // device status word (0 = ok); points at the workspace's word (simt::Ws::status)
+    int fwd_only;               // 1: the backward-only panels (T, M~, Z^T, dH', dZ^T, Rm^T) have no storage and are not written
 };
 
 inline TcWs carve_tc(const KdaChunkShape& sh, void* mem, size_t* bytes = nullptr) {
     TcWs t;
     const size_t nch = (size_t)simt::slots_for(sh, false) * sh.heads;
+    const size_t bw = sh.forward_only ? 0 : 1;      // panels only the backward reads
     simt::Carver c(mem);
     t.WT = c.take<__nv_bfloat16>(nch * 8192);
     t.RT = c.take<__nv_bfloat16>(nch * 8192);
     t.E = c.take<__nv_bfloat16>(nch * 8192);
     t.AT = c.take<__nv_bfloat16>(nch * 4096);
     t.UT = c.take<__nv_bfloat16>(nch * 8192);
-    t.Tp = c.take<__nv_bfloat16>(nch * 4096);
-    t.Mt = c.take<__nv_bfloat16>(nch * 4096);
+    t.Tp = c.take<__nv_bfloat16>(bw * nch * 4096);
+    t.Mt = c.take<__nv_bfloat16>(bw * nch * 4096);
     t.Hp = c.take<__nv_bfloat16>(nch * 16384);
-    t.ZT = c.take<__nv_bfloat16>(nch * 8192);
-    t.dHp = c.take<__nv_bfloat16>(nch * 16384);
-    t.dZT = c.take<__nv_bfloat16>(nch * 8192);
+    t.ZT = c.take<__nv_bfloat16>(bw * nch * 8192);
+    t.dHp = c.take<__nv_bfloat16>(bw * nch * 16384);
+    t.dZT = c.take<__nv_bfloat16>(bw * nch * 8192);
     t.Pn = c.take<__nv_bfloat16>(nch * 16384);
-    t.RmT = c.take<__nv_bfloat16>(nch * 8192);
+    t.RmT = c.take<__nv_bfloat16>(bw * nch * 8192);
     t.decay_end = c.take<float>(nch * 128);
     t.status = c.take<int>(64);
+    t.fwd_only = sh.forward_only ? 1 : 0;
     if (bytes) *bytes = align_up(c.off, 256);
     return t;
 }

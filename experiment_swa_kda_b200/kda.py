@@ -154,6 +154,14 @@ def chunk_kda(q: Tensor, k: Tensor, v: Tensor, g: Tensor, beta: Tensor, *, initi
     initial_state / final state are V-first [N,H,V,K] float32 with N = B, or the number of
     packed segments when cu_seqlens (int32 [N+1], B must be 1) is given.
     q,k,v share one dtype (float32 or bfloat16); g, beta share one dtype.
+
+    Range of g: the tensor-core lane (lane="tc", and "auto" for bfloat16 with K = V = 128) forms its decay factors
+    exp(+-(G - c)) in bfloat16 around a reference c per 16-token block, which is in range for g in [-5, 0] per token -
+    the range the reference's gate produces (k3_decay_gate with lower_bound >= -5).  Pass lane="fp32" for log-decays
+    below -5 per token.
+
+    When gradients are disabled, or no input requires one, the call is a prefill: the kernels skip every panel that
+    only a backward would read and no workspace outlives the call.
     """
     n_states = None
     if cu_seqlens is not None:
@@ -171,8 +179,18 @@ def chunk_kda(q: Tensor, k: Tensor, v: Tensor, g: Tensor, beta: Tensor, *, initi
     sc = float(q.shape[-1] ** -0.5 if scale is None else scale)
     lane_id = _select_lane(lane, q, v)
     cu = None if cu_seqlens is None else cu_seqlens.contiguous()
-    o, fs = ops.ChunkKDAFunction.apply(q, k, v, g, beta, initial_state, bool(output_final_state), cu, sc,
-                                       bool(use_qk_l2norm), lane_id)
+    return _chunk_dispatch(q, k, v, g, beta, initial_state, bool(output_final_state), cu, sc, bool(use_qk_l2norm), lane_id)
+
+
+def _chunk_dispatch(q, k, v, g, beta, initial_state, output_final_state, cu, scale, l2norm, lane_id):
+    """Training calls go through the autograd Function (workspace kept for the backward); calls that cannot need a
+    backward take the forward-only kernels' path (the reference sends those to its token loop, chunk.cu:1694-1698)."""
+    tracked = torch.is_grad_enabled() and any(t is not None and t.requires_grad for t in (q, k, v, g, beta, initial_state))
+    if tracked:
+        return ops.ChunkKDAFunction.apply(q, k, v, g, beta, initial_state, output_final_state, cu, scale, l2norm, lane_id)
+    q, k, v, g, beta = (t.detach().contiguous() for t in (q, k, v, g, beta))
+    h0 = None if initial_state is None else initial_state.detach().contiguous()
+    o, fs, _ = ops.chunk_kda_fwd(q, k, v, g, beta, h0, cu, scale, l2norm, output_final_state, lane_id, forward_only=True)
     return o, fs
 
 
@@ -226,9 +244,7 @@ def kda(q: Tensor, k: Tensor, v: Tensor, raw_gate: Tensor, beta_logits: Tensor, 
         o, new_state = ops.decode_step(q, k, v, g, beta, state.contiguous(), sc, True)
         return o, (new_state if output_final_state else None)
     cu = None if cu_seqlens is None else cu_seqlens.contiguous()
-    o, fs = ops.ChunkKDAFunction.apply(q, k, v, g, beta, initial_state, bool(output_final_state), cu, sc, True,
-                                       _select_lane(lane, q, v))
-    return o, fs
+    return _chunk_dispatch(q, k, v, g, beta, initial_state, bool(output_final_state), cu, sc, True, _select_lane(lane, q, v))
 
 
 # ------------------------------------------------------------------------------------------

@@ -54,23 +54,74 @@ def _bytes(n: int, dev) -> Tensor:
 # chunked KDA on activated inputs
 # --------------------------------------------------------------------------------------------
 
-def _shape(q, v, g, n_seq, seq_len, scale, l2norm, lane) -> "_lib.ChunkShape":
+def _shape(q, v, g, n_seq, seq_len, scale, l2norm, lane, forward_only=False) -> "_lib.ChunkShape":
     tokens = q.shape[0] * q.shape[1]
     return _lib.ChunkShape(n_seq, seq_len, tokens, q.shape[2], q.shape[3], v.shape[3], _dt(q), _dt(g), lane,
-                           1 if l2norm else 0, float(scale))
+                           1 if l2norm else 0, float(scale), 1 if forward_only else 0)
 
 
-def chunk_kda_fwd(q, k, v, g, beta, h0, cu_seqlens, scale, l2norm, want_final, lane=_lib.LANE_FP32):
-    """Returns (o, final_state or None, saved) where saved = (shape, workspace) for the backward."""
+# ---- device status word without a hot-path synchronisation ------------------------------------
+# Every chunk forward / backward queues a 4-byte copy of its workspace's status word into a page-locked ring with an
+# event behind it.  The next call on that device reads the words whose events have completed (host memory, no wait) and
+# raises if one is non-zero, so an expired bounded wait or an inconsistent cu_seqlens cannot pass silently.  Nothing is
+# queued or polled while the stream is being captured into a CUDA graph.
+_STATUS_SLOTS = 64
+_status = {}      # device index -> [pinned int32 words, deque of (event, slot), next slot]
+
+
+def _capturing() -> bool:
+    return torch.cuda.is_current_stream_capturing()
+
+
+def poll_status(dev) -> None:
+    ring = _status.get(dev.index)
+    if ring is None or _capturing():
+        return
+    words, pending, _ = ring
+    bad = 0
+    while pending and pending[0][0].query():
+        _, slot = pending.popleft()
+        w = int(words[slot])
+        words[slot] = 0
+        bad = bad or w
+    if bad:
+        code = _lib.load().kda_status_word_code(bad)
+        msg = _lib.load().kda_error_string(code).decode()
+        raise RuntimeError(f"an earlier KDA call on {dev} reported device status {bad}: {msg} ({code}); its results are undefined")
+
+
+def _queue_status(sh, ws, dev) -> None:
+    if _capturing():
+        return
+    ring = _status.get(dev.index)
+    if ring is None:
+        import collections
+        ring = _status[dev.index] = [torch.zeros(_STATUS_SLOTS, dtype=torch.int32).pin_memory(), collections.deque(), 0]
+    words, pending, nxt = ring
+    if len(pending) >= _STATUS_SLOTS:      # the host is far ahead of the device: skip this sample
+        return
+    slot = nxt % _STATUS_SLOTS
+    ring[2] = nxt + 1
+    rc = _lib.load().kda_chunk_status_async(sh, _ptr(ws), words.data_ptr() + 4 * slot, _stream(dev))
+    if rc == _lib.OK:
+        ev = torch.cuda.Event()
+        ev.record(torch.cuda.current_stream(dev))
+        pending.append((ev, slot))
+
+
+def chunk_kda_fwd(q, k, v, g, beta, h0, cu_seqlens, scale, l2norm, want_final, lane=_lib.LANE_FP32, forward_only=False):
+    """Returns (o, final_state or None, saved) where saved = (shape, workspace) for the backward.
+    forward_only: inference / prefill - the panels only a backward reads are neither stored nor allocated."""
     lib = _lib.load()
     dev = _need_cuda(q, k, v, g, beta, h0, cu_seqlens)
+    poll_status(dev)
     B, T, H, K = q.shape
     V = v.shape[-1]
     if cu_seqlens is not None:
         n_seq, seq_len = cu_seqlens.numel() - 1, 0
     else:
         n_seq, seq_len = B, T
-    sh = _shape(q, v, g, n_seq, seq_len, scale, l2norm, lane)
+    sh = _shape(q, v, g, n_seq, seq_len, scale, l2norm, lane, forward_only)
     o = torch.empty(B, T, H, V, dtype=v.dtype, device=dev)
     fs = torch.empty(n_seq, H, V, K, dtype=torch.float32, device=dev) if want_final else None
     nbytes = lib.kda_chunk_workspace_bytes(sh)
@@ -78,7 +129,8 @@ def chunk_kda_fwd(q, k, v, g, beta, h0, cu_seqlens, scale, l2norm, want_final, l
     with torch.cuda.device(dev):
         rc = lib.kda_chunk_fwd(sh, _ptr(q), _ptr(k), _ptr(v), _ptr(g), _ptr(beta), _ptr(h0), _ptr(cu_seqlens), _ptr(o),
                                _ptr(fs), _ptr(ws), ws.numel(), _stream(dev))
-    _lib.check(rc, "kda_chunk_fwd")
+        _lib.check(rc, "kda_chunk_fwd")
+        _queue_status(sh, ws, dev)
     return o, fs, (sh, ws)
 
 
@@ -86,6 +138,7 @@ def chunk_kda_bwd(q, k, v, g, beta, cu_seqlens, do, dfs, saved, want_dh0):
     lib = _lib.load()
     sh, ws = saved
     dev = q.device
+    poll_status(dev)
     dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
     dg, db = torch.empty_like(g), torch.empty_like(beta)
     n_seq = sh.n_seq
@@ -95,7 +148,8 @@ def chunk_kda_bwd(q, k, v, g, beta, cu_seqlens, do, dfs, saved, want_dh0):
         rc = lib.kda_chunk_bwd(sh, _ptr(q), _ptr(k), _ptr(v), _ptr(g), _ptr(beta), _ptr(cu_seqlens), _ptr(do), _ptr(dfs),
                                _ptr(ws), ws.numel(), _ptr(scr), scr.numel(), _ptr(dq), _ptr(dk), _ptr(dv), _ptr(dg),
                                _ptr(db), _ptr(dh0), _stream(dev))
-    _lib.check(rc, "kda_chunk_bwd")
+        _lib.check(rc, "kda_chunk_bwd")
+        _queue_status(sh, ws, dev)
     return dq, dk, dv, dg, db, dh0
 
 
@@ -119,22 +173,23 @@ class ChunkKDAFunction(torch.autograd.Function):
     def forward(ctx, q, k, v, g, beta, initial_state, output_final_state, cu_seqlens, scale, l2norm, lane):
         q, k, v, g, beta = (t.contiguous() for t in (q, k, v, g, beta))
         h0 = None if initial_state is None else initial_state.contiguous()
-        o, fs, saved = chunk_kda_fwd(q, k, v, g, beta, h0, cu_seqlens, scale, l2norm, output_final_state, lane)
-        ctx.saved = saved
+        o, fs, (sh, ws) = chunk_kda_fwd(q, k, v, g, beta, h0, cu_seqlens, scale, l2norm, output_final_state, lane)
+        ctx.shape = sh
         ctx.cu = cu_seqlens
         ctx.has_h0 = initial_state is not None
-        ctx.save_for_backward(q, k, v, g, beta)
+        # The workspace rides with the saved tensors: it lives exactly as long as the graph does, and a second backward
+        # through a retained graph finds it intact (the backward kernels only read it).
+        ctx.save_for_backward(q, k, v, g, beta, ws)
         ctx.set_materialize_grads(False)
         return o, fs
 
     @staticmethod
     def backward(ctx, do, dfs):
-        q, k, v, g, beta = ctx.saved_tensors
+        q, k, v, g, beta, ws = ctx.saved_tensors
         do = torch.zeros_like(v) if do is None else do.contiguous()
         if dfs is not None:
             dfs = dfs.contiguous().float()
-        dq, dk, dv, dg, db, dh0 = chunk_kda_bwd(q, k, v, g, beta, ctx.cu, do, dfs, ctx.saved, ctx.has_h0)
-        ctx.saved = None
+        dq, dk, dv, dg, db, dh0 = chunk_kda_bwd(q, k, v, g, beta, ctx.cu, do, dfs, (ctx.shape, ws), ctx.has_h0)
         return dq, dk, dv, dg, db, dh0, None, None, None, None, None
 
 

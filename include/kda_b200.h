@@ -32,6 +32,7 @@ extern "C" {
 #define KDA_ERR_CUDA (-4)          /* a CUDA launch or runtime call reported an error */
 #define KDA_ERR_NULL (-5)          /* a required pointer is null */
 #define KDA_ERR_DEVICE_STATUS (-6) /* a kernel raised its device-side status word (bounded wait expired) */
+#define KDA_ERR_CU_SEQLENS (-7)    /* cu_seqlens (read on the device) is inconsistent with tokens / the workspace */
 
 #define KDA_DTYPE_F32 0
 #define KDA_DTYPE_BF16 1
@@ -57,6 +58,9 @@ typedef struct KdaChunkShape {
     int32_t lane;       /* KDA_LANE_* */
     int32_t l2norm;     /* 1: L2-normalise q and k inside the kernels (reference behaviour) */
     float scale;        /* multiplies the normalised q */
+    int32_t forward_only; /* 1: inference / prefill - no backward will follow: the forward skips every panel only the
+                             backward reads, kda_chunk_workspace_bytes shrinks accordingly, and the workspace is free
+                             again as soon as the call's kernels have run; kda_chunk_bwd rejects such a shape */
 } KdaChunkShape;
 
 const char* kda_error_string(int code);
@@ -72,6 +76,8 @@ const char* kda_build_arch(void);
  * workspace: kda_chunk_workspace_bytes(shape) bytes, 256-byte aligned.  The
  * forward leaves in it everything the backward needs; keep it untouched until
  * kda_chunk_bwd has run.  h0 and final_state may be NULL.
+ * With shape->forward_only set this is the no-grad prefill path (the reference
+ * sends such calls to its token loop, chunk.cu:1694-1698).
  */
 size_t kda_chunk_workspace_bytes(const KdaChunkShape* shape);
 int kda_chunk_fwd(const KdaChunkShape* shape, const void* q, const void* k, const void* v, const void* g,
@@ -90,17 +96,30 @@ int kda_chunk_bwd(const KdaChunkShape* shape, const void* q, const void* k, cons
                   const void* workspace, size_t workspace_bytes, void* scratch, size_t scratch_bytes, void* dq,
                   void* dk, void* dv, void* dg, void* dbeta, float* dh0, void* stream);
 
+/* ---- device status word ---------------------------------------------------
+ * Every forward starts by checking cu_seqlens on the device and clearing the status word that lives in its workspace;
+ * a tensor-core-lane kernel whose bounded wait expires writes its wait code there (its results are then undefined).
+ * kda_chunk_status copies the word back over `stream` and SYNCHRONISES it - for tests and post-mortems, not for the hot
+ * path and not under stream capture.  It returns KDA_OK, KDA_ERR_CU_SEQLENS (segments that were inconsistent were
+ * treated as empty, so no kernel left the tensors) or KDA_ERR_DEVICE_STATUS.
+ * kda_chunk_status_async only queues the 4-byte copy into caller-owned page-locked host memory (nothing waits, so it
+ * may sit at the end of every call); the caller reads the word once the stream has passed that point and turns it
+ * into a code with kda_status_word_code.  No reference counterpart (the reference's kernels have no device-side waits
+ * and no packed batches). */
+int kda_chunk_status(const KdaChunkShape* shape, const void* workspace, void* stream);
+int kda_chunk_status_async(const KdaChunkShape* shape, const void* workspace, int32_t* host_word, void* stream);
+int kda_status_word_code(int32_t word);
+/* Self-test of the bounded wait: a one-warp kernel waits poll_limit (<= 1,000,000) polls on a barrier nothing arrives
+ * at, then returns.  device_words[0] receives the status word (non-zero after the wait ran out), device_words[1] is 2
+ * when the kernel carried on past the expired wait.  Never traps and never spins without bound.  No reference
+ * counterpart. */
+int kda_selftest_bounded_wait(int32_t* device_words, uint32_t poll_limit, void* stream);
+
 /* ---- gate / beta activations ----------------------------------------------
  * g = lower_bound * sigmoid(exp(A_log[h]) * (raw_gate + dt_bias[h,k])), beta = sigmoid(beta_logits)
  * (reference chunk.cu:98-132, chunk_wy_forward.cu:188-264; oracle tests/kda_oracle.py:31-47).
  * g_out and beta_out are float32 regardless of io_dtype.
  */
-/* Device status word of the forward / backward that used `workspace`: KDA_OK, or KDA_ERR_DEVICE_STATUS when a bounded
- * wait inside a tensor-core-lane kernel expired (its results are then undefined).  Copies one word back over `stream`
- * and SYNCHRONISES it: for tests and post-mortems, not for the hot path, and not under stream capture.  No reference
- * counterpart (the reference's kernels have no device-side waits to bound). */
-int kda_chunk_status(const KdaChunkShape* shape, const void* workspace, void* stream);
-
 int kda_gate_fwd(int32_t tokens, int32_t heads, int32_t key_dim, int32_t io_dtype, const void* raw_gate,
                  const void* beta_logits, const float* A_log, const float* dt_bias, float lower_bound, float* g_out,
                  float* beta_out, void* stream);
@@ -139,11 +158,6 @@ int kda_conv_bwd(int32_t batch, int32_t seq_len, int32_t channels, int32_t width
                  const void* d_final_state, void* dx, float* dweight, void* d_initial_state, void* scratch,
                  size_t scratch_bytes, void* stream);
 
-/* ---- gated RMSNorm --------------------------------------------------------------
- * y = x * rsqrt(mean(x^2) + eps) * weight * sigmoid(gate) over the last dimension.
- * x, gate, y [rows, dim] in io_dtype; weight float32 [dim]; inv_rms float32 [rows].
- * Stands in for nanochat_kda::rmsnorm_gate_forward / _backward (reference rmsnorm_gate.cu:31-273).
- */
 /* n_items (1..4) same-shaped convolutions in ONE launch each way - the q, k and v branches of a layer (the reference
  * issues three separate operator calls, nanochat/mixers/kda.py:758-766; there is no batched counterpart there).
  * Training path only: no carried-in window, no final state, width <= 4, even channel count, 16-byte aligned tensors;
@@ -157,6 +171,11 @@ int kda_conv_bwd_multi(int32_t n_items, int32_t batch, int32_t seq_len, int32_t 
                        int32_t silu, const void* const* x, const void* const* weight, const void* const* d_y,
                        void* const* dx, float* const* dweight, void* scratch, size_t scratch_bytes, void* stream);
 
+/* ---- gated RMSNorm --------------------------------------------------------------
+ * y = x * rsqrt(mean(x^2) + eps) * weight * sigmoid(gate) over the last dimension.
+ * x, gate, y [rows, dim] in io_dtype; weight float32 [dim]; inv_rms float32 [rows].
+ * Stands in for nanochat_kda::rmsnorm_gate_forward / _backward (reference rmsnorm_gate.cu:31-273).
+ */
 int kda_rmsnorm_gate_fwd(int64_t rows, int32_t dim, int32_t io_dtype, float eps, const void* x, const void* gate,
                          const float* weight, void* y, float* inv_rms, void* stream);
 size_t kda_rmsnorm_gate_bwd_scratch_bytes(int64_t rows, int32_t dim);

@@ -88,3 +88,61 @@ def test_nanochat_kda_namespace_registers_the_reference_schemas():
     x = torch.randn(1, 4, 8)
     with pytest.raises((RuntimeError, NotImplementedError)):
         torch.ops.nanochat_kda.causal_convolution_forward(x, torch.randn(8, 4), None, False)
+
+
+def test_registered_schemas_carry_the_reference_return_names_and_the_trailing_cu_seqlens():
+    from experiment_swa_kda_b200 import nanochat_ops
+    s = nanochat_ops.schemas()
+    assert s["chunk_forward"].endswith("float scale, Tensor? cu_seqlens=None) -> (Tensor output, Tensor? final_state)")
+    assert "Tensor? cu_seqlens=None) -> (Tensor dq, Tensor dk, Tensor dv, Tensor draw_gate, Tensor dbeta_logits, " \
+           "Tensor dA_log, Tensor ddt_bias, Tensor? dinitial_state)" in s["chunk_backward"]
+    assert s["rmsnorm_gate_forward"].endswith("-> (Tensor output, Tensor inverse_rms)")
+    assert s["causal_convolution_backward"].endswith("-> (Tensor dx, Tensor dweight, Tensor? dinitial_state)")
+
+
+def test_operator_input_checks_run_before_any_launch():
+    """The checks chunk_forward / chunk_backward / recurrent_decode apply before they touch the GPU
+    (the role of the reference's validate_chunk_inputs, nanochat/mixers/cuda_kda/chunk.cu:1622-1663), driven through
+    nanochat_kda::_validate_chunk_inputs, which is the same function and runs on tensors of any device."""
+    from experiment_swa_kda_b200 import nanochat_ops
+    nanochat_ops.register()
+    check = torch.ops.nanochat_kda._validate_chunk_inputs
+    B, T, H, K, V = 1, 5, 2, 8, 6
+    bf = torch.bfloat16
+    q, v, beta = torch.zeros(B, T, H, K, dtype=bf), torch.zeros(B, T, H, V, dtype=bf), torch.zeros(B, T, H, dtype=bf)
+    A, bias = torch.zeros(H), torch.zeros(H, K)
+    cases = {
+        "shapes must match": (q, q[:, :4], v, q, beta, A, bias, None, -5.0),
+        "v must match q": (q, q, v[:, :, :1], q, beta, A, bias, None, -5.0),
+        r"beta_logits must have shape \[B, T, H\]": (q, q, v, q, beta[..., :1], A, bias, None, -5.0),
+        r"A_log must be contiguous CUDA float32 \[H\]": (q, q, v, q, beta, torch.zeros(3), bias, None, -5.0),
+        r"dt_bias must be contiguous CUDA float32 with H\*K elements": (q, q, v, q, beta, A, torch.zeros(H, K + 1), None, -5.0),
+        r"initial_state must have shape \[B, H, V, K\]": (q, q, v, q, beta, A, bias, torch.zeros(B, H, K, V), -5.0),
+        r"lower_bound must be in \[-5, 0\)": (q, q, v, q, beta, A, bias, None, -6.0),
+        "activation tensors must be bfloat16": (q.float(), q.float(), v, q.float(), beta, A, bias, None, -5.0),
+        "A_log and dt_bias must be float32": (q, q, v, q, beta, A.double(), bias, None, -5.0),
+        "head dimensions must be in": (torch.zeros(B, T, H, 300, dtype=bf),) * 2 + (v, torch.zeros(B, T, H, 300, dtype=bf), beta, A,
+                                                                                torch.zeros(H, 300), None, -5.0),
+        # everything consistent, but nothing lives on a GPU: rejected, not handed to a kernel
+        "q must be a CUDA tensor": (q, q, v, q, beta, A, bias, torch.zeros(B, H, V, K), -5.0),
+    }
+    for pattern, args in cases.items():
+        with pytest.raises(RuntimeError, match=pattern):
+            check(*args)
+    with pytest.raises(RuntimeError, match=r"cu_seqlens must be int32 \[N\+1\]"):
+        check(q, q, v, q, beta, A, bias, None, -5.0, torch.zeros(3, dtype=torch.int64))
+    with pytest.raises(RuntimeError, match="require batch size 1"):
+        q2, v2, b2 = (t.repeat(2, *([1] * (t.dim() - 1))) for t in (q, v, beta))
+        check(q2, q2, v2, q2, b2, A, bias, None, -5.0, torch.zeros(3, dtype=torch.int32))
+
+
+def test_forward_only_shapes_need_less_workspace_and_refuse_a_backward():
+    from experiment_swa_kda_b200 import _lib
+    lib = _lib.load()
+    train = _lib.ChunkShape(2, 4096, 8192, 3, 128, 128, 1, 0, 1, 1, 0.0884, 0)
+    infer = _lib.ChunkShape(2, 4096, 8192, 3, 128, 128, 1, 0, 1, 1, 0.0884, 1)
+    assert 0 < lib.kda_chunk_workspace_bytes(infer) < lib.kda_chunk_workspace_bytes(train)
+    assert lib.kda_chunk_bwd(infer, *([None] * 9), 0, None, 0, *([None] * 7)) == -2
+    bad = _lib.ChunkShape(2, 4096, 8192, 3, 128, 128, 1, 0, 1, 1, 0.0884, 7)
+    assert lib.kda_chunk_fwd(bad, *([None] * 10), 0, None) == -1
+    assert lib.kda_status_word_code(0) == 0 and lib.kda_status_word_code(10) == -7 and lib.kda_status_word_code(53) == -6
