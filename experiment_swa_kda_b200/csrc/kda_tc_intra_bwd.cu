@@ -120,6 +120,7 @@ __global__ void __launch_bounds__(512, 1)
     float* rowv = dots + 512;                              // [3][64]  qinv | kinv | beta
     __shared__ uint64_t bar_in, bar_mma;
     __shared__ uint32_t tmem_slot;
+    __shared__ float dA_diag[64];      // dA[i][i]: applied to dq, dk in float32, outside the pull-back products
 
 #ifdef KDA_PHASE_TIMING
     long long tick[20];
@@ -190,6 +191,17 @@ __global__ void __launch_bounds__(512, 1)
     }
     KDA_TICKB(1);
     bool ok = mbar_wait(&bar_in, 0, p.status, 40);
+    if (len < 64 && ok) {
+        // rows past a ragged tail hold the next sequence's tokens: blank them in the dO and v tiles, which feed UMMAs
+        // as they are (0 x Inf would otherwise reach this sequence's gradients)
+        for (int idx = tid; idx < (64 - len) * 16; idx += 512) {
+            const int r = len + (idx >> 4), c = idx & 15;
+            const uint32_t off = (uint32_t)(c >> 3) * 8192 + sw128_off(r, c & 7);
+            *reinterpret_cast<uint4*>(dOs + off) = make_uint4(0, 0, 0, 0);
+            *reinterpret_cast<uint4*>(vs + off) = make_uint4(0, 0, 0, 0);
+        }
+        fence_async_smem();
+    }
     ok = __syncthreads_and(ok);          // also publishes cref
     const float egend = __expf(gend);
     KDA_TICKB(2);
@@ -429,7 +441,11 @@ __global__ void __launch_bounds__(512, 1)
         for (int e = 0; e < 16; ++e) {
             const int l = 16 * I + e;
             const float dm = (l < j) ? -tm[e] : 0.f;
-            const float da = (l <= j) ? ta[e] : 0.f;
+            // The diagonal of dA adds q k dA to dG through the row part and takes the same amount away through the
+            // column part; left inside two bf16 products those O(1) terms cancel only to bf16 accuracy, which swamps dg
+            // when the decay is strong.  It goes to dq and dk directly instead (decay factor 1, no dG term).
+            const float da = (l < j) ? ta[e] : 0.f;
+            if (l == j && rowown) dA_diag[j] = ta[e];
             dbeta_acc += dm * mv16[e];
             if (e & 1) { pa[e >> 1] = pk2(__uint_as_float(pa[e >> 1]), da); pm[e >> 1] = pk2(__uint_as_float(pm[e >> 1]), bj * dm); }
             else { pa[e >> 1] = __float_as_uint(da); pm[e >> 1] = __float_as_uint(bj * dm); }
@@ -510,7 +526,12 @@ __global__ void __launch_bounds__(512, 1)
         // row parts, e2 = e^{c_own - G} for the column parts (a later block I' contributes e^{c_I' - c_own} e2)
         float e1[16];
 #pragma unroll
-        for (int r = 0; r < 16; ++r) e1[r] = __expf(G[r] - cOwn);
+        for (int r = 0; r < 16; ++r) {
+            e1[r] = __expf(G[r] - cOwn);
+            const float dd = dA_diag[16 * I + r];
+            dqn[r] += dd * kn[r];
+            dkn[r] += dd * qn[r];
+        }
         tmem_ld16(tmem + lane_base + cRP + 32 * I, t);          // row part through dA
 #pragma unroll
         for (int r = 0; r < 16; ++r) {

@@ -147,6 +147,7 @@ __global__ void __launch_bounds__(256, 2)
 struct AffineScanArgs {
     const int* seq_chunk0;
     const int* chunk_tok0;
+    const int* chunk_len;
     const float* decay_end;   // [nch][128] exp(G_end)
     const float* s_in;        // V-first initial state (forward: h0, backward: cotangent of the final state), or null
     float* s_out;             // V-first final state of the scan (forward: final state, backward: dh0), or null
@@ -234,6 +235,21 @@ __global__ void __launch_bounds__(kAffineScanThreads, 1)
         }
     } else if (warp == 4 * kScanGroups + 1) {
         // ------------------------------------------------------------------ UMMA / panel-store thread
+        if (kBwd && n > 0) {
+            // Only a sequence's last chunk (the adjoint scan's first step) can be ragged; the dO rows past its tail
+            // belong to the next sequence and are blanked by the whole warp before lane 0 issues the product on them.
+            const int len0 = p.chunk_len[slot_of(0)];
+            if (len0 < 64) {
+                if (mbar_wait(&bar_full[0], 0, p.status, 51)) {
+                    for (int idx = lane; idx < (64 - len0) * 16; idx += 32) {
+                        const int r = len0 + (idx >> 4), c = idx & 15;
+                        *reinterpret_cast<uint4*>(sm + 49152 + (c >> 3) * 8192 + sw128_off(r, c & 7)) = make_uint4(0, 0, 0, 0);
+                    }
+                    fence_async_smem();
+                }
+                __syncwarp();
+            }
+        }
         if (lane == 0 && n > 0) {
             // state-independent product:  forward U^T E (A K-major, B MN-major), backward dO^T Rm (A MN-major, B K-major)
             const uint32_t id_ind = kBwd ? umma_idesc_bf16(128, 128, kMajorMN, kMajorK) : umma_idesc_bf16(128, 128, kMajorK, kMajorMN);
@@ -527,7 +543,8 @@ __global__ void __launch_bounds__(256, 3)
     __shared__ uint64_t bar_in, bar_mma;
     __shared__ uint32_t tmem_slot;
     const int slot = blockIdx.x, h = blockIdx.y, H = p.H;
-    if (p.chunk_len[slot] == 0) return;
+    const int len = p.chunk_len[slot];
+    if (len == 0) return;
     const int tok0 = p.chunk_tok0[slot];
     const int ch = slot * H + h;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -552,7 +569,19 @@ __global__ void __launch_bounds__(256, 3)
     const uint32_t tmem = tmem_slot;
     const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
     bool ok = true;
-    if (tid == 0) {
+    if (len < 64) {
+        // ragged tail: the dO rows past it belong to the next sequence; blank them before they feed the UMMA
+        ok = mbar_wait(&bar_in, 0, p.status, 70);
+        if (ok) {
+            for (int idx = tid; idx < (64 - len) * 16; idx += 256) {
+                const int r = len + (idx >> 4), c = idx & 15;
+                *reinterpret_cast<uint4*>(sm + kDzO + (c >> 3) * 8192 + sw128_off(r, c & 7)) = make_uint4(0, 0, 0, 0);
+            }
+            fence_async_smem();
+        }
+        ok = __syncthreads_and(ok);
+    }
+    if (tid == 0 && ok) {
         ok = mbar_wait(&bar_in, 0, p.status, 70);
         if (ok) {
             tc_fence_after();
@@ -619,7 +648,7 @@ int tc_scan_forward(const simt::Ws& w, const tc::TcWs& t, int n_seq, const float
                tc_transition_kernel<<<dim3(w.nslots, w.H), 256, kTransSmem, st>>>(mW, mE, mAT, ta));
     if (int e = launch_status()) return e;
     AffineScanArgs a;
-    a.seq_chunk0 = w.seq_chunk0; a.chunk_tok0 = w.chunk_tok0; a.decay_end = t.decay_end; a.s_in = h0; a.s_out = final_state;
+    a.seq_chunk0 = w.seq_chunk0; a.chunk_tok0 = w.chunk_tok0; a.chunk_len = w.chunk_len; a.decay_end = t.decay_end; a.s_in = h0; a.s_out = final_state;
     a.H = w.H; a.status = t.status;
     KDA_LAUNCH("tc_affine_scan_fwd_kernel", st,
                tc_affine_scan_kernel<false><<<dim3(n_seq, w.H), kAffineScanThreads, kAffineScanSmem, st>>>(mP, mUT, mE, mH, a));
@@ -650,7 +679,7 @@ int tc_scan_backward(const simt::Ws& w, const simt::Scr& s, const tc::TcWs& t, i
         cudaFuncSetAttribute(tc_chunk_dz_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kChunkDzSmem) != cudaSuccess)
         return KDA_ERR_CUDA;
     AffineScanArgs a;
-    a.seq_chunk0 = w.seq_chunk0; a.chunk_tok0 = w.chunk_tok0; a.decay_end = t.decay_end; a.s_in = d_final; a.s_out = dh0;
+    a.seq_chunk0 = w.seq_chunk0; a.chunk_tok0 = w.chunk_tok0; a.chunk_len = w.chunk_len; a.decay_end = t.decay_end; a.s_in = d_final; a.s_out = dh0;
     a.H = w.H; a.status = t.status;
     KDA_LAUNCH("tc_affine_scan_bwd_kernel", st,
                tc_affine_scan_kernel<true><<<dim3(n_seq, w.H), kAffineScanThreads, kAffineScanSmem, st>>>(mP, mRm, mdO, mdH, a));
