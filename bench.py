@@ -174,6 +174,83 @@ class Chain:
         return sum(h.numel() * h.element_size() for h in self.host_out)
 
 
+class OpsChain:
+    """The same chain driven the way the reference mixer drives it: autograd Functions that save only the operator inputs
+    and the forward output and call `torch.ops.nanochat_kda.*` positionally (reference nanochat/mixers/kda.py:383-466):
+    causal_convolution_forward x3 -> chunk_forward (raw gate and beta logits, activations fused) -> rmsnorm_gate_forward,
+    and the three backwards."""
+
+    def __init__(self, chain):
+        from experiment_swa_kda_b200 import nanochat_ops
+        nanochat_ops.register()
+        ops = torch.ops.nanochat_kda
+        self.c = chain
+        cfg, dev = chain.cfg, chain.dev
+        H, D = cfg["H"], cfg["D"]
+        self.A_log = torch.zeros(H, device=dev, requires_grad=True)
+        self.dt_bias = torch.zeros(H * D, device=dev, requires_grad=True)
+        self.w = [c.weight.detach().squeeze(1).to(torch.bfloat16).requires_grad_(True) for c in chain.convs]
+        self.nw = chain.norm.weight.detach().clone().requires_grad_(True)
+        self.scale = D ** -0.5
+
+        class Conv(torch.autograd.Function):
+            @staticmethod
+            def forward(ctx, x, w):
+                y, _ = ops.causal_convolution_forward(x, w, None, False)
+                ctx.save_for_backward(x, w, y)
+                return y
+
+            @staticmethod
+            def backward(ctx, dy):
+                x, w, y = ctx.saved_tensors
+                dx, dw, _ = ops.causal_convolution_backward(x, w, None, y, None, dy, None)
+                return dx, dw
+
+        class KDA(torch.autograd.Function):
+            @staticmethod
+            def forward(ctx, q, k, v, raw, bl, A, b, scale):
+                o, _ = ops.chunk_forward(q, k, v, raw, bl, A, b, None, False, -5.0, scale)
+                ctx.scale = scale
+                ctx.save_for_backward(q, k, v, raw, bl, A, b, o)
+                return o
+
+            @staticmethod
+            def backward(ctx, do):
+                q, k, v, raw, bl, A, b, o = ctx.saved_tensors
+                g = ops.chunk_backward(q, k, v, raw, bl, A, b, None, o, None, do, None, -5.0, ctx.scale)
+                return (*g[:7], None)
+
+        class Norm(torch.autograd.Function):
+            @staticmethod
+            def forward(ctx, x, gate, w, eps):
+                y, inv = ops.rmsnorm_gate_forward(x, gate, w, eps)
+                ctx.eps = eps
+                ctx.save_for_backward(x, gate, w, inv)
+                return y
+
+            @staticmethod
+            def backward(ctx, dy):
+                x, gate, w, inv = ctx.saved_tensors
+                return (*ops.rmsnorm_gate_backward(x, gate, w, inv, dy, ctx.eps), None)
+
+        self.Conv, self.KDA, self.Norm = Conv, KDA, Norm
+        # raw gate / beta logits that activate to the chain's g and beta (A_log = 0, dt_bias = 0, lower bound -5)
+        with torch.no_grad():
+            p = (chain.x["g"].float() / -5.0).clamp(1e-7, 1 - 1e-7)
+            self.raw = (torch.log(p) - torch.log1p(-p)).to(torch.bfloat16).requires_grad_(True)
+            b = chain.x["beta"].float().clamp(1e-6, 1 - 1e-6)
+            self.bl = (torch.log(b) - torch.log1p(-b)).to(torch.bfloat16).requires_grad_(True)
+
+    def step(self):
+        c, x, cfg = self.c, self.c.x, self.c.cfg
+        sh = (cfg["B"], cfg["T"], cfg["H"], cfg["D"])
+        q, k, v = (self.Conv.apply(x[n], w).view(sh) for n, w in zip(("xq", "xk", "xv"), self.w))
+        o = self.KDA.apply(q, k, v, self.raw, self.bl, self.A_log, self.dt_bias, self.scale)
+        y = self.Norm.apply(o, x["gate"], self.nw, cfg["eps"])
+        leaves = [x["xq"], x["xk"], x["xv"], self.raw, self.bl, x["gate"], *self.w, self.nw, self.A_log, self.dt_bias]
+        return y, torch.autograd.grad(y, leaves, x["probe"])
+
+
 def oracle_chain_step(cfg, T, seed, threads):
     """The CPU oracle on the same chain, T tokens per sequence (cost is linear in T)."""
     sys.path.insert(0, os.path.join(ROOT, "oracle"))
@@ -229,6 +306,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-graph", action="store_true", help="launch every step eagerly instead of replaying a CUDA graph")
+    ap.add_argument("--no-sharded", action="store_true", help="skip the config-3 / config-4 sharded workloads attached to the line")
     ap.add_argument("--tokens", type=int, default=8 * 8192, help="packed tokens of the varlen workload")
     ap.add_argument("--workload", default="chain", choices=["chain", "varlen", "decode", "pointwise"],
                     help="chain = config 1 (default, the driver's line); varlen = config 3; decode = config 4; pointwise = conv / gated RMSNorm at 256 MiB tensors")
@@ -379,9 +457,76 @@ def main():
         barrier()
         return t_begin.elapsed_time(t_end), sum(t.numel() * t.element_size() for t in flat)
 
+    def copy_only(steps):
+        """The end-to-end arm's copies alone (same pinned buffers and sizes, both directions at once, no kernels): the
+        host-path ceiling of the end-to-end figure."""
+        flat = [outs[0]] + list(outs[1]) if outs is not None else list(chain.step()[1])
+        n_in = chain.h2d_bytes()
+        n_out = sum(t.numel() * t.element_size() for t in flat)
+        h_in, h_out = torch.empty(n_in, dtype=torch.uint8).pin_memory(), torch.empty(n_out, dtype=torch.uint8).pin_memory()
+        d_in, d_out = torch.empty(n_in, dtype=torch.uint8, device=dev), torch.empty(n_out, dtype=torch.uint8, device=dev)
+        s_in, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+        barrier()
+        a, b, c = (torch.cuda.Event(enable_timing=True) for _ in range(3))
+        s_in.wait_stream(torch.cuda.current_stream(dev))
+        s_out.wait_stream(torch.cuda.current_stream(dev))
+        a.record(s_in)
+        s_out.wait_event(a)
+        for _ in range(steps):
+            with torch.cuda.stream(s_in):
+                d_in.copy_(h_in, non_blocking=True)
+            with torch.cuda.stream(s_out):
+                h_out.copy_(d_out, non_blocking=True)
+        b.record(s_in)
+        c.record(s_out)
+        s_in.synchronize()
+        s_out.synchronize()
+        barrier()
+        return max(a.elapsed_time(b), a.elapsed_time(c))
+
     e2e_run = e2e_serial if graph is None else e2e_pipelined
     e2e_run(3)
     e2e_ms, d2h = e2e_run(args.steps)
+    copy_only(3)
+    t3 = torch.tensor([copy_only(args.steps)], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t3, op=dist.ReduceOp.MAX)
+    copy_ms_step = float(t3.item()) / args.steps
+
+    # ---- the raw operator surface (torch.ops.nanochat_kda.*), driven like the reference mixer, same timing protocol ----
+    ops_ms_step, ops_launches, ops_error = None, None, None
+    try:
+        oc = OpsChain(chain)
+        for _ in range(3):
+            oc.step()
+        barrier()
+        l1 = _lib.launch_count()
+        if not args.no_graph:
+            og = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(og):
+                oc.step()
+            run_ops = og.replay
+        else:
+            run_ops = oc.step
+        ops_launches = _lib.launch_count() - l1
+        for _ in range(3):
+            run_ops()
+        barrier()
+        ev3 = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+        for a, b in ev3:
+            flush.zero_()
+            a.record()
+            run_ops()
+            b.record()
+        barrier()
+        t4 = torch.tensor([sum(a.elapsed_time(b) for a, b in ev3)], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(t4, op=dist.ReduceOp.MAX)
+        ops_ms_step = float(t4.item()) / args.steps
+        del oc
+    except Exception as exc:      # the operator library is optional for the headline number; say why it is missing
+        ops_ms_step = None
+        ops_error = f"{type(exc).__name__}: {exc}"
     t2 = torch.tensor([e2e_ms], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(t2, op=dist.ReduceOp.MAX)
@@ -399,6 +544,12 @@ def main():
     torch.cuda.synchronize(dev)
     rep = _lib.profile_report()
     _lib.profile(False)
+
+    sharded = None
+    if not args.no_sharded:
+        import bench_extra
+        torch.cuda.empty_cache()
+        sharded = bench_extra.sharded_summary(args, rank, world, local, dist)
 
     if rank == 0:
         peaks = {}
@@ -422,7 +573,7 @@ def main():
             if name in nbytes:
                 row["gbs"] = nbytes[name] / (avg_ms * 1e-3) / 1e9
             kern[name] = row
-        top = max(rep, key=lambda k: rep[k][1]) if rep else None
+        top = max(rep, key=lambda k: rep[k][1]) if rep else None      # per kernel name; the two scans are separate instantiations
         traffic = None
         try:
             traffic = json.load(open(os.path.join(ROOT, "profiles", "ncu_traffic.json"))).get(top)
@@ -448,7 +599,16 @@ def main():
                        "launch": "eager" if args.no_graph else "CUDA graph replay of the captured step", "sharding": "replicated per-GPU batches, no collective"},
             "tflops_algorithmic": flops["_fwd_bwd_total"] * nch * world / (ms_step * 1e-3) / 1e12,
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": chain.h2d_bytes(), "d2h_bytes_per_step": d2h,
-                    "ms_per_step": float(t2.item()) / args.steps, "copies": e2e_mode},
+                    "ms_per_step": float(t2.item()) / args.steps, "copies": e2e_mode,
+                    "copy_only_ms_per_step": copy_ms_step,
+                    "copy_only_note": "the same bytes per step in both directions at once from/to pinned host memory with no "
+                                      "kernel in between: the host-path floor of ms_per_step"},
+            "ops_path": ({"ms_per_step": ops_ms_step, "tokens_per_s": chain.tokens() * world / (ops_ms_step * 1e-3),
+                          "launches_per_step": ops_launches, "ratio_to_value_arm": ops_ms_step / ms_step,
+                          "what": "the same chain through torch.ops.nanochat_kda.* (raw gate / beta logits, activations fused, "
+                                  "forward sidecar instead of a recompute), driven by reference-style autograd Functions"}
+                         if ops_ms_step else {"unavailable": ops_error}),
+            "sharded": sharded,
             "gpu_launches": int(launches), "clocks": clocks, "roofline": roof, "kernels": kern,
         }
         if world == 1 and not args.no_cpu_baseline:

@@ -49,18 +49,18 @@ def run_varlen(args, rank, world, local, dist):
     Hl = H // world                                     # heads of this rank
     lens = _lengths(total, 0)
     cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32, device=dev)
-    gen = torch.Generator().manual_seed(100 + rank)
+    gen = torch.Generator(device=dev).manual_seed(100 + rank)      # seeded, drawn on the device (same distributions)
+    rn = lambda *sh: torch.randn(*sh, generator=gen, device=dev)
     unit = lambda t: t / t.norm(dim=-1, keepdim=True)
     bf = torch.bfloat16
     x = {
-        "q": unit(torch.randn(1, total, Hl, D, generator=gen)).to(bf), "k": unit(torch.randn(1, total, Hl, D, generator=gen)).to(bf),
-        "v": torch.randn(1, total, Hl, D, generator=gen).to(bf),
-        "g": (-torch.nn.functional.softplus(torch.randn(1, total, Hl, D, generator=gen)) * 0.1).clamp(-5, 0).to(bf),
-        "beta": torch.sigmoid(torch.randn(1, total, Hl, generator=gen)).to(bf),
+        "q": unit(rn(1, total, Hl, D)).to(bf), "k": unit(rn(1, total, Hl, D)).to(bf), "v": rn(1, total, Hl, D).to(bf),
+        "g": (-torch.nn.functional.softplus(rn(1, total, Hl, D)) * 0.1).clamp(-5, 0).to(bf),
+        "beta": torch.sigmoid(rn(1, total, Hl)).to(bf),
     }
-    x = {n: t.to(dev).requires_grad_(True) for n, t in x.items()}
-    h0 = (torch.randn(len(lens), Hl, D, D, generator=gen) * 0.02).to(dev).requires_grad_(True)
-    probe = torch.randn(1, total, Hl, D, generator=gen).to(bf).to(dev)
+    x = {n: t.requires_grad_(True) for n, t in x.items()}
+    h0 = (rn(len(lens), Hl, D, D) * 0.02).requires_grad_(True)
+    probe = rn(1, total, Hl, D).to(bf)
 
     def step():
         o, fs = m.chunk_kda(x["q"], x["k"], x["v"], x["g"], x["beta"], initial_state=h0, output_final_state=True, cu_seqlens=cu)
@@ -93,7 +93,7 @@ def run_varlen(args, rank, world, local, dist):
     rep = _lib.profile_report()
     _lib.profile(False)
     if rank != 0:
-        return
+        return None
     peaks, src = _peaks()
     nch = sum((n + 63) // 64 for n in lens) * Hl
     flops = kda_kernel_flops(D, D)
@@ -119,7 +119,7 @@ def run_varlen(args, rank, world, local, dist):
                      "unit": "TFLOP/s", "frac": kern[top].get("frac_of_bf16_peak"), "traffic": None, "peak_source": src},
         "kernels": kern,
     }
-    print(json.dumps(line), flush=True)
+    return line
 
 
 def run_decode(args, rank, world, local, dist):
@@ -131,24 +131,24 @@ def run_decode(args, rank, world, local, dist):
     gen = torch.Generator().manual_seed(7 + rank)
     bf = torch.bfloat16
     unit = lambda t: t / t.norm(dim=-1, keepdim=True)
-    NI = 16           # distinct per-step inputs, cycled (1 MiB each; the 256 MiB state dominates the traffic)
-    q = unit(torch.randn(NI, B, H, D, generator=gen)).to(bf).to(dev)
-    k = unit(torch.randn(NI, B, H, D, generator=gen)).to(bf).to(dev)
-    v = torch.randn(NI, B, H, D, generator=gen).to(bf).to(dev)
-    g = (-torch.nn.functional.softplus(torch.randn(NI, B, H, D, generator=gen)) * 0.1).clamp(-5, 0).to(bf).to(dev)
-    beta = torch.sigmoid(torch.randn(NI, B, H, generator=gen)).to(bf).to(dev)
-    s = [(torch.randn(B, H, D, D, generator=gen) * 0.02).to(dev), torch.empty(B, H, D, D, device=dev)]
-    o = torch.empty(B, H, D, dtype=bf, device=dev)
+    NI = 64           # distinct per-step inputs, cycled (1 MiB each at N=1; the 256 MiB state dominates the traffic)
+    rn = lambda *sh: torch.randn(*sh, generator=gen)
+    q = unit(rn(NI, B, H, D)).to(bf).to(dev)
+    k = unit(rn(NI, B, H, D)).to(bf).to(dev)
+    v = rn(NI, B, H, D).to(bf).to(dev)
+    g = (-torch.nn.functional.softplus(rn(NI, B, H, D)) * 0.1).clamp(-5, 0).to(bf).to(dev)
+    beta = torch.sigmoid(rn(NI, B, H)).to(bf).to(dev)
+    state = (rn(B, H, D, D) * 0.02).to(dev)
+    o = torch.empty(NI, B, H, D, dtype=bf, device=dev)
     st = torch.cuda.current_stream(dev).cuda_stream
     p = lambda t: t.data_ptr()
 
     def run(n):
-        for i in range(n):
-            j = i % NI
-            rc = lib.kda_decode_step(B, H, D, D, 1, 1, 1, D ** -0.5, p(q[j]), p(k[j]), p(v[j]), p(g[j]), p(beta[j]),
-                                     p(s[i & 1]), p(s[(i + 1) & 1]), p(o), st)
+        # one library call per NI steps: the per-token launches are issued from C, the state is updated in place
+        for _ in range(n // NI):
+            rc = lib.kda_decode_steps(NI, B, H, D, D, 1, 1, 1, D ** -0.5, p(q), p(k), p(v), p(g), p(beta), p(state), p(o), st)
             if rc:
-                raise RuntimeError(f"kda_decode_step failed: {rc}")
+                raise RuntimeError(f"kda_decode_steps failed: {rc}")
 
     def barrier():
         if world > 1:
@@ -167,7 +167,7 @@ def run_decode(args, rank, world, local, dist):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms = float(t.item()) / n_steps
     if rank != 0:
-        return
+        return None
     peaks, src = _peaks()
     Bt = B * world
     bytes_step = 2 * Bt * H * D * D * 4 + Bt * H * (3 * D + D) * 2 + Bt * H * 2 + Bt * H * D * 2
@@ -177,13 +177,13 @@ def run_decode(args, rank, world, local, dist):
         "us_per_step": ms * 1e3, "tokens_per_s": Bt / (ms * 1e-3), "higher_is_better": True, "scaling": "strong",
         "dtype": "f32 state, bf16 activations", "data": "synthetic",
         "config": {"workload": f"config4 recurrent decode: batch {Bt} ({B}/GPU), H16, Dk=Dv=128, fp32 state read+written every step, "
-                               f"{n_steps} steps in one timed region", "l2": "state (256 MiB at N=1) larger than L2; at N=8 the 32 MiB "
+                               f"{n_steps} steps in one timed region", "launch": "kda_decode_steps: 64 steps per library call, one kernel launch per step, state in place", "l2": "state (256 MiB at N=1) larger than L2; at N=8 the 32 MiB "
                                "per-GPU state can sit in L2, so the figure is effective bandwidth"},
         "bytes_per_step": bytes_step,
         "roofline": {"kernel": "decode_kernel", "bound": "hbm", "achieved": gbs / world, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                      "frac": gbs / world / peaks["hbm_gbs"], "traffic": None, "peak_source": src},
     }
-    print(json.dumps(line), flush=True)
+    return line
 
 
 def run_pointwise(args, rank, world, local, dist):
@@ -222,7 +222,7 @@ def run_pointwise(args, rank, world, local, dist):
         gbs = nbytes / (ms * 1e-3) / 1e9
         out[name] = {"us": ms * 1e3, "algorithmic_bytes": nbytes, "gbs": gbs, "frac_of_hbm_peak": gbs / peaks["hbm_gbs"]}
     if rank != 0:
-        return
+        return None
     worst = min(out, key=lambda k: out[k]["frac_of_hbm_peak"])
     line = {
         "metric": "pointwise_hbm_GBps_min", "value": out[worst]["gbs"], "unit": "GB/s", "n_gpus": world, "steps": max(args.steps, 5),
@@ -234,7 +234,7 @@ def run_pointwise(args, rank, world, local, dist):
         "roofline": {"kernel": worst, "bound": "hbm", "achieved": out[worst]["gbs"], "peak": peaks["hbm_gbs"], "unit": "GB/s",
                      "frac": out[worst]["frac_of_hbm_peak"], "traffic": None, "peak_source": src},
     }
-    print(json.dumps(line), flush=True)
+    return line
 
 
 def run(args, rank, world, local):
@@ -243,6 +243,33 @@ def run(args, rank, world, local):
     torch.cuda.set_device(dev)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
-    {"varlen": run_varlen, "decode": run_decode, "pointwise": run_pointwise}[args.workload](args, rank, world, local, dist)
+    line = {"varlen": run_varlen, "decode": run_decode, "pointwise": run_pointwise}[args.workload](args, rank, world, local, dist)
+    if line is not None:
+        print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
+
+
+def sharded_summary(args, rank, world, local, dist):
+    """BASELINE configs 3 (packed, heads sharded) and 4 (decode, batch sharded) at this world size, condensed for the
+    main benchmark line: strong scaling, no data-path collective, max-over-ranks device time."""
+    import copy
+    a = copy.copy(args)
+    a.steps, a.warmup = min(args.steps, 10), 3
+    v = run_varlen(a, rank, world, local, dist)
+    torch.cuda.empty_cache()
+    d = run_decode(a, rank, world, local, dist)
+    torch.cuda.empty_cache()
+    if rank != 0:
+        return None
+    intra = {k: round(r["avg_us"], 1) for k, r in v["kernels"].items()}
+    return {
+        "varlen": {"workload": v["config"]["workload"], "ms_per_step": v["ms_per_step"], "tokens_per_s": v["tokens_per_s"],
+                   "token_heads_per_s": v["value"], "tflops_algorithmic": v["tflops_algorithmic"],
+                   "frac_of_bf16_peak": v["tflops_algorithmic"] / world / _peaks()[0]["bf16_tflops"], "kernel_us": intra,
+                   "scaling": "strong (16 heads / N per GPU)"},
+        "decode": {"workload": d["config"]["workload"], "us_per_step": d["us_per_step"], "gbs_aggregate": d["value"],
+                   "gbs_per_gpu": d["value"] / world, "frac_of_hbm_peak_per_gpu": d["roofline"]["frac"],
+                   "launch": d["config"].get("launch"), "scaling": "strong (256 rows / N per GPU)",
+                   "note": d["config"]["l2"]},
+    }

@@ -1266,20 +1266,14 @@ extern "C" int kda_gate_bwd(int32_t tokens, int32_t heads, int32_t key_dim, int3
     return launch_status();
 }
 
-extern "C" int kda_decode_step(int32_t n_seq, int32_t heads, int32_t key_dim, int32_t value_dim, int32_t io_dtype,
-                               int32_t gate_dtype, int32_t l2norm, float scale, const void* q, const void* k, const void* v, const void* g,
-                               const void* beta, const float* state_in, float* state_out, void* o, void* stream) {
-    if (n_seq < 0 || heads <= 0 || key_dim <= 0 || value_dim <= 0 || key_dim > KDA_MAX_DIM || value_dim > KDA_MAX_DIM)
-        return KDA_ERR_BAD_SHAPE;
-    if (n_seq == 0) return KDA_OK;
-    if (!q || !k || !v || !g || !beta || !state_in || !state_out || !o) return KDA_ERR_NULL;
-    const int bf16 = io_dtype == KDA_DTYPE_BF16, gbf16 = gate_dtype == KDA_DTYPE_BF16;
+static int decode_launch(int n_seq, int heads, int key_dim, int value_dim, int bf16, int gbf16, int l2norm, float scale, const void* q,
+                         const void* k, const void* v, const void* g, const void* beta, const float* state_in, float* state_out,
+                         void* o, cudaStream_t st) {
     // four rows in flight per warp: at ~70 registers three to four CTAs share an SM, so one CTA's prologue (norms, decay) hides
     // under the others' streaming; eight rows per warp measured 20 % slower
     // one CTA per (sequence, head) once there are enough of them to fill the GPU; otherwise split the value rows
     const int rows_per_cta = (n_seq * heads >= 148 * 4) ? value_dim : 32;
     dim3 grid(n_seq * heads, ceil_div(value_dim, rows_per_cta));
-    cudaStream_t st = (cudaStream_t)stream;
     const bool vec = (key_dim % 4 == 0) &&
                      ((reinterpret_cast<uintptr_t>(state_in) | reinterpret_cast<uintptr_t>(state_out)) % 16 == 0);
     if (vec && key_dim <= 128)
@@ -1289,6 +1283,38 @@ extern "C" int kda_decode_step(int32_t n_seq, int32_t heads, int32_t key_dim, in
     else
         KDA_LAUNCH("decode_kernel", st, pw::decode_kernel<0, 4><<<grid, 256, 0, st>>>(heads, key_dim, value_dim, bf16, gbf16, l2norm, scale, q, k, v, g, beta, state_in, state_out, o, rows_per_cta));
     return launch_status();
+}
+
+extern "C" int kda_decode_step(int32_t n_seq, int32_t heads, int32_t key_dim, int32_t value_dim, int32_t io_dtype,
+                               int32_t gate_dtype, int32_t l2norm, float scale, const void* q, const void* k, const void* v, const void* g,
+                               const void* beta, const float* state_in, float* state_out, void* o, void* stream) {
+    if (n_seq < 0 || heads <= 0 || key_dim <= 0 || value_dim <= 0 || key_dim > KDA_MAX_DIM || value_dim > KDA_MAX_DIM)
+        return KDA_ERR_BAD_SHAPE;
+    if (n_seq == 0) return KDA_OK;
+    if (!q || !k || !v || !g || !beta || !state_in || !state_out || !o) return KDA_ERR_NULL;
+    return decode_launch(n_seq, heads, key_dim, value_dim, io_dtype == KDA_DTYPE_BF16, gate_dtype == KDA_DTYPE_BF16, l2norm, scale, q, k,
+                         v, g, beta, state_in, state_out, o, (cudaStream_t)stream);
+}
+
+extern "C" int kda_decode_steps(int32_t n_steps, int32_t n_seq, int32_t heads, int32_t key_dim, int32_t value_dim, int32_t io_dtype,
+                                int32_t gate_dtype, int32_t l2norm, float scale, const void* q, const void* k, const void* v,
+                                const void* g, const void* beta, float* state, void* o, void* stream) {
+    if (n_steps < 0 || n_seq < 0 || heads <= 0 || key_dim <= 0 || value_dim <= 0 || key_dim > KDA_MAX_DIM || value_dim > KDA_MAX_DIM)
+        return KDA_ERR_BAD_SHAPE;
+    if (n_seq == 0 || n_steps == 0) return KDA_OK;
+    if (!q || !k || !v || !g || !beta || !state || !o) return KDA_ERR_NULL;
+    const int bf16 = io_dtype == KDA_DTYPE_BF16, gbf16 = gate_dtype == KDA_DTYPE_BF16;
+    const size_t io_b = bf16 ? 2 : 4, g_b = gbf16 ? 2 : 4;
+    const size_t nk = (size_t)n_seq * heads * key_dim, nv = (size_t)n_seq * heads * value_dim, nb = (size_t)n_seq * heads;
+    auto at = [](const void* p, size_t bytes) { return static_cast<const void*>(static_cast<const char*>(p) + bytes); };
+    for (int i = 0; i < n_steps; ++i) {
+        // the state is updated in place: a warp reads a whole row before it writes it, and no row is shared between warps
+        int rc = decode_launch(n_seq, heads, key_dim, value_dim, bf16, gbf16, l2norm, scale, at(q, i * nk * io_b), at(k, i * nk * io_b),
+                               at(v, i * nv * io_b), at(g, i * nk * g_b), at(beta, i * nb * g_b), state, state,
+                               static_cast<char*>(o) + i * nv * io_b, (cudaStream_t)stream);
+        if (rc) return rc;
+    }
+    return KDA_OK;
 }
 
 namespace {

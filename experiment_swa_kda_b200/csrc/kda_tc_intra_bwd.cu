@@ -532,34 +532,49 @@ __global__ void __launch_bounds__(512, 1)
             dqn[r] += dd * kn[r];
             dkn[r] += dd * qn[r];
         }
+        // The decay gradient is a telescoping sum: a pair (i, s) adds its summand to dG at row i (row part) and takes the
+        // same summand away at row s (column part), and only the rows in between keep it after the reverse cumulative
+        // sum.  The two parts come from different UMMAs, so they cancel exactly only if both are built from the SAME
+        // rounded factors: dG therefore uses the bf16 values that sit in the operand panels (target rows q~, k~ and
+        // source rows k-), while dq and dk keep the float32 factors.
+        auto rb = [](float x) { return __bfloat162float(__float2bfloat16(x)); };
         tmem_ld16(tmem + lane_base + cRP + 32 * I, t);          // row part through dA
 #pragma unroll
         for (int r = 0; r < 16; ++r) {
-            const float x = e1[r] * t[r];
-            dqn[r] += x;
-            dG[r] += qn[r] * x;
+            dqn[r] += e1[r] * t[r];
+            dG[r] += rb(qn[r] * e1[r]) * t[r];
         }
         tmem_ld16(tmem + lane_base + cRP + 32 * I + 16, t);     // row part through beta*dM
 #pragma unroll
         for (int r = 0; r < 16; ++r) {
-            const float x = e1[r] * t[r];
-            dkn[r] += x;
-            dG[r] += kn[r] * x;
+            dkn[r] += e1[r] * t[r];
+            dG[r] += rb(kn[r] * e1[r]) * t[r];
         }
+        // column part: sources of block I receive from target blocks I' >= I, each with its own decay reference; the
+        // source factor is rebuilt exactly as the panel code built it (own-block factor, then one block step at a time)
+        float fsrc[16], esrc[16];
 #pragma unroll
-        for (int r = 0; r < 16; ++r) e1[r] = __expf(cOwn - G[r]);   // now e2
-        // column part: sources of block I receive from target blocks I' >= I, each with its own decay reference
+        for (int r = 0; r < 16; ++r) {
+            esrc[r] = __expf(cOwn - G[r]);
+            fsrc[r] = kn[r] * esrc[r];
+        }
+        const float fb0 = __expf(c1 - c0), fb1 = __expf(c2 - c1), fb2 = __expf(c3 - c2);
 #pragma unroll
         for (int Ib = 0; Ib < 4; ++Ib) {
             if (Ib >= I) {
-                const float cI = Ib == 0 ? c0 : (Ib == 1 ? c1 : (Ib == 2 ? c2 : c3));
-                const float fI = __expf(cI - cOwn);
                 tmem_ld16(tmem + lane_base + cCP[Ib] + 16 * I, t);
 #pragma unroll
                 for (int r = 0; r < 16; ++r) {
-                    const float x = fI * e1[r] * t[r];
-                    dkn[r] += x;
-                    dG[r] -= kn[r] * x;
+                    dkn[r] += esrc[r] * t[r];
+                    dG[r] -= rb(fsrc[r]) * t[r];
+                }
+            }
+            const float step = Ib == 0 ? fb0 : (Ib == 1 ? fb1 : fb2);
+            if (Ib >= I && Ib < 3) {
+#pragma unroll
+                for (int r = 0; r < 16; ++r) {
+                    fsrc[r] *= step;
+                    esrc[r] *= step;
                 }
             }
         }

@@ -270,6 +270,27 @@ def decode_step(q, k, v, g, beta, state, scale, l2norm=True, out_state: Optional
     return o, new_state
 
 
+def decode_steps(q, k, v, g, beta, state, scale, l2norm=True):
+    """n consecutive decode steps in one library call.  q,k,g [n,B,H,K]; v [n,B,H,V]; beta [n,B,H]; `state` [B,H,V,K]
+    float32 is UPDATED IN PLACE.  Returns o [n,B,H,V].  One kernel launch per step, issued from C without a host round
+    trip per token (the serving loop of the reference makes one operator call per token: nanochat/engine.py:83-226)."""
+    lib = _lib.load()
+    dev = _need_cuda(q, k, v, g, beta, state)
+    q, k, v, g, beta = (t.contiguous() for t in (q, k, v, g, beta))
+    if g.dtype != beta.dtype:
+        beta = beta.to(g.dtype)
+    n, B, H, K = q.shape
+    V = v.shape[-1]
+    if state.dtype != torch.float32 or not state.is_contiguous() or tuple(state.shape) != (B, H, V, K):
+        raise ValueError(f"state must be contiguous float32 V-first [B, H, V, K] with shape {(B, H, V, K)}")
+    o = torch.empty_like(v)
+    with torch.cuda.device(dev):
+        rc = lib.kda_decode_steps(n, B, H, K, V, _dt(q), _dt(g), 1 if l2norm else 0, float(scale), _ptr(q), _ptr(k), _ptr(v),
+                                  _ptr(g), _ptr(beta), _ptr(state), _ptr(o), _stream(dev))
+    _lib.check(rc, "kda_decode_steps")
+    return o
+
+
 # --------------------------------------------------------------------------------------------
 # short convolution
 # --------------------------------------------------------------------------------------------

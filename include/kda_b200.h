@@ -141,6 +141,15 @@ int kda_decode_step(int32_t n_seq, int32_t heads, int32_t key_dim, int32_t value
                     int32_t gate_dtype, int32_t l2norm, float scale, const void* q, const void* k, const void* v, const void* g, const void* beta,
                     const float* state_in, float* state_out, void* o, void* stream);
 
+/* n_steps consecutive decode steps in one call: step i reads q,k,g [n_steps,n_seq,H,K], v [n_steps,n_seq,H,V],
+ * beta [n_steps,n_seq,H] at index i, updates `state` in place and writes o[i].  One kernel launch per step (the state
+ * crosses HBM once each way per step, exactly as n_steps calls of kda_decode_step would), without a host round trip
+ * per token; the reference's decode loop makes one operator call per token and layer (nanochat/engine.py:83-226,
+ * recurrent_decode.cu:96-181). */
+int kda_decode_steps(int32_t n_steps, int32_t n_seq, int32_t heads, int32_t key_dim, int32_t value_dim, int32_t io_dtype,
+                     int32_t gate_dtype, int32_t l2norm, float scale, const void* q, const void* k, const void* v,
+                     const void* g, const void* beta, float* state, void* o, void* stream);
+
 /* ---- short causal depthwise convolution + SiLU --------------------------------
  * x,y [B,T,C]; weight [C,W] in io_dtype; cache [B,C,W] in io_dtype holds the last W
  * inputs including the current token.  Stands in for

@@ -259,6 +259,52 @@ def test_decode_step_in_place_state_equals_out_of_place(K, V):
     assert torch.equal(o, o_ref) and torch.equal(state, s_ref)
 
 
+def test_decode_1024_steps_in_library_calls_match_the_oracle_and_the_single_step_entry():
+    """1,024 decode steps at a reduced batch through kda_decode_steps (state updated in place, launches issued from C)
+    against the oracle's token loop, and bit-identical to 1,024 calls of the single-step entry."""
+    from experiment_swa_kda_b200 import ops
+    n, B, H, D = 1024, 2, 2, 128
+    d = O.make_inputs(B, n, H, D, D, seed=77, with_state=True)
+    x = to_dev(d, torch.bfloat16)
+    steps = {k_: x[k_].transpose(0, 1).contiguous() for k_ in ("q", "k", "v", "g", "beta")}     # [n, B, H, ...]
+    state = x["h0"].clone()
+    o = ops.decode_steps(steps["q"], steps["k"], steps["v"], steps["g"], steps["beta"], state, D ** -0.5)
+    eo, es = O.kda_recurrence(*(x[k_].float().cpu() for k_ in ("q", "k", "v", "g", "beta")), initial_state=x["h0"].cpu())
+    assert O.rel_l2(o.transpose(0, 1).float(), eo) <= BF16_TOL and O.rel_l2(state, es) <= 1e-4
+    cur, outs = x["h0"].clone(), []
+    for i in range(n):
+        oi, cur = ops.decode_step(steps["q"][i], steps["k"][i], steps["v"][i], steps["g"][i], steps["beta"][i], cur, D ** -0.5, True)
+        outs.append(oi)
+    assert torch.equal(torch.stack(outs), o) and torch.equal(cur, state)
+
+
+def test_prefill_then_decode_equals_one_shot_and_forward_only_path_matches_training_forward():
+    """No-grad prefill (the forward-only kernels' path: no backward panels are written) over T tokens, then token-by-token
+    decode from its final state, equals one call over T + n tokens; and the prefill output is bit-identical to the
+    gradient-tracking forward."""
+    m = kda_mod()
+    T, n = 300, 9
+    d = O.make_inputs(2, T + n, 2, 128, 128, seed=61, with_state=True)
+    x = to_dev(d, torch.bfloat16)
+    with torch.no_grad():
+        full, fs_full = m.chunk_kda(x["q"], x["k"], x["v"], x["g"], x["beta"], initial_state=x["h0"], output_final_state=True)
+        pre = {k_: x[k_][:, :T] for k_ in ("q", "k", "v", "g", "beta")}
+        o_pre, s = m.chunk_kda(pre["q"], pre["k"], pre["v"], pre["g"], pre["beta"], initial_state=x["h0"], output_final_state=True)
+        pieces = []
+        for i in range(T, T + n):
+            oi, s = m.recurrent_kda_step(x["q"][:, i:i + 1], x["k"][:, i:i + 1], x["v"][:, i:i + 1], x["g"][:, i:i + 1],
+                                         x["beta"][:, i:i + 1], s)
+            pieces.append(oi)
+    assert torch.equal(o_pre, full[:, :T])
+    assert O.rel_l2(torch.cat(pieces, 1).float(), full[:, T:].float()) <= BF16_TOL
+    assert O.rel_l2(s, fs_full) <= BF16_TOL      # exact float32 steps against the bf16 tensor-core scan
+    xg = {k_: t.clone().requires_grad_(True) for k_, t in x.items()}
+    tracked, fs_tracked = m.chunk_kda(xg["q"], xg["k"], xg["v"], xg["g"], xg["beta"], initial_state=xg["h0"], output_final_state=True)
+    assert torch.equal(tracked, full) and torch.equal(fs_tracked, fs_full)
+    eo, es = O.kda_recurrence(*(x[k_].float().cpu() for k_ in ("q", "k", "v", "g", "beta")), initial_state=x["h0"].cpu())
+    assert O.rel_l2(full.float(), eo) <= BF16_TOL and O.rel_l2(fs_full, es) <= BF16_TOL
+
+
 def test_device_status_word_is_clean_after_tensor_core_forward_backward():
     from experiment_swa_kda_b200 import _lib, ops
     d = O.make_inputs(2, 200, 2, 128, 128, seed=5, with_state=True)

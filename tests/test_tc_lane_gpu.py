@@ -81,6 +81,25 @@ def test_scaled_gates_clamped_to_range_tensor_core_lane():
     _run_activated(d)
 
 
+def test_default_initialisation_gate_regime_keeps_the_decay_gradient_accurate():
+    """g around -2.5 per token (raw gate logits near zero, where a freshly initialised layer sits): contexts are a few
+    tokens long, so dg is a local quantity while the chunked pull-back builds it from row and column parts that must
+    cancel over up to 64 rows.  Both parts are formed from the same bf16-rounded factors, which keeps dg - and its sum
+    over tokens, the bias gradient of the gate - inside the bar instead of growing a random walk of rounding errors."""
+    d = O.make_inputs(2, 256, 2, 128, 128, seed=5, with_state=True)
+    d["g"] = (-5 * torch.sigmoid(torch.randn(d["g"].shape, generator=torch.Generator().manual_seed(9)) * 0.5)).clamp(-5, 0)
+    m = _kda_mod()
+    x = {n: (t.float() if n == "h0" else t.bfloat16()).to(D0).requires_grad_(True) for n, t in d.items()}
+    o, s = m.chunk_kda(x["q"], x["k"], x["v"], x["g"], x["beta"], initial_state=x["h0"], output_final_state=True, lane="tc")
+    do = torch.randn(o.shape, generator=torch.Generator().manual_seed(1)).bfloat16().to(D0)
+    dg, = torch.autograd.grad(o, [x["g"]], do)
+    leaf = {n: t.detach().float().cpu().requires_grad_(True) for n, t in x.items()}
+    eo, _ = O.kda_recurrence(leaf["q"], leaf["k"], leaf["v"], leaf["g"], leaf["beta"], initial_state=leaf["h0"])
+    want, = torch.autograd.grad(eo, [leaf["g"]], do.float().cpu())
+    assert O.rel_l2(dg.float(), want) <= BF16_TOL
+    assert O.rel_l2(dg.float().sum((0, 1)), want.sum((0, 1))) <= BF16_TOL      # what the gate's bias gradient sums
+
+
 def _raw_inputs(T, D, seed, heads=2, batch=1, grad=True):
     gen = torch.Generator().manual_seed(seed)
     act = lambda *shape: torch.randn(*shape, generator=gen).to(torch.bfloat16).to(D0).requires_grad_(grad)
