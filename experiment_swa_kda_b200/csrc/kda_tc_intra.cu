@@ -1,13 +1,18 @@
-// Tensor-core lane, chunk-parallel part of the forward: one CTA per (chunk, head) builds every operand panel
-// the scans consume.  K = V = 128, chunk = 64 tokens, bf16 UMMA operands, fp32 accumulation.
+// Tensor-core lane, chunk-parallel part of the forward: one CTA (256 threads, two CTAs per SM) per (chunk, head) builds
+// every operand panel the scans consume.  K = V = 128, chunk = 64 tokens, bf16 UMMA operands, fp32 accumulation.
 //
-//   norms, cumulative log-decay G (fp32)                                       CUDA cores, thread = channel
+//   norms, cumulative log-decay G (fp32)                                       CUDA cores, thread = 4 rows x 8 channels
 //   A[t][s], M~[t][s] = sum_d (q|k)[t,d] e^{G_t-c} * k[s,d] e^{c-G_s}         tcgen05, M=128 N=64 K=128, two chains
 //       c = G at the first row of the 16-row target block, so both factors stay in range for any g in [-5, 0]
 //       (restates the per-tile decay centre of reference chunk_wy_forward.cu:312-376, 447-450)
 //   T = (I + beta M~)^-1                                                       fp32, block forward substitution
 //   U^T = P^T T^T,  W^T = Q^T T^T   (P = beta v, Q = beta e^G k)                tcgen05, M=128 N=64 K=64, MN-major A
 //   R^T = (q e^G)^T, E = k e^{G_end-G}, e^{G_end}, A^T, T                       panels for the scans / backward
+// Every operand panel is written as 16-byte pieces of the 128-byte-swizzled layout the UMMA descriptors read: a thread
+// owns 8 adjacent channels of 4 consecutive rows, takes q, k, g straight from global memory (a half-warp reads one
+// 256-byte row segment) and needs two exponentials and one reciprocal per element.  The source panels of the two
+// chains share one buffer (the second is written once the first chain has completed), which together with 256 threads
+// keeps the CTA at 105 KB / <= 128 registers so that two CTAs share an SM and fill each other's waits.
 // Restates reference chunk_wy_forward.cu:125-405 and 761-858.
 
 #include <cstdio>
@@ -20,65 +25,129 @@
 namespace kda {
 namespace tc {
 
-#ifdef KDA_PHASE_TIMING
-#define KDA_TICK(n) do { if (threadIdx.x == 0 && blockIdx.y == 0 && (blockIdx.x == 0 || blockIdx.x == 100)) tick[n] = clock64(); } while (0)
-#else
-#define KDA_TICK(n) do { } while (0)
-#endif
-
 int make_map_bf16(CUtensorMap* m, const void* ptr, uint64_t rows, uint64_t cols, uint32_t box_cols, uint32_t box_rows);
+
+namespace {
+
+constexpr int kLDs = 68;      // leading dimension (floats) of the 64x64 fp32 tiles of the inverse
+constexpr int kNT = 256;
 
 __device__ __forceinline__ uint32_t pack2(float a, float b) {
     __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
     return *reinterpret_cast<uint32_t*>(&h);
 }
-__device__ __forceinline__ void st_bf16(uint8_t* base, uint32_t off, float x) {
-    *reinterpret_cast<__nv_bfloat16*>(base + off) = __float2bfloat16(x);
+__device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
+    return make_uint4(pack2(f[0], f[1]), pack2(f[2], f[3]), pack2(f[4], f[5]), pack2(f[6], f[7]));
 }
-// byte offset of element (row r, column d) of a K-major / MN-major swizzled panel whose 64-column blocks are
-// `blk_bytes` apart
-__device__ __forceinline__ uint32_t el_off(int r, int d, uint32_t blk_bytes) {
-    return (uint32_t)(d >> 6) * blk_bytes + sw128_off(r, (d & 63) >> 3) + (uint32_t)(d & 7) * 2;
+// byte offset of the 16-byte piece holding channels 8*cg .. 8*cg+7 of row r in a K-major / MN-major swizzled panel whose
+// 64-column blocks are blk_bytes apart
+__device__ __forceinline__ uint32_t piece_off(int r, int cg, uint32_t blk_bytes) {
+    return (uint32_t)(cg >> 3) * blk_bytes + sw128_off(r, cg & 7);
+}
+__device__ __forceinline__ void ld8(const void* base, size_t idx, int bf16, float (&f)[8]) {
+    if (bf16) {
+        unpack_bf16x8(__ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(base) + idx)), f);
+    } else {
+        const float4 a = __ldg(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(base) + idx));
+        const float4 b = __ldg(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(base) + idx + 4));
+        f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+    }
+}
+__device__ __forceinline__ void lds8(const float* p, float (&f)[8]) {
+    const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+    f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+}
+__device__ __forceinline__ void sts8(float* p, const float (&f)[8]) {
+    *reinterpret_cast<float4*>(p) = make_float4(f[0], f[1], f[2], f[3]);
+    *reinterpret_cast<float4*>(p + 4) = make_float4(f[4], f[5], f[6], f[7]);
+}
+__device__ __forceinline__ float fast_rcp(float x) {
+    float y;
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
 }
 
-constexpr int kLDs = 68;
-
-constexpr int kNT = 512;   // threads per CTA: thread (I, d) = 16-token row block I (warp >> 2), channel d (tid & 127)
-
-// dst[S x S] = alpha * A[S x S] * B[S x S] (row-major fp32, leading dimension kLDs, 16-byte aligned columns) for NB
-// independent problems addressed through the callers' pointer functions.  Each of the first S*S*NB/8 threads owns a
-// 2 x 4 tile of one product, so a step of the contraction costs a warp three shared-memory wavefronts (two broadcast
-// words of A, one 16-byte row piece of B) for eight multiply-adds per thread.
-template <int S, int NB, class PA, class PB, class PD>
-__device__ __forceinline__ void block_mm(PA pa, PB pb, PD pd, float alpha) {
-    constexpr int TPP = S * S / 8;                // threads per problem
+// dst = alpha * A * B for NP independent S x S problems (row-major fp32, leading dimension kLDs), all 256 threads busy:
+// a thread owns one row piece of CW adjacent columns of one product.
+template <int S, int NP, class PA, class PB, class PD>
+__device__ __forceinline__ void tile_mm(PA pa, PB pb, PD pd, float alpha) {
+    constexpr int CW = S * S * NP / kNT;          // columns per thread: 1 (8x8x4), 2 (16x16x2), 4 (32x32x1)
+    constexpr int TPR = S / CW;                   // threads per row
     const int tid = threadIdx.x;
-    if (tid >= TPP * NB) return;
-    const int prob = tid / TPP, rem = tid - prob * TPP;
-    const int i0 = (rem / (S / 4)) * 2, j0 = (rem % (S / 4)) * 4;
-    const float* A0 = pa(prob) + i0 * kLDs;
+    const int prob = tid / (S * TPR), rem = tid % (S * TPR);
+    const int i = rem / TPR, j0 = (rem % TPR) * CW;
+    const float* A = pa(prob) + i * kLDs;
     const float* B = pb(prob) + j0;
-    float acc[2][4];
+    float acc[CW];
 #pragma unroll
-    for (int r = 0; r < 2; ++r)
-#pragma unroll
-        for (int c = 0; c < 4; ++c) acc[r][c] = 0.f;
+    for (int c = 0; c < CW; ++c) acc[c] = 0.f;
 #pragma unroll
     for (int t = 0; t < S; ++t) {
-        const float a0 = A0[t], a1 = A0[kLDs + t];
-        const float4 bv = *reinterpret_cast<const float4*>(B + t * kLDs);
-        acc[0][0] += a0 * bv.x; acc[0][1] += a0 * bv.y; acc[0][2] += a0 * bv.z; acc[0][3] += a0 * bv.w;
-        acc[1][0] += a1 * bv.x; acc[1][1] += a1 * bv.y; acc[1][2] += a1 * bv.z; acc[1][3] += a1 * bv.w;
+        const float a = A[t];
+        if (CW == 4) {
+            const float4 b = *reinterpret_cast<const float4*>(B + t * kLDs);
+            acc[0] += a * b.x; acc[1 % CW] += a * b.y; acc[2 % CW] += a * b.z; acc[3 % CW] += a * b.w;
+        } else if (CW == 2) {
+            const float2 b = *reinterpret_cast<const float2*>(B + t * kLDs);
+            acc[0] += a * b.x; acc[1 % CW] += a * b.y;
+        } else {
+            acc[0] += a * B[t * kLDs];
+        }
     }
-    float* D = pd(prob) + i0 * kLDs + j0;
+    float* D = pd(prob) + i * kLDs + j0;
 #pragma unroll
-    for (int r = 0; r < 2; ++r)
-        *reinterpret_cast<float4*>(D + r * kLDs) = make_float4(alpha * acc[r][0], alpha * acc[r][1], alpha * acc[r][2], alpha * acc[r][3]);
+    for (int c = 0; c < CW; ++c) D[c] = alpha * acc[c];
+}
+
+// D = alpha * A * B for S x S fp32 tiles in shared memory (leading dimension kLDs) on the warp-level tensor-core path:
+// mma.sync m16n8k8 with every operand split into two TF32 terms (hi + lo; lo*lo dropped), which keeps float32-class
+// accuracy - T feeds every later product - while one product costs a warp S/8 short steps instead of S dependent
+// shared-memory round trips.  These few 16..32-wide dependent products are latency-bound; a tcgen05 round trip
+// (stage operands, issue, commit, read tensor memory back) costs more than the whole product does here.
+// NP problems of S x S; a warp owns one 16 x 8 output tile; warps beyond the tile count idle.
+__device__ __forceinline__ void split_tf32(float x, uint32_t& hi, uint32_t& lo) {
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(hi) : "f"(x));
+    const float r = x - __uint_as_float(hi);
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(lo) : "f"(r));
+}
+__device__ __forceinline__ void mma_tf32(float (&d)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
+    asm volatile("mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+}
+template <int S, int NP, class PA, class PB, class PD>
+__device__ __forceinline__ void warp_mm(PA pa, PB pb, PD pd, float alpha) {
+    constexpr int TR = S / 16, TC = S / 8;         // output tiles per problem
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (warp >= NP * TR * TC) return;
+    const int prob = warp / (TR * TC), tile = warp % (TR * TC);
+    const int r0 = 16 * (tile / TC), c0 = 8 * (tile % TC);
+    const int g = lane >> 2, tig = lane & 3;
+    const float* A = pa(prob) + (r0 + g) * kLDs + tig;
+    const float* B = pb(prob) + tig * kLDs + c0 + g;
+    float d[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int ks = 0; ks < S / 8; ++ks) {
+        uint32_t ah[4], al[4], bh[2], bl[2];
+        split_tf32(A[8 * ks], ah[0], al[0]);
+        split_tf32(A[8 * kLDs + 8 * ks], ah[1], al[1]);
+        split_tf32(A[8 * ks + 4], ah[2], al[2]);
+        split_tf32(A[8 * kLDs + 8 * ks + 4], ah[3], al[3]);
+        split_tf32(B[(8 * ks) * kLDs], bh[0], bl[0]);
+        split_tf32(B[(8 * ks + 4) * kLDs], bh[1], bl[1]);
+        mma_tf32(d, al, bh);
+        mma_tf32(d, ah, bl);
+        mma_tf32(d, ah, bh);
+    }
+    float* D = pd(prob) + (r0 + g) * kLDs + c0 + 2 * tig;
+    *reinterpret_cast<float2*>(D) = make_float2(alpha * d[0], alpha * d[1]);
+    *reinterpret_cast<float2*>(D + 8 * kLDs) = make_float2(alpha * d[2], alpha * d[3]);
 }
 
 // Ts = (I + Ms)^-1 for strictly lower-triangular Ms (64x64): 8x8 diagonal solves (a short dependent chain per thread),
-// then merges to 16, 32 and 64 with   inv([[A,0],[C,B]]) = [[Ai,0],[-Bi C Ai, Bi]].
-__device__ void unit_lower_inverse(const float* Ms, float* Ts, float* tmp) {
+// then merges to 16 (CUDA cores), 32 and 64 (warp-level tensor cores) with
+//   inv([[A,0],[C,B]]) = [[Ai,0],[-Bi C Ai, Bi]].
+__device__ __forceinline__ void unit_lower_inverse(const float* Ms, float* Ts, float* tmp) {
     const int tid = threadIdx.x;
     for (int idx = tid; idx < 64 * kLDs / 4; idx += kNT) reinterpret_cast<float4*>(Ts)[idx] = make_float4(0.f, 0.f, 0.f, 0.f);
     __syncthreads();
@@ -100,49 +169,31 @@ __device__ void unit_lower_inverse(const float* Ms, float* Ts, float* tmp) {
         for (int i = 0; i < 8; ++i) Tb[i * kLDs + j] = x[i];
     }
     __syncthreads();
-    // 16x16 merges, four independent pairs of 8x8 blocks: tmp_p = C_p Ai_p ; T21_p = -Bi_p tmp_p
-    {
-        const int p = tid >> 6, i = (tid >> 3) & 7, j = tid & 7;
-        if (tid < 256) {
-            const float* C = Ms + (16 * p + 8 + i) * kLDs + 16 * p;
-            const float* Ai = Ts + (16 * p) * kLDs + 16 * p + j;
-            float a = 0.f;
-#pragma unroll
-            for (int t = 0; t < 8; ++t) a += C[t] * Ai[t * kLDs];
-            tmp[(p * 8 + i) * kLDs + j] = a;
-        }
-        __syncthreads();
-            if (tid < 256) {
-            const float* Bi = Ts + (16 * p + 8 + i) * kLDs + 16 * p + 8;
-            const float* Tm = tmp + (p * 8) * kLDs + j;
-            float a = 0.f;
-#pragma unroll
-            for (int t = 0; t < 8; ++t) a += Bi[t] * Tm[t * kLDs];
-            Ts[(16 * p + 8 + i) * kLDs + 16 * p + j] = -a;
-        }
-        __syncthreads();
-        }
-    // 32x32 merges, two independent pairs: tmp_p = C_p Ai_p ; T21_p = -Bi_p tmp_p
-    block_mm<16, 2>([&](int p) { return Ms + (32 * p + 16) * kLDs + 32 * p; },
-                    [&](int p) { return Ts + (32 * p) * kLDs + 32 * p; },
-                    [&](int p) { return tmp + p * 16 * kLDs; }, 1.f);
+    // merges: tmp_p = C_p Ai_p ; T21_p = -Bi_p tmp_p
+    tile_mm<8, 4>([&](int p) { return Ms + (16 * p + 8) * kLDs + 16 * p; }, [&](int p) { return Ts + (16 * p) * kLDs + 16 * p; },
+                  [&](int p) { return tmp + p * 8 * kLDs; }, 1.f);
     __syncthreads();
-    block_mm<16, 2>([&](int p) { return Ts + (32 * p + 16) * kLDs + 32 * p + 16; },
-                    [&](int p) { return tmp + p * 16 * kLDs; },
-                    [&](int p) { return Ts + (32 * p + 16) * kLDs + 32 * p; }, -1.f);
+    tile_mm<8, 4>([&](int p) { return Ts + (16 * p + 8) * kLDs + 16 * p + 8; }, [&](int p) { return tmp + p * 8 * kLDs; },
+                  [&](int p) { return Ts + (16 * p + 8) * kLDs + 16 * p; }, -1.f);
     __syncthreads();
-    // 64x64 merge
-    block_mm<32, 1>([&](int) { return Ms + 32 * kLDs; }, [&](int) { return Ts; }, [&](int) { return tmp; }, 1.f);
+    warp_mm<16, 2>([&](int p) { return Ms + (32 * p + 16) * kLDs + 32 * p; }, [&](int p) { return Ts + (32 * p) * kLDs + 32 * p; },
+                   [&](int p) { return tmp + p * 16 * kLDs; }, 1.f);
     __syncthreads();
-    block_mm<32, 1>([&](int) { return Ts + 32 * kLDs + 32; }, [&](int) { return tmp; },
-                    [&](int) { return Ts + 32 * kLDs; }, -1.f);
+    warp_mm<16, 2>([&](int p) { return Ts + (32 * p + 16) * kLDs + 32 * p + 16; }, [&](int p) { return tmp + p * 16 * kLDs; },
+                   [&](int p) { return Ts + (32 * p + 16) * kLDs + 32 * p; }, -1.f);
+    __syncthreads();
+    warp_mm<32, 1>([&](int) { return Ms + 32 * kLDs; }, [&](int) { return Ts; }, [&](int) { return tmp; }, 1.f);
+    __syncthreads();
+    warp_mm<32, 1>([&](int) { return Ts + 32 * kLDs + 32; }, [&](int) { return tmp; }, [&](int) { return Ts + 32 * kLDs; }, -1.f);
     __syncthreads();
 }
+
+}  // namespace
 
 struct IntraFwdArgs {
     const int* chunk_tok0;
     const int* chunk_len;
-    const __nv_bfloat16 *q, *k, *v;   // [tokens][H][128]
+    const __nv_bfloat16 *q, *k;       // [tokens][H][128]
     const void* g;                    // [tokens][H][128], gate dtype
     const void* beta;                 // [tokens][H]
     int gbf16, l2norm, H;
@@ -152,267 +203,357 @@ struct IntraFwdArgs {
 };
 
 // shared-memory map (bytes from a 1024-aligned base)
-constexpr int kFS0 = 0;          // 32 KB  source stack, target blocks 0|1   -> later Ms, Ts, tmp (fp32)
-constexpr int kFX0 = 32768;      // 16 KB  target stack, blocks 0|1
-constexpr int kFS1 = 49152;      // 32 KB  source stack, target blocks 2|3
-constexpr int kFX1 = 81920;      // 16 KB  target stack, blocks 2|3          -> later T and T diag(beta) (bf16)
-constexpr int kFQ = 98304;       // 16 KB  Q = beta e^G k (MN-major A)
-constexpr int kFIn = 114688;     // 48 KB  q | k | v tiles (TMA)
-constexpr int kFSmall = 163840;  // floats: gsum[4][128] cref[4][128] qinv[64] kinv[64] beta[64]
-constexpr int kIntraFwdSmem = kFSmall + (2 * 512 + 3 * 64) * 4 + 1024;
+constexpr int kFS = 0;             // 32 KB  source stack of the chain in flight: [2 target blocks][64 rows], 2 k-blocks of 16 KB
+constexpr int kFX = 32768;         // 32 KB  target stacks, chain pr at pr * 16 KB: rows (blk & 1) * 32 + {q: r, k: 16 + r}
+constexpr int kFV = 65536;         // 16 KB  v tile (TMA): MN-major A of U^T = v^T (T diag(beta))^T
+constexpr int kFQ = 81920;         // 16 KB  Q = beta e^G k: MN-major A of W^T = Q^T T^T
+constexpr int kFTab = 98304;       // floats: cref[4][128] eC[4][128] eEnd[4][128] fb[3][128] | gend[128] | bet[64]
+constexpr int kTabFloats = 15 * 128 + 128 + 64;
+// after the A / M~ chains the stacks are dead: Ms, Ts, tmp (fp32) and the two bf16 T operands live in [0, 64 KB)
+constexpr int kFMs = 0, kFTs = 64 * kLDs * 4, kFTmp = 2 * 64 * kLDs * 4, kFTb = 49152, kFTbb = 57344;
+static_assert(kFTmp + 32 * kLDs * 4 <= kFTb, "inverse scratch overlaps the T operands");
+constexpr int kIntraFwdSmem = kFTab + kTabFloats * 4 + 1024;
 
-__device__ __forceinline__ void tmem_ld16f(uint32_t taddr, float (&f)[16]) {
-    uint32_t r[16];
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-        : "r"(taddr)
-        : "memory");
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-    for (int j = 0; j < 16; ++j) f[j] = __uint_as_float(r[j]);
-}
-
-__global__ void __launch_bounds__(kNT, 1)
-    tc_intra_fwd_kernel(const __grid_constant__ CUtensorMap mq, const __grid_constant__ CUtensorMap mk,
-                        const __grid_constant__ CUtensorMap mv, IntraFwdArgs p) {
+template <bool GBF16>
+__global__ void __launch_bounds__(kNT, 2)
+    tc_intra_fwd_kernel(const __grid_constant__ CUtensorMap mv, const __grid_constant__ CUtensorMap mUT,
+                        const __grid_constant__ CUtensorMap mWT, const __grid_constant__ CUtensorMap mAT,
+                        const __grid_constant__ CUtensorMap mMt, IntraFwdArgs p) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* sm = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-    uint8_t* S0 = sm + kFS0;
-    uint8_t* X0 = sm + kFX0;
-    uint8_t* S1 = sm + kFS1;
-    uint8_t* X1 = sm + kFX1;
-    float* Ms = reinterpret_cast<float*>(sm);      // phase-2 view of the source/target stacks
-    float* Ts = Ms + 64 * kLDs;
-    float* tmp = Ts + 64 * kLDs;
-    uint8_t* Tb = sm + kFX1;                       // [64 rows x 128 B] K-major B: T
-    uint8_t* Tbb = sm + kFX1 + 8192;               //                              T diag(beta)
+    uint8_t* Sst = sm + kFS;
+    uint8_t* vs = sm + kFV;
     uint8_t* Qs = sm + kFQ;
-    uint8_t* qs = sm + kFIn;
-    uint8_t* ks = qs + 16384;
-    uint8_t* vs = ks + 16384;                      // doubles as the MN-major A operand of U^T = v^T (T diag(beta))^T
-    float* gsum = reinterpret_cast<float*>(sm + kFSmall);
-    float* cref = gsum + 512;
-    float* qinv = cref + 512;
-    float* kinv = qinv + 64;
-    float* bet = kinv + 64;
-    __shared__ uint64_t bar_am, bar_uw, bar_in;
+    float* cref = reinterpret_cast<float*>(sm + kFTab);      // [4][128] G at the first row of each 16-row block
+    float* eC = cref + 512;                                  // [4][128] exp(cref)
+    float* eEnd = eC + 512;                                  // [4][128] exp(G_end - cref)
+    float* fbk = eEnd + 512;                                 // [3][128] exp(cref[I+1] - cref[I])
+    float* gends = fbk + 384;                                // [128]    G_end
+    float* bet = gends + 128;                                // [64]
+    float* wtot = reinterpret_cast<float*>(sm + kFS);        // [8][128] per-warp sums of g (dead before the stacks are written)
+    float* Ms = reinterpret_cast<float*>(sm + kFMs);
+    float* Ts = reinterpret_cast<float*>(sm + kFTs);
+    float* tmp = reinterpret_cast<float*>(sm + kFTmp);
+    uint8_t* Tb = sm + kFTb;                                 // [64 rows x 128 B] K-major B: T
+    uint8_t* Tbb = sm + kFTbb;                               //                              T diag(beta)
+    __shared__ uint64_t bar_in, bar_am[2], bar_uw;
     __shared__ uint32_t tmem_slot;
-#ifdef KDA_PHASE_TIMING
-    long long tick[12];
-#endif
+
     const int slot = blockIdx.x, h = blockIdx.y, H = p.H;
     const int len = p.chunk_len[slot];
     if (len == 0) return;
     const int tok0 = p.chunk_tok0[slot];
     const size_t ch = (size_t)slot * H + h;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int I = warp >> 2, d = tid & 127;
+    const int cg = lane & 15;                      // channels 8*cg .. 8*cg+7
+    const int rq = 2 * warp + (lane >> 4);         // rows 4*rq .. 4*rq+3
+    const int J = warp >> 1;                       // 16-row block of this thread's rows
     const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
-    KDA_TICK(0);
 
     if (tid == 0) {
-        mbar_init(&bar_am, 1);
-        mbar_init(&bar_uw, 1);
         mbar_init(&bar_in, 1);
+        mbar_init(&bar_am[0], 1);
+        mbar_init(&bar_am[1], 1);
+        mbar_init(&bar_uw, 1);
         mbar_fence_init();
-        mbar_expect_tx(&bar_in, 49152);
-        for (int kb = 0; kb < 2; ++kb) {
-            tma_load_2d(qs + kb * 8192, &mq, &bar_in, h * 128 + kb * 64, tok0);
-            tma_load_2d(ks + kb * 8192, &mk, &bar_in, h * 128 + kb * 64, tok0);
-            tma_load_2d(vs + kb * 8192, &mv, &bar_in, h * 128 + kb * 64, tok0);
-        }
+        mbar_expect_tx(&bar_in, 16384);
+        for (int kb = 0; kb < 2; ++kb) tma_load_2d(vs + kb * 8192, &mv, &bar_in, h * 128 + kb * 64, tok0);
     }
     if (warp == 1) tmem_alloc(&tmem_slot, 256);
 
-    // ---- cumulative log-decay of this thread's 16 rows (loads unconditional, row index clamped into the chunk)
+    // ---- loads: this thread's 4 rows x 8 channels of g, q, k (row index clamped into the chunk, values masked)
     const size_t rstride = (size_t)H * 128;
-    const size_t col = ((size_t)tok0 * H + h) * 128 + d;
-    float G[16];
-    {
+    const size_t base = ((size_t)tok0 * H + h) * 128 + 8 * cg;
+    float G[4][8];
+    uint4 qraw[4], kraw[4];
+    float brow[4];
 #pragma unroll
-        for (int r = 0; r < 16; ++r) G[r] = ld_io(p.g, col + (size_t)min(16 * I + r, len - 1) * rstride, p.gbf16);
-        float run = 0.f;
+    for (int j = 0; j < 4; ++j) {
+        const int i = 4 * rq + j, ic = min(i, len - 1);
+        ld8(p.g, base + (size_t)ic * rstride, GBF16, G[j]);
+        qraw[j] = __ldg(reinterpret_cast<const uint4*>(p.q + base + (size_t)ic * rstride));
+        kraw[j] = __ldg(reinterpret_cast<const uint4*>(p.k + base + (size_t)ic * rstride));
+        brow[j] = ld_io(p.beta, (size_t)(tok0 + ic) * H + h, GBF16);
+        if (i >= len) {
 #pragma unroll
-        for (int r = 0; r < 16; ++r) {
-            run += (16 * I + r < len) ? G[r] : 0.f;
-            G[r] = run;
+            for (int c = 0; c < 8; ++c) G[j][c] = 0.f;
+            qraw[j] = make_uint4(0, 0, 0, 0);
+            kraw[j] = make_uint4(0, 0, 0, 0);
+            brow[j] = 0.f;
         }
-        gsum[I * 128 + d] = run;
     }
-    if (tid < 64) {
-        const float b = tid < len ? ld_io(p.beta, (size_t)(tok0 + tid) * H + h, p.gbf16) : 0.f;
-        bet[tid] = b;
-        p.w.beta[ch * 64 + tid] = b;
+    // ---- cumulative log-decay: within the thread, across the two half-warps, then across warps through shared memory
+#pragma unroll
+    for (int j = 1; j < 4; ++j)
+#pragma unroll
+        for (int c = 0; c < 8; ++c) G[j][c] += G[j - 1][c];
+    float pre[8];      // sum of the rows of the other half-warp (added to the upper half's rows)
+#pragma unroll
+    for (int c = 0; c < 8; ++c) pre[c] = __shfl_xor_sync(0xffffffffu, G[3][c], 16);
+    if (lane < 16) {
+        float tot[8];
+#pragma unroll
+        for (int c = 0; c < 8; ++c) tot[c] = G[3][c] + pre[c];
+        sts8(wtot + warp * 128 + 8 * cg, tot);
+#pragma unroll
+        for (int c = 0; c < 8; ++c) pre[c] = 0.f;
+    }
+    // ---- inverse norms of this thread's rows: 16 lanes hold one row
+    float qi[4], ki[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        float fq[8], fk[8];
+        unpack_bf16x8(qraw[j], fq);
+        unpack_bf16x8(kraw[j], fk);
+        float sq = 0.f, sk = 0.f;
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+            sq += fq[c] * fq[c];
+            sk += fk[c] * fk[c];
+        }
+#pragma unroll
+        for (int o = 8; o > 0; o >>= 1) {
+            sq += __shfl_xor_sync(0xffffffffu, sq, o);
+            sk += __shfl_xor_sync(0xffffffffu, sk, o);
+        }
+        const bool valid = 4 * rq + j < len;
+        qi[j] = valid ? (p.l2norm ? rsqrtf(fmaxf(sq, 1e-24f)) : 1.0f) : 0.f;      // 1 / max(|q|, 1e-12)
+        ki[j] = valid ? (p.l2norm ? rsqrtf(fmaxf(sk, 1e-24f)) : 1.0f) : 0.f;
+        if (cg == 0) {
+            const int i = 4 * rq + j;
+            bet[i] = brow[j];
+            p.w.beta[ch * 64 + i] = brow[j];
+            p.w.qinv[ch * 64 + i] = qi[j];
+            p.w.kinv[ch * 64 + i] = ki[j];
+        }
+        qi[j] *= p.scale;
     }
     tc_fence_before();
-    __syncthreads();
+    __syncthreads();                                   // (1) warp sums, TMEM slot
     tc_fence_after();
     const uint32_t tmem = tmem_slot;
-    bool ok = mbar_wait(&bar_in, 0, p.t.status, 30);
-    KDA_TICK(1);
-    // ---- inverse norms: one thread per row (q rows on threads 0..63, k rows on 64..127)
-    if (tid < 128) {
-        const int r = tid & 63;
-        const uint8_t* tile = tid < 64 ? qs : ks;
-        float ss = 0.f;
-        if (r < len) {
+    {
+        float gend[8];
 #pragma unroll
-            for (int c = 0; c < 16; ++c) {
-                uint4 u = *reinterpret_cast<const uint4*>(tile + (c >> 3) * 8192 + sw128_off(r, c & 7));
-                const __nv_bfloat162* hh = reinterpret_cast<const __nv_bfloat162*>(&u);
+        for (int c = 0; c < 8; ++c) gend[c] = 0.f;
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    float2 f = __bfloat1622float2(hh[j]);
-                    ss += f.x * f.x + f.y * f.y;
+        for (int w2 = 0; w2 < 8; ++w2) {
+            float t[8];
+            lds8(wtot + w2 * 128 + 8 * cg, t);
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {
+                gend[c] += t[c];
+                pre[c] += (w2 < warp) ? t[c] : 0.f;
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+#pragma unroll
+            for (int c = 0; c < 8; ++c) G[j][c] += pre[c];
+        if ((rq & 3) == 0) sts8(cref + J * 128 + 8 * cg, G[0]);      // first row of block J
+        if (rq == 0) {
+            sts8(gends + 8 * cg, gend);
+            float e[8];
+#pragma unroll
+            for (int c = 0; c < 8; ++c) e[c] = __expf(gend[c]);
+            float* de = p.t.decay_end + ch * 128 + 8 * cg;
+            *reinterpret_cast<float4*>(de) = make_float4(e[0], e[1], e[2], e[3]);
+            *reinterpret_cast<float4*>(de + 4) = make_float4(e[4], e[5], e[6], e[7]);
+        }
+    }
+    __syncthreads();                                   // (2) block references; wtot is dead from here
+    // per (block, channel) factors, 512 + 384 entries over 256 threads
+    for (int e = tid; e < 512; e += kNT) {
+        const int I = e >> 7, d = e & 127;
+        const float c = cref[e];
+        eC[e] = __expf(c);
+        eEnd[e] = __expf(gends[d] - c);
+        if (I < 3) fbk[e] = __expf(cref[e + 128] - c);
+    }
+    __syncthreads();                                   // (3) tables
+
+    // ---- operand panels, one row at a time: 16-byte pieces of the swizzled layouts
+    {
+        float cJ[8];
+        lds8(cref + J * 128 + 8 * cg, cJ);
+        uint8_t* X = sm + kFX + (J >> 1) * 16384;
+        __nv_bfloat16* Eg = p.t.E + ch * 8192 + 8 * cg;
+        uint32_t rt[8][2];                             // R^T: channel c, rows 4rq .. 4rq+3 as two bf16 pairs
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int i = 4 * rq + j, r16 = i & 15;
+            float fq[8], fk[8], ec[8], ee[8], f0[8], o8[8];
+            unpack_bf16x8(qraw[j], fq);
+            unpack_bf16x8(kraw[j], fk);
+            lds8(eC + J * 128 + 8 * cg, ec);
+            lds8(eEnd + J * 128 + 8 * cg, ee);
+            float tq[8], inv[8];
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {
+                tq[c] = __expf(G[j][c] - cJ[c]);       // e^{G - c_J} in (0, 1]
+                inv[c] = fast_rcp(tq[c]);              // e^{c_J - G}
+                fq[c] *= qi[j];
+                fk[c] *= ki[j];
+            }
+            const int xr = (J & 1) * 32 + r16;
+#pragma unroll
+            for (int c = 0; c < 8; ++c) o8[c] = fq[c] * tq[c];
+            *reinterpret_cast<uint4*>(X + piece_off(xr, cg, 8192)) = pack8(o8);
+#pragma unroll
+            for (int c = 0; c < 8; ++c) o8[c] = fk[c] * tq[c];
+            *reinterpret_cast<uint4*>(X + piece_off(xr + 16, cg, 8192)) = pack8(o8);
+#pragma unroll
+            for (int c = 0; c < 8; ++c) f0[c] = fk[c] * inv[c];      // source row scaled to its own block
+            if (J <= 1) {                              // chain 0: target blocks 0, 1
+                if (J == 0) {
+                    *reinterpret_cast<uint4*>(Sst + piece_off(i, cg, 16384)) = pack8(f0);
+                    float fb[8];
+                    lds8(fbk + 8 * cg, fb);
+#pragma unroll
+                    for (int c = 0; c < 8; ++c) o8[c] = f0[c] * fb[c];
+                    *reinterpret_cast<uint4*>(Sst + piece_off(64 + i, cg, 16384)) = pack8(o8);
+                } else {
+                    *reinterpret_cast<uint4*>(Sst + piece_off(64 + i, cg, 16384)) = pack8(f0);
                 }
             }
-        } else if (tid < 64) {
-            // rows past a ragged tail hold other tokens: blank the value rows that feed the U product
+            // E = k e^{G_end - G} (global, token-major), Q = beta e^G k, R = q e^G
 #pragma unroll
-            for (int c = 0; c < 16; ++c)
-                *reinterpret_cast<uint4*>(vs + (c >> 3) * 8192 + sw128_off(r, c & 7)) = make_uint4(0, 0, 0, 0);
-        }
-        float inv = 0.f;
-        if (r < len) inv = p.l2norm ? 1.0f / fmaxf(sqrtf(ss), 1e-12f) : 1.0f;
-        if (tid < 64) {
-            qinv[r] = inv;
-            p.w.qinv[ch * 64 + r] = inv;
-        } else {
-            kinv[r] = inv;
-            p.w.kinv[ch * 64 + r] = inv;
-        }
-    }
-    float gend;
-    {
-        const float s0 = gsum[d], s1 = gsum[128 + d], s2 = gsum[256 + d], s3 = gsum[384 + d];
-        const float pre = I == 0 ? 0.f : (I == 1 ? s0 : (I == 2 ? s0 + s1 : s0 + s1 + s2));
-        gend = s0 + s1 + s2 + s3;
+            for (int c = 0; c < 8; ++c) o8[c] = f0[c] * ee[c];
+            *reinterpret_cast<uint4*>(Eg + (size_t)i * 128) = pack8(o8);
 #pragma unroll
-        for (int r = 0; r < 16; ++r) G[r] += pre;
-        cref[I * 128 + d] = G[0];
-        if (I == 0) p.t.decay_end[ch * 128 + d] = __expf(gend);
-    }
-    __syncthreads();
-    KDA_TICK(2);
-
-    // ---- operand panels for this thread's 16 rows of channel d
-    {
-        const float c0 = cref[d], c1 = cref[128 + d], c2 = cref[256 + d], c3 = cref[384 + d];
-        const float cI = I == 0 ? c0 : (I == 1 ? c1 : (I == 2 ? c2 : c3));
-        const float fb0 = __expf(c1 - c0), fb1 = __expf(c2 - c1), fb2 = __expf(c3 - c2);
-        uint8_t* X = (I < 2) ? X0 : X1;
-        uint32_t rt[8];
-#pragma unroll
-        for (int r = 0; r < 16; ++r) {
-            const int i = 16 * I + r;
-            float qv = 0.f, kv = 0.f;
-            if (i < len) {
-                qv = __bfloat162float(*reinterpret_cast<const __nv_bfloat16*>(qs + el_off(i, d, 8192)));
-                kv = __bfloat162float(*reinterpret_cast<const __nv_bfloat16*>(ks + el_off(i, d, 8192)));
+            for (int c = 0; c < 8; ++c) {
+                const float eg = tq[c] * ec[c];        // e^G
+                o8[c] = brow[j] * eg * fk[c];
+                const float r = fq[c] * eg;
+                if (j & 1) rt[c][j >> 1] = pack2(__uint_as_float(rt[c][j >> 1]), r);
+                else rt[c][j >> 1] = __float_as_uint(r);
             }
-            const float qn = qv * qinv[i] * p.scale, kn = kv * kinv[i];
-            const float gi = G[r];
-            const float eG = __expf(gi);
-            const float r_ = qn * eG;
-            if (r & 1) rt[r >> 1] = pack2(__uint_as_float(rt[r >> 1]), r_);
-            else rt[r >> 1] = __float_as_uint(r_);
-            p.t.E[ch * 8192 + i * 128 + d] = __float2bfloat16(kn * __expf(gend - gi));
-            st_bf16(Qs, el_off(i, d, 8192), bet[i] * eG * kn);
-            // decay-masked product operands: targets relative to their own 16-row block, sources to every later block
-            const float tq = __expf(gi - cI);
-            const int xr = (I & 1) * 32 + r;
-            st_bf16(X, el_off(xr, d, 8192), qn * tq);
-            st_bf16(X, el_off(xr + 16, d, 8192), kn * tq);
-            float f = kn * __expf(cI - gi);      // source row i scaled to its own block
-            float s0v = 0.f, s1v = 0.f, s2v = 0.f, s3v = 0.f;
-            if (I == 0) { s0v = f; f *= fb0; }
-            if (I <= 1) { s1v = f; f *= fb1; }
-            if (I <= 2) { s2v = f; f *= fb2; }
-            s3v = f;
-            st_bf16(S0, el_off(i, d, 16384), s0v);
-            st_bf16(S0, el_off(64 + i, d, 16384), s1v);
-            st_bf16(S1, el_off(i, d, 16384), s2v);
-            st_bf16(S1, el_off(64 + i, d, 16384), s3v);
+            *reinterpret_cast<uint4*>(Qs + piece_off(i, cg, 8192)) = pack8(o8);
         }
-        uint4* dst = reinterpret_cast<uint4*>(p.t.RT + ch * 8192 + (size_t)d * 64 + 16 * I);
-        dst[0] = make_uint4(rt[0], rt[1], rt[2], rt[3]);
-        dst[1] = make_uint4(rt[4], rt[5], rt[6], rt[7]);
+        __nv_bfloat16* Rg = p.t.RT + ch * 8192 + (size_t)(8 * cg) * 64 + 4 * rq;
+#pragma unroll
+        for (int c = 0; c < 8; ++c) *reinterpret_cast<uint2*>(Rg + c * 64) = make_uint2(rt[c][0], rt[c][1]);
     }
-    KDA_TICK(3);
     fence_async_smem();
     tc_fence_before();
-    __syncthreads();
-    if (tid == 0) {
+    __syncthreads();                                   // (4) chain-0 operands complete
+    auto issue_am = [&](int pr) {
         tc_fence_after();
         const uint32_t idesc = umma_idesc_bf16(128, 64, kMajorK, kMajorK);
+        const uint32_t a0 = smem_u32(Sst), b0 = smem_u32(sm + kFX + pr * 16384);
 #pragma unroll
-        for (int pr = 0; pr < 2; ++pr) {
-            const uint32_t a0 = smem_u32(pr ? S1 : S0), b0 = smem_u32(pr ? X1 : X0);
+        for (int k16 = 0; k16 < 8; ++k16)
+            umma_bf16_ss(tmem + pr * 64, umma_smem_desc_sw128(a0 + (k16 >> 2) * 16384 + (k16 & 3) * 32, 16, 1024),
+                         umma_smem_desc_sw128(b0 + (k16 >> 2) * 8192 + (k16 & 3) * 32, 16, 1024), idesc, k16 > 0);
+        umma_commit(&bar_am[pr]);
+    };
+    if (tid == 0) issue_am(0);
+    // ---- chain 1 (target blocks 2, 3): its source rows go into the same buffer once chain 0 has read it
+    bool ok = mbar_wait(&bar_am[0], 0, p.t.status, 31);
+    {
+        float c2[8];
+        lds8(cref + 2 * 128 + 8 * cg, c2);
+        float fb2[8];
+        lds8(fbk + 2 * 128 + 8 * cg, fb2);
 #pragma unroll
-            for (int k16 = 0; k16 < 8; ++k16)
-                umma_bf16_ss(tmem + pr * 64, umma_smem_desc_sw128(a0 + (k16 >> 2) * 16384 + (k16 & 3) * 32, 16, 1024),
-                             umma_smem_desc_sw128(b0 + (k16 >> 2) * 8192 + (k16 & 3) * 32, 16, 1024), idesc, k16 > 0);
-        }
-        umma_commit(&bar_am);
-    }
-    ok = mbar_wait(&bar_am, 0, p.t.status, 31) && ok;
-    ok = __syncthreads_and(ok);
-    tc_fence_after();
-    KDA_TICK(4);
-    if (ok) {
-        // ---- A^T panel, M~ panel and beta*M~ (fp32) from the two accumulators.  Lane = source row (two 64-row
-        // halves per chain); the four warp groups split chain x {A columns, M~ columns}.
-        {
-            const int m = (warp & 3) * 32 + lane;          // accumulator row
-            const int half = m >> 6, s = m & 63;
-            const int pr = I >> 1, sub = I & 1;            // chain, 0: A columns / 1: M~ columns
-            const int Ib = 2 * pr + half;                  // target block held in these columns
-            float t[16];
-            tmem_ld16f(tmem + lane_base + pr * 64 + 32 * half + 16 * sub, t);
-            if (sub == 0) {
-                uint32_t at[8];
+        for (int j = 0; j < 4; ++j) {
+            const int i = 4 * rq + j;
+            float fk[8], s2[8], s3[8];
+            unpack_bf16x8(kraw[j], fk);
+            if (J <= 2) {
+                // e^{c_2 - G} for rows of blocks 0..2 (for block 2 this is the own-block factor)
 #pragma unroll
-                for (int c = 0; c < 16; ++c) {
-                    const float a = (s <= 16 * Ib + c) ? t[c] : 0.f;
-                    if (c & 1) at[c >> 1] = pack2(__uint_as_float(at[c >> 1]), a);
-                    else at[c >> 1] = __float_as_uint(a);
+                for (int c = 0; c < 8; ++c) {
+                    s2[c] = fk[c] * ki[j] * __expf(c2[c] - G[j][c]);
+                    s3[c] = s2[c] * fb2[c];
                 }
-                uint4* dst = reinterpret_cast<uint4*>(p.t.AT + ch * 4096 + s * 64 + 16 * Ib);
-                dst[0] = make_uint4(at[0], at[1], at[2], at[3]);
-                dst[1] = make_uint4(at[4], at[5], at[6], at[7]);
+                *reinterpret_cast<uint4*>(Sst + piece_off(i, cg, 16384)) = pack8(s2);
             } else {
+                float c3[8];
+                lds8(cref + 3 * 128 + 8 * cg, c3);
 #pragma unroll
-                for (int c = 0; c < 16; ++c) {
-                    const int tt = 16 * Ib + c;
-                    const float mt = (s < tt) ? t[c] : 0.f;
-                    Ms[tt * kLDs + s] = bet[tt] * mt;
-                    if (!p.t.fwd_only) p.t.Mt[ch * 4096 + tt * 64 + s] = __float2bfloat16(mt);
-                }
+                for (int c = 0; c < 8; ++c) s3[c] = fk[c] * ki[j] * __expf(c3[c] - G[j][c]);
+            }
+            *reinterpret_cast<uint4*>(Sst + piece_off(64 + i, cg, 16384)) = pack8(s3);
+        }
+    }
+    fence_async_smem();
+    tc_fence_before();
+    ok = __syncthreads_and(ok);                        // (5) chain-1 operands complete
+    if (tid == 0 && ok) issue_am(1);
+    ok = mbar_wait(&bar_am[1], 0, p.t.status, 31) && ok;
+    ok = __syncthreads_and(ok);                        // (6) both accumulators complete, stacks dead
+    tc_fence_after();
+    if (ok) {
+        // ---- A^T panel, M~ panel and beta*M~ (fp32) from the two accumulators.  Lane = source row within a 64-row half;
+        // warps 0-3 read chain 0, warps 4-7 chain 1; 32 columns: 16 of A (q targets), 16 of M~ (k targets).
+        {
+            const int m = (warp & 3) * 32 + lane;
+            const int half = m >> 6, s = m & 63, pr = warp >> 2;
+            const int Ib = 2 * pr + half;              // target block held in these columns
+            uint32_t t[32];
+            tmem_ld32(tmem + lane_base + pr * 64 + 32 * half, t);
+            tmem_ld_wait();
+            uint32_t at[8];
+#pragma unroll
+            for (int c = 0; c < 16; c += 2) {
+                const float a0 = (s <= 16 * Ib + c) ? __uint_as_float(t[c]) : 0.f;
+                const float a1 = (s <= 16 * Ib + c + 1) ? __uint_as_float(t[c + 1]) : 0.f;
+                at[c >> 1] = pack2(a0, a1);
+            }
+            // both panels leave through shared memory (the T operands' region is still free) as one TMA store each
+            uint8_t* ATs = sm + kFTb;              // [64 s][64 i]  bf16, 128-byte swizzle
+            uint8_t* Mts = sm + kFTb + 8192;       // [64 tt][64 s]
+            *reinterpret_cast<uint4*>(ATs + sw128_off(s, 2 * Ib)) = make_uint4(at[0], at[1], at[2], at[3]);
+            *reinterpret_cast<uint4*>(ATs + sw128_off(s, 2 * Ib + 1)) = make_uint4(at[4], at[5], at[6], at[7]);
+#pragma unroll
+            for (int c = 0; c < 16; ++c) {
+                const int tt = 16 * Ib + c;
+                const float mt = (s < tt) ? __uint_as_float(t[16 + c]) : 0.f;
+                Ms[tt * kLDs + s] = bet[tt] * mt;
+                *reinterpret_cast<__nv_bfloat16*>(Mts + sw128_off(tt, s >> 3) + (s & 7) * 2) = __float2bfloat16(mt);
             }
         }
+        fence_async_smem();
         __syncthreads();
-        KDA_TICK(5);
+        if (tid == 0) {
+            tma_store_2d(&mAT, sm + kFTb, 0, (int)(ch * 64));
+            if (!p.t.fwd_only) tma_store_2d(&mMt, sm + kFTb + 8192, 0, (int)(ch * 64));
+            tma_store_commit();
+        }
         unit_lower_inverse(Ms, Ts, tmp);
-        KDA_TICK(6);
-        // ---- T: bf16 K-major B operands (plain and column-scaled by beta) and the bf16 panel; one 16-byte chunk each
+        if (tid == 0) tma_store_wait_read();       // the staging region becomes the T operands below
+        __syncthreads();
+        // ---- T: bf16 K-major B operands (plain and column-scaled by beta) and the bf16 panel; 32 bytes of a row each
         {
-            const int i = tid >> 3, c16 = tid & 7;
-            const float* src = Ts + i * kLDs + 8 * c16;
-            const float* bb = bet + 8 * c16;
-            uint4 u = make_uint4(pack2(src[0], src[1]), pack2(src[2], src[3]), pack2(src[4], src[5]), pack2(src[6], src[7]));
-            *reinterpret_cast<uint4*>(Tb + sw128_off(i, c16)) = u;
-            if (!p.t.fwd_only) *reinterpret_cast<uint4*>(p.t.Tp + ch * 4096 + i * 64 + 8 * c16) = u;
-            *reinterpret_cast<uint4*>(Tbb + sw128_off(i, c16)) =
-                make_uint4(pack2(src[0] * bb[0], src[1] * bb[1]), pack2(src[2] * bb[2], src[3] * bb[3]),
-                           pack2(src[4] * bb[4], src[5] * bb[5]), pack2(src[6] * bb[6], src[7] * bb[7]));
+            const int i = tid >> 2, seg = tid & 3;
+            const float* src = Ts + i * kLDs + 16 * seg;
+            const float* bb = bet + 16 * seg;
+#pragma unroll
+            for (int hh = 0; hh < 2; ++hh) {
+                float x[8], b8[8];
+                lds8(src + 8 * hh, x);
+                lds8(bb + 8 * hh, b8);
+                const uint4 u = pack8(x);
+                *reinterpret_cast<uint4*>(Tb + sw128_off(i, 2 * seg + hh)) = u;
+                if (!p.t.fwd_only) *reinterpret_cast<uint4*>(p.t.Tp + ch * 4096 + i * 64 + 16 * seg + 8 * hh) = u;
+#pragma unroll
+                for (int c = 0; c < 8; ++c) x[c] *= b8[c];
+                *reinterpret_cast<uint4*>(Tbb + sw128_off(i, 2 * seg + hh)) = pack8(x);
+            }
+        }
+        // the value tile: wait for it, blank the rows past a ragged tail (they hold other tokens)
+        ok = mbar_wait(&bar_in, 0, p.t.status, 30);
+        if (len < 64 && ok) {
+            for (int idx = tid; idx < (64 - len) * 16; idx += kNT) {
+                const int r = len + (idx >> 4), c = idx & 15;
+                *reinterpret_cast<uint4*>(vs + (c >> 3) * 8192 + sw128_off(r, c & 7)) = make_uint4(0, 0, 0, 0);
+            }
         }
         fence_async_smem();
         tc_fence_before();
-        __syncthreads();
-        if (tid == 0) {
+        ok = __syncthreads_and(ok);
+        if (tid == 0 && ok) {
             tc_fence_after();
             const uint32_t idesc = umma_idesc_bf16(128, 64, kMajorMN, kMajorK);
             const uint32_t b0 = smem_u32(Tb), b1 = smem_u32(Tbb);
@@ -426,34 +567,41 @@ __global__ void __launch_bounds__(kNT, 1)
                              umma_smem_desc_sw128(b0 + k16 * 32, 16, 1024), idesc, k16 > 0);
             umma_commit(&bar_uw);
         }
-        KDA_TICK(7);
-        ok = mbar_wait(&bar_uw, 0, p.t.status, 32);
-        ok = __syncthreads_and(ok);
+        if (ok) ok = mbar_wait(&bar_uw, 0, p.t.status, 32);
         tc_fence_after();
-        KDA_TICK(8);
         if (ok) {
-            // lane = value channel (U^T) / key channel (W^T); warp groups split {U, W} x {tokens 0..31, 32..63}
-            const int which = I >> 1, hb = I & 1;
-            __nv_bfloat16* base = (which ? p.t.WT : p.t.UT) + ch * 8192 + (size_t)d * 64 + hb * 32;
-            uint32_t r[32];
-            tmem_ld32(tmem + lane_base + 128 + which * 64 + hb * 32, r);
-            tmem_ld_wait();
-            uint4* dst = reinterpret_cast<uint4*>(base);
+            // lane = value channel (U^T, warps 0-3) / key channel (W^T, warps 4-7): one 128-byte panel row per thread,
+            // staged in the swizzled layout (the inverse's scratch is dead) and stored by TMA, 16 KB per panel
+            const int which = warp >> 2;
+            const int d = (warp & 3) * 32 + lane;
+            uint8_t* stg = sm + which * 16384;
 #pragma unroll
-            for (int c = 0; c < 4; ++c)
-                dst[c] = make_uint4(pack2(__uint_as_float(r[8 * c]), __uint_as_float(r[8 * c + 1])),
-                                    pack2(__uint_as_float(r[8 * c + 2]), __uint_as_float(r[8 * c + 3])),
-                                    pack2(__uint_as_float(r[8 * c + 4]), __uint_as_float(r[8 * c + 5])),
-                                    pack2(__uint_as_float(r[8 * c + 6]), __uint_as_float(r[8 * c + 7])));
+            for (int hb = 0; hb < 2; ++hb) {
+                uint32_t r[32];
+                tmem_ld32(tmem + lane_base + 128 + which * 64 + hb * 32, r);
+                tmem_ld_wait();
+#pragma unroll
+                for (int c = 0; c < 4; ++c)
+                    *reinterpret_cast<uint4*>(stg + sw128_off(d, 4 * hb + c)) =
+                        make_uint4(pack2(__uint_as_float(r[8 * c]), __uint_as_float(r[8 * c + 1])),
+                                   pack2(__uint_as_float(r[8 * c + 2]), __uint_as_float(r[8 * c + 3])),
+                                   pack2(__uint_as_float(r[8 * c + 4]), __uint_as_float(r[8 * c + 5])),
+                                   pack2(__uint_as_float(r[8 * c + 6]), __uint_as_float(r[8 * c + 7])));
+            }
         }
+        fence_async_smem();
+        ok = __syncthreads_and(ok);
+        if (tid == 0 && ok) {
+            tma_store_2d(&mUT, sm, 0, (int)(ch * 128));
+            tma_store_2d(&mWT, sm + 16384, 0, (int)(ch * 128));
+            tma_store_commit();
+            tma_store_wait_read();                 // shared memory must outlive the reads of the bulk stores
+        }
+    } else {
+        // unwinding: the value tile must have landed before the block may exit
+        mbar_wait(&bar_in, 0, nullptr, 0);
+        if (tid == 0) tma_store_wait_read();
     }
-    KDA_TICK(9);
-#ifdef KDA_PHASE_TIMING
-    if (threadIdx.x == 0 && blockIdx.y == 0 && (blockIdx.x == 0 || blockIdx.x == 100))
-        printf("intra_fwd blk %d: g+tma %lld | norms %lld | panels %lld | mma_am %lld | readout %lld | inverse %lld | T+issue %lld | mma_uw %lld | epilogue %lld | total %lld\n",
-               blockIdx.x, tick[1] - tick[0], tick[2] - tick[1], tick[3] - tick[2], tick[4] - tick[3], tick[5] - tick[4],
-               tick[6] - tick[5], tick[7] - tick[6], tick[8] - tick[7], tick[9] - tick[8], tick[9] - tick[0]);
-#endif
     tc_fence_before();
     __syncthreads();
     if (warp == 1) tmem_dealloc(tmem, 256);
@@ -467,17 +615,18 @@ int tc_intra_forward(const simt::Ws& w, const tc::TcWs& t, const void* q, const 
     IntraFwdArgs a;
     a.chunk_tok0 = w.chunk_tok0; a.chunk_len = w.chunk_len;
     a.q = static_cast<const __nv_bfloat16*>(q); a.k = static_cast<const __nv_bfloat16*>(k);
-    a.v = static_cast<const __nv_bfloat16*>(v);
     a.g = g; a.beta = beta; a.gbf16 = gbf16; a.l2norm = l2norm; a.H = w.H; a.scale = scale; a.t = t; a.w = w;
-    CUtensorMap mq, mk, mv;
-    if (make_map_bf16(&mq, q, (uint64_t)tokens, (uint64_t)w.H * 128, 64, 64) ||
-        make_map_bf16(&mk, k, (uint64_t)tokens, (uint64_t)w.H * 128, 64, 64) ||
-        make_map_bf16(&mv, v, (uint64_t)tokens, (uint64_t)w.H * 128, 64, 64))
-        return KDA_ERR_CUDA;
-    if (cudaFuncSetAttribute(tc_intra_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kIntraFwdSmem) != cudaSuccess)
-        return KDA_ERR_CUDA;
-    KDA_LAUNCH("tc_intra_fwd_kernel", st,
-               tc_intra_fwd_kernel<<<dim3(w.nslots, w.H), kNT, kIntraFwdSmem, st>>>(mq, mk, mv, a));
+    const uint64_t nch = (uint64_t)w.nslots * w.H;
+    CUtensorMap mv, mUT, mWT, mAT, mMt;
+    int rc = make_map_bf16(&mv, v, (uint64_t)tokens, (uint64_t)w.H * 128, 64, 64);
+    rc |= make_map_bf16(&mUT, t.UT, nch * 128, 64, 64, 128);
+    rc |= make_map_bf16(&mWT, t.WT, nch * 128, 64, 64, 128);
+    rc |= make_map_bf16(&mAT, t.AT, nch * 64, 64, 64, 64);
+    rc |= make_map_bf16(&mMt, t.fwd_only ? t.AT : t.Mt, nch * 64, 64, 64, 64);      // not stored in a forward-only call
+    if (rc) return KDA_ERR_CUDA;
+    auto kern = gbf16 ? tc_intra_fwd_kernel<true> : tc_intra_fwd_kernel<false>;
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kIntraFwdSmem) != cudaSuccess) return KDA_ERR_CUDA;
+    KDA_LAUNCH("tc_intra_fwd_kernel", st, kern<<<dim3(w.nslots, w.H), kNT, kIntraFwdSmem, st>>>(mv, mUT, mWT, mAT, mMt, a));
     return launch_status();
 }
 
