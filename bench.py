@@ -308,14 +308,19 @@ def main():
     ap.add_argument("--no-graph", action="store_true", help="launch every step eagerly instead of replaying a CUDA graph")
     ap.add_argument("--no-sharded", action="store_true", help="skip the config-3 / config-4 sharded workloads attached to the line")
     ap.add_argument("--tokens", type=int, default=8 * 8192, help="packed tokens of the varlen workload")
-    ap.add_argument("--workload", default="chain", choices=["chain", "varlen", "decode", "pointwise"],
-                    help="chain = config 1 (default, the driver's line); varlen = config 3; decode = config 4; pointwise = conv / gated RMSNorm at 256 MiB tensors")
+    ap.add_argument("--workload", default="chain", choices=["chain", "varlen", "decode", "pointwise", "train"],
+                    help="chain = config 1 (default, the driver's line); varlen = config 3; decode = config 4; pointwise = conv / gated RMSNorm at 256 MiB tensors; "
+                         "train = config 2 (the reference's GPT + MuonAdamW step on these kernels)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
     if args.impl == "reference":
         run_reference(args, rank, world)
+        return
+    if args.workload == "train":
+        import bench_train
+        bench_train.run(args, rank, world, local)
         return
     if args.workload != "chain":
         import bench_extra
