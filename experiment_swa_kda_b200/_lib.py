@@ -39,6 +39,8 @@ _SIGNATURES = {
     "kda_gate_bwd_scratch_bytes": (C.c_size_t, [C.c_int32] * 3),
     "kda_gate_bwd": (C.c_int, [C.c_int32] * 4 + [_P] * 4 + [C.c_float] + [_P] * 7 + [C.c_size_t, _P]),
     "kda_decode_step": (C.c_int, [C.c_int32] * 7 + [C.c_float] + [_P] * 9),
+    "kda_decode_step_raw": (C.c_int, [C.c_int32] * 5 + [C.c_float] + [_P] * 7 + [C.c_float] + [_P] * 4),
+    "kda_conv_step_multi": (C.c_int, [C.c_int32] * 6 + [_P] * 5),
     "kda_decode_steps": (C.c_int, [C.c_int32] * 8 + [C.c_float] + [_P] * 8),
     "kda_conv_fwd": (C.c_int, [C.c_int32] * 6 + [_P] * 6),
     "kda_conv_bwd_scratch_bytes": (C.c_size_t, [C.c_int32] * 4),

@@ -113,12 +113,20 @@ __global__ void gate_bwd_reduce_kernel(int nblk, int H, int K, const float* __re
 // NV4 > 0: K % 4 == 0, lane owns NV4 float4 of a row (keys 128*j + 4*lane + 0..3); NV4 == 0: scalar layout,
 // lane owns keys lane + 32*e.  R rows are kept in flight per warp; every load is issued unconditionally
 // (addresses clamped, values masked) so the loads of a row group overlap.
+// When raw.A_log is set, g and beta hold the raw gate logits and beta logits instead and are activated here
+// (g = lb * sigmoid(exp(A_log[h]) * (raw + dt_bias[h,k])), beta = sigmoid(logit)): one launch less per token and layer.
+struct RawGate {
+    const float* A_log;      // [H], or nullptr: g and beta are already activated
+    const float* dt_bias;    // [H*K]
+    float lb;
+};
+
 template <int NV4, int R>
 __global__ void __launch_bounds__(256) decode_kernel(int H, int K, int V, int bf16, int gbf16, int l2norm, float scale,
                                                      const void* __restrict__ q, const void* __restrict__ k,
                                                      const void* __restrict__ v, const void* __restrict__ g,
                                                      const void* __restrict__ beta, const float* s_in, float* s_out,
-                                                     void* __restrict__ o, int rows_per_cta) {
+                                                     void* __restrict__ o, int rows_per_cta, RawGate raw) {
     constexpr int NE = NV4 > 0 ? 4 * NV4 : 8;     // state elements per lane per row
     const int bh = blockIdx.x;                    // sequence * H + head
     const int v_base = blockIdx.y * rows_per_cta;
@@ -157,7 +165,15 @@ __global__ void __launch_bounds__(256) decode_kernel(int H, int K, int V, int bf
         ke[e] = ld_io(k, i, bf16);
         dec[e] = ld_io(g, i, gbf16);
     }
-    const float bt = ld_io(beta, bh, gbf16);
+    float bt = ld_io(beta, bh, gbf16);
+    if (raw.A_log != nullptr) {
+        const int hh = bh % H;
+        const float ea = expf(raw.A_log[hh]);
+        bt = sigmoidf_(bt);
+#pragma unroll
+        for (int e = 0; e < NE; ++e)
+            dec[e] = raw.lb * sigmoidf_(ea * (dec[e] + raw.dt_bias[hh * K + min(key_of(e), K - 1)]));
+    }
     float sq = 0.f, sk = 0.f;
 #pragma unroll
     for (int e = 0; e < NE; ++e) {
@@ -403,6 +419,35 @@ __global__ void __launch_bounds__(256) conv_fwd_kernel(int B, int T, int C, int 
             for (int e = 0; e < VEC; ++e) st_io(fin, ((size_t)b * C + c0 + e) * W + j, BF16, tmp[e]);
         }
     }
+}
+
+// One decode token through n same-shaped convolutions (the q, k and v branches of a layer) in ONE launch: every cache
+// row [W] is shifted by one, the new input appended, y = act(w . row) - the cache is updated IN PLACE.  Same arithmetic
+// order as conv_fwd_kernel, so the result equals the non-mutating call bit for bit.
+struct ConvStepItems {
+    const void* x[4];
+    const void* w[4];
+    void* cache[4];
+    void* y[4];
+};
+
+template <int W, bool BF16>
+__global__ void __launch_bounds__(256) conv_step_kernel(int B, int C, int silu, int wf32, ConvStepItems items) {
+    const int item = blockIdx.y;
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;      // b * C + c
+    if (idx >= (size_t)B * C) return;
+    const int c = (int)(idx % C);
+    void* cache = items.cache[item];
+    float xx[W];
+#pragma unroll
+    for (int j = 0; j + 1 < W; ++j) xx[j] = ld_io(cache, idx * W + j + 1, BF16);
+    xx[W - 1] = ld_io(items.x[item], idx, BF16);
+    float z = 0.f;
+#pragma unroll
+    for (int j = 0; j < W; ++j) z += ld_w(items.w[item], (size_t)c * W + j, BF16, wf32) * xx[j];
+    st_io(items.y[item], idx, BF16, silu ? z * sigmoid_t<BF16>(z) : z);
+#pragma unroll
+    for (int j = 0; j < W; ++j) st_io(cache, idx * W + j, BF16, xx[j]);
 }
 
 // Forward without a carried-in window and without a final-state output (the training path).  Lane = channel pair, so
@@ -1268,7 +1313,7 @@ extern "C" int kda_gate_bwd(int32_t tokens, int32_t heads, int32_t key_dim, int3
 
 static int decode_launch(int n_seq, int heads, int key_dim, int value_dim, int bf16, int gbf16, int l2norm, float scale, const void* q,
                          const void* k, const void* v, const void* g, const void* beta, const float* state_in, float* state_out,
-                         void* o, cudaStream_t st) {
+                         void* o, cudaStream_t st, pw::RawGate raw = pw::RawGate{nullptr, nullptr, 0.f}) {
     // four rows in flight per warp: at ~70 registers three to four CTAs share an SM, so one CTA's prologue (norms, decay) hides
     // under the others' streaming; eight rows per warp measured 20 % slower
     // one CTA per (sequence, head) once there are enough of them to fill the GPU; otherwise split the value rows
@@ -1277,12 +1322,25 @@ static int decode_launch(int n_seq, int heads, int key_dim, int value_dim, int b
     const bool vec = (key_dim % 4 == 0) &&
                      ((reinterpret_cast<uintptr_t>(state_in) | reinterpret_cast<uintptr_t>(state_out)) % 16 == 0);
     if (vec && key_dim <= 128)
-        KDA_LAUNCH("decode_kernel", st, pw::decode_kernel<1, 4><<<grid, 256, 0, st>>>(heads, key_dim, value_dim, bf16, gbf16, l2norm, scale, q, k, v, g, beta, state_in, state_out, o, rows_per_cta));
+        KDA_LAUNCH("decode_kernel", st, pw::decode_kernel<1, 4><<<grid, 256, 0, st>>>(heads, key_dim, value_dim, bf16, gbf16, l2norm, scale, q, k, v, g, beta, state_in, state_out, o, rows_per_cta, raw));
     else if (vec)
-        KDA_LAUNCH("decode_kernel", st, pw::decode_kernel<2, 4><<<grid, 256, 0, st>>>(heads, key_dim, value_dim, bf16, gbf16, l2norm, scale, q, k, v, g, beta, state_in, state_out, o, rows_per_cta));
+        KDA_LAUNCH("decode_kernel", st, pw::decode_kernel<2, 4><<<grid, 256, 0, st>>>(heads, key_dim, value_dim, bf16, gbf16, l2norm, scale, q, k, v, g, beta, state_in, state_out, o, rows_per_cta, raw));
     else
-        KDA_LAUNCH("decode_kernel", st, pw::decode_kernel<0, 4><<<grid, 256, 0, st>>>(heads, key_dim, value_dim, bf16, gbf16, l2norm, scale, q, k, v, g, beta, state_in, state_out, o, rows_per_cta));
+        KDA_LAUNCH("decode_kernel", st, pw::decode_kernel<0, 4><<<grid, 256, 0, st>>>(heads, key_dim, value_dim, bf16, gbf16, l2norm, scale, q, k, v, g, beta, state_in, state_out, o, rows_per_cta, raw));
     return launch_status();
+}
+
+extern "C" int kda_decode_step_raw(int32_t n_seq, int32_t heads, int32_t key_dim, int32_t value_dim, int32_t io_dtype, float scale,
+                                   const void* q, const void* k, const void* v, const void* raw_gate, const void* beta_logits,
+                                   const float* A_log, const float* dt_bias, float lower_bound, const float* state_in,
+                                   float* state_out, void* o, void* stream) {
+    if (n_seq < 0 || heads <= 0 || key_dim <= 0 || value_dim <= 0 || key_dim > KDA_MAX_DIM || value_dim > KDA_MAX_DIM)
+        return KDA_ERR_BAD_SHAPE;
+    if (n_seq == 0) return KDA_OK;
+    if (!q || !k || !v || !raw_gate || !beta_logits || !A_log || !dt_bias || !state_in || !state_out || !o) return KDA_ERR_NULL;
+    const int bf16 = io_dtype == KDA_DTYPE_BF16;
+    return decode_launch(n_seq, heads, key_dim, value_dim, bf16, bf16, 1, scale, q, k, v, raw_gate, beta_logits, state_in, state_out, o,
+                         (cudaStream_t)stream, pw::RawGate{A_log, dt_bias, lower_bound});
 }
 
 extern "C" int kda_decode_step(int32_t n_seq, int32_t heads, int32_t key_dim, int32_t value_dim, int32_t io_dtype,
@@ -1502,6 +1560,35 @@ extern "C" int kda_conv_fwd_multi(int32_t n_items, int32_t batch, int32_t seq_le
         case 3: return conv_fwd_fast<3>(n_items, batch, seq_len, channels, bf16, wf32, silu, it, st);
         default: return conv_fwd_fast<4>(n_items, batch, seq_len, channels, bf16, wf32, silu, it, st);
     }
+}
+
+extern "C" int kda_conv_step_multi(int32_t n_items, int32_t batch, int32_t channels, int32_t width, int32_t io_dtype, int32_t silu,
+                                   const void* const* x, const void* const* weight, void* const* cache, void* const* y, void* stream) {
+    if (n_items < 1 || n_items > 4 || batch <= 0 || channels <= 0) return KDA_ERR_BAD_SHAPE;
+    if (width < 1 || width > 4) return KDA_ERR_UNSUPPORTED;
+    if (!x || !weight || !cache || !y) return KDA_ERR_NULL;
+    const int wf32 = (io_dtype & KDA_WEIGHT_F32) != 0;
+    const int bf16 = (io_dtype & 0xff) == KDA_DTYPE_BF16;
+    pw::ConvStepItems it = {};
+    for (int i = 0; i < n_items; ++i) {
+        if (!x[i] || !weight[i] || !cache[i] || !y[i]) return KDA_ERR_NULL;
+        it.x[i] = x[i]; it.w[i] = weight[i]; it.cache[i] = cache[i]; it.y[i] = y[i];
+    }
+    cudaStream_t st = (cudaStream_t)stream;
+    const dim3 grid(ceil_div(batch * channels, 256), n_items);
+#define KDA_CONV_STEP(WW)                                                                                                          \
+    do {                                                                                                                           \
+        if (bf16) KDA_LAUNCH("conv_step_kernel", st, pw::conv_step_kernel<WW, true><<<grid, 256, 0, st>>>(batch, channels, silu, wf32, it)); \
+        else KDA_LAUNCH("conv_step_kernel", st, pw::conv_step_kernel<WW, false><<<grid, 256, 0, st>>>(batch, channels, silu, wf32, it));     \
+    } while (0)
+    switch (width) {
+        case 1: KDA_CONV_STEP(1); break;
+        case 2: KDA_CONV_STEP(2); break;
+        case 3: KDA_CONV_STEP(3); break;
+        default: KDA_CONV_STEP(4); break;
+    }
+#undef KDA_CONV_STEP
+    return launch_status();
 }
 
 extern "C" size_t kda_conv_bwd_multi_scratch_bytes(int32_t n_items, int32_t batch, int32_t seq_len, int32_t channels, int32_t width) {

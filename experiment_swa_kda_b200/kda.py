@@ -37,6 +37,16 @@ class KDAState:
     k_conv: Tensor
     v_conv: Tensor
 
+    @staticmethod
+    def zeros(batch: int, num_heads: int, head_dim: int, conv_size: int, device, dtype=torch.bfloat16) -> "KDAState":
+        """An empty state a serving loop can own and hand to `KimiDeltaAttention.decode_token`, which updates it in place."""
+        hid = num_heads * head_dim
+        conv = lambda: torch.zeros(batch, hid, conv_size, device=device, dtype=dtype)
+        return KDAState(torch.zeros(batch, num_heads, head_dim, head_dim, device=device, dtype=torch.float32), conv(), conv(), conv())
+
+    def clone(self) -> "KDAState":
+        return KDAState(self.memory.clone(), self.q_conv.clone(), self.k_conv.clone(), self.v_conv.clone())
+
 
 def prepare_kda_backend(backend: str = "project_cuda") -> None:
     """Build (if stale) and load the CUDA library; fail early when it is unavailable."""
@@ -375,6 +385,33 @@ class KimiDeltaAttention(nn.Module):
         output = self.o_proj(mixed.reshape(batch, length, self.hidden_size))
         final_state = KDAState(final_memory, q_final, k_final, v_final) if want_state else None
         return output, final_state
+
+    @torch.no_grad()
+    def decode_token(self, hidden_states: Tensor, state: KDAState) -> Tensor:
+        """One decode token with the state updated IN PLACE (inference only).
+
+        The non-mutating contract of `forward(..., state, output_final_state=True, mode="project_recurrent")` costs a
+        serving loop six library launches and four freshly allocated state tensors per layer and token (the reference's
+        cache plumbing: nanochat/engine.py:83-226, get/set_kda_state :160-170).  Here the caller owns one `KDAState`
+        (see `KDAState.zeros`); the three convolution caches are advanced by one fused launch, the gate and beta
+        activations run inside the decode kernel, and the memory is rewritten where it lies: three library launches, no
+        state allocation.  Same arithmetic, same results as the non-mutating path."""
+        if hidden_states.ndim != 3 or hidden_states.shape[1] != 1 or hidden_states.shape[-1] != self.hidden_size:
+            raise ValueError(f"hidden_states must have shape [B,1,{self.hidden_size}]")
+        if not hidden_states.is_cuda:
+            raise RuntimeError("project CUDA KDA backend unavailable: project KDA requires CUDA")
+        batch = hidden_states.shape[0]
+        x = hidden_states
+        conv_w = [c.weight.squeeze(1) for c in (self.q_conv1d, self.k_conv1d, self.v_conv1d)]
+        q, k, v = ops.conv_step_multi((self.q_proj(x), self.k_proj(x), self.v_proj(x)), conv_w,
+                                      (state.q_conv, state.k_conv, state.v_conv))
+        shape4 = (batch, 1, self.num_heads, self.head_dim)
+        raw_gate = self.f_b_proj(self.f_a_proj(x)).reshape(shape4)
+        beta_logits = self.b_proj(x)
+        o, _ = ops.decode_step_raw(q.reshape(shape4), k.reshape(shape4), v.reshape(shape4), raw_gate, beta_logits, self.A_log,
+                                   self.dt_bias, self.lower_bound, state.memory, self.head_dim ** -0.5, out_state=state.memory)
+        mixed = self.o_norm(o, self.g_proj(x).reshape(shape4))
+        return self.o_proj(mixed.reshape(batch, 1, self.hidden_size))
 
 
 __all__ = ["KDAState", "KimiDeltaAttention", "RMSNormGated", "ShortConvolution", "chunk_kda", "k3_decay_gate", "kda",

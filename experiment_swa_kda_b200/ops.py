@@ -270,6 +270,52 @@ def decode_step(q, k, v, g, beta, state, scale, l2norm=True, out_state: Optional
     return o, new_state
 
 
+def decode_step_raw(q, k, v, raw_gate, beta_logits, A_log, dt_bias, lower_bound, state, scale, out_state: Optional[Tensor] = None):
+    """One decode token on RAW inputs (gate and beta activations fused into the kernel, q and k L2-normalised): the
+    signature of the reference's recurrent_decode operator in a single launch.  `out_state` may be `state` itself."""
+    lib = _lib.load()
+    dev = _need_cuda(q, k, v, raw_gate, beta_logits, A_log, dt_bias, state)
+    q, k, v, raw_gate, beta_logits = (t.contiguous() for t in (q, k, v, raw_gate, beta_logits))
+    if not (q.dtype == k.dtype == v.dtype == raw_gate.dtype == beta_logits.dtype):
+        raise RuntimeError("decode_step_raw takes q, k, v, raw_gate and beta_logits in one dtype")
+    H, K = q.shape[-2], q.shape[-1]
+    V = v.shape[-1]
+    n = q.numel() // (H * K)
+    if state.dtype != torch.float32 or not state.is_contiguous() or tuple(state.shape) != (n, H, V, K):
+        raise ValueError(f"state must be contiguous float32 V-first [B, H, V, K] with shape {(n, H, V, K)}")
+    if A_log.dtype != torch.float32 or dt_bias.dtype != torch.float32 or A_log.numel() != H or dt_bias.numel() != H * K:
+        raise ValueError("A_log [H] and dt_bias [H*K] must be float32")
+    new_state = torch.empty_like(state) if out_state is None else out_state
+    o = torch.empty_like(v)
+    with torch.cuda.device(dev):
+        rc = lib.kda_decode_step_raw(n, H, K, V, _dt(q), float(scale), _ptr(q), _ptr(k), _ptr(v), _ptr(raw_gate), _ptr(beta_logits),
+                                     _ptr(A_log.contiguous()), _ptr(dt_bias.contiguous()), float(lower_bound), _ptr(state),
+                                     _ptr(new_state), _ptr(o), _stream(dev))
+    _lib.check(rc, "kda_decode_step_raw")
+    return o, new_state
+
+
+def conv_step_multi(xs, weights, caches, silu=True):
+    """One decode token through several same-shaped convolutions in one launch; `caches` ([B,C,W] each) are updated IN
+    PLACE.  xs: [B,C] (or [B,1,C]) tensors.  Returns the outputs, shaped like xs."""
+    import ctypes as C
+    lib = _lib.load()
+    xs = [x.contiguous() for x in xs]
+    ws = [w.contiguous() for w in weights]
+    dev = _need_cuda(*xs, *ws, *caches)
+    Bn, Cc, W = caches[0].shape
+    for x, w, c in zip(xs, ws, caches):
+        if x.numel() != Bn * Cc or tuple(c.shape) != (Bn, Cc, W) or tuple(w.shape) != (Cc, W) or not c.is_contiguous() or c.dtype != x.dtype:
+            raise ValueError("conv_step_multi needs x [B,C], weight [C,W] and a contiguous cache [B,C,W] of the activation dtype per branch")
+    ys = [torch.empty_like(x) for x in xs]
+    with torch.cuda.device(dev):
+        rc = lib.kda_conv_step_multi(len(xs), Bn, Cc, W, _dt(xs[0]) | _wflag(xs[0], ws[0]), 1 if silu else 0,
+                                     C.cast(_ptr_array(xs), C.c_void_p), C.cast(_ptr_array(ws), C.c_void_p),
+                                     C.cast(_ptr_array(caches), C.c_void_p), C.cast(_ptr_array(ys), C.c_void_p), _stream(dev))
+    _lib.check(rc, "kda_conv_step_multi")
+    return ys
+
+
 def decode_steps(q, k, v, g, beta, state, scale, l2norm=True):
     """n consecutive decode steps in one library call.  q,k,g [n,B,H,K]; v [n,B,H,V]; beta [n,B,H]; `state` [B,H,V,K]
     float32 is UPDATED IN PLACE.  Returns o [n,B,H,V].  One kernel launch per step, issued from C without a host round

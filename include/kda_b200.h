@@ -141,6 +141,15 @@ int kda_decode_step(int32_t n_seq, int32_t heads, int32_t key_dim, int32_t value
                     int32_t gate_dtype, int32_t l2norm, float scale, const void* q, const void* k, const void* v, const void* g, const void* beta,
                     const float* state_in, float* state_out, void* o, void* stream);
 
+/* The decode step on RAW inputs: raw_gate [n_seq,H,K] and beta_logits [n_seq,H] (io_dtype) are activated inside the
+ * kernel (g = lower_bound * sigmoid(exp(A_log[h]) * (raw + dt_bias[h,k])), beta = sigmoid(logit)), which is exactly
+ * nanochat_kda::recurrent_decode's signature (reference recurrent_decode.cu:96-181) in one launch instead of two.
+ * q and k are L2-normalised.  state_out may alias state_in. */
+int kda_decode_step_raw(int32_t n_seq, int32_t heads, int32_t key_dim, int32_t value_dim, int32_t io_dtype, float scale,
+                        const void* q, const void* k, const void* v, const void* raw_gate, const void* beta_logits,
+                        const float* A_log, const float* dt_bias, float lower_bound, const float* state_in, float* state_out,
+                        void* o, void* stream);
+
 /* n_steps consecutive decode steps in one call: step i reads q,k,g [n_steps,n_seq,H,K], v [n_steps,n_seq,H,V],
  * beta [n_steps,n_seq,H] at index i, updates `state` in place and writes o[i].  One kernel launch per step (the state
  * crosses HBM once each way per step, exactly as n_steps calls of kda_decode_step would), without a host round trip
@@ -173,6 +182,13 @@ int kda_conv_bwd(int32_t batch, int32_t seq_len, int32_t channels, int32_t width
  * any other case returns KDA_ERR_UNSUPPORTED and the caller issues the per-tensor calls.  x, weight, y, d_y, dx, dweight
  * are HOST arrays of n_items device pointers; io_dtype may carry KDA_WEIGHT_F32.  scratch:
  * kda_conv_bwd_multi_scratch_bytes. */
+/* One decode token through n_items (1..4) same-shaped convolutions in ONE launch, caches updated IN PLACE: for every
+ * (batch, channel) the cache row [W] drops its oldest value, takes x (x, y [batch, channels]) and y = act(w . row).
+ * The reference's decode path makes three non-mutating operator calls per layer and token, each allocating a new cache
+ * (nanochat/mixers/kda.py:758-766, nanochat/engine.py:160-170); this is the opt-in in-place form for a serving loop that
+ * owns its state.  width <= 4; io_dtype may carry KDA_WEIGHT_F32.  x, weight, cache, y: HOST arrays of device pointers. */
+int kda_conv_step_multi(int32_t n_items, int32_t batch, int32_t channels, int32_t width, int32_t io_dtype, int32_t silu,
+                        const void* const* x, const void* const* weight, void* const* cache, void* const* y, void* stream);
 int kda_conv_fwd_multi(int32_t n_items, int32_t batch, int32_t seq_len, int32_t channels, int32_t width, int32_t io_dtype,
                        int32_t silu, const void* const* x, const void* const* weight, void* const* y, void* stream);
 size_t kda_conv_bwd_multi_scratch_bytes(int32_t n_items, int32_t batch, int32_t seq_len, int32_t channels, int32_t width);

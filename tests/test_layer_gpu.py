@@ -119,3 +119,28 @@ def test_layer_gradients_of_input_and_every_parameter_match_the_oracle_layer():
         errs[n] = O.rel_l2(p.grad.float(), P[n].grad)
     bad = {n: e for n, e in errs.items() if not e <= LAYER_TOL}
     assert not bad, f"layer gradients above {LAYER_TOL}: {bad} (all: {errs})"
+
+
+def test_in_place_decode_token_equals_the_non_mutating_recurrent_path():
+    """`decode_token` (one fused convolution-cache step, gate activations inside the decode kernel, memory rewritten in
+    place: three library launches per token) against `forward(mode="project_recurrent")` (six launches, every state tensor
+    reallocated): identical outputs and identical states after every token, starting from a non-trivial prefilled state."""
+    from experiment_swa_kda_b200 import _lib
+    layer = _layer(5).eval()
+    gen = torch.Generator().manual_seed(3)
+    x = torch.randn(3, 40, HID, generator=gen).bfloat16().to(D0)
+    with torch.no_grad():
+        _, prefilled = layer(x[:, :33], state=None, output_final_state=True, mode="project_chunk")
+        owned = prefilled.clone()
+        ref_state = prefilled
+        for i in range(33, 40):
+            n0 = _lib.launch_count()
+            want, ref_state = layer(x[:, i:i + 1], state=ref_state, output_final_state=True, mode="project_recurrent")
+            n1 = _lib.launch_count()
+            got = layer.decode_token(x[:, i:i + 1], owned)
+            n2 = _lib.launch_count()
+            assert (n2 - n1, n1 - n0) == (3, 6)
+            assert torch.equal(got, want)
+            for a, b in ((owned.memory, ref_state.memory), (owned.q_conv, ref_state.q_conv), (owned.k_conv, ref_state.k_conv),
+                         (owned.v_conv, ref_state.v_conv)):
+                assert torch.equal(a, b)
