@@ -159,8 +159,7 @@ class Chain:
         x, cfg = self.x, self.cfg
         sh = (cfg["B"], cfg["T"], cfg["H"], cfg["D"])
         q, k, v = (t.view(sh) for t in self.m.short_convolutions(self.convs, (x["xq"], x["xk"], x["xv"])))
-        o, _ = self.m.chunk_kda(q, k, v, x["g"], x["beta"])
-        y = self.norm(o, x["gate"])
+        y, _ = self.m.chunk_kda_norm(q, k, v, x["g"], x["beta"], x["gate"], self.norm.weight, eps=cfg["eps"])
         leaves = [x[n] for n in self.leaf_names] + [c.weight for c in self.convs] + [self.norm.weight]
         grads = torch.autograd.grad(y, leaves, x["probe"])
         return y, grads

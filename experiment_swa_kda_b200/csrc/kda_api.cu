@@ -13,7 +13,8 @@
 
 namespace kda {
 int simt_chunk_fwd(const KdaChunkShape* sh, const void* q, const void* k, const void* v, const void* g, const void* beta,
-                   const float* h0, const int32_t* cu, void* o, float* final_state, void* workspace, cudaStream_t st);
+                   const float* h0, const int32_t* cu, void* o, float* final_state, void* workspace, cudaStream_t st,
+                   const tc::NormEpilogue* norm);
 int chunk_status(const KdaChunkShape* sh, const void* workspace, cudaStream_t st);
 int chunk_status_async(const KdaChunkShape* sh, const void* workspace, int32_t* host_word, cudaStream_t st);
 int status_word_to_code(int v);
@@ -86,7 +87,23 @@ extern "C" int kda_chunk_fwd(const KdaChunkShape* shape, const void* q, const vo
     if (!workspace || (reinterpret_cast<uintptr_t>(workspace) % 256) != 0 ||
         workspace_bytes < kda_chunk_workspace_bytes(shape))
         return KDA_ERR_WORKSPACE;
-    return simt_chunk_fwd(shape, q, k, v, g, beta, h0, cu_seqlens, o, final_state, workspace, (cudaStream_t)stream);
+    return simt_chunk_fwd(shape, q, k, v, g, beta, h0, cu_seqlens, o, final_state, workspace, (cudaStream_t)stream, nullptr);
+}
+
+extern "C" int kda_chunk_fwd_norm(const KdaChunkShape* shape, const void* q, const void* k, const void* v, const void* g,
+                                  const void* beta, const float* h0, const int32_t* cu_seqlens, void* o, float* final_state,
+                                  void* workspace, size_t workspace_bytes, const void* gate, const float* norm_weight, float eps,
+                                  void* y, float* inv_rms, void* stream) {
+    int rc = check_shape(shape, cu_seqlens);
+    if (rc) return rc;
+    if (shape->lane != KDA_LANE_TC) return KDA_ERR_UNSUPPORTED;      // the epilogue lives in the tensor-core lane's output kernel
+    if (shape->tokens > 0 && (!q || !k || !v || !g || !beta || !o || !gate || !norm_weight || !y || !inv_rms)) return KDA_ERR_NULL;
+    if (!workspace || (reinterpret_cast<uintptr_t>(workspace) % 256) != 0 || workspace_bytes < kda_chunk_workspace_bytes(shape))
+        return KDA_ERR_WORKSPACE;
+    if ((reinterpret_cast<uintptr_t>(gate) | reinterpret_cast<uintptr_t>(y) | reinterpret_cast<uintptr_t>(norm_weight)) % 16 != 0)
+        return KDA_ERR_UNSUPPORTED;
+    tc::NormEpilogue ep{static_cast<const __nv_bfloat16*>(gate), norm_weight, eps, static_cast<__nv_bfloat16*>(y), inv_rms};
+    return simt_chunk_fwd(shape, q, k, v, g, beta, h0, cu_seqlens, o, final_state, workspace, (cudaStream_t)stream, &ep);
 }
 
 extern "C" int kda_chunk_bwd(const KdaChunkShape* shape, const void* q, const void* k, const void* v, const void* g,

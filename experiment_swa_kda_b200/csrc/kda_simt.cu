@@ -918,8 +918,8 @@ __global__ void __launch_bounds__(256) finalize_kernel(Ws w, Scr s, const void* 
 using simt::Scr;
 using simt::Ws;
 
-int tc_scan_forward(const simt::Ws& w, const tc::TcWs& t, int n_seq, const float* h0, float* final_state, void* o,
-                    cudaStream_t st);
+int tc_scan_forward(const simt::Ws& w, const tc::TcWs& t, int n_seq, int tokens, const float* h0, float* final_state, void* o,
+                    const tc::NormEpilogue& norm, cudaStream_t st);
 int tc_intra_forward(const simt::Ws& w, const tc::TcWs& t, const void* q, const void* k, const void* v, const void* g,
                      const void* beta, int gbf16, int l2norm, float scale, int tokens, cudaStream_t st);
 int tc_scan_backward(const simt::Ws& w, const simt::Scr& s, const tc::TcWs& t, int n_seq, int tokens, const void* d_o,
@@ -938,8 +938,10 @@ static int set_smem(Kern kern, size_t bytes) {
 }
 
 int simt_chunk_fwd(const KdaChunkShape* sh, const void* q, const void* k, const void* v, const void* g, const void* beta,
-                   const float* h0, const int32_t* cu, void* o, float* final_state, void* workspace, cudaStream_t st) {
+                   const float* h0, const int32_t* cu, void* o, float* final_state, void* workspace, cudaStream_t st,
+                   const tc::NormEpilogue* norm) {
     Ws w = simt::carve_ws(*sh, workspace);
+    if (norm != nullptr && norm->gate != nullptr && sh->lane != KDA_LANE_TC) return KDA_ERR_UNSUPPORTED;
     const int bf16 = sh->io_dtype == KDA_DTYPE_BF16, gbf16 = sh->gate_dtype == KDA_DTYPE_BF16;
     const int KT = w.Kp / 64, VT = w.Vp / 64;
     if (sh->lane == KDA_LANE_TC) {
@@ -952,7 +954,8 @@ int simt_chunk_fwd(const KdaChunkShape* sh, const void* q, const void* k, const 
         if (w.nslots > 0) {
             int rc = tc_intra_forward(w, t, q, k, v, g, beta, gbf16, sh->l2norm, sh->scale, sh->tokens, st);
             if (rc) return rc;
-            rc = tc_scan_forward(w, t, sh->n_seq, h0, final_state, o, st);
+            rc = tc_scan_forward(w, t, sh->n_seq, sh->tokens, h0, final_state, o,
+                                 norm != nullptr ? *norm : tc::NormEpilogue{nullptr, nullptr, 0.f, nullptr, nullptr}, st);
             if (rc) return rc;
         }
         return launch_status();

@@ -399,17 +399,19 @@ struct ChunkOutArgs {
     __nv_bfloat16* o;          // [tokens][H][128]
     int H;
     int* status;
+    NormEpilogue norm;
 };
 
 // Z^T reuses the [W^T|R^T] tile and the output tile reuses the state tile: both are dead once the first UMMA chain has
 // completed, and the smaller footprint lets two CTAs share an SM.
-constexpr int kOutH = 0, kOutWR = 32768, kOutU = 65536, kOutA = 81920, kOutZ = kOutWR, kOutO = kOutH;
+constexpr int kOutH = 0, kOutWR = 32768, kOutU = 65536, kOutA = 81920, kOutZ = kOutWR, kOutO = kOutH, kOutG = 90112;
 constexpr int kChunkOutSmem = kOutA + 8192 + 1024;
+constexpr int kChunkOutNormSmem = kOutG + 16384 + 1024;      // + the norm gate's tile when the epilogue is on
 
 __global__ void __launch_bounds__(256, 2)
     tc_chunk_out_kernel(const __grid_constant__ CUtensorMap mH, const __grid_constant__ CUtensorMap mW,
                         const __grid_constant__ CUtensorMap mR, const __grid_constant__ CUtensorMap mUT,
-                        const __grid_constant__ CUtensorMap mAT, ChunkOutArgs p) {
+                        const __grid_constant__ CUtensorMap mAT, const __grid_constant__ CUtensorMap mG, ChunkOutArgs p) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* sm = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     uint8_t* Zop = sm + kOutZ;                     // [128 rows x 128 B] K-major A operand
@@ -429,7 +431,9 @@ __global__ void __launch_bounds__(256, 2)
         mbar_init(&bar_mma1, 1);
         mbar_init(&bar_mma2, 1);
         mbar_fence_init();
-        mbar_expect_tx(&bar_in, 32768 + 32768 + 16384 + 8192);
+        mbar_expect_tx(&bar_in, 32768 + 32768 + 16384 + 8192 + (p.norm.gate != nullptr ? 16384 : 0));
+        if (p.norm.gate != nullptr)      // the norm gate's tile, needed last: its latency hides under the products
+            for (int kb = 0; kb < 2; ++kb) tma_load_2d(sm + kOutG + kb * 8192, &mG, &bar_in, h * 128 + kb * 64, tok0);
         for (int kb = 0; kb < 2; ++kb) tma_load_2d(sm + kOutH + kb * 16384, &mH, &bar_in, kb * 64, ch * 128);
         tma_load_2d(sm + kOutWR, &mW, &bar_in, 0, ch * 128);
         tma_load_2d(sm + kOutWR + 16384, &mR, &bar_in, 0, ch * 128);
@@ -504,7 +508,7 @@ __global__ void __launch_bounds__(256, 2)
         for (int j = 0; j < 32; ++j) Ot[(32 * g + j) * 128 + v] = __float2bfloat16(__uint_as_float(r1[j]) + __uint_as_float(r2[j]));
     }
     ok = __syncthreads_and(ok);
-    if (ok) {
+    if (ok && p.norm.gate == nullptr) {
         // 64 token rows of 256 bytes: 16 threads per row, 16 rows per pass
         const int c = tid & 15;
 #pragma unroll
@@ -513,6 +517,40 @@ __global__ void __launch_bounds__(256, 2)
             if (i < len)
                 *reinterpret_cast<uint4*>(p.o + ((size_t)(tok0 + i) * H + h) * 128 + 8 * c) =
                     *reinterpret_cast<const uint4*>(Ot + i * 128 + 8 * c);
+        }
+    } else if (ok) {
+        // Gated RMSNorm on the tile: a warp per token row, lane = 4 adjacent values - the decomposition (per-lane sum of
+        // four squares, xor-shuffle tree, one rsqrt) of the stand-alone norm kernel, so both give the same bits.
+        const float4 ww = *reinterpret_cast<const float4*>(p.norm.weight + 4 * lane);
+        const float wa[4] = {ww.x, ww.y, ww.z, ww.w};
+#pragma unroll
+        for (int pass = 0; pass < 8; ++pass) {
+            const int i = pass * 8 + warp;
+            const size_t row = (size_t)(tok0 + min(i, len - 1)) * H + h;
+            const uint2 ou = *reinterpret_cast<const uint2*>(Ot + i * 128 + 4 * lane);
+            const uint2 gu = *reinterpret_cast<const uint2*>(sm + kOutG + (lane >> 4) * 8192 + sw128_off(i, (lane >> 1) & 7) + (lane & 1) * 8);
+            const __nv_bfloat162* oh = reinterpret_cast<const __nv_bfloat162*>(&ou);
+            const __nv_bfloat162* gh = reinterpret_cast<const __nv_bfloat162*>(&gu);
+            const float2 o01 = __bfloat1622float2(oh[0]), o23 = __bfloat1622float2(oh[1]);
+            const float2 g01 = __bfloat1622float2(gh[0]), g23 = __bfloat1622float2(gh[1]);
+            const float a[4] = {o01.x, o01.y, o23.x, o23.y}, gt[4] = {g01.x, g01.y, g23.x, g23.y};
+            float ss = a[0] * a[0] + a[1] * a[1] + a[2] * a[2] + a[3] * a[3];
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off);
+            if (i < len) {
+                const float inv = rsqrtf(ss * (1.0f / 128.0f) + p.norm.eps);
+                if (lane == 0) p.norm.inv_rms[row] = inv;
+                float out[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    float th;
+                    asm("tanh.approx.f32 %0, %1;" : "=f"(th) : "f"(0.5f * gt[e]));
+                    out[e] = a[e] * inv * wa[e] * fmaf(0.5f, th, 0.5f);
+                }
+                *reinterpret_cast<uint2*>(p.o + row * 128 + 4 * lane) = ou;
+                *reinterpret_cast<uint2*>(p.norm.y + row * 128 + 4 * lane) =
+                    make_uint2(pack_bf16(out[0], out[1]), pack_bf16(out[2], out[3]));
+            }
         }
     }
     tc_fence_before();
@@ -624,11 +662,11 @@ __global__ void __launch_bounds__(256, 3)
 // ---------------------------------------------------------------------------------------------
 // host entries used by the chunk forward / backward when the tensor-core lane is selected
 // ---------------------------------------------------------------------------------------------
-int tc_scan_forward(const simt::Ws& w, const tc::TcWs& t, int n_seq, const float* h0, float* final_state, void* o,
-                    cudaStream_t st) {
+int tc_scan_forward(const simt::Ws& w, const tc::TcWs& t, int n_seq, int tokens, const float* h0, float* final_state, void* o,
+                    const tc::NormEpilogue& norm, cudaStream_t st) {
     using namespace tc;
     const uint64_t nch = (uint64_t)w.nslots * w.H;
-    CUtensorMap mW, mR, mE, mAT, mUT, mH, mP;
+    CUtensorMap mW, mR, mE, mAT, mUT, mH, mP, mG;
     int rc = 0;
     rc |= make_map_bf16(&mW, t.WT, nch * 128, 64, 64, 128);
     rc |= make_map_bf16(&mR, t.RT, nch * 128, 64, 64, 128);
@@ -637,10 +675,14 @@ int tc_scan_forward(const simt::Ws& w, const tc::TcWs& t, int n_seq, const float
     rc |= make_map_bf16(&mUT, t.UT, nch * 128, 64, 64, 128);
     rc |= make_map_bf16(&mH, t.Hp, nch * 128, 128, 64, 128);
     rc |= make_map_bf16(&mP, t.Pn, nch * 128, 128, 64, 128);
+    const bool fused_norm = norm.gate != nullptr;
+    if (fused_norm) rc |= make_map_bf16(&mG, norm.gate, (uint64_t)tokens, (uint64_t)w.H * 128, 64, 64);
+    else mG = mAT;
     if (rc) return KDA_ERR_CUDA;
+    const int out_smem = fused_norm ? kChunkOutNormSmem : kChunkOutSmem;
     if (cudaFuncSetAttribute(tc_transition_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kTransSmem) != cudaSuccess ||
         cudaFuncSetAttribute(tc_affine_scan_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kAffineScanSmem) != cudaSuccess ||
-        cudaFuncSetAttribute(tc_chunk_out_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kChunkOutSmem) != cudaSuccess)
+        cudaFuncSetAttribute(tc_chunk_out_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kChunkOutNormSmem) != cudaSuccess)
         return KDA_ERR_CUDA;
     TransArgs ta;
     ta.chunk_len = w.chunk_len; ta.RT = t.RT; ta.Pn = t.Pn; ta.RmT = t.fwd_only ? nullptr : t.RmT; ta.H = w.H; ta.status = t.status;
@@ -656,8 +698,9 @@ int tc_scan_forward(const simt::Ws& w, const tc::TcWs& t, int n_seq, const float
     ChunkOutArgs oa;
     oa.chunk_tok0 = w.chunk_tok0; oa.chunk_len = w.chunk_len; oa.ZT = t.fwd_only ? nullptr : t.ZT; oa.o = static_cast<__nv_bfloat16*>(o); oa.H = w.H;
     oa.status = t.status;
+    oa.norm = norm;
     KDA_LAUNCH("tc_chunk_out_kernel", st,
-               tc_chunk_out_kernel<<<dim3(w.nslots, w.H), 256, kChunkOutSmem, st>>>(mH, mW, mR, mUT, mAT, oa));
+               tc_chunk_out_kernel<<<dim3(w.nslots, w.H), 256, out_smem, st>>>(mH, mW, mR, mUT, mAT, mG, oa));
     return launch_status();
 }
 

@@ -26,6 +26,17 @@ struct TcWs {
     int fwd_only;               // 1: the backward-only panels (T, M~, Z^T, dH', dZ^T, Rm^T) have no storage and are not written
 };
 
+// Optional epilogue of the chunk-output kernel: the gated RMSNorm that follows the operator in the layer
+// (y = o * rsqrt(mean(o^2) + eps) * weight * sigmoid(gate) over the 128 values of a token and head), applied to the
+// output tile while it is still on chip.  o is written as well: the norm's backward needs it.
+struct NormEpilogue {
+    const __nv_bfloat16* gate;   // [tokens][H][128], or nullptr: no epilogue
+    const float* weight;         // [128]
+    float eps;
+    __nv_bfloat16* y;            // [tokens][H][128]
+    float* inv_rms;              // [tokens][H]
+};
+
 inline TcWs carve_tc(const KdaChunkShape& sh, void* mem, size_t* bytes = nullptr) {
     TcWs t;
     const size_t nch = (size_t)simt::slots_for(sh, false) * sh.heads;

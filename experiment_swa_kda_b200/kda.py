@@ -204,6 +204,42 @@ def _chunk_dispatch(q, k, v, g, beta, initial_state, output_final_state, cu, sca
     return o, fs
 
 
+def chunk_kda_norm(q: Tensor, k: Tensor, v: Tensor, g: Tensor, beta: Tensor, gate: Tensor, norm_weight: Tensor, *,
+                   eps: float = 1e-5, initial_state: Optional[Tensor] = None, output_final_state: bool = False,
+                   cu_seqlens: Optional[Tensor] = None, scale: Optional[float] = None,
+                   use_qk_l2norm: bool = True) -> Tuple[Tensor, Optional[Tensor]]:
+    """`RMSNormGated(chunk_kda(q, k, v, g, beta), gate)` with the norm applied inside the chunk-output kernel.
+
+    Same results as the two operators in sequence (bit for bit in the forward), one launch and one read of the output
+    less.  Needs the tensor-core lane: bfloat16 activations and K = V = 128; anything else raises.  gate [B,T,H,V];
+    norm_weight [V]."""
+    n_states = None
+    if cu_seqlens is not None:
+        if q.shape[0] != 1:
+            raise ValueError("packed inputs (cu_seqlens) require batch size 1")
+        if cu_seqlens.dtype != torch.int32 or cu_seqlens.ndim != 1 or cu_seqlens.numel() < 2:
+            raise ValueError("cu_seqlens must be int32 [N+1]")
+        n_states = cu_seqlens.numel() - 1
+    _validate_operator_inputs(q, k, v, g, beta, initial_state, n_states)
+    if gate.shape != v.shape:
+        raise ValueError("gate must have the shape of v")
+    if tuple(norm_weight.shape) != (v.shape[-1],):
+        raise ValueError(f"norm_weight must have shape {(v.shape[-1],)}")
+    reason = _backend_reason(q, k, v, g, beta, None, None, initial_state, lower_bound=-1.0, allow_fp32=True)
+    if reason is None and g.dtype != beta.dtype:
+        reason = "g and beta must share a dtype"
+    if reason is None and not (q.dtype == torch.bfloat16 and q.shape[-1] == 128 and v.shape[-1] == 128):
+        reason = "the fused output norm needs the tensor-core lane (bfloat16, K = V = 128)"
+    if reason is None and (gate.device != q.device or norm_weight.device != q.device):
+        reason = "all KDA tensors must be on the same CUDA device"
+    if reason is not None:
+        raise RuntimeError(f"project CUDA KDA backend unavailable: {reason}")
+    sc = float(q.shape[-1] ** -0.5 if scale is None else scale)
+    cu = None if cu_seqlens is None else cu_seqlens.contiguous()
+    return ops.ChunkKDANormFunction.apply(q, k, v, g, beta, gate, norm_weight, initial_state, bool(output_final_state), cu, sc,
+                                          bool(use_qk_l2norm), float(eps))
+
+
 def _select_lane(lane: str, q: Tensor, v: Tensor) -> int:
     """"tc": tcgen05 tensor-core tiles (128-wide heads, bf16 activations); "fp32": CUDA-core float32
     arithmetic for any head size up to 256; "auto": tc whenever the shape allows it."""
@@ -378,10 +414,20 @@ class KimiDeltaAttention(nn.Module):
         q, k, v = q.reshape(shape4), k.reshape(shape4), v.reshape(shape4)
         raw_gate = self.f_b_proj(self.f_a_proj(hidden_states)).reshape(shape4)
         beta_logits = self.b_proj(hidden_states)
-        mixed, final_memory = kda(q, k, v, raw_gate, beta_logits, self.A_log, self.dt_bias, initial_state=memory,
-                                  output_final_state=want_state, mode=requested_mode, lower_bound=self.lower_bound)
         output_gate = self.g_proj(hidden_states).reshape(shape4)
-        mixed = self.o_norm(mixed, output_gate)
+        fuse_norm = (requested_mode == "project_chunk" and length > 0 and q.is_cuda and q.dtype == torch.bfloat16
+                     and self.head_dim == 128 and torch.is_grad_enabled())
+        if fuse_norm:
+            # training path at the tensor-core lane's shape: gate activations, then chunked KDA with the output norm in
+            # the chunk-output kernel's epilogue
+            _validate_operator_inputs(q, k, v, raw_gate, beta_logits, memory)
+            g, beta = ops.GateFunction.apply(raw_gate, beta_logits, self.A_log, self.dt_bias, float(self.lower_bound))
+            mixed, final_memory = chunk_kda_norm(q, k, v, g, beta, output_gate, self.o_norm.weight, eps=self.o_norm.eps,
+                                                 initial_state=memory, output_final_state=want_state)
+        else:
+            mixed, final_memory = kda(q, k, v, raw_gate, beta_logits, self.A_log, self.dt_bias, initial_state=memory,
+                                      output_final_state=want_state, mode=requested_mode, lower_bound=self.lower_bound)
+            mixed = self.o_norm(mixed, output_gate)
         output = self.o_proj(mixed.reshape(batch, length, self.hidden_size))
         final_state = KDAState(final_memory, q_final, k_final, v_final) if want_state else None
         return output, final_state
@@ -414,5 +460,5 @@ class KimiDeltaAttention(nn.Module):
         return self.o_proj(mixed.reshape(batch, 1, self.hidden_size))
 
 
-__all__ = ["KDAState", "KimiDeltaAttention", "RMSNormGated", "ShortConvolution", "chunk_kda", "k3_decay_gate", "kda",
+__all__ = ["KDAState", "KimiDeltaAttention", "RMSNormGated", "ShortConvolution", "chunk_kda", "chunk_kda_norm", "k3_decay_gate", "kda",
            "kda_backend_provenance", "prepare_kda_backend", "recurrent_kda_step", "short_convolutions"]

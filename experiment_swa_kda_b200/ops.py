@@ -109,9 +109,11 @@ def _queue_status(sh, ws, dev) -> None:
         pending.append((ev, slot))
 
 
-def chunk_kda_fwd(q, k, v, g, beta, h0, cu_seqlens, scale, l2norm, want_final, lane=_lib.LANE_FP32, forward_only=False):
+def chunk_kda_fwd(q, k, v, g, beta, h0, cu_seqlens, scale, l2norm, want_final, lane=_lib.LANE_FP32, forward_only=False, norm=None):
     """Returns (o, final_state or None, saved) where saved = (shape, workspace) for the backward.
-    forward_only: inference / prefill - the panels only a backward reads are neither stored nor allocated."""
+    forward_only: inference / prefill - the panels only a backward reads are neither stored nor allocated.
+    norm = (gate, weight float32 [V], eps): also apply the gated RMSNorm in the output kernel's epilogue (tensor-core lane
+    only); the return value then is (o, final_state, saved, y, inv_rms)."""
     lib = _lib.load()
     dev = _need_cuda(q, k, v, g, beta, h0, cu_seqlens)
     poll_status(dev)
@@ -127,10 +129,21 @@ def chunk_kda_fwd(q, k, v, g, beta, h0, cu_seqlens, scale, l2norm, want_final, l
     nbytes = lib.kda_chunk_workspace_bytes(sh)
     ws = _bytes(nbytes, dev)
     with torch.cuda.device(dev):
-        rc = lib.kda_chunk_fwd(sh, _ptr(q), _ptr(k), _ptr(v), _ptr(g), _ptr(beta), _ptr(h0), _ptr(cu_seqlens), _ptr(o),
-                               _ptr(fs), _ptr(ws), ws.numel(), _stream(dev))
-        _lib.check(rc, "kda_chunk_fwd")
+        if norm is None:
+            rc = lib.kda_chunk_fwd(sh, _ptr(q), _ptr(k), _ptr(v), _ptr(g), _ptr(beta), _ptr(h0), _ptr(cu_seqlens), _ptr(o),
+                                   _ptr(fs), _ptr(ws), ws.numel(), _stream(dev))
+            _lib.check(rc, "kda_chunk_fwd")
+        else:
+            gate, nw, eps = norm
+            y = torch.empty_like(o)
+            inv = torch.empty(B * T * H, dtype=torch.float32, device=dev)
+            rc = lib.kda_chunk_fwd_norm(sh, _ptr(q), _ptr(k), _ptr(v), _ptr(g), _ptr(beta), _ptr(h0), _ptr(cu_seqlens), _ptr(o),
+                                        _ptr(fs), _ptr(ws), ws.numel(), _ptr(gate), _ptr(nw), float(eps), _ptr(y), _ptr(inv),
+                                        _stream(dev))
+            _lib.check(rc, "kda_chunk_fwd_norm")
         _queue_status(sh, ws, dev)
+    if norm is not None:
+        return o, fs, (sh, ws), y, inv
     return o, fs, (sh, ws)
 
 
@@ -191,6 +204,35 @@ class ChunkKDAFunction(torch.autograd.Function):
             dfs = dfs.contiguous().float()
         dq, dk, dv, dg, db, dh0 = chunk_kda_bwd(q, k, v, g, beta, ctx.cu, do, dfs, (ctx.shape, ws), ctx.has_h0)
         return dq, dk, dv, dg, db, dh0, None, None, None, None, None
+
+
+class ChunkKDANormFunction(torch.autograd.Function):
+    """Chunked KDA followed by the layer's gated RMSNorm, the norm applied in the output kernel's epilogue (one launch and
+    one pass over the output less than the two operators in sequence; the reference layer crosses an operator boundary
+    here, nanochat/mixers/kda.py:768-795).  Tensor-core lane only.  The backward is the two existing backwards in sequence."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, g, beta, gate, norm_weight, initial_state, output_final_state, cu_seqlens, scale, l2norm, eps):
+        q, k, v, g, beta = (t.contiguous() for t in (q, k, v, g, beta))
+        gate = gate.contiguous().to(v.dtype)
+        w32 = norm_weight.contiguous().float()
+        h0 = None if initial_state is None else initial_state.contiguous()
+        o, fs, (sh, ws), y, inv = chunk_kda_fwd(q, k, v, g, beta, h0, cu_seqlens, scale, l2norm, output_final_state,
+                                                _lib.LANE_TC, norm=(gate, w32, eps))
+        ctx.shape, ctx.cu, ctx.has_h0, ctx.wdtype = sh, cu_seqlens, initial_state is not None, norm_weight.dtype
+        ctx.save_for_backward(q, k, v, g, beta, ws, o, gate, w32, inv)
+        ctx.set_materialize_grads(False)
+        return y, fs
+
+    @staticmethod
+    def backward(ctx, dy, dfs):
+        q, k, v, g, beta, ws, o, gate, w32, inv = ctx.saved_tensors
+        dy = torch.zeros_like(o) if dy is None else dy.contiguous().to(o.dtype)
+        do, dgate, dw = rmsnorm_gate_bwd(o, gate, w32, inv, dy)
+        if dfs is not None:
+            dfs = dfs.contiguous().float()
+        dq, dk, dv, dg, db, dh0 = chunk_kda_bwd(q, k, v, g, beta, ctx.cu, do, dfs, (ctx.shape, ws), ctx.has_h0)
+        return dq, dk, dv, dg, db, dgate, dw.to(ctx.wdtype), dh0, None, None, None, None, None
 
 
 # --------------------------------------------------------------------------------------------

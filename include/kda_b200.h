@@ -84,6 +84,17 @@ int kda_chunk_fwd(const KdaChunkShape* shape, const void* q, const void* k, cons
                   const void* beta, const float* h0, const int32_t* cu_seqlens, void* o, float* final_state,
                   void* workspace, size_t workspace_bytes, void* stream);
 
+/* The forward with the layer's gated RMSNorm applied in the output kernel's epilogue, while the output tile is still on
+ * chip (tensor-core lane only, otherwise KDA_ERR_UNSUPPORTED and the caller runs kda_rmsnorm_gate_fwd itself):
+ *   y = o * rsqrt(mean_v(o^2) + eps) * norm_weight * sigmoid(gate),   gate, y [tokens,H,V] bf16, inv_rms [tokens,H] float32.
+ * o is written too (the norm's backward, kda_rmsnorm_gate_bwd, takes it as x); y and inv_rms equal the stand-alone
+ * kernel's results bit for bit.  Fuses the operator boundary the reference layer crosses between chunk_forward and
+ * rmsnorm_gate_forward (nanochat/mixers/kda.py:768-795); no counterpart operator in the reference. */
+int kda_chunk_fwd_norm(const KdaChunkShape* shape, const void* q, const void* k, const void* v, const void* g,
+                       const void* beta, const float* h0, const int32_t* cu_seqlens, void* o, float* final_state,
+                       void* workspace, size_t workspace_bytes, const void* gate, const float* norm_weight, float eps,
+                       void* y, float* inv_rms, void* stream);
+
 /* ---- chunked KDA, backward ------------------------------------------------
  * Stands in for nanochat_kda::chunk_backward (reference chunk.cu:1758-2113,
  * chunk_wy_backward.cu:3991-4323).  `workspace` is the buffer the matching

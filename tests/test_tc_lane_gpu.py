@@ -174,6 +174,48 @@ def test_non_finite_tokens_of_the_next_packed_sequence_do_not_leak_into_a_ragged
         assert torch.equal(a[:, :100], b)
 
 
+def test_output_norm_in_the_chunk_output_epilogue_equals_the_two_operators_in_sequence():
+    """chunk_kda_norm (gated RMSNorm applied to the output tile inside the chunk-output kernel) against chunk_kda followed
+    by RMSNormGated: identical y, final state and gradients (the epilogue repeats the stand-alone kernel's arithmetic),
+    one library launch less; ragged packed batch with states."""
+    from experiment_swa_kda_b200 import _lib
+    m = _kda_mod()
+    cu = [0, 70, 199, 200, 333]
+    d = O.make_inputs(1, 333, 2, 128, 128, seed=77, with_state=True, n_states=4)
+    gen = torch.Generator().manual_seed(2)
+    gate = torch.randn(1, 333, 2, 128, generator=gen).bfloat16().to(D0)
+    nw = (1 + 0.1 * torch.randn(128, generator=gen)).to(D0)
+    cy = torch.randn(1, 333, 2, 128, generator=gen).bfloat16().to(D0)
+    cu_dev = torch.tensor(cu, dtype=torch.int32, device=D0)
+    outs, counts = [], []
+    for fused in (True, False):
+        x = {n: (t.float() if n == "h0" else t.bfloat16()).to(D0).requires_grad_(True) for n, t in d.items()}
+        gt, w = gate.clone().requires_grad_(True), nw.clone().requires_grad_(True)
+        n0 = _lib.launch_count()
+        if fused:
+            y, s = m.chunk_kda_norm(x["q"], x["k"], x["v"], x["g"], x["beta"], gt, w, eps=1e-6, initial_state=x["h0"],
+                                    output_final_state=True, cu_seqlens=cu_dev)
+        else:
+            o, s = m.chunk_kda(x["q"], x["k"], x["v"], x["g"], x["beta"], initial_state=x["h0"], output_final_state=True,
+                               cu_seqlens=cu_dev)
+            norm = m.RMSNormGated(128, eps=1e-6).to(D0)
+            norm.weight = torch.nn.Parameter(w.detach().clone())
+            y = norm(o, gt)
+            w = norm.weight
+        counts.append(_lib.launch_count() - n0)
+        grads = torch.autograd.grad((y, s), list(x.values()) + [gt, w], (cy, torch.ones_like(s)))
+        outs.append((y, s, grads))
+    assert counts[0] == counts[1] - 1
+    assert torch.equal(outs[0][0], outs[1][0]) and torch.equal(outs[0][1], outs[1][1])
+    for a, b in zip(outs[0][2], outs[1][2]):
+        assert torch.equal(a, b)
+    # and against the oracle
+    leaf = {n: (t.float() if n == "h0" else t.bfloat16().float()) for n, t in d.items()}
+    eo, _ = O.kda_recurrence_varlen(leaf["q"], leaf["k"], leaf["v"], leaf["g"], leaf["beta"], cu, initial_state=leaf["h0"])
+    ey = O.rmsnorm_gated(eo, gate.float().cpu(), nw.cpu(), 1e-6)
+    assert O.rel_l2(outs[0][0].float(), ey) <= BF16_TOL
+
+
 # ---------------------------------------------------------------------------------- the campaign chain, full size
 def test_config1_chain_full_shape_every_gradient():
     """B2 T4096 H3 D128 bf16: short conv (width 4, SiLU) on q/k/v -> chunked KDA -> gated RMSNorm (eps 1e-6) through the
