@@ -153,6 +153,14 @@ struct AffineScanArgs {
     float* s_out;             // V-first final state of the scan (forward: final state, backward: dh0), or null
     int H;
     int* status;
+    // Split scans (few long sequences: most SMs would idle behind a handful of 64-step chains).  Every (sequence, head)
+    // then runs as THREE units side by side: role 0 walks the first half of the steps from s_in; role 1 the second half
+    // from a zero state (its "local" states L); role 2 the second half's state-to-state map alone, from the identity and
+    // without the state-independent term (the composites P of the affine maps).  The true states of the second half are
+    // S_mid P + L, formed chunk-parallel by tc_scan_fixup_kernel.  Units leave their final state as float32 (seg_fin)
+    // and as a bf16 panel (through mF).
+    int split;
+    float* seg_fin;           // [n_seq*H*3][128][128]
 };
 
 constexpr int kPStage = 65536;                              // Pn 32 KB | X 16 KB (U^T or Rm^T) | Y 16 KB (E or dO)
@@ -166,7 +174,8 @@ constexpr int kAffineScanThreads = (4 * kScanGroups + 2) * 32;
 template <bool kBwd>
 __global__ void __launch_bounds__(kAffineScanThreads, 1)
     tc_affine_scan_kernel(const __grid_constant__ CUtensorMap mP, const __grid_constant__ CUtensorMap mX,
-                          const __grid_constant__ CUtensorMap mY, const __grid_constant__ CUtensorMap mS, AffineScanArgs p) {
+                          const __grid_constant__ CUtensorMap mY, const __grid_constant__ CUtensorMap mS,
+                          const __grid_constant__ CUtensorMap mS2, const __grid_constant__ CUtensorMap mF, AffineScanArgs p) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* sm = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     uint8_t* Sop = sm + 2 * kPStage;               // 2 x [2 k-blocks][128 rows x 128 B]: bf16 state panel of step c in c % 2
@@ -180,10 +189,16 @@ __global__ void __launch_bounds__(kAffineScanThreads, 1)
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int v = (warp & 3) * 32 + lane;          // value row = TMEM lane
-    const int seq = blockIdx.x, h = blockIdx.y, H = p.H;
+    const int seq = p.split ? blockIdx.x / 3 : blockIdx.x, role = p.split ? blockIdx.x % 3 : 0;
+    const int h = blockIdx.y, H = p.H;
     const int c_begin = p.seq_chunk0[seq], c_end = p.seq_chunk0[seq + 1];
-    const int n = c_end - c_begin;
-    auto slot_of = [&](int c) { return kBwd ? c_end - 1 - c : c_begin + c; };   // chunk slot of step c
+    const int n_total = c_end - c_begin;
+    const int half = p.split ? (n_total + 1) / 2 : n_total;
+    const int step0 = role == 0 ? 0 : half;                      // first step of this unit, in the sequence's scan order
+    const int n = role == 0 ? half : n_total - half;
+    const bool composite = role == 2;                            // state-to-state map only: no state-independent term
+    const int unit = (seq * H + h) * 3 + role;
+    auto slot_of = [&](int c) { return kBwd ? c_end - 1 - (step0 + c) : c_begin + step0 + c; };   // chunk slot of step c
 
     if (tid == 0) {
         mbar_init(&bar_full[0], 1);
@@ -211,9 +226,10 @@ __global__ void __launch_bounds__(kAffineScanThreads, 1)
                 const int slot = slot_of(c);
                 const int ch = slot * H + h;
                 uint8_t* b = sm + st * kPStage;
-                mbar_expect_tx(&bar_full[st], kPStageBytes);
+                mbar_expect_tx(&bar_full[st], composite ? 32768 + 512 : kPStageBytes);
                 bulk_load_1d(dec_ring[c & 3], p.decay_end + (size_t)ch * 128, 512, &bar_full[st]);
                 for (int nb = 0; nb < 2; ++nb) tma_load_2d(b + nb * 16384, &mP, &bar_full[st], nb * 64, ch * 128);
+                if (composite) return;
                 tma_load_2d(b + 32768, &mX, &bar_full[st], 0, ch * 128);                  // U^T / Rm^T: [128][64]
                 if (!kBwd) {
                     for (int nb = 0; nb < 2; ++nb) tma_load_2d(b + 49152 + nb * 8192, &mY, &bar_full[st], nb * 64, ch * 64);
@@ -235,7 +251,7 @@ __global__ void __launch_bounds__(kAffineScanThreads, 1)
         }
     } else if (warp == 4 * kScanGroups + 1) {
         // ------------------------------------------------------------------ UMMA / panel-store thread
-        if (kBwd && n > 0) {
+        if (kBwd && n > 0 && !composite && step0 == 0) {
             // Only a sequence's last chunk (the adjoint scan's first step) can be ragged; the dO rows past its tail
             // belong to the next sequence and are blanked by the whole warp before lane 0 issues the product on them.
             const int len0 = p.chunk_len[slot_of(0)];
@@ -249,6 +265,14 @@ __global__ void __launch_bounds__(kAffineScanThreads, 1)
                 }
                 __syncwarp();
             }
+        }
+        if (lane == 0 && n == 0 && p.split) {
+            if (mbar_wait(&bar_pan, 0, p.status, 55)) {
+                tma_store_2d(&mF, Sop, 0, unit * 128);
+                tma_store_2d(&mF, Sop + 16384, 64, unit * 128);
+                tma_store_commit();
+            }
+            tma_store_wait_all();
         }
         if (lane == 0 && n > 0) {
             // state-independent product:  forward U^T E (A K-major, B MN-major), backward dO^T Rm (A MN-major, B K-major)
@@ -269,10 +293,11 @@ __global__ void __launch_bounds__(kAffineScanThreads, 1)
                                      umma_smem_desc_sw128(s0 + 32768 + k16 * 32, 16, 1024), id_ind, k16 > 0);
                 }
             };
+            const CUtensorMap* mstore = composite ? &mS2 : &mS;      // composites go to their own panel array
             bool ok = mbar_wait(&bar_full[0], 0, p.status, 51);
             if (ok) {
                 tc_fence_after();
-                issue_independent(0);
+                if (!composite) issue_independent(0);
             } else abort_flag = 1;
             for (int c = 0; c < n && ok; ++c) {
                 const int st = c & 1;
@@ -284,7 +309,7 @@ __global__ void __launch_bounds__(kAffineScanThreads, 1)
                 for (int k16 = 0; k16 < 8; ++k16) {   // A = the packed state in tensor memory, 8 columns per K = 16
                     const uint64_t bd = kBwd ? umma_smem_desc_sw128(s0 + (k16 >> 2) * 16384 + (k16 & 3) * 32, 16, 1024)
                                              : umma_smem_desc_sw128(s0 + k16 * 2048, 16384, 1024);
-                    umma_bf16_ts(tmem + 128 * st, tmem + kScanPanelCol + 8 * k16, bd, id_st, 1);
+                    umma_bf16_ts(tmem + 128 * st, tmem + kScanPanelCol + 8 * k16, bd, id_st, (composite && k16 == 0) ? 0u : 1u);
                 }
                 // The store of panel c-1 has read its buffer before this commit lets the state threads write panel c+1
                 // into it.
@@ -293,14 +318,22 @@ __global__ void __launch_bounds__(kAffineScanThreads, 1)
                 umma_commit(&bar_free[st]);
                 // the copy of the panel in shared memory (written after the tensor-memory one, off the critical path)
                 if (!mbar_wait(&bar_pan, c & 1, p.status, 55)) { abort_flag = 1; break; }
-                tma_store_2d(&mS, Sop + st * 32768, 0, ch * 128);
-                tma_store_2d(&mS, Sop + st * 32768 + 16384, 64, ch * 128);
+                tma_store_2d(mstore, Sop + st * 32768, 0, ch * 128);
+                tma_store_2d(mstore, Sop + st * 32768 + 16384, 64, ch * 128);
                 tma_store_commit();
                 if (c + 1 < n) {
                     // accumulator (c+1) % 2 was last read by the state threads in step c-1, before they packed panel c
                     if (!mbar_wait(&bar_full[(c + 1) & 1], ((c + 1) >> 1) & 1, p.status, 51)) { abort_flag = 1; break; }
                     tc_fence_after();
-                    issue_independent(c + 1);
+                    if (!composite) issue_independent(c + 1);
+                }
+            }
+            if (ok && p.split && abort_flag == 0) {
+                // the unit's final state as one more bf16 panel (the state threads pack it after their last step)
+                if (mbar_wait(&bar_pan, n & 1, p.status, 55)) {
+                    tma_store_2d(&mF, Sop + (n & 1) * 32768, 0, unit * 128);
+                    tma_store_2d(&mF, Sop + (n & 1) * 32768 + 16384, 64, unit * 128);
+                    tma_store_commit();
                 }
             }
             tma_store_wait_all();
@@ -309,7 +342,10 @@ __global__ void __launch_bounds__(kAffineScanThreads, 1)
         // ------------------------------------------------------------------ state warpgroups
         const int col0 = (warp >> 2) * kScanCols;  // first key column of this thread
         float s[kScanCols];
-        if (p.s_in) {
+        if (role == 2) {
+#pragma unroll
+            for (int j = 0; j < kScanCols; ++j) s[j] = (col0 + j == v) ? 1.f : 0.f;
+        } else if (p.s_in && role == 0) {
             const float4* src = reinterpret_cast<const float4*>(p.s_in + (((size_t)seq * H + h) * 128 + v) * 128 + col0);
 #pragma unroll
             for (int j = 0; j < kScanCols / 4; ++j) {
@@ -329,14 +365,17 @@ __global__ void __launch_bounds__(kAffineScanThreads, 1)
         // step c frees the stage for the loads of step c + 2, so a state warp that looked at the stage barrier only
         // after that commit could find it two phases on and read the parity as "not yet complete".
         auto pack_state = [&](int c) -> bool {
-            if (!mbar_wait(&bar_full[c & 1], (c >> 1) & 1, p.status, 54)) return false;
+            const bool last = c >= n;      // the final state's panel: shared-memory copy only, nothing consumes it on chip
+            if (!last && !mbar_wait(&bar_full[c & 1], (c >> 1) & 1, p.status, 54)) return false;
             uint32_t w[32];
 #pragma unroll
             for (int j = 0; j < 32; ++j) w[j] = pack_bf16(s[2 * j], s[2 * j + 1]);
-            tmem_st32(tmem + lane_base + kScanPanelCol + 32 * kh, w);
-            tmem_st_wait();
-            tc_fence_before();
-            warp_arrive(&bar_sop, lane);
+            if (!last) {
+                tmem_st32(tmem + lane_base + kScanPanelCol + 32 * kh, w);
+                tmem_st_wait();
+                tc_fence_before();
+                warp_arrive(&bar_sop, lane);
+            }
             uint8_t* dst = Sop + (c & 1) * 32768 + kh * 16384;
 #pragma unroll
             for (int q = 0; q < 8; ++q)
@@ -346,7 +385,7 @@ __global__ void __launch_bounds__(kAffineScanThreads, 1)
             return true;
         };
         bool ok = true;
-        if (n > 0 && !pack_state(0)) { abort_flag = 1; ok = false; }
+        if ((n > 0 || p.split) && !pack_state(0)) { abort_flag = 1; ok = false; }
         for (int c = 0; c < n && ok; ++c) {
             if (!mbar_wait(&bar_mma, c & 1, p.status, 53)) {
                 abort_flag = 1; ok = false;
@@ -371,10 +410,11 @@ __global__ void __launch_bounds__(kAffineScanThreads, 1)
                     }
             }
             tc_fence_before();
-            if (c + 1 < n && !pack_state(c + 1)) { abort_flag = 1; ok = false; }
+            if ((c + 1 < n || p.split) && !pack_state(c + 1)) { abort_flag = 1; ok = false; }
         }
-        if (ok && abort_flag == 0 && p.s_out) {
-            float4* dst = reinterpret_cast<float4*>(p.s_out + (((size_t)seq * H + h) * 128 + v) * 128 + col0);
+        float* fin = p.split ? p.seg_fin + (size_t)unit * 16384 : (p.s_out ? p.s_out + ((size_t)seq * H + h) * 16384 : nullptr);
+        if (ok && abort_flag == 0 && fin) {
+            float4* dst = reinterpret_cast<float4*>(fin + (size_t)v * 128 + col0);
 #pragma unroll
             for (int j = 0; j < kScanCols / 4; ++j) dst[j] = make_float4(s[4 * j], s[4 * j + 1], s[4 * j + 2], s[4 * j + 3]);
         }
@@ -382,6 +422,135 @@ __global__ void __launch_bounds__(kAffineScanThreads, 1)
     tc_fence_before();
     __syncthreads();
     if (warp == 1) tmem_dealloc(tmem, 512);
+}
+
+// ---------------------------------------------------------------------------------------------
+// split scans, second pass: the true state at the start of every chunk of a sequence's second half,
+//     S = S_mid P + L        (S_mid: final state of the first half; P, L: the chunk's composite and local state)
+// one CTA per chunk-head, plus one per (sequence, head) for the scan's final state (P, L of the half's end).
+// S_mid enters as two bf16 terms (hi + lo), so only P's own bf16 rounding touches the carried state.
+// ---------------------------------------------------------------------------------------------
+struct ScanFixArgs {
+    const int* seq_chunk0;
+    const int* chunk_seq;
+    const int* chunk_len;
+    const float* seg_fin;      // [units][128][128]
+    __nv_bfloat16* Hp;         // [nch][128][128]: local states in, true states out
+    float* s_out;              // final state of the scan, V-first [n_seq][H][128][128], or null
+    int H, nslots, bwd;
+    int* status;
+};
+
+constexpr int kFixSmem = 3 * 32768 + 1024;      // S_mid hi | S_mid lo | P
+
+__global__ void __launch_bounds__(256, 2)
+    tc_scan_fixup_kernel(const __grid_constant__ CUtensorMap mPp, const __grid_constant__ CUtensorMap mF, ScanFixArgs p) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* sm = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    __shared__ uint64_t bar_in, bar_mma;
+    __shared__ uint32_t tmem_slot;
+    const int h = blockIdx.y, H = p.H;
+    const bool fin = (int)blockIdx.x >= p.nslots;
+    const int slot = fin ? 0 : blockIdx.x;
+    if (!fin && p.chunk_len[slot] == 0) return;
+    const int seq = fin ? (int)blockIdx.x - p.nslots : p.chunk_seq[slot];
+    const int c_begin = p.seq_chunk0[seq], c_end = p.seq_chunk0[seq + 1];
+    const int half = (c_end - c_begin + 1) / 2;
+    if (!fin && (p.bwd ? c_end - 1 - slot : slot - c_begin) < half) return;      // first-half chunks are already true
+    if (fin && p.s_out == nullptr) return;
+    const int unit0 = (seq * H + h) * 3;
+    const int ch = slot * H + h;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int g = warp >> 2;                       // key half handled by this warpgroup
+    const int v = (warp & 3) * 32 + lane;          // value row = TMEM lane
+    if (tid == 0) {
+        mbar_init(&bar_in, 1);
+        mbar_init(&bar_mma, 1);
+        mbar_fence_init();
+        mbar_expect_tx(&bar_in, 32768);
+        for (int nb = 0; nb < 2; ++nb) {
+            if (fin) tma_load_2d(sm + 65536 + nb * 16384, &mF, &bar_in, nb * 64, (unit0 + 2) * 128);
+            else tma_load_2d(sm + 65536 + nb * 16384, &mPp, &bar_in, nb * 64, ch * 128);
+        }
+    }
+    if (warp == 1) tmem_alloc(&tmem_slot, 128);
+    {   // S_mid[v][64 g .. 64 g + 63] as hi + lo bf16, K-major swizzled
+        const float4* src = reinterpret_cast<const float4*>(p.seg_fin + ((size_t)unit0 * 128 + v) * 128 + 64 * g);
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+            const float4 a = src[2 * c], b = src[2 * c + 1];
+            const float f[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+            uint32_t hi[4], lo[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const __nv_bfloat162 hh = __floats2bfloat162_rn(f[2 * e], f[2 * e + 1]);
+                const float2 back = __bfloat1622float2(hh);
+                hi[e] = *reinterpret_cast<const uint32_t*>(&hh);
+                lo[e] = pack_bf16(f[2 * e] - back.x, f[2 * e + 1] - back.y);
+            }
+            *reinterpret_cast<uint4*>(sm + g * 16384 + sw128_off(v, c)) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+            *reinterpret_cast<uint4*>(sm + 32768 + g * 16384 + sw128_off(v, c)) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+        }
+    }
+    fence_async_smem();
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = tmem_slot;
+    const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
+    bool ok = true;
+    if (tid == 0) {
+        ok = mbar_wait(&bar_in, 0, p.status, 80);
+        if (ok) {
+            tc_fence_after();
+            const uint32_t b0 = smem_u32(sm + 65536);
+            const uint32_t idesc = umma_idesc_bf16(128, 128, kMajorK, kMajorMN);
+#pragma unroll
+            for (int part = 0; part < 2; ++part) {
+                const uint32_t a0 = smem_u32(sm + part * 32768);
+#pragma unroll
+                for (int k16 = 0; k16 < 8; ++k16)
+                    umma_bf16_ss(tmem, umma_smem_desc_sw128(a0 + (k16 >> 2) * 16384 + (k16 & 3) * 32, 16, 1024),
+                                 umma_smem_desc_sw128(b0 + k16 * 2048, 16384, 1024), idesc, (part | k16) != 0);
+            }
+            umma_commit(&bar_mma);
+        }
+    }
+    ok = mbar_wait(&bar_mma, 0, p.status, 81) && ok;
+    ok = __syncthreads_and(ok);
+    tc_fence_after();
+    if (ok) {
+#pragma unroll
+        for (int b = 0; b < 2; ++b) {
+            uint32_t r[32];
+            tmem_ld32(tmem + lane_base + 64 * g + 32 * b, r);
+            tmem_ld_wait();
+            if (fin) {
+                const float4* Lp = reinterpret_cast<const float4*>(p.seg_fin + ((size_t)(unit0 + 1) * 128 + v) * 128 + 64 * g + 32 * b);
+                float4* dst = reinterpret_cast<float4*>(p.s_out + (((size_t)seq * H + h) * 128 + v) * 128 + 64 * g + 32 * b);
+#pragma unroll
+                for (int c = 0; c < 8; ++c) {
+                    const float4 l = Lp[c];
+                    dst[c] = make_float4(__uint_as_float(r[4 * c]) + l.x, __uint_as_float(r[4 * c + 1]) + l.y,
+                                         __uint_as_float(r[4 * c + 2]) + l.z, __uint_as_float(r[4 * c + 3]) + l.w);
+                }
+            } else {
+                uint4* io = reinterpret_cast<uint4*>(p.Hp + (size_t)ch * 16384 + (size_t)v * 128 + 64 * g + 32 * b);
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    float l[8];
+                    unpack_bf16x8(io[c], l);
+                    io[c] = make_uint4(pack_bf16(__uint_as_float(r[8 * c]) + l[0], __uint_as_float(r[8 * c + 1]) + l[1]),
+                                       pack_bf16(__uint_as_float(r[8 * c + 2]) + l[2], __uint_as_float(r[8 * c + 3]) + l[3]),
+                                       pack_bf16(__uint_as_float(r[8 * c + 4]) + l[4], __uint_as_float(r[8 * c + 5]) + l[5]),
+                                       pack_bf16(__uint_as_float(r[8 * c + 6]) + l[6], __uint_as_float(r[8 * c + 7]) + l[7]));
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tmem, 128);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -691,10 +860,24 @@ int tc_scan_forward(const simt::Ws& w, const tc::TcWs& t, int n_seq, int tokens,
     if (int e = launch_status()) return e;
     AffineScanArgs a;
     a.seq_chunk0 = w.seq_chunk0; a.chunk_tok0 = w.chunk_tok0; a.chunk_len = w.chunk_len; a.decay_end = t.decay_end; a.s_in = h0; a.s_out = final_state;
-    a.H = w.H; a.status = t.status;
+    a.H = w.H; a.status = t.status; a.split = t.split; a.seg_fin = t.seg_fin;
+    CUtensorMap mPp = mH, mF = mH;
+    if (t.split) {
+        if (make_map_bf16(&mPp, t.Pp, nch * 128, 128, 64, 128) ||
+            make_map_bf16(&mF, t.fin_panel, (uint64_t)n_seq * w.H * 3 * 128, 128, 64, 128))
+            return KDA_ERR_CUDA;
+    }
     KDA_LAUNCH("tc_affine_scan_fwd_kernel", st,
-               tc_affine_scan_kernel<false><<<dim3(n_seq, w.H), kAffineScanThreads, kAffineScanSmem, st>>>(mP, mUT, mE, mH, a));
+               tc_affine_scan_kernel<false><<<dim3(n_seq * (t.split ? 3 : 1), w.H), kAffineScanThreads, kAffineScanSmem, st>>>(mP, mUT, mE, mH, mPp, mF, a));
     if (int e = launch_status()) return e;
+    if (t.split) {
+        if (cudaFuncSetAttribute(tc_scan_fixup_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kFixSmem) != cudaSuccess) return KDA_ERR_CUDA;
+        ScanFixArgs f;
+        f.seq_chunk0 = w.seq_chunk0; f.chunk_seq = w.chunk_seq; f.chunk_len = w.chunk_len; f.seg_fin = t.seg_fin; f.Hp = t.Hp;
+        f.s_out = final_state; f.H = w.H; f.nslots = w.nslots; f.bwd = 0; f.status = t.status;
+        KDA_LAUNCH("tc_scan_fixup_kernel", st, tc_scan_fixup_kernel<<<dim3(w.nslots + n_seq, w.H), 256, kFixSmem, st>>>(mPp, mF, f));
+        if (int e = launch_status()) return e;
+    }
     ChunkOutArgs oa;
     oa.chunk_tok0 = w.chunk_tok0; oa.chunk_len = w.chunk_len; oa.ZT = t.fwd_only ? nullptr : t.ZT; oa.o = static_cast<__nv_bfloat16*>(o); oa.H = w.H;
     oa.status = t.status;
@@ -723,10 +906,24 @@ int tc_scan_backward(const simt::Ws& w, const simt::Scr& s, const tc::TcWs& t, i
         return KDA_ERR_CUDA;
     AffineScanArgs a;
     a.seq_chunk0 = w.seq_chunk0; a.chunk_tok0 = w.chunk_tok0; a.chunk_len = w.chunk_len; a.decay_end = t.decay_end; a.s_in = d_final; a.s_out = dh0;
-    a.H = w.H; a.status = t.status;
+    a.H = w.H; a.status = t.status; a.split = t.split; a.seg_fin = t.seg_fin;
+    CUtensorMap mPp = mdH, mF = mdH;
+    if (t.split) {
+        if (make_map_bf16(&mPp, t.Pp, nch * 128, 128, 64, 128) ||
+            make_map_bf16(&mF, t.fin_panel, (uint64_t)n_seq * w.H * 3 * 128, 128, 64, 128))
+            return KDA_ERR_CUDA;
+    }
     KDA_LAUNCH("tc_affine_scan_bwd_kernel", st,
-               tc_affine_scan_kernel<true><<<dim3(n_seq, w.H), kAffineScanThreads, kAffineScanSmem, st>>>(mP, mRm, mdO, mdH, a));
+               tc_affine_scan_kernel<true><<<dim3(n_seq * (t.split ? 3 : 1), w.H), kAffineScanThreads, kAffineScanSmem, st>>>(mP, mRm, mdO, mdH, mPp, mF, a));
     if (int e = launch_status()) return e;
+    if (t.split) {
+        if (cudaFuncSetAttribute(tc_scan_fixup_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kFixSmem) != cudaSuccess) return KDA_ERR_CUDA;
+        ScanFixArgs f;
+        f.seq_chunk0 = w.seq_chunk0; f.chunk_seq = w.chunk_seq; f.chunk_len = w.chunk_len; f.seg_fin = t.seg_fin; f.Hp = t.dHp;
+        f.s_out = dh0; f.H = w.H; f.nslots = w.nslots; f.bwd = 1; f.status = t.status;
+        KDA_LAUNCH("tc_scan_fixup_kernel", st, tc_scan_fixup_kernel<<<dim3(w.nslots + n_seq, w.H), 256, kFixSmem, st>>>(mPp, mF, f));
+        if (int e = launch_status()) return e;
+    }
     ChunkDzArgs da;
     da.chunk_tok0 = w.chunk_tok0; da.chunk_len = w.chunk_len; da.dZT = t.dZT; da.H = w.H; da.status = t.status;
     KDA_LAUNCH("tc_chunk_dz_kernel", st,

@@ -21,6 +21,10 @@ struct TcWs {
     __nv_bfloat16* dZT;         // [nch][128][64]   dZ transposed
     __nv_bfloat16* Pn;          // [nch][128][128]  W^T E: [key k][key k'], the state-to-state part of the chunk transition
     __nv_bfloat16* RmT;         // [nch][128][64]   (R - A W)^T: [key][token]
+    __nv_bfloat16* Pp;          // [nch][128][128]  split scans only: composite state-to-state maps at each chunk start
+    __nv_bfloat16* fin_panel;   // [n_seq*H*3][128][128]  split scans only: final state of every scan unit as a bf16 panel
+    float* seg_fin;             // [n_seq*H*3][128][128]  split scans only: the same in float32
+    int split;                  // 1: every (sequence, head) scan runs as three units (see AffineScanArgs)
     float* decay_end;           // [nch][128]       exp(G_end)
     int* status;                // device status word (0 = ok); points at the workspace's word (simt::Ws::status)
     int fwd_only;               // 1: the backward-only panels (T, M~, Z^T, dH', dZ^T, Rm^T) have no storage and are not written
@@ -36,6 +40,13 @@ struct NormEpilogue {
     __nv_bfloat16* y;            // [tokens][H][128]
     float* inv_rms;              // [tokens][H]
 };
+
+// Scans are split when a fixed-length batch has so few (sequence, head) recurrences that most SMs would idle behind
+// them, and the sequences are long enough for half a chain to outweigh the fix-up pass.
+inline int scan_split(const KdaChunkShape& sh) {
+    const bool fixed = sh.seq_len > 0 && (long long)sh.n_seq * sh.seq_len == sh.tokens;
+    return (fixed && sh.n_seq * sh.heads * 3 <= 148 && sh.seq_len >= 16 * 64) ? 1 : 0;
+}
 
 inline TcWs carve_tc(const KdaChunkShape& sh, void* mem, size_t* bytes = nullptr) {
     TcWs t;
@@ -55,6 +66,11 @@ inline TcWs carve_tc(const KdaChunkShape& sh, void* mem, size_t* bytes = nullptr
     t.dZT = c.take<__nv_bfloat16>(bw * nch * 8192);
     t.Pn = c.take<__nv_bfloat16>(nch * 16384);
     t.RmT = c.take<__nv_bfloat16>(bw * nch * 8192);
+    t.split = scan_split(sh);
+    const size_t units = t.split ? (size_t)sh.n_seq * sh.heads * 3 : 0;
+    t.Pp = c.take<__nv_bfloat16>(t.split ? nch * 16384 : 0);
+    t.fin_panel = c.take<__nv_bfloat16>(units * 16384);
+    t.seg_fin = c.take<float>(units * 16384);
     t.decay_end = c.take<float>(nch * 128);
     t.status = c.take<int>(64);
     t.fwd_only = sh.forward_only ? 1 : 0;

@@ -174,6 +174,31 @@ def test_non_finite_tokens_of_the_next_packed_sequence_do_not_leak_into_a_ragged
         assert torch.equal(a[:, :100], b)
 
 
+def test_split_scans_agree_with_the_single_chain_and_the_oracle():
+    """A long fixed-length batch with few (sequence, head) recurrences runs every state scan as three units (first half,
+    second half from zero, second half's composite maps) plus a chunk-parallel fix-up; the same tokens handed over as a
+    packed batch (cu_seqlens) take the single 64-step-per-4096-token chain.  Both must agree with each other closely and
+    with the oracle inside the bar: outputs, final state (non-zero initial state) and every gradient."""
+    m = _kda_mod()
+    T = 2048 + 64 * 3 + 17                     # 36 chunks, ragged tail
+    d = O.make_inputs(1, T, 2, 128, 128, seed=91, with_state=True)
+    gen = torch.Generator().manual_seed(4)
+    do = torch.randn(1, T, 2, 128, generator=gen).bfloat16().to(D0)
+    ds = torch.randn(1, 2, 128, 128, generator=gen).to(D0)
+    res = []
+    for packed in (False, True):
+        x = {n: (t.float() if n == "h0" else t.bfloat16()).to(D0).requires_grad_(True) for n, t in d.items()}
+        cu = torch.tensor([0, T], dtype=torch.int32, device=D0) if packed else None
+        o, s = m.chunk_kda(x["q"], x["k"], x["v"], x["g"], x["beta"], initial_state=x["h0"], output_final_state=True,
+                           cu_seqlens=cu, lane="tc")
+        res.append((o, s, torch.autograd.grad((o, s), list(x.values()), (do, ds))))
+    (o1, s1, g1), (o2, s2, g2) = res
+    assert O.rel_l2(o1.float(), o2.float()) <= 4e-3 and O.rel_l2(s1, s2) <= 4e-3
+    for a, b in zip(g1, g2):
+        assert O.rel_l2(a.float(), b.float()) <= 6e-3
+    _run_activated(d)                           # the split path against the oracle
+
+
 def test_output_norm_in_the_chunk_output_epilogue_equals_the_two_operators_in_sequence():
     """chunk_kda_norm (gated RMSNorm applied to the output tile inside the chunk-output kernel) against chunk_kda followed
     by RMSNormGated: identical y, final state and gradients (the epilogue repeats the stand-alone kernel's arithmetic),
