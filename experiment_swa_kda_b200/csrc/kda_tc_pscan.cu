@@ -153,15 +153,19 @@ struct AffineScanArgs {
     float* s_out;             // V-first final state of the scan (forward: final state, backward: dh0), or null
     int H;
     int* status;
-    // Split scans (few long sequences: most SMs would idle behind a handful of 64-step chains).  Every (sequence, head)
-    // then runs as THREE units side by side: role 0 walks the first half of the steps from s_in; role 1 the second half
-    // from a zero state (its "local" states L); role 2 the second half's state-to-state map alone, from the identity and
-    // without the state-independent term (the composites P of the affine maps).  The true states of the second half are
-    // S_mid P + L, formed chunk-parallel by tc_scan_fixup_kernel.  Units leave their final state as float32 (seg_fin)
-    // and as a bf16 panel (through mF).
-    int split;
-    float* seg_fin;           // [n_seq*H*3][128][128]
+    // Split scans (few long sequences: most SMs would idle behind a handful of 64-step chains).  The steps of every
+    // (sequence, head) are cut into nseg segments that run side by side as 2 nseg - 1 units: unit 0 walks segment 0 from
+    // s_in; for every later segment k, unit 2k-1 walks it from a zero state (its "local" states L) and unit 2k walks its
+    // state-to-state map alone, from the identity and without the state-independent term (the composites P of the
+    // affine maps).  The true state at a chunk of segment k is S_k P + L with S_k the state at the segment's start;
+    // tc_scan_fixup_kernel forms the S_k (a chain of nseg - 1 small products) and then the chunk states, chunk-parallel.
+    // Units leave their final state as float32 (seg_fin) and as a bf16 panel (through mF).
+    int nseg;                 // 1: no split
+    float* seg_fin;           // [n_seq*H*(2 nseg - 1)][128][128]
 };
+
+// first scan step of segment k of a sequence of n steps
+__host__ __device__ __forceinline__ int seg_begin(int k, int nseg, int n) { return (int)(((long long)k * n) / nseg); }
 
 constexpr int kPStage = 65536;                              // Pn 32 KB | X 16 KB (U^T or Rm^T) | Y 16 KB (E or dO)
 constexpr int kPStageBytes = kPStage + 512;                 // + exp(G_end), which lands in a ring of its own
@@ -189,15 +193,17 @@ __global__ void __launch_bounds__(kAffineScanThreads, 1)
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int v = (warp & 3) * 32 + lane;          // value row = TMEM lane
-    const int seq = p.split ? blockIdx.x / 3 : blockIdx.x, role = p.split ? blockIdx.x % 3 : 0;
+    const bool split = p.nseg > 1;
+    const int units = 2 * p.nseg - 1;
+    const int seq = split ? blockIdx.x / units : blockIdx.x, role = split ? blockIdx.x % units : 0;
     const int h = blockIdx.y, H = p.H;
     const int c_begin = p.seq_chunk0[seq], c_end = p.seq_chunk0[seq + 1];
     const int n_total = c_end - c_begin;
-    const int half = p.split ? (n_total + 1) / 2 : n_total;
-    const int step0 = role == 0 ? 0 : half;                      // first step of this unit, in the sequence's scan order
-    const int n = role == 0 ? half : n_total - half;
-    const bool composite = role == 2;                            // state-to-state map only: no state-independent term
-    const int unit = (seq * H + h) * 3 + role;
+    const int seg = (role + 1) >> 1;                             // segment this unit walks
+    const int step0 = seg_begin(seg, p.nseg, n_total);           // its first step, in the sequence's scan order
+    const int n = seg_begin(seg + 1, p.nseg, n_total) - step0;
+    const bool composite = role > 0 && (role & 1) == 0;          // state-to-state map only: no state-independent term
+    const int unit = (seq * H + h) * units + role;
     auto slot_of = [&](int c) { return kBwd ? c_end - 1 - (step0 + c) : c_begin + step0 + c; };   // chunk slot of step c
 
     if (tid == 0) {
@@ -266,7 +272,7 @@ __global__ void __launch_bounds__(kAffineScanThreads, 1)
                 __syncwarp();
             }
         }
-        if (lane == 0 && n == 0 && p.split) {
+        if (lane == 0 && n == 0 && split) {
             if (mbar_wait(&bar_pan, 0, p.status, 55)) {
                 tma_store_2d(&mF, Sop, 0, unit * 128);
                 tma_store_2d(&mF, Sop + 16384, 64, unit * 128);
@@ -328,7 +334,7 @@ __global__ void __launch_bounds__(kAffineScanThreads, 1)
                     if (!composite) issue_independent(c + 1);
                 }
             }
-            if (ok && p.split && abort_flag == 0) {
+            if (ok && split && abort_flag == 0) {
                 // the unit's final state as one more bf16 panel (the state threads pack it after their last step)
                 if (mbar_wait(&bar_pan, n & 1, p.status, 55)) {
                     tma_store_2d(&mF, Sop + (n & 1) * 32768, 0, unit * 128);
@@ -342,7 +348,7 @@ __global__ void __launch_bounds__(kAffineScanThreads, 1)
         // ------------------------------------------------------------------ state warpgroups
         const int col0 = (warp >> 2) * kScanCols;  // first key column of this thread
         float s[kScanCols];
-        if (role == 2) {
+        if (composite) {
 #pragma unroll
             for (int j = 0; j < kScanCols; ++j) s[j] = (col0 + j == v) ? 1.f : 0.f;
         } else if (p.s_in && role == 0) {
@@ -385,7 +391,7 @@ __global__ void __launch_bounds__(kAffineScanThreads, 1)
             return true;
         };
         bool ok = true;
-        if ((n > 0 || p.split) && !pack_state(0)) { abort_flag = 1; ok = false; }
+        if ((n > 0 || split) && !pack_state(0)) { abort_flag = 1; ok = false; }
         for (int c = 0; c < n && ok; ++c) {
             if (!mbar_wait(&bar_mma, c & 1, p.status, 53)) {
                 abort_flag = 1; ok = false;
@@ -410,9 +416,9 @@ __global__ void __launch_bounds__(kAffineScanThreads, 1)
                     }
             }
             tc_fence_before();
-            if ((c + 1 < n || p.split) && !pack_state(c + 1)) { abort_flag = 1; ok = false; }
+            if ((c + 1 < n || split) && !pack_state(c + 1)) { abort_flag = 1; ok = false; }
         }
-        float* fin = p.split ? p.seg_fin + (size_t)unit * 16384 : (p.s_out ? p.s_out + ((size_t)seq * H + h) * 16384 : nullptr);
+        float* fin = split ? p.seg_fin + (size_t)unit * 16384 : (p.s_out ? p.s_out + ((size_t)seq * H + h) * 16384 : nullptr);
         if (ok && abort_flag == 0 && fin) {
             float4* dst = reinterpret_cast<float4*>(fin + (size_t)v * 128 + col0);
 #pragma unroll
@@ -425,74 +431,180 @@ __global__ void __launch_bounds__(kAffineScanThreads, 1)
 }
 
 // ---------------------------------------------------------------------------------------------
-// split scans, second pass: the true state at the start of every chunk of a sequence's second half,
-//     S = S_mid P + L        (S_mid: final state of the first half; P, L: the chunk's composite and local state)
-// one CTA per chunk-head, plus one per (sequence, head) for the scan's final state (P, L of the half's end).
-// S_mid enters as two bf16 terms (hi + lo), so only P's own bf16 rounding touches the carried state.
+// split scans, second and third pass.
+//   boundary (one CTA per sequence-head): the true state at the start of every segment,
+//       S_1 = final state of unit 0;  S_{k+1} = S_k Pfin_k + Lfin_k;  the scan's final state = S_nseg
+//     a chain of nseg - 1 products with the running state in registers and every Pfin panel fetched up front;
+//     each S_k is left as two bf16 panels (hi, lo: their sum carries float32-class accuracy)
+//   chunks (one CTA per chunk-head of segments >= 1): the true state at the chunk's start,  (S_k hi + S_k lo) P + L
+// so that only P's own bf16 rounding touches the carried state.
 // ---------------------------------------------------------------------------------------------
 struct ScanFixArgs {
     const int* seq_chunk0;
     const int* chunk_seq;
     const int* chunk_len;
-    const float* seg_fin;      // [units][128][128]
+    const float* seg_fin;      // [rec*units][128][128]
+    __nv_bfloat16* seg_start;  // [rec*nseg][2][128][128]
     __nv_bfloat16* Hp;         // [nch][128][128]: local states in, true states out
     float* s_out;              // final state of the scan, V-first [n_seq][H][128][128], or null
-    int H, nslots, bwd;
+    int H, nseg, bwd;
     int* status;
 };
 
-constexpr int kFixSmem = 3 * 32768 + 1024;      // S_mid hi | S_mid lo | P
+constexpr int kFixSmem = 3 * 32768 + 1024;          // S_k hi | S_k lo | P
+constexpr int kBoundarySmem = 5 * 32768 + 1024;     // S_k hi | S_k lo | up to three Pfin panels
+
+// D[tmem] = (A_hi + A_lo) B: A K-major [128 v][128 k] in two bf16 terms, B = P [k][n] MN-major
+__device__ __forceinline__ void issue_hilo_product(uint32_t tmem, const uint8_t* a_hi, const uint8_t* b) {
+    const uint32_t b0 = smem_u32(b);
+    const uint32_t idesc = umma_idesc_bf16(128, 128, kMajorK, kMajorMN);
+#pragma unroll
+    for (int part = 0; part < 2; ++part) {
+        const uint32_t a0 = smem_u32(a_hi + part * 32768);
+#pragma unroll
+        for (int k16 = 0; k16 < 8; ++k16)
+            umma_bf16_ss(tmem, umma_smem_desc_sw128(a0 + (k16 >> 2) * 16384 + (k16 & 3) * 32, 16, 1024),
+                         umma_smem_desc_sw128(b0 + k16 * 2048, 16384, 1024), idesc, (part | k16) != 0);
+    }
+}
+
+__global__ void __launch_bounds__(256, 1)
+    tc_scan_boundary_kernel(const __grid_constant__ CUtensorMap mF, ScanFixArgs p) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* sm = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    __shared__ uint64_t bar_in[3], bar_mma;
+    __shared__ uint32_t tmem_slot;
+    const int seq = blockIdx.x, h = blockIdx.y, H = p.H, units = 2 * p.nseg - 1;
+    const int rec = seq * H + h;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int g = warp >> 2;                        // key half handled by this warpgroup
+    const int v = (warp & 3) * 32 + lane;           // value row = TMEM lane
+    if (tid == 0) {
+        for (int k = 0; k < 3; ++k) mbar_init(&bar_in[k], 1);
+        mbar_init(&bar_mma, 1);
+        mbar_fence_init();
+        for (int k = 1; k < p.nseg; ++k) {          // every segment's final composite, up front
+            mbar_expect_tx(&bar_in[k - 1], 32768);
+            for (int nb = 0; nb < 2; ++nb)
+                tma_load_2d(sm + 65536 + (k - 1) * 32768 + nb * 16384, &mF, &bar_in[k - 1], nb * 64, (rec * units + 2 * k) * 128);
+        }
+    }
+    if (warp == 1) tmem_alloc(&tmem_slot, 128);
+    float cur[64];                                  // S_k[v][64 g .. 64 g + 63]
+    {
+        const float4* src = reinterpret_cast<const float4*>(p.seg_fin + ((size_t)rec * units * 128 + v) * 128 + 64 * g);
+#pragma unroll
+        for (int c = 0; c < 16; ++c) {
+            const float4 a = src[c];
+            cur[4 * c] = a.x; cur[4 * c + 1] = a.y; cur[4 * c + 2] = a.z; cur[4 * c + 3] = a.w;
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = tmem_slot;
+    const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
+    bool ok = true;
+    for (int k = 1; k < p.nseg && ok; ++k) {
+        // S_k as hi + lo: the A operand of this product and, in global memory, of the chunk fix-ups of segment k
+        uint4* ghi = reinterpret_cast<uint4*>(p.seg_start + (((size_t)rec * p.nseg + k) * 2) * 16384 + (size_t)v * 128 + 64 * g);
+        uint4* glo = ghi + 16384 / 8;
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+            uint32_t hi[4], lo[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const __nv_bfloat162 hh = __floats2bfloat162_rn(cur[8 * c + 2 * e], cur[8 * c + 2 * e + 1]);
+                const float2 back = __bfloat1622float2(hh);
+                hi[e] = *reinterpret_cast<const uint32_t*>(&hh);
+                lo[e] = pack_bf16(cur[8 * c + 2 * e] - back.x, cur[8 * c + 2 * e + 1] - back.y);
+            }
+            const uint4 uh = make_uint4(hi[0], hi[1], hi[2], hi[3]), ul = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+            *reinterpret_cast<uint4*>(sm + g * 16384 + sw128_off(v, c)) = uh;
+            *reinterpret_cast<uint4*>(sm + 32768 + g * 16384 + sw128_off(v, c)) = ul;
+            ghi[c] = uh;
+            glo[c] = ul;
+        }
+        fence_async_smem();
+        tc_fence_before();
+        __syncthreads();
+        if (tid == 0) {
+            ok = mbar_wait(&bar_in[k - 1], 0, p.status, 82);
+            if (ok) {
+                tc_fence_after();
+                issue_hilo_product(tmem, sm, sm + 65536 + (k - 1) * 32768);
+                umma_commit(&bar_mma);
+            }
+        }
+        // the segment's local final state, while the product runs
+        float l[64];
+        {
+            const float4* Lp = reinterpret_cast<const float4*>(p.seg_fin + ((size_t)(rec * units + 2 * k - 1) * 128 + v) * 128 + 64 * g);
+#pragma unroll
+            for (int c = 0; c < 16; ++c) {
+                const float4 a = Lp[c];
+                l[4 * c] = a.x; l[4 * c + 1] = a.y; l[4 * c + 2] = a.z; l[4 * c + 3] = a.w;
+            }
+        }
+        ok = mbar_wait(&bar_mma, (uint32_t)(k - 1) & 1, p.status, 83) && ok;
+        ok = __syncthreads_and(ok);
+        tc_fence_after();
+        if (ok) {
+#pragma unroll
+            for (int b = 0; b < 2; ++b) {
+                uint32_t r[32];
+                tmem_ld32(tmem + lane_base + 64 * g + 32 * b, r);
+                tmem_ld_wait();
+#pragma unroll
+                for (int j = 0; j < 32; ++j) cur[32 * b + j] = __uint_as_float(r[j]) + l[32 * b + j];
+            }
+        }
+        tc_fence_before();
+        __syncthreads();      // the next product overwrites the operand buffers and the accumulator
+        tc_fence_after();
+    }
+    if (ok && p.s_out != nullptr) {                 // S_nseg: the scan's final state
+        float4* dst = reinterpret_cast<float4*>(p.s_out + ((size_t)rec * 128 + v) * 128 + 64 * g);
+#pragma unroll
+        for (int c = 0; c < 16; ++c) dst[c] = make_float4(cur[4 * c], cur[4 * c + 1], cur[4 * c + 2], cur[4 * c + 3]);
+    }
+    if (warp == 1) tmem_dealloc(tmem, 128);
+}
 
 __global__ void __launch_bounds__(256, 2)
-    tc_scan_fixup_kernel(const __grid_constant__ CUtensorMap mPp, const __grid_constant__ CUtensorMap mF, ScanFixArgs p) {
+    tc_scan_fixup_kernel(const __grid_constant__ CUtensorMap mPp, const __grid_constant__ CUtensorMap mSs, ScanFixArgs p) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* sm = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     __shared__ uint64_t bar_in, bar_mma;
     __shared__ uint32_t tmem_slot;
     const int h = blockIdx.y, H = p.H;
-    const bool fin = (int)blockIdx.x >= p.nslots;
-    const int slot = fin ? 0 : blockIdx.x;
-    if (!fin && p.chunk_len[slot] == 0) return;
-    const int seq = fin ? (int)blockIdx.x - p.nslots : p.chunk_seq[slot];
+    const int slot = blockIdx.x;
+    if (p.chunk_len[slot] == 0) return;
+    const int seq = p.chunk_seq[slot];
     const int c_begin = p.seq_chunk0[seq], c_end = p.seq_chunk0[seq + 1];
-    const int half = (c_end - c_begin + 1) / 2;
-    if (!fin && (p.bwd ? c_end - 1 - slot : slot - c_begin) < half) return;      // first-half chunks are already true
-    if (fin && p.s_out == nullptr) return;
-    const int unit0 = (seq * H + h) * 3;
+    const int n_total = c_end - c_begin;
+    const int step = p.bwd ? c_end - 1 - slot : slot - c_begin;
+    int k = p.nseg - 1;
+    while (k > 0 && step < seg_begin(k, p.nseg, n_total)) --k;
+    if (k == 0) return;                             // segment 0 holds true states already
+    const int rec = seq * H + h;
     const int ch = slot * H + h;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int g = warp >> 2;                       // key half handled by this warpgroup
-    const int v = (warp & 3) * 32 + lane;          // value row = TMEM lane
+    const int g = warp >> 2;
+    const int v = (warp & 3) * 32 + lane;
     if (tid == 0) {
         mbar_init(&bar_in, 1);
         mbar_init(&bar_mma, 1);
         mbar_fence_init();
-        mbar_expect_tx(&bar_in, 32768);
+        mbar_expect_tx(&bar_in, 3 * 32768);
+        const int srow = (rec * p.nseg + k) * 2 * 128;
         for (int nb = 0; nb < 2; ++nb) {
-            if (fin) tma_load_2d(sm + 65536 + nb * 16384, &mF, &bar_in, nb * 64, (unit0 + 2) * 128);
-            else tma_load_2d(sm + 65536 + nb * 16384, &mPp, &bar_in, nb * 64, ch * 128);
+            tma_load_2d(sm + nb * 16384, &mSs, &bar_in, nb * 64, srow);                 // S_k hi
+            tma_load_2d(sm + 32768 + nb * 16384, &mSs, &bar_in, nb * 64, srow + 128);   // S_k lo
+            tma_load_2d(sm + 65536 + nb * 16384, &mPp, &bar_in, nb * 64, ch * 128);     // P of this chunk
         }
     }
     if (warp == 1) tmem_alloc(&tmem_slot, 128);
-    {   // S_mid[v][64 g .. 64 g + 63] as hi + lo bf16, K-major swizzled
-        const float4* src = reinterpret_cast<const float4*>(p.seg_fin + ((size_t)unit0 * 128 + v) * 128 + 64 * g);
-#pragma unroll
-        for (int c = 0; c < 8; ++c) {
-            const float4 a = src[2 * c], b = src[2 * c + 1];
-            const float f[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
-            uint32_t hi[4], lo[4];
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const __nv_bfloat162 hh = __floats2bfloat162_rn(f[2 * e], f[2 * e + 1]);
-                const float2 back = __bfloat1622float2(hh);
-                hi[e] = *reinterpret_cast<const uint32_t*>(&hh);
-                lo[e] = pack_bf16(f[2 * e] - back.x, f[2 * e + 1] - back.y);
-            }
-            *reinterpret_cast<uint4*>(sm + g * 16384 + sw128_off(v, c)) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
-            *reinterpret_cast<uint4*>(sm + 32768 + g * 16384 + sw128_off(v, c)) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
-        }
-    }
-    fence_async_smem();
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -503,16 +615,7 @@ __global__ void __launch_bounds__(256, 2)
         ok = mbar_wait(&bar_in, 0, p.status, 80);
         if (ok) {
             tc_fence_after();
-            const uint32_t b0 = smem_u32(sm + 65536);
-            const uint32_t idesc = umma_idesc_bf16(128, 128, kMajorK, kMajorMN);
-#pragma unroll
-            for (int part = 0; part < 2; ++part) {
-                const uint32_t a0 = smem_u32(sm + part * 32768);
-#pragma unroll
-                for (int k16 = 0; k16 < 8; ++k16)
-                    umma_bf16_ss(tmem, umma_smem_desc_sw128(a0 + (k16 >> 2) * 16384 + (k16 & 3) * 32, 16, 1024),
-                                 umma_smem_desc_sw128(b0 + k16 * 2048, 16384, 1024), idesc, (part | k16) != 0);
-            }
+            issue_hilo_product(tmem, sm, sm + 65536);
             umma_commit(&bar_mma);
         }
     }
@@ -525,26 +628,15 @@ __global__ void __launch_bounds__(256, 2)
             uint32_t r[32];
             tmem_ld32(tmem + lane_base + 64 * g + 32 * b, r);
             tmem_ld_wait();
-            if (fin) {
-                const float4* Lp = reinterpret_cast<const float4*>(p.seg_fin + ((size_t)(unit0 + 1) * 128 + v) * 128 + 64 * g + 32 * b);
-                float4* dst = reinterpret_cast<float4*>(p.s_out + (((size_t)seq * H + h) * 128 + v) * 128 + 64 * g + 32 * b);
+            uint4* io = reinterpret_cast<uint4*>(p.Hp + (size_t)ch * 16384 + (size_t)v * 128 + 64 * g + 32 * b);
 #pragma unroll
-                for (int c = 0; c < 8; ++c) {
-                    const float4 l = Lp[c];
-                    dst[c] = make_float4(__uint_as_float(r[4 * c]) + l.x, __uint_as_float(r[4 * c + 1]) + l.y,
-                                         __uint_as_float(r[4 * c + 2]) + l.z, __uint_as_float(r[4 * c + 3]) + l.w);
-                }
-            } else {
-                uint4* io = reinterpret_cast<uint4*>(p.Hp + (size_t)ch * 16384 + (size_t)v * 128 + 64 * g + 32 * b);
-#pragma unroll
-                for (int c = 0; c < 4; ++c) {
-                    float l[8];
-                    unpack_bf16x8(io[c], l);
-                    io[c] = make_uint4(pack_bf16(__uint_as_float(r[8 * c]) + l[0], __uint_as_float(r[8 * c + 1]) + l[1]),
-                                       pack_bf16(__uint_as_float(r[8 * c + 2]) + l[2], __uint_as_float(r[8 * c + 3]) + l[3]),
-                                       pack_bf16(__uint_as_float(r[8 * c + 4]) + l[4], __uint_as_float(r[8 * c + 5]) + l[5]),
-                                       pack_bf16(__uint_as_float(r[8 * c + 6]) + l[6], __uint_as_float(r[8 * c + 7]) + l[7]));
-                }
+            for (int c = 0; c < 4; ++c) {
+                float l[8];
+                unpack_bf16x8(io[c], l);
+                io[c] = make_uint4(pack_bf16(__uint_as_float(r[8 * c]) + l[0], __uint_as_float(r[8 * c + 1]) + l[1]),
+                                   pack_bf16(__uint_as_float(r[8 * c + 2]) + l[2], __uint_as_float(r[8 * c + 3]) + l[3]),
+                                   pack_bf16(__uint_as_float(r[8 * c + 4]) + l[4], __uint_as_float(r[8 * c + 5]) + l[5]),
+                                   pack_bf16(__uint_as_float(r[8 * c + 6]) + l[6], __uint_as_float(r[8 * c + 7]) + l[7]));
             }
         }
     }
@@ -831,6 +923,24 @@ __global__ void __launch_bounds__(256, 3)
 // ---------------------------------------------------------------------------------------------
 // host entries used by the chunk forward / backward when the tensor-core lane is selected
 // ---------------------------------------------------------------------------------------------
+// split scans: segment-start states (and the scan's final state), then the chunk states of segments >= 1
+static int scan_fixup(const simt::Ws& w, const tc::TcWs& t, int n_seq, __nv_bfloat16* panels, float* s_out, int bwd,
+                      const CUtensorMap& mPp, const CUtensorMap& mF, cudaStream_t st) {
+    using namespace tc;
+    CUtensorMap mSs;
+    if (make_map_bf16(&mSs, t.seg_start, (uint64_t)n_seq * w.H * t.nseg * 2 * 128, 128, 64, 128)) return KDA_ERR_CUDA;
+    if (cudaFuncSetAttribute(tc_scan_fixup_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kFixSmem) != cudaSuccess ||
+        cudaFuncSetAttribute(tc_scan_boundary_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kBoundarySmem) != cudaSuccess)
+        return KDA_ERR_CUDA;
+    ScanFixArgs f;
+    f.seq_chunk0 = w.seq_chunk0; f.chunk_seq = w.chunk_seq; f.chunk_len = w.chunk_len; f.seg_fin = t.seg_fin; f.seg_start = t.seg_start;
+    f.Hp = panels; f.s_out = s_out; f.H = w.H; f.nseg = t.nseg; f.bwd = bwd; f.status = t.status;
+    KDA_LAUNCH("tc_scan_boundary_kernel", st, tc_scan_boundary_kernel<<<dim3(n_seq, w.H), 256, kBoundarySmem, st>>>(mF, f));
+    if (int e = launch_status()) return e;
+    KDA_LAUNCH("tc_scan_fixup_kernel", st, tc_scan_fixup_kernel<<<dim3(w.nslots, w.H), 256, kFixSmem, st>>>(mPp, mSs, f));
+    return launch_status();
+}
+
 int tc_scan_forward(const simt::Ws& w, const tc::TcWs& t, int n_seq, int tokens, const float* h0, float* final_state, void* o,
                     const tc::NormEpilogue& norm, cudaStream_t st) {
     using namespace tc;
@@ -860,23 +970,19 @@ int tc_scan_forward(const simt::Ws& w, const tc::TcWs& t, int n_seq, int tokens,
     if (int e = launch_status()) return e;
     AffineScanArgs a;
     a.seq_chunk0 = w.seq_chunk0; a.chunk_tok0 = w.chunk_tok0; a.chunk_len = w.chunk_len; a.decay_end = t.decay_end; a.s_in = h0; a.s_out = final_state;
-    a.H = w.H; a.status = t.status; a.split = t.split; a.seg_fin = t.seg_fin;
+    a.H = w.H; a.status = t.status; a.nseg = t.nseg; a.seg_fin = t.seg_fin;
+    const int units = 2 * t.nseg - 1;
     CUtensorMap mPp = mH, mF = mH;
-    if (t.split) {
+    if (t.nseg > 1) {
         if (make_map_bf16(&mPp, t.Pp, nch * 128, 128, 64, 128) ||
-            make_map_bf16(&mF, t.fin_panel, (uint64_t)n_seq * w.H * 3 * 128, 128, 64, 128))
+            make_map_bf16(&mF, t.fin_panel, (uint64_t)n_seq * w.H * units * 128, 128, 64, 128))
             return KDA_ERR_CUDA;
     }
     KDA_LAUNCH("tc_affine_scan_fwd_kernel", st,
-               tc_affine_scan_kernel<false><<<dim3(n_seq * (t.split ? 3 : 1), w.H), kAffineScanThreads, kAffineScanSmem, st>>>(mP, mUT, mE, mH, mPp, mF, a));
+               tc_affine_scan_kernel<false><<<dim3(n_seq * units, w.H), kAffineScanThreads, kAffineScanSmem, st>>>(mP, mUT, mE, mH, mPp, mF, a));
     if (int e = launch_status()) return e;
-    if (t.split) {
-        if (cudaFuncSetAttribute(tc_scan_fixup_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kFixSmem) != cudaSuccess) return KDA_ERR_CUDA;
-        ScanFixArgs f;
-        f.seq_chunk0 = w.seq_chunk0; f.chunk_seq = w.chunk_seq; f.chunk_len = w.chunk_len; f.seg_fin = t.seg_fin; f.Hp = t.Hp;
-        f.s_out = final_state; f.H = w.H; f.nslots = w.nslots; f.bwd = 0; f.status = t.status;
-        KDA_LAUNCH("tc_scan_fixup_kernel", st, tc_scan_fixup_kernel<<<dim3(w.nslots + n_seq, w.H), 256, kFixSmem, st>>>(mPp, mF, f));
-        if (int e = launch_status()) return e;
+    if (t.nseg > 1) {
+        if (int e = scan_fixup(w, t, n_seq, t.Hp, final_state, 0, mPp, mF, st)) return e;
     }
     ChunkOutArgs oa;
     oa.chunk_tok0 = w.chunk_tok0; oa.chunk_len = w.chunk_len; oa.ZT = t.fwd_only ? nullptr : t.ZT; oa.o = static_cast<__nv_bfloat16*>(o); oa.H = w.H;
@@ -906,23 +1012,19 @@ int tc_scan_backward(const simt::Ws& w, const simt::Scr& s, const tc::TcWs& t, i
         return KDA_ERR_CUDA;
     AffineScanArgs a;
     a.seq_chunk0 = w.seq_chunk0; a.chunk_tok0 = w.chunk_tok0; a.chunk_len = w.chunk_len; a.decay_end = t.decay_end; a.s_in = d_final; a.s_out = dh0;
-    a.H = w.H; a.status = t.status; a.split = t.split; a.seg_fin = t.seg_fin;
+    a.H = w.H; a.status = t.status; a.nseg = t.nseg; a.seg_fin = t.seg_fin;
+    const int units = 2 * t.nseg - 1;
     CUtensorMap mPp = mdH, mF = mdH;
-    if (t.split) {
+    if (t.nseg > 1) {
         if (make_map_bf16(&mPp, t.Pp, nch * 128, 128, 64, 128) ||
-            make_map_bf16(&mF, t.fin_panel, (uint64_t)n_seq * w.H * 3 * 128, 128, 64, 128))
+            make_map_bf16(&mF, t.fin_panel, (uint64_t)n_seq * w.H * units * 128, 128, 64, 128))
             return KDA_ERR_CUDA;
     }
     KDA_LAUNCH("tc_affine_scan_bwd_kernel", st,
-               tc_affine_scan_kernel<true><<<dim3(n_seq * (t.split ? 3 : 1), w.H), kAffineScanThreads, kAffineScanSmem, st>>>(mP, mRm, mdO, mdH, mPp, mF, a));
+               tc_affine_scan_kernel<true><<<dim3(n_seq * units, w.H), kAffineScanThreads, kAffineScanSmem, st>>>(mP, mRm, mdO, mdH, mPp, mF, a));
     if (int e = launch_status()) return e;
-    if (t.split) {
-        if (cudaFuncSetAttribute(tc_scan_fixup_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kFixSmem) != cudaSuccess) return KDA_ERR_CUDA;
-        ScanFixArgs f;
-        f.seq_chunk0 = w.seq_chunk0; f.chunk_seq = w.chunk_seq; f.chunk_len = w.chunk_len; f.seg_fin = t.seg_fin; f.Hp = t.dHp;
-        f.s_out = dh0; f.H = w.H; f.nslots = w.nslots; f.bwd = 1; f.status = t.status;
-        KDA_LAUNCH("tc_scan_fixup_kernel", st, tc_scan_fixup_kernel<<<dim3(w.nslots + n_seq, w.H), 256, kFixSmem, st>>>(mPp, mF, f));
-        if (int e = launch_status()) return e;
+    if (t.nseg > 1) {
+        if (int e = scan_fixup(w, t, n_seq, t.dHp, dh0, 1, mPp, mF, st)) return e;
     }
     ChunkDzArgs da;
     da.chunk_tok0 = w.chunk_tok0; da.chunk_len = w.chunk_len; da.dZT = t.dZT; da.H = w.H; da.status = t.status;

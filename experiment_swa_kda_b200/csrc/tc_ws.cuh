@@ -22,9 +22,11 @@ struct TcWs {
     __nv_bfloat16* Pn;          // [nch][128][128]  W^T E: [key k][key k'], the state-to-state part of the chunk transition
     __nv_bfloat16* RmT;         // [nch][128][64]   (R - A W)^T: [key][token]
     __nv_bfloat16* Pp;          // [nch][128][128]  split scans only: composite state-to-state maps at each chunk start
-    __nv_bfloat16* fin_panel;   // [n_seq*H*3][128][128]  split scans only: final state of every scan unit as a bf16 panel
-    float* seg_fin;             // [n_seq*H*3][128][128]  split scans only: the same in float32
-    int split;                  // 1: every (sequence, head) scan runs as three units (see AffineScanArgs)
+    __nv_bfloat16* fin_panel;   // [n_seq*H*units][128][128]  split scans only: final state of every scan unit as a bf16 panel
+    float* seg_fin;             // [n_seq*H*units][128][128]  split scans only: the same in float32
+    __nv_bfloat16* seg_start;   // [n_seq*H*nseg][2][128][128] split scans only: true state at the start of each segment as two
+                                //                             bf16 panels (hi, lo) whose sum carries float32-class accuracy
+    int nseg;                   // scan segments per (sequence, head): 1 (no split), 2 or 4; units = 2 * nseg - 1
     float* decay_end;           // [nch][128]       exp(G_end)
     int* status;                // device status word (0 = ok); points at the workspace's word (simt::Ws::status)
     int fwd_only;               // 1: the backward-only panels (T, M~, Z^T, dH', dZ^T, Rm^T) have no storage and are not written
@@ -43,9 +45,13 @@ struct NormEpilogue {
 
 // Scans are split when a fixed-length batch has so few (sequence, head) recurrences that most SMs would idle behind
 // them, and the sequences are long enough for half a chain to outweigh the fix-up pass.
-inline int scan_split(const KdaChunkShape& sh) {
+inline int scan_segments(const KdaChunkShape& sh) {
     const bool fixed = sh.seq_len > 0 && (long long)sh.n_seq * sh.seq_len == sh.tokens;
-    return (fixed && sh.n_seq * sh.heads * 3 <= 148 && sh.seq_len >= 16 * 64) ? 1 : 0;
+    if (!fixed) return 1;
+    const int rec = sh.n_seq * sh.heads, chunks = (sh.seq_len + 63) / 64;
+    if (rec * 7 <= 148 && chunks >= 32) return 4;
+    if (rec * 3 <= 148 && chunks >= 16) return 2;
+    return 1;
 }
 
 inline TcWs carve_tc(const KdaChunkShape& sh, void* mem, size_t* bytes = nullptr) {
@@ -66,11 +72,12 @@ inline TcWs carve_tc(const KdaChunkShape& sh, void* mem, size_t* bytes = nullptr
     t.dZT = c.take<__nv_bfloat16>(bw * nch * 8192);
     t.Pn = c.take<__nv_bfloat16>(nch * 16384);
     t.RmT = c.take<__nv_bfloat16>(bw * nch * 8192);
-    t.split = scan_split(sh);
-    const size_t units = t.split ? (size_t)sh.n_seq * sh.heads * 3 : 0;
-    t.Pp = c.take<__nv_bfloat16>(t.split ? nch * 16384 : 0);
+    t.nseg = scan_segments(sh);
+    const size_t units = t.nseg > 1 ? (size_t)sh.n_seq * sh.heads * (2 * t.nseg - 1) : 0;
+    t.Pp = c.take<__nv_bfloat16>(t.nseg > 1 ? nch * 16384 : 0);
     t.fin_panel = c.take<__nv_bfloat16>(units * 16384);
     t.seg_fin = c.take<float>(units * 16384);
+    t.seg_start = c.take<__nv_bfloat16>(t.nseg > 1 ? (size_t)sh.n_seq * sh.heads * t.nseg * 2 * 16384 : 0);
     t.decay_end = c.take<float>(nch * 128);
     t.status = c.take<int>(64);
     t.fwd_only = sh.forward_only ? 1 : 0;
