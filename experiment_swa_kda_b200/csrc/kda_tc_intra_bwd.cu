@@ -23,12 +23,6 @@
 namespace kda {
 namespace tc {
 
-#ifdef KDA_PHASE_TIMING
-#define KDA_TICKB(n) do { if (threadIdx.x == 0 && blockIdx.y == 0 && (blockIdx.x == 0 || blockIdx.x == 100)) tick[n] = clock64(); } while (0)
-#else
-#define KDA_TICKB(n) do { } while (0)
-#endif
-
 int make_map_bf16(CUtensorMap* m, const void* ptr, uint64_t rows, uint64_t cols, uint32_t box_cols, uint32_t box_rows);
 
 namespace {
@@ -37,8 +31,11 @@ __device__ __forceinline__ uint32_t pk2(float a, float b) {
     __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
     return *reinterpret_cast<uint32_t*>(&h);
 }
-__device__ __forceinline__ void st16(uint8_t* base, uint32_t off, float x) {
-    *reinterpret_cast<__nv_bfloat16*>(base + off) = __float2bfloat16(x);
+// one MUFU: the operands here are decay factors in [e^-75, 1], far from the flush-to-zero and overflow ends
+__device__ __forceinline__ float rcp_approx(float x) {
+    float y;
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
 }
 __device__ __forceinline__ float ld16(const uint8_t* base, uint32_t off) {
     return __bfloat162float(*reinterpret_cast<const __nv_bfloat16*>(base + off));
@@ -122,15 +119,11 @@ __global__ void __launch_bounds__(512, 1)
     __shared__ uint32_t tmem_slot;
     __shared__ float dA_diag[64];      // dA[i][i]: applied to dq, dk in float32, outside the pull-back products
 
-#ifdef KDA_PHASE_TIMING
-    long long tick[20];
-#endif
     const int slot = blockIdx.x, h = blockIdx.y, H = p.H;
     const int len = p.chunk_len[slot];
     if (len == 0) return;
     const int tok0 = p.chunk_tok0[slot];
     const int ch = slot * H + h;
-    KDA_TICKB(0);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int I = warp >> 2;             // row block of this thread
     const int d = tid & 127;             // channel (and TMEM lane) of this thread
@@ -189,7 +182,6 @@ __global__ void __launch_bounds__(512, 1)
         for (int r = 0; r < 16; ++r) G[r] += pre;
         cref[I * 128 + d] = G[0];
     }
-    KDA_TICKB(1);
     bool ok = mbar_wait(&bar_in, 0, p.status, 40);
     if (len < 64 && ok) {
         // rows past a ragged tail hold the next sequence's tokens: blank them in the dO and v tiles, which feed UMMAs
@@ -204,7 +196,15 @@ __global__ void __launch_bounds__(512, 1)
     }
     ok = __syncthreads_and(ok);          // also publishes cref
     const float egend = __expf(gend);
-    KDA_TICKB(2);
+    // From here on only decay factors relative to this thread's own block reference cI = G[first row of the block] are
+    // needed: E[r] = e^{G[r] - cI} (in (0, 1], at least e^-75), its reciprocal, and the two per-thread scalars that move
+    // the reference to the chunk start (e^{cI}) and to the chunk end (e^{gend - cI}).  One exponential per row instead
+    // of eight, and the operand panels and the gradient assembly use bit-identical factors by construction.
+    const float cI = G[0];
+    const float eCI = __expf(cI), eEndI = __expf(gend - cI);
+#pragma unroll
+    for (int r = 0; r < 16; ++r) G[r] = __expf(G[r] - cI);
+    float (&E)[16] = G;
 
     // TMEM columns
     constexpr uint32_t cDa = 0, cDb = 64, cDc = 128, cDd = 192, cDg = 256, cDf = 320, cDe = 384;
@@ -263,16 +263,19 @@ __global__ void __launch_bounds__(512, 1)
             }
             qn[r] = qv * rowv[i] * p.scale;
             kn[r] = kv * rowv[64 + i];
-            // Q' = e^G k (K-major, rows = token) for Xraw^T -= Q' dW^T
-            st16(Qp, eoff(i, d, 8192), __expf(G[r]) * kn[r]);
         }
+        // Q' = e^G k for Xraw^T -= Q' dW^T, stored [key d][token] (MN-major A): this thread's 16 tokens are 32
+        // contiguous bytes of row d
+        uint32_t w[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) w[e] = pk2(E[2 * e] * eCI * kn[2 * e], E[2 * e + 1] * eCI * kn[2 * e + 1]);
+        *reinterpret_cast<uint4*>(Qp + sw128_off(d, 2 * I)) = make_uint4(w[0], w[1], w[2], w[3]);
+        *reinterpret_cast<uint4*>(Qp + sw128_off(d, 2 * I + 1)) = make_uint4(w[4], w[5], w[6], w[7]);
     }
-    KDA_TICKB(3);
     ok = ok && mbar_wait(&bar_mma, 0, p.status, 41);
     ok = __syncthreads_and(ok);
     tc_fence_after();
 
-    KDA_TICKB(4);
     // ================================================================ phase 2a: first read-out
     float dqn[16], dkn[16], dG[16];
     float ge_part = 0.f;
@@ -288,37 +291,47 @@ __global__ void __launch_bounds__(512, 1)
         tmem_ld16(tmem + lane_base + cDa + 16 * I, t);
 #pragma unroll
         for (int r = 0; r < 16; ++r) {
-            dqn[r] = t[r] * __expf(G[r]);
+            dqn[r] = t[r] * (E[r] * eCI);
             dG[r] = dqn[r] * qn[r];
         }
         tmem_ld16(tmem + lane_base + cDc + 16 * I, t);
 #pragma unroll
         for (int r = 0; r < 16; ++r) {
-            const float ee = __expf(gend - G[r]);
+            const float ee = rcp_approx(E[r]) * eEndI;
             const float eE = t[r] * kn[r] * ee;    // dE * E
             dkn[r] = t[r] * ee;
             dG[r] -= eE;
             ge_part += eE;
         }
-        // dv = beta dP
+        // dv = beta dP, staged [token][channel] in the state-panel region (its products and dD are done) so that it
+        // leaves as 16-byte row segments
         tmem_ld16(tmem + lane_base + cDd + 16 * I, t);
+        __nv_bfloat16* tv = reinterpret_cast<__nv_bfloat16*>(sm + kR1);
 #pragma unroll
-        for (int r = 0; r < 16; ++r) {
-            const int i = 16 * I + r;
-            if (i < len) p.dv[col + (size_t)i * rstride] = __float2bfloat16(rowv[128 + i] * t[r]);
-        }
+        for (int r = 0; r < 16; ++r) tv[(16 * I + r) * 128 + d] = __float2bfloat16(rowv[128 + 16 * I + r] * t[r]);
     }
     fence_async_smem();
     tc_fence_before();
     __syncthreads();
+    if (ok) {
+        const __nv_bfloat16* tv = reinterpret_cast<const __nv_bfloat16*>(sm + kR1);
+        const int c = tid & 15;
+#pragma unroll
+        for (int pass = 0; pass < 2; ++pass) {
+            const int i = pass * 32 + (tid >> 4);
+            if (i < len)
+                *reinterpret_cast<uint4*>(p.dv + ((size_t)(tok0 + i) * H + h) * 128 + 8 * c) =
+                    *reinterpret_cast<const uint4*>(tv + i * 128 + 8 * c);
+        }
+    }
     if (ok && tid == 0) {
         tc_fence_after();
-        const uint32_t id64_neg = umma_idesc_bf16(64, 64, kMajorK, kMajorMN, 1);
+        const uint32_t id64_neg = umma_idesc_bf16(64, 64, kMajorMN, kMajorMN, 1);
         const uint32_t id_k_mn = umma_idesc_bf16(128, 64, kMajorK, kMajorMN);
         const uint32_t aQ = smem_u32(Qp), aW = smem_u32(dWs), bT = smem_u32(Ts);
 #pragma unroll
         for (int k16 = 0; k16 < 8; ++k16)     // Xraw^T -= Q' dW^T   (dW^T panel read as MN-major B: [key][token])
-            umma_bf16_ss(tmem + cDf, umma_smem_desc_sw128(aQ + (k16 >> 2) * 8192 + (k16 & 3) * 32, 16, 1024),
+            umma_bf16_ss(tmem + cDf, umma_smem_desc_sw128(aQ + k16 * 2048, 8192, 1024),
                          umma_smem_desc_sw128(aW + k16 * 2048, 8192, 1024), id64_neg, 1);
 #pragma unroll
         for (int k16 = 0; k16 < 4; ++k16)     // (T^T dW)^T = dW^T T ;  dQ = -that
@@ -326,12 +339,10 @@ __global__ void __launch_bounds__(512, 1)
                          umma_smem_desc_sw128(bT + k16 * 2048, 8192, 1024), id_k_mn, k16 > 0);
         umma_commit(&bar_mma);
     }
-    KDA_TICKB(5);
     ok = ok && mbar_wait(&bar_mma, 1, p.status, 42);
     ok = __syncthreads_and(ok);
     tc_fence_after();
 
-    KDA_TICKB(6);
     // ================================================================ phase 3: X, Y, dM
     // M = 64 accumulators keep row (16*w + l) in lane l < 16 of warp w < 4.  tcgen05.ld is warp-collective, so all 32
     // lanes of those warps run the loads; lanes >= 16 mirror a row and never store.  All four warp groups see the same lanes, so each takes 16 of the 64 columns.
@@ -364,7 +375,7 @@ __global__ void __launch_bounds__(512, 1)
         tmem_ld16(tmem + lane_base + cDe + 16 * I, t);
 #pragma unroll
         for (int r = 0; r < 16; ++r) {
-            const float dQ = -t[r] * rowv[128 + 16 * I + r] * __expf(G[r]);   // dQ * beta * e^G
+            const float dQ = -t[r] * rowv[128 + 16 * I + r] * (E[r] * eCI);   // dQ * beta * e^G
             dkn[r] += dQ;
             dG[r] += dQ * kn[r];
         }
@@ -381,7 +392,6 @@ __global__ void __launch_bounds__(512, 1)
                          umma_smem_desc_sw128(smem_u32(XT) + k16 * 32, 16, 1024), id, k16 > 0);
         umma_commit(&bar_mma);
     }
-    KDA_TICKB(7);
     ok = ok && mbar_wait(&bar_mma, 0, p.status, 43);
     ok = __syncthreads_and(ok);
     tc_fence_after();
@@ -407,15 +417,13 @@ __global__ void __launch_bounds__(512, 1)
                          umma_smem_desc_sw128(smem_u32(Ts) + k16 * 32, 16, 1024), id, k16 > 0);
         umma_commit(&bar_mma);
     }
-    KDA_TICKB(8);
     ok = ok && mbar_wait(&bar_mma, 1, p.status, 44);
     ok = __syncthreads_and(ok);
     tc_fence_after();
 
-    KDA_TICKB(9);
     // ================================================================ phase 4: pull-back operands
-    uint8_t* Sk = sm + kR1;           // k~_I panels: [I][2 blocks][64 rows s x 128 B]     MN-major A
-    uint8_t* Xk = sm + kR3;           // target stacks: [I][2 blocks][32 rows x 128 B]     MN-major A
+    uint8_t* Sk = sm + kR1;           // k~_I source panels: [I][128 rows d][64 s]                        K-major A
+    uint8_t* Xk = sm + kR3;           // target stacks: [I / 2][128 rows d][32 rows of I even | 32 of I odd] K-major A
     uint8_t* DAt = sm + kR7;          // [I][32 rows: 16 dA rows, 16 beta*dM rows][64 s]   K-major / MN-major B
     {
         // row j of dM = -stril(Y T^T) and of dA = tril(dO Z^T), 16 source columns per warp group;
@@ -459,30 +467,41 @@ __global__ void __launch_bounds__(512, 1)
             dbp[I * 64 + j] = dbeta_acc;
         }
     }
-    KDA_TICKB(13);
     {
+        // Both operand families are stored transposed, [channel d][row], so that this thread's 16 rows are contiguous
+        // bytes of row d and leave as 16-byte stores (K-major A operands of the pull-back products).
         const float c0 = cref[d], c1 = cref[128 + d], c2 = cref[256 + d], c3 = cref[384 + d];
-        const float cI = I == 0 ? c0 : (I == 1 ? c1 : (I == 2 ? c2 : c3));
         const float fb0 = __expf(c1 - c0), fb1 = __expf(c2 - c1), fb2 = __expf(c3 - c2);
+        uint8_t* X = Xk + (I >> 1) * 16384;      // two target blocks share a panel: 32 stack rows each
+        const int xc = (I & 1) * 4;
 #pragma unroll
-        for (int r = 0; r < 16; ++r) {
-            const int i = 16 * I + r;
-            const float tq = __expf(G[r] - cI);
-            // targets of this row's own block
-            uint8_t* X = Xk + I * 8192;
-            st16(X, eoff(r, d, 4096), qn[r] * tq);
-            st16(X, eoff(16 + r, d, 4096), kn[r] * tq);
-            // this row as a source for its own and every later block
-            float f = kn[r] * __expf(cI - G[r]);
-            float s0v = 0.f, s1v = 0.f, s2v = 0.f, s3v = 0.f;
-            if (I == 0) { s0v = f; f *= fb0; }
-            if (I <= 1) { s1v = f; f *= fb1; }
-            if (I <= 2) { s2v = f; f *= fb2; }
-            s3v = f;
-            st16(Sk, eoff(i, d, 8192), s0v);
-            st16(Sk + 16384, eoff(i, d, 8192), s1v);
-            st16(Sk + 32768, eoff(i, d, 8192), s2v);
-            st16(Sk + 49152, eoff(i, d, 8192), s3v);
+        for (int hf = 0; hf < 2; ++hf) {
+            uint32_t a[4], b[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int r = 8 * hf + 2 * e;
+                a[e] = pk2(qn[r] * E[r], qn[r + 1] * E[r + 1]);      // q~ rows of this block
+                b[e] = pk2(kn[r] * E[r], kn[r + 1] * E[r + 1]);      // k~ rows of this block
+            }
+            *reinterpret_cast<uint4*>(X + sw128_off(d, xc + hf)) = make_uint4(a[0], a[1], a[2], a[3]);
+            *reinterpret_cast<uint4*>(X + sw128_off(d, xc + 2 + hf)) = make_uint4(b[0], b[1], b[2], b[3]);
+            // these rows as sources of their own and every later block (zero for the earlier ones: the products sum
+            // over all 64 source rows)
+            uint32_t w[4][4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int r = 8 * hf + 2 * e;
+                float f0 = kn[r] * rcp_approx(E[r]), f1 = kn[r + 1] * rcp_approx(E[r + 1]);
+                w[0][e] = w[1][e] = w[2][e] = 0u;
+                if (I == 0) { w[0][e] = pk2(f0, f1); f0 *= fb0; f1 *= fb0; }
+                if (I <= 1) { w[1][e] = pk2(f0, f1); f0 *= fb1; f1 *= fb1; }
+                if (I <= 2) { w[2][e] = pk2(f0, f1); f0 *= fb2; f1 *= fb2; }
+                w[3][e] = pk2(f0, f1);
+            }
+#pragma unroll
+            for (int ver = 0; ver < 4; ++ver)
+                *reinterpret_cast<uint4*>(Sk + ver * 16384 + sw128_off(d, 2 * I + hf)) =
+                    make_uint4(w[ver][0], w[ver][1], w[ver][2], w[ver][3]);
         }
     }
     fence_async_smem();
@@ -495,39 +514,36 @@ __global__ void __launch_bounds__(512, 1)
     const uint32_t cCP[4] = {0, 64, 128, 320};
     if (ok && tid == 0) {
         tc_fence_after();
-        const uint32_t id_rp = umma_idesc_bf16(128, 32, kMajorMN, kMajorK);
-        const uint32_t id_cp = umma_idesc_bf16(128, 64, kMajorMN, kMajorMN);
+        const uint32_t id_rp = umma_idesc_bf16(128, 32, kMajorK, kMajorK);
+        const uint32_t id_cp = umma_idesc_bf16(128, 64, kMajorK, kMajorMN);
 #pragma unroll
         for (int Ib = 0; Ib < 4; ++Ib) {
-            const uint32_t aS = smem_u32(Sk + Ib * 16384), aX = smem_u32(Xk + Ib * 8192), bD = smem_u32(DAt + Ib * 4096);
+            const uint32_t aS = smem_u32(Sk + Ib * 16384), aX = smem_u32(Xk + (Ib >> 1) * 16384) + (Ib & 1) * 64;
+            const uint32_t bD = smem_u32(DAt + Ib * 4096);
 #pragma unroll
             for (int k16 = 0; k16 < 4; ++k16)     // RP_I^T[d][n] = sum_s k~_I[s][d] * rows_I[n][s]
-                umma_bf16_ss(tmem + cRP + 32 * Ib, umma_smem_desc_sw128(aS + k16 * 2048, 8192, 1024),
+                umma_bf16_ss(tmem + cRP + 32 * Ib, umma_smem_desc_sw128(aS + k16 * 32, 16, 1024),
                              umma_smem_desc_sw128(bD + k16 * 32, 16, 1024), id_rp, k16 > 0);
 #pragma unroll
             for (int k16 = 0; k16 < 2; ++k16)     // CP_I^T[d][s] = sum_{n<32} stack_I[n][d] * rows_I[n][s]
-                umma_bf16_ss(tmem + cCP[Ib], umma_smem_desc_sw128(aX + k16 * 2048, 4096, 1024),
+                umma_bf16_ss(tmem + cCP[Ib], umma_smem_desc_sw128(aX + k16 * 32, 16, 1024),
                              umma_smem_desc_sw128(bD + k16 * 2048, 4096, 1024), id_cp, k16 > 0);
         }
         umma_commit(&bar_mma);
     }
-    KDA_TICKB(10);
     ok = ok && mbar_wait(&bar_mma, 0, p.status, 45);
     ok = __syncthreads_and(ok);
     tc_fence_after();
 
-    KDA_TICKB(11);
     // ================================================================ phase 5: assemble the gradients
     {
         float t[16];
         const float c0 = cref[d], c1 = cref[128 + d], c2 = cref[256 + d], c3 = cref[384 + d];
-        const float cOwn = I == 0 ? c0 : (I == 1 ? c1 : (I == 2 ? c2 : c3));
         // decay factors of this thread's rows relative to its own block reference: e1 = e^{G - c_own} (<= 1) for the
         // row parts, e2 = e^{c_own - G} for the column parts (a later block I' contributes e^{c_I' - c_own} e2)
-        float e1[16];
+        const float (&e1)[16] = E;
 #pragma unroll
         for (int r = 0; r < 16; ++r) {
-            e1[r] = __expf(G[r] - cOwn);
             const float dd = dA_diag[16 * I + r];
             dqn[r] += dd * kn[r];
             dkn[r] += dd * qn[r];
@@ -555,7 +571,7 @@ __global__ void __launch_bounds__(512, 1)
         float fsrc[16], esrc[16];
 #pragma unroll
         for (int r = 0; r < 16; ++r) {
-            esrc[r] = __expf(cOwn - G[r]);
+            esrc[r] = rcp_approx(E[r]);
             fsrc[r] = kn[r] * esrc[r];
         }
         const float fb0 = __expf(c1 - c0), fb1 = __expf(c2 - c1), fb2 = __expf(c3 - c2);
@@ -579,7 +595,6 @@ __global__ void __launch_bounds__(512, 1)
             }
         }
     }
-    KDA_TICKB(14);
     // chunk-end term and reverse cumulative sum of dG over the 64 rows of this channel
     float suffix = 0.f;
     {
@@ -598,7 +613,6 @@ __global__ void __launch_bounds__(512, 1)
         for (int Ib = 3; Ib > 0; --Ib)
             if (Ib > I) suffix += tot[Ib * 128 + d];
     }
-    KDA_TICKB(15);
     // L2-normalisation VJP needs per-row dots over the channels: unit k is kn, unit q is qn / scale
     const float inv_scale = p.scale != 0.f ? 1.0f / p.scale : 0.f;
     {
@@ -627,14 +641,12 @@ __global__ void __launch_bounds__(512, 1)
         // lane L holds value L = (row L/2, q or k): quadrant partial
         dots[(16 * I + (lane >> 1)) * 8 + (warp & 3) * 2 + (lane & 1)] = vals[0];
     }
-    KDA_TICKB(16);
     __syncthreads();
     if (tid < 128) {          // the four quadrant partials of (row, q|k) -> one number, in place
         const int i = tid >> 1, w = tid & 1;
         dots[i * 8 + w] = dots[i * 8 + w] + dots[i * 8 + 2 + w] + dots[i * 8 + 4 + w] + dots[i * 8 + 6 + w];
     }
     __syncthreads();
-    KDA_TICKB(17);
     {
         // The gradients of this thread's 16 rows go through shared memory (the source-panel region is free now), so
         // that they leave as 16-byte row segments instead of one 2-byte store per row, tensor and thread.
@@ -684,17 +696,6 @@ __global__ void __launch_bounds__(512, 1)
             }
         }
     }
-    KDA_TICKB(12);
-#ifdef KDA_PHASE_TIMING
-    if (threadIdx.x == 0 && blockIdx.y == 0 && (blockIdx.x == 0 || blockIdx.x == 100))
-        printf("intra_bwd blk %d: setup+g %lld | tma wait %lld | issue1+dD/Q' %lld | mma1 wait %lld | readout2a %lld | mma2 wait %lld | X^T %lld | Y wait %lld | Ywrite+dM wait %lld | p4 operands %lld | mma pb wait %lld | assemble %lld | total %lld\n",
-               blockIdx.x, tick[1] - tick[0], tick[2] - tick[1], tick[3] - tick[2], tick[4] - tick[3], tick[5] - tick[4], tick[6] - tick[5],
-               tick[7] - tick[6], tick[8] - tick[7], tick[9] - tick[8], tick[10] - tick[9], tick[11] - tick[10], tick[12] - tick[11], tick[12] - tick[0]);
-    if (threadIdx.x == 0 && blockIdx.y == 0 && blockIdx.x == 100)
-        printf("   detail: p4 rows %lld | p4 panels %lld || RP/CP reads %lld | sums+sync %lld | shuffles %lld | sync %lld | stores %lld\n",
-               tick[13] - tick[9], tick[10] - tick[13], tick[14] - tick[11], tick[15] - tick[14], tick[16] - tick[15],
-               tick[17] - tick[16], tick[12] - tick[17]);
-#endif
     tc_fence_before();
     __syncthreads();
     if (warp == 0) tmem_dealloc(tmem, 512);
