@@ -498,7 +498,7 @@ def main():
     copy_ms_step = float(t3.item()) / args.steps
 
     # ---- the raw operator surface (torch.ops.nanochat_kda.*), driven like the reference mixer, same timing protocol ----
-    ops_ms_step, ops_launches, ops_error = None, None, None
+    ops_ms_step, ops_launches, ops_error, ops_kernels = None, None, None, None
     try:
         oc = OpsChain(chain)
         for _ in range(3):
@@ -527,6 +527,15 @@ def main():
         if world > 1:
             dist.all_reduce(t4, op=dist.ReduceOp.MAX)
         ops_ms_step = float(t4.item()) / args.steps
+        # where the operator surface spends its launches (eager, the library's launch accounting as below)
+        torch.cuda.synchronize(dev)
+        _lib.profile(True)
+        for _ in range(args.steps):
+            flush.zero_()
+            oc.step()
+        torch.cuda.synchronize(dev)
+        ops_kernels = {k: [n / args.steps, round(tot / n * 1e3, 2)] for k, (n, tot) in _lib.profile_report().items()}
+        _lib.profile(False)
         del oc
     except Exception as exc:      # the operator library is optional for the headline number; say why it is missing
         ops_ms_step = None
@@ -610,7 +619,8 @@ def main():
             "ops_path": ({"ms_per_step": ops_ms_step, "tokens_per_s": chain.tokens() * world / (ops_ms_step * 1e-3),
                           "launches_per_step": ops_launches, "ratio_to_value_arm": ops_ms_step / ms_step,
                           "what": "the same chain through torch.ops.nanochat_kda.* (raw gate / beta logits, activations fused, "
-                                  "forward sidecar instead of a recompute), driven by reference-style autograd Functions"}
+                                  "forward sidecar instead of a recompute), driven by reference-style autograd Functions",
+                          "kernels": ops_kernels}
                          if ops_ms_step else {"unavailable": ops_error}),
             "sharded": sharded,
             "gpu_launches": int(launches), "clocks": clocks, "roofline": roof, "kernels": kern,

@@ -220,7 +220,7 @@ __global__ void __launch_bounds__(kNT, 2)
                         const __grid_constant__ CUtensorMap mWT, const __grid_constant__ CUtensorMap mAT,
                         const __grid_constant__ CUtensorMap mMt, IntraFwdArgs p) {
     extern __shared__ uint8_t smem_raw[];
-    uint8_t* sm = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint8_t* sm = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);   // pointer arithmetic keeps the shared address space
     uint8_t* Sst = sm + kFS;
     uint8_t* vs = sm + kFV;
     uint8_t* Qs = sm + kFQ;

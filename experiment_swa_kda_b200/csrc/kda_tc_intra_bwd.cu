@@ -96,7 +96,7 @@ __global__ void __launch_bounds__(512, 1)
                         const __grid_constant__ CUtensorMap mdZT, const __grid_constant__ CUtensorMap mMt,
                         IntraBwdArgs p) {
     extern __shared__ uint8_t smem_raw[];
-    uint8_t* sm = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint8_t* sm = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);   // pointer arithmetic keeps the shared address space
     uint8_t* Hs = sm + kR1;
     uint8_t* dHs = sm + kR1 + 32768;
     uint8_t* dOs = sm + kR2;

@@ -41,7 +41,7 @@ __global__ void __launch_bounds__(256, 2)
     tc_transition_kernel(const __grid_constant__ CUtensorMap mW, const __grid_constant__ CUtensorMap mE,
                          const __grid_constant__ CUtensorMap mAT, TransArgs p) {
     extern __shared__ uint8_t smem_raw[];
-    uint8_t* sm = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint8_t* sm = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);   // pointer arithmetic keeps the shared address space
     __shared__ uint64_t bar_in, bar_mma;
     __shared__ uint32_t tmem_slot;
     const int slot = blockIdx.x, h = blockIdx.y;
@@ -181,7 +181,7 @@ __global__ void __launch_bounds__(kAffineScanThreads, 1)
                           const __grid_constant__ CUtensorMap mY, const __grid_constant__ CUtensorMap mS,
                           const __grid_constant__ CUtensorMap mS2, const __grid_constant__ CUtensorMap mF, AffineScanArgs p) {
     extern __shared__ uint8_t smem_raw[];
-    uint8_t* sm = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint8_t* sm = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);   // pointer arithmetic keeps the shared address space
     uint8_t* Sop = sm + 2 * kPStage;               // 2 x [2 k-blocks][128 rows x 128 B]: bf16 state panel of step c in c % 2
     __shared__ __align__(16) float dec_ring[4][128];   // exp(G_end) of step c in slot c % 4
     // full: a stage has landed.  free: every product that reads a stage is complete (one per stage, so that the load
@@ -471,7 +471,7 @@ __device__ __forceinline__ void issue_hilo_product(uint32_t tmem, const uint8_t*
 __global__ void __launch_bounds__(256, 1)
     tc_scan_boundary_kernel(const __grid_constant__ CUtensorMap mF, ScanFixArgs p) {
     extern __shared__ uint8_t smem_raw[];
-    uint8_t* sm = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint8_t* sm = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);   // pointer arithmetic keeps the shared address space
     __shared__ uint64_t bar_in[3], bar_mma;
     __shared__ uint32_t tmem_slot;
     const int seq = blockIdx.x, h = blockIdx.y, H = p.H, units = 2 * p.nseg - 1;
@@ -574,7 +574,7 @@ __global__ void __launch_bounds__(256, 1)
 __global__ void __launch_bounds__(256, 2)
     tc_scan_fixup_kernel(const __grid_constant__ CUtensorMap mPp, const __grid_constant__ CUtensorMap mSs, ScanFixArgs p) {
     extern __shared__ uint8_t smem_raw[];
-    uint8_t* sm = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint8_t* sm = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);   // pointer arithmetic keeps the shared address space
     __shared__ uint64_t bar_in, bar_mma;
     __shared__ uint32_t tmem_slot;
     const int h = blockIdx.y, H = p.H;
@@ -674,7 +674,7 @@ __global__ void __launch_bounds__(256, 2)
                         const __grid_constant__ CUtensorMap mR, const __grid_constant__ CUtensorMap mUT,
                         const __grid_constant__ CUtensorMap mAT, const __grid_constant__ CUtensorMap mG, ChunkOutArgs p) {
     extern __shared__ uint8_t smem_raw[];
-    uint8_t* sm = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint8_t* sm = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);   // pointer arithmetic keeps the shared address space
     uint8_t* Zop = sm + kOutZ;                     // [128 rows x 128 B] K-major A operand
     __nv_bfloat16* Ot = reinterpret_cast<__nv_bfloat16*>(sm + kOutO);   // [64 tokens][128 values]
     __shared__ uint64_t bar_in, bar_mma1, bar_mma2;
@@ -838,7 +838,7 @@ __global__ void __launch_bounds__(256, 3)
     tc_chunk_dz_kernel(const __grid_constant__ CUtensorMap mdH, const __grid_constant__ CUtensorMap mE,
                        const __grid_constant__ CUtensorMap mdO, const __grid_constant__ CUtensorMap mAT, ChunkDzArgs p) {
     extern __shared__ uint8_t smem_raw[];
-    uint8_t* sm = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint8_t* sm = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);   // pointer arithmetic keeps the shared address space
     __shared__ uint64_t bar_in, bar_mma;
     __shared__ uint32_t tmem_slot;
     const int slot = blockIdx.x, h = blockIdx.y, H = p.H;
