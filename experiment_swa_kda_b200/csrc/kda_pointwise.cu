@@ -42,7 +42,7 @@ __global__ void gate_fwd_kernel(size_t n_gate, size_t n_beta, int H, int K, int 
         beta[i] = sigmoidf_(ld_io(bl, i, bf16));
 }
 
-constexpr int kGateRows = 64;  // tokens per first-stage reduction block
+constexpr int kGateRows = 32;  // tokens per first-stage reduction block
 
 // stage 1: d_raw, d_beta_logits and per-block column partials of ddt_bias / dA_log
 __global__ void gate_bwd_kernel(int tokens, int H, int K, int bf16, const void* __restrict__ raw,
@@ -77,30 +77,42 @@ __global__ void gate_bwd_kernel(int tokens, int H, int K, int bf16, const void* 
     }
 }
 
-// stage 2: one block per head; fixed summation order
-__global__ void gate_bwd_reduce_kernel(int nblk, int H, int K, const float* __restrict__ part_b,
-                                       const float* __restrict__ part_a, float* __restrict__ ddt_bias,
-                                       float* __restrict__ dA_log) {
-    __shared__ float red[256];
+// stage 2: one block (1024 threads = 32 row segments x 32 columns) per head; fixed summation order
+__global__ void __launch_bounds__(1024) gate_bwd_reduce_kernel(int nblk, int H, int K, const float* __restrict__ part_b,
+                                                               const float* __restrict__ part_a,
+                                                               float* __restrict__ ddt_bias, float* __restrict__ dA_log) {
+    __shared__ float redb[32][33], reda[32][33];
     const int h = blockIdx.x, HK = H * K;
-    float accA = 0.f;
-    for (int kk = threadIdx.x; kk < K; kk += 256) {
-        const int c = h * K + kk;
+    const int lane = threadIdx.x & 31, seg = threadIdx.x >> 5;
+    float accA = 0.f;                      // seg 0 only: this lane's columns of sum_k (dr * x)
+    for (int k0 = 0; k0 < K; k0 += 32) {
+        const int kk = k0 + lane, c = h * K + kk;
         float sb = 0.f, sa = 0.f;
-        for (int b = 0; b < nblk; ++b) {
-            sb += part_b[(size_t)b * HK + c];
-            sa += part_a[(size_t)b * HK + c];
+        if (kk < K)
+            for (int b = seg; b < nblk; b += 32) {
+                sb += part_b[(size_t)b * HK + c];
+                sa += part_a[(size_t)b * HK + c];
+            }
+        redb[seg][lane] = sb;
+        reda[seg][lane] = sa;
+        __syncthreads();
+        if (seg == 0 && kk < K) {
+            float tb = 0.f, ta = 0.f;
+#pragma unroll
+            for (int r = 0; r < 32; ++r) {
+                tb += redb[r][lane];
+                ta += reda[r][lane];
+            }
+            ddt_bias[c] = tb;
+            accA += ta;
         }
-        ddt_bias[c] = sb;
-        accA += sa;
-    }
-    red[threadIdx.x] = accA;
-    __syncthreads();
-    for (int o = 128; o > 0; o >>= 1) {
-        if (threadIdx.x < o) red[threadIdx.x] += red[threadIdx.x + o];
         __syncthreads();
     }
-    if (threadIdx.x == 0) dA_log[h] = red[0];
+    if (seg == 0) {
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) accA += __shfl_xor_sync(0xffffffffu, accA, o);
+        if (lane == 0) dA_log[h] = accA;
+    }
 }
 
 // =============================================================================================
@@ -526,6 +538,103 @@ __device__ __forceinline__ void st_cvec(void* p, size_t i, const float (&s)[VEC]
         *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(p) + i) = u;
     } else {
         *reinterpret_cast<float4*>(reinterpret_cast<float*>(p) + i) = make_float4(s[0], s[1], s[2], s[3]);
+    }
+}
+
+// Gate activations, K % 4 == 0: a thread owns 4 adjacent channels (one head), so raw gate, bias, g and their gradients
+// move as 8- / 16-byte accesses and the head's exp(A_log) is computed once per 4 elements.
+template <bool BF16>
+__global__ void __launch_bounds__(256) gate_fwd4_kernel(unsigned n4, unsigned n_beta, int H, int K, const void* __restrict__ raw,
+                                                        const void* __restrict__ bl, const float* __restrict__ A_log,
+                                                        const float* __restrict__ dt_bias, float lb, float* __restrict__ g,
+                                                        float* __restrict__ beta) {
+    const unsigned hk4 = (unsigned)(H * K) >> 2;
+    const unsigned stride = gridDim.x * blockDim.x;
+    for (unsigned i4 = blockIdx.x * blockDim.x + threadIdx.x; i4 < n4; i4 += stride) {
+        const unsigned c = (i4 % hk4) * 4;
+        const float ea = expf(A_log[c / (unsigned)K]);
+        const float4 bias = *reinterpret_cast<const float4*>(dt_bias + c);
+        float r[4];
+        ld_cvec<4, BF16>(r, raw, (size_t)i4 * 4);
+        float4 o;
+        o.x = lb * sigmoidf_(ea * (r[0] + bias.x));
+        o.y = lb * sigmoidf_(ea * (r[1] + bias.y));
+        o.z = lb * sigmoidf_(ea * (r[2] + bias.z));
+        o.w = lb * sigmoidf_(ea * (r[3] + bias.w));
+        *reinterpret_cast<float4*>(g + (size_t)i4 * 4) = o;
+    }
+    for (unsigned i = blockIdx.x * blockDim.x + threadIdx.x; i < n_beta; i += stride) beta[i] = sigmoidf_(ld_io(bl, i, BF16));
+}
+
+// grid: x = blocks of 128 columns (lane = 4 channels), y = blocks of kGateRows tokens; warp w takes rows w, w + 8, ...
+template <bool BF16>
+__global__ void __launch_bounds__(256) gate_bwd4_kernel(int tokens, int H, int K, const void* __restrict__ raw,
+                                                        const void* __restrict__ bl, const float* __restrict__ A_log,
+                                                        const float* __restrict__ dt_bias, float lb, const float* __restrict__ dg,
+                                                        const float* __restrict__ dbeta, void* __restrict__ d_raw,
+                                                        void* __restrict__ d_bl, float* __restrict__ part_b,
+                                                        float* __restrict__ part_a) {
+    constexpr int RPW = kGateRows / 8;
+    __shared__ float red[2][8][128];
+    const int HK = H * K;
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    const int c = (blockIdx.x * 32 + lane) * 4;
+    const int t0 = blockIdx.y * kGateRows;
+    const bool cok = c < HK;
+    const int cl = cok ? c : 0;
+    const float ea = expf(A_log[cl / K]);
+    const float4 bias = *reinterpret_cast<const float4*>(dt_bias + cl);
+    const float bz[4] = {bias.x, bias.y, bias.z, bias.w};
+    float rv[RPW][4];
+    float4 gv[RPW];
+#pragma unroll
+    for (int j = 0; j < RPW; ++j) {          // every load of the thread in flight at once
+        const int t = min(t0 + w + 8 * j, tokens - 1);
+        ld_cvec<4, BF16>(rv[j], raw, (size_t)t * HK + cl);
+        gv[j] = __ldg(reinterpret_cast<const float4*>(dg + (size_t)t * HK + cl));
+    }
+    float sb[4] = {0.f, 0.f, 0.f, 0.f}, sa[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int j = 0; j < RPW; ++j) {
+        const int t = t0 + w + 8 * j;
+        if (t < tokens && cok) {
+            const float gg[4] = {gv[j].x, gv[j].y, gv[j].z, gv[j].w};
+            float dr[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float x = rv[j][e] + bz[e];
+                const float sg = sigmoidf_(ea * x);
+                dr[e] = gg[e] * lb * sg * (1.f - sg) * ea;
+                sb[e] += dr[e];
+                sa[e] += dr[e] * x;
+            }
+            st_cvec<4, BF16>(d_raw, (size_t)t * HK + c, dr);
+        }
+    }
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+        red[0][w][4 * lane + e] = sb[e];
+        red[1][w][4 * lane + e] = sa[e];
+    }
+    __syncthreads();
+    if (threadIdx.x < 128 && blockIdx.x * 128 + threadIdx.x < HK) {
+        float tb = 0.f, ta = 0.f;
+#pragma unroll
+        for (int r = 0; r < 8; ++r) {
+            tb += red[0][r][threadIdx.x];
+            ta += red[1][r][threadIdx.x];
+        }
+        const size_t o = (size_t)blockIdx.y * HK + blockIdx.x * 128 + threadIdx.x;
+        part_b[o] = tb;
+        part_a[o] = ta;
+    }
+    if (blockIdx.x == 0) {                  // beta logits of this block's rows
+        const int nb = min(kGateRows, tokens - t0) * H;
+        for (int i = threadIdx.x; i < nb; i += 256) {
+            const size_t o = (size_t)t0 * H + i;
+            const float b = sigmoidf_(ld_io(bl, o, BF16));
+            st_io(d_bl, o, BF16, dbeta[o] * b * (1.f - b));
+        }
     }
 }
 
@@ -1279,6 +1388,17 @@ extern "C" int kda_gate_fwd(int32_t tokens, int32_t heads, int32_t key_dim, int3
     if (tokens == 0) return KDA_OK;
     if (!raw_gate || !beta_logits || !A_log || !dt_bias || !g_out || !beta_out) return KDA_ERR_NULL;
     const size_t n = (size_t)tokens * heads * key_dim;
+    cudaStream_t fst = (cudaStream_t)stream;
+    const bool al = ((reinterpret_cast<uintptr_t>(raw_gate) | reinterpret_cast<uintptr_t>(dt_bias) | reinterpret_cast<uintptr_t>(g_out)) % 16) == 0;
+    if (key_dim % 4 == 0 && al && n / 4 < (1ull << 31) && (size_t)tokens * heads < (1ull << 31)) {
+        const unsigned n4 = (unsigned)(n / 4), nb = (unsigned)((size_t)tokens * heads);
+        const int blocks4 = (int)std::min<size_t>(((size_t)n4 + 255) / 256, 148 * 16);
+        if (io_dtype == KDA_DTYPE_BF16)
+            KDA_LAUNCH("gate_fwd_kernel", fst, pw::gate_fwd4_kernel<true><<<blocks4, 256, 0, fst>>>(n4, nb, heads, key_dim, raw_gate, beta_logits, A_log, dt_bias, lower_bound, g_out, beta_out));
+        else
+            KDA_LAUNCH("gate_fwd_kernel", fst, pw::gate_fwd4_kernel<false><<<blocks4, 256, 0, fst>>>(n4, nb, heads, key_dim, raw_gate, beta_logits, A_log, dt_bias, lower_bound, g_out, beta_out));
+        return launch_status();
+    }
     const int blocks = (int)std::min<size_t>((n + 255) / 256, 148 * 16);
     KDA_LAUNCH("gate_fwd_kernel", (cudaStream_t)stream, pw::gate_fwd_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(n, (size_t)tokens * heads, heads, key_dim,
                                                                    io_dtype == KDA_DTYPE_BF16, raw_gate, beta_logits,
@@ -1303,11 +1423,19 @@ extern "C" int kda_gate_bwd(int32_t tokens, int32_t heads, int32_t key_dim, int3
     const int nblk = tokens > 0 ? ceil_div(tokens, pw::kGateRows) : 0;
     float* part_b = static_cast<float*>(scratch);
     float* part_a = part_b + (size_t)(nblk > 0 ? nblk : 1) * heads * key_dim;
-    if (nblk > 0)
+    const bool al = ((reinterpret_cast<uintptr_t>(raw_gate) | reinterpret_cast<uintptr_t>(dt_bias) | reinterpret_cast<uintptr_t>(dg) |
+                      reinterpret_cast<uintptr_t>(d_raw_gate)) % 16) == 0;
+    if (nblk > 0 && key_dim % 4 == 0 && al) {
+        const dim3 grid(ceil_div(heads * key_dim, 128), nblk);
+        if (io_dtype == KDA_DTYPE_BF16)
+            KDA_LAUNCH("gate_bwd_kernel", st, pw::gate_bwd4_kernel<true><<<grid, 256, 0, st>>>(tokens, heads, key_dim, raw_gate, beta_logits, A_log, dt_bias, lower_bound, dg, dbeta, d_raw_gate, d_beta_logits, part_b, part_a));
+        else
+            KDA_LAUNCH("gate_bwd_kernel", st, pw::gate_bwd4_kernel<false><<<grid, 256, 0, st>>>(tokens, heads, key_dim, raw_gate, beta_logits, A_log, dt_bias, lower_bound, dg, dbeta, d_raw_gate, d_beta_logits, part_b, part_a));
+    } else if (nblk > 0)
         KDA_LAUNCH("gate_bwd_kernel", st, pw::gate_bwd_kernel<<<nblk, 256, 0, st>>>(tokens, heads, key_dim, io_dtype == KDA_DTYPE_BF16, raw_gate,
                                                   beta_logits, A_log, dt_bias, lower_bound, dg, dbeta, d_raw_gate,
                                                   d_beta_logits, part_b, part_a));
-    KDA_LAUNCH("gate_bwd_reduce_kernel", st, pw::gate_bwd_reduce_kernel<<<heads, 256, 0, st>>>(nblk, heads, key_dim, part_b, part_a, ddt_bias, dA_log));
+    KDA_LAUNCH("gate_bwd_reduce_kernel", st, pw::gate_bwd_reduce_kernel<<<heads, 1024, 0, st>>>(nblk, heads, key_dim, part_b, part_a, ddt_bias, dA_log));
     return launch_status();
 }
 
