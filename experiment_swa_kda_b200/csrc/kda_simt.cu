@@ -111,6 +111,7 @@ __device__ __forceinline__ void st_acc_g(float* dst, size_t ld, const float (&ac
 // empty; chunks beyond the slot budget are dropped; either raises the status word (kStatusBadCuSeqlens), as does a
 // table that does not start at 0 or does not end at `tokens`.
 constexpr int kStatusBadCuSeqlens = 10;
+constexpr int kScanOrderMax = 512;      // batches up to this many sequences get a longest-first scan order
 
 __global__ void chunk_table_kernel(Ws w, const int32_t* __restrict__ cu, int n_seq, int seq_len, int tokens, int* status) {
     __shared__ int total;
@@ -145,6 +146,21 @@ __global__ void chunk_table_kernel(Ws w, const int32_t* __restrict__ cu, int n_s
             w.chunk_tok0[c0 + j] = t0 + j * kChunk;
             w.chunk_len[c0 + j] = min(kChunk, len - j * kChunk);
         }
+    }
+    // Scan order: the scans run one CTA per (sequence, head) with one CTA per SM, so starting the longest chains first
+    // keeps the tail of the launch short (longest-processing-time-first).  Rank by counting; identity for large batches,
+    // which balance by themselves.
+    for (int s = threadIdx.x; s < n_seq; s += blockDim.x) {
+        int rank = s;
+        if (n_seq <= kScanOrderMax) {
+            const int nc = w.seq_chunk0[s + 1] - w.seq_chunk0[s];
+            rank = 0;
+            for (int j = 0; j < n_seq; ++j) {
+                const int ncj = w.seq_chunk0[j + 1] - w.seq_chunk0[j];
+                rank += (ncj > nc || (ncj == nc && j < s)) ? 1 : 0;
+            }
+        }
+        w.seq_order[rank] = s;
     }
     for (int c = total + threadIdx.x; c < w.nslots; c += blockDim.x) {
         w.chunk_seq[c] = -1;

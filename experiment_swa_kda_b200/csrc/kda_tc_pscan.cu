@@ -146,6 +146,7 @@ __global__ void __launch_bounds__(256, 2)
 // ---------------------------------------------------------------------------------------------
 struct AffineScanArgs {
     const int* seq_chunk0;
+    const int* seq_order;     // unsplit scans: grid = (heads, sequences), block (h, r) walks sequence seq_order[r]
     const int* chunk_tok0;
     const int* chunk_len;
     const float* decay_end;   // [nch][128] exp(G_end)
@@ -195,8 +196,11 @@ __global__ void __launch_bounds__(kAffineScanThreads, 1)
     const int v = (warp & 3) * 32 + lane;          // value row = TMEM lane
     const bool split = p.nseg > 1;
     const int units = 2 * p.nseg - 1;
-    const int seq = split ? blockIdx.x / units : blockIdx.x, role = split ? blockIdx.x % units : 0;
-    const int h = blockIdx.y, H = p.H;
+    // split: grid (sequences x units, heads); unsplit with an order table: grid (heads, sequences), longest first, so that
+    // the blocks the hardware starts first are the longest chains
+    const bool lpt = !split && p.seq_order != nullptr;
+    const int seq = split ? blockIdx.x / units : (lpt ? p.seq_order[blockIdx.y] : blockIdx.x), role = split ? blockIdx.x % units : 0;
+    const int h = lpt ? blockIdx.x : blockIdx.y, H = p.H;
     const int c_begin = p.seq_chunk0[seq], c_end = p.seq_chunk0[seq + 1];
     const int n_total = c_end - c_begin;
     const int seg = (role + 1) >> 1;                             // segment this unit walks
@@ -972,6 +976,9 @@ int tc_scan_forward(const simt::Ws& w, const tc::TcWs& t, int n_seq, int tokens,
     a.seq_chunk0 = w.seq_chunk0; a.chunk_tok0 = w.chunk_tok0; a.chunk_len = w.chunk_len; a.decay_end = t.decay_end; a.s_in = h0; a.s_out = final_state;
     a.H = w.H; a.status = t.status; a.nseg = t.nseg; a.seg_fin = t.seg_fin;
     const int units = 2 * t.nseg - 1;
+    const bool lpt = t.nseg == 1 && n_seq > 1 && n_seq <= 65535;
+    a.seq_order = lpt ? w.seq_order : nullptr;
+    const dim3 scan_grid = lpt ? dim3(w.H, n_seq) : dim3(n_seq * units, w.H);
     CUtensorMap mPp = mH, mF = mH;
     if (t.nseg > 1) {
         if (make_map_bf16(&mPp, t.Pp, nch * 128, 128, 64, 128) ||
@@ -979,7 +986,7 @@ int tc_scan_forward(const simt::Ws& w, const tc::TcWs& t, int n_seq, int tokens,
             return KDA_ERR_CUDA;
     }
     KDA_LAUNCH("tc_affine_scan_fwd_kernel", st,
-               tc_affine_scan_kernel<false><<<dim3(n_seq * units, w.H), kAffineScanThreads, kAffineScanSmem, st>>>(mP, mUT, mE, mH, mPp, mF, a));
+               tc_affine_scan_kernel<false><<<scan_grid, kAffineScanThreads, kAffineScanSmem, st>>>(mP, mUT, mE, mH, mPp, mF, a));
     if (int e = launch_status()) return e;
     if (t.nseg > 1) {
         if (int e = scan_fixup(w, t, n_seq, t.Hp, final_state, 0, mPp, mF, st)) return e;
@@ -1014,6 +1021,9 @@ int tc_scan_backward(const simt::Ws& w, const simt::Scr& s, const tc::TcWs& t, i
     a.seq_chunk0 = w.seq_chunk0; a.chunk_tok0 = w.chunk_tok0; a.chunk_len = w.chunk_len; a.decay_end = t.decay_end; a.s_in = d_final; a.s_out = dh0;
     a.H = w.H; a.status = t.status; a.nseg = t.nseg; a.seg_fin = t.seg_fin;
     const int units = 2 * t.nseg - 1;
+    const bool lpt = t.nseg == 1 && n_seq > 1 && n_seq <= 65535;
+    a.seq_order = lpt ? w.seq_order : nullptr;
+    const dim3 scan_grid = lpt ? dim3(w.H, n_seq) : dim3(n_seq * units, w.H);
     CUtensorMap mPp = mdH, mF = mdH;
     if (t.nseg > 1) {
         if (make_map_bf16(&mPp, t.Pp, nch * 128, 128, 64, 128) ||
@@ -1021,7 +1031,7 @@ int tc_scan_backward(const simt::Ws& w, const simt::Scr& s, const tc::TcWs& t, i
             return KDA_ERR_CUDA;
     }
     KDA_LAUNCH("tc_affine_scan_bwd_kernel", st,
-               tc_affine_scan_kernel<true><<<dim3(n_seq * units, w.H), kAffineScanThreads, kAffineScanSmem, st>>>(mP, mRm, mdO, mdH, mPp, mF, a));
+               tc_affine_scan_kernel<true><<<scan_grid, kAffineScanThreads, kAffineScanSmem, st>>>(mP, mRm, mdO, mdH, mPp, mF, a));
     if (int e = launch_status()) return e;
     if (t.nseg > 1) {
         if (int e = scan_fixup(w, t, n_seq, t.dHp, dh0, 1, mPp, mF, st)) return e;

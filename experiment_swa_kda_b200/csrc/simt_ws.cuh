@@ -10,6 +10,7 @@ namespace simt {
 
 struct Ws {
     int *chunk_seq, *chunk_tok0, *chunk_len, *seq_chunk0;
+    int* seq_order;             // [n_seq] sequences by falling chunk count: the order the state scans start them in
     float *qn, *kn, *G, *W;     // [nch][64][Kp]   scaled unit q, unit k, cumulative log-decay, W
     float* Z;                   // [nch][64][Vp]   U after the intra-chunk step, Z after the scan
     float *A, *T;               // [nch][64][64]
@@ -67,6 +68,7 @@ inline Ws carve_ws(const KdaChunkShape& sh, void* mem, size_t* bytes = nullptr) 
     w.chunk_tok0 = c.take<int>(w.nslots + 1);
     w.chunk_len = c.take<int>(w.nslots + 1);
     w.seq_chunk0 = c.take<int>(sh.n_seq + 1);
+    w.seq_order = c.take<int>(sh.n_seq);
     w.qn = c.take<float>(big * nch * 64 * w.Kp);
     w.kn = c.take<float>(big * nch * 64 * w.Kp);
     w.G = c.take<float>(big * nch * 64 * w.Kp);
