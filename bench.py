@@ -49,8 +49,7 @@ def kda_kernel_flops(K, V, C=64):
     bwd["bwd_local_kernel"] = 2 * fwd_total - sum(bwd.values())
     tcl = {   # tensor-core lane kernels: the multiply-adds each one actually performs (different kernel boundaries and
         # a regrouped recurrence, so the parts do not add up to the reference-algorithm total below)
-        "tc_intra_fwd_kernel": fwd["build_am_kernel"] + fwd["uw_kernel"],
-        "tc_transition_kernel": C * K * K + C * C * K,
+        "tc_intra_fwd_kernel": fwd["build_am_kernel"] + fwd["uw_kernel"] + C * K * K + C * C * K,   # + the chunk transition
         "tc_affine_scan_fwd_kernel": K * K * V + C * K * V,
         "tc_chunk_out_kernel": 2 * C * K * V + C * C * V,
         "tc_affine_scan_bwd_kernel": K * K * V + C * K * V,

@@ -8,6 +8,8 @@
 //   T = (I + beta M~)^-1                                                       fp32, block forward substitution
 //   U^T = P^T T^T,  W^T = Q^T T^T   (P = beta v, Q = beta e^G k)                tcgen05, M=128 N=64 K=64, MN-major A
 //   R^T = (q e^G)^T, E = k e^{G_end-G}, e^{G_end}, A^T, T                       panels for the scans / backward
+//   Pn = W^T E,  Rm^T = R^T - W^T A^T   (the chunk's state transition)         tcgen05, M=128 N=128|64 K=64, at the end:
+//       W^T is still staged in shared memory for its store, E and A^T come back by TMA into the dead value / Q tiles
 // Every operand panel is written as 16-byte pieces of the 128-byte-swizzled layout the UMMA descriptors read: a thread
 // owns 8 adjacent channels of 4 consecutive rows, takes q, k, g straight from global memory (a half-warp reads one
 // 256-byte row segment) and needs two exponentials and one reciprocal per element.  The source panels of the two
@@ -218,7 +220,8 @@ template <bool GBF16>
 __global__ void __launch_bounds__(kNT, 2)
     tc_intra_fwd_kernel(const __grid_constant__ CUtensorMap mv, const __grid_constant__ CUtensorMap mUT,
                         const __grid_constant__ CUtensorMap mWT, const __grid_constant__ CUtensorMap mAT,
-                        const __grid_constant__ CUtensorMap mMt, IntraFwdArgs p) {
+                        const __grid_constant__ CUtensorMap mMt, const __grid_constant__ CUtensorMap mE,
+                        const __grid_constant__ CUtensorMap mP, const __grid_constant__ CUtensorMap mRm, IntraFwdArgs p) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* sm = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);   // pointer arithmetic keeps the shared address space
     uint8_t* Sst = sm + kFS;
@@ -236,7 +239,7 @@ __global__ void __launch_bounds__(kNT, 2)
     float* tmp = reinterpret_cast<float*>(sm + kFTmp);
     uint8_t* Tb = sm + kFTb;                                 // [64 rows x 128 B] K-major B: T
     uint8_t* Tbb = sm + kFTbb;                               //                              T diag(beta)
-    __shared__ uint64_t bar_in, bar_am[2], bar_uw;
+    __shared__ uint64_t bar_in, bar_am[2], bar_uw, bar_tr;
     __shared__ uint32_t tmem_slot;
 
     const int slot = blockIdx.x, h = blockIdx.y, H = p.H;
@@ -255,6 +258,7 @@ __global__ void __launch_bounds__(kNT, 2)
         mbar_init(&bar_am[0], 1);
         mbar_init(&bar_am[1], 1);
         mbar_init(&bar_uw, 1);
+        mbar_init(&bar_tr, 1);
         mbar_fence_init();
         mbar_expect_tx(&bar_in, 16384);
         for (int kb = 0; kb < 2; ++kb) tma_load_2d(vs + kb * 8192, &mv, &bar_in, h * 128 + kb * 64, tok0);
@@ -551,6 +555,9 @@ __global__ void __launch_bounds__(kNT, 2)
             }
         }
         fence_async_smem();
+        // the E rows this block wrote with plain stores long ago come back by a bulk load below: order them for it
+        __threadfence();
+        asm volatile("fence.proxy.async.global;" ::: "memory");
         tc_fence_before();
         ok = __syncthreads_and(ok);
         if (tid == 0 && ok) {
@@ -569,6 +576,21 @@ __global__ void __launch_bounds__(kNT, 2)
         }
         if (ok) ok = mbar_wait(&bar_uw, 0, p.t.status, 32);
         tc_fence_after();
+        // ---- chunk transition, fused: Pn = W^T E and Rm^T = R^T - W^T A^T need W^T (about to be staged below), E and
+        // A^T.  The value and Q tiles are dead now: E and A^T come back into them by TMA while the panels are read out.
+        const int kt = (warp & 3) * 32 + lane, gt = warp >> 2;      // transition read-out: key row, column half
+        uint4 rtv[4];
+        if (tid == 0 && ok) {
+            tma_store_wait_all();                  // the A^T panel stored above is complete in global memory
+            mbar_expect_tx(&bar_tr, 16384 + (p.t.fwd_only ? 0 : 8192));
+            for (int nb = 0; nb < 2; ++nb) tma_load_2d(vs + nb * 8192, &mE, &bar_tr, nb * 64, (int)(ch * 64));
+            if (!p.t.fwd_only) tma_load_2d(Qs, &mAT, &bar_tr, 0, (int)(ch * 64));
+        }
+        if (ok && !p.t.fwd_only) {
+            const uint4* src = reinterpret_cast<const uint4*>(p.t.RT + ch * 8192 + (size_t)kt * 64 + 32 * gt);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) rtv[j] = src[j];
+        }
         if (ok) {
             // lane = value channel (U^T, warps 0-3) / key channel (W^T, warps 4-7): one 128-byte panel row per thread,
             // staged in the swizzled layout (the inverse's scratch is dead) and stored by TMA, 16 KB per panel
@@ -590,13 +612,76 @@ __global__ void __launch_bounds__(kNT, 2)
             }
         }
         fence_async_smem();
+        tc_fence_before();
         ok = __syncthreads_and(ok);
         if (tid == 0 && ok) {
             tma_store_2d(&mUT, sm, 0, (int)(ch * 128));
             tma_store_2d(&mWT, sm + 16384, 0, (int)(ch * 128));
             tma_store_commit();
-            tma_store_wait_read();                 // shared memory must outlive the reads of the bulk stores
+            ok = mbar_wait(&bar_tr, 0, p.t.status, 33);
+            if (ok) {
+                tc_fence_after();
+                // every accumulator column has been read out: Pn takes columns 0..127, (A W)^T columns 128..191
+                const uint32_t a0 = smem_u32(sm + 16384), bE = smem_u32(vs), bA = smem_u32(Qs);
+                const uint32_t id128 = umma_idesc_bf16(128, 128, kMajorK, kMajorMN);
+                const uint32_t id64 = umma_idesc_bf16(128, 64, kMajorK, kMajorMN);
+#pragma unroll
+                for (int k16 = 0; k16 < 4; ++k16)     // Pn = W^T E
+                    umma_bf16_ss(tmem, umma_smem_desc_sw128(a0 + k16 * 32, 16, 1024),
+                                 umma_smem_desc_sw128(bE + k16 * 2048, 8192, 1024), id128, k16 > 0);
+                if (!p.t.fwd_only) {
+#pragma unroll
+                    for (int k16 = 0; k16 < 4; ++k16)     // (A W)^T = W^T A^T
+                        umma_bf16_ss(tmem + 128, umma_smem_desc_sw128(a0 + k16 * 32, 16, 1024),
+                                     umma_smem_desc_sw128(bA + k16 * 2048, 8192, 1024), id64, k16 > 0);
+                }
+                umma_commit(&bar_uw);
+            }
         }
+        if (ok) ok = mbar_wait(&bar_uw, 1, p.t.status, 34);
+        ok = __syncthreads_and(ok);
+        tc_fence_after();
+        if (ok) {
+            // both results leave through shared memory in the swizzled layout (Pn over the dead T operands and inverse
+            // scratch, Rm^T over the E tile the products have finished reading) and are stored by TMA
+            uint8_t* Pst = sm + 32768 + gt * 16384;          // [128 key rows][64 columns of half gt]
+#pragma unroll
+            for (int b = 0; b < 2; ++b) {
+                uint32_t r[32];
+                tmem_ld32(tmem + lane_base + 64 * gt + 32 * b, r);
+                tmem_ld_wait();
+#pragma unroll
+                for (int c = 0; c < 4; ++c)
+                    *reinterpret_cast<uint4*>(Pst + sw128_off(kt, 4 * b + c)) =
+                        make_uint4(pack2(__uint_as_float(r[8 * c]), __uint_as_float(r[8 * c + 1])),
+                                   pack2(__uint_as_float(r[8 * c + 2]), __uint_as_float(r[8 * c + 3])),
+                                   pack2(__uint_as_float(r[8 * c + 4]), __uint_as_float(r[8 * c + 5])),
+                                   pack2(__uint_as_float(r[8 * c + 6]), __uint_as_float(r[8 * c + 7])));
+            }
+            if (!p.t.fwd_only) {     // the adjoint scan's operand is not needed in a forward-only call
+                uint32_t r[32];
+                tmem_ld32(tmem + lane_base + 128 + 32 * gt, r);
+                tmem_ld_wait();
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    float f[8];
+                    unpack_bf16x8(rtv[c], f);
+                    *reinterpret_cast<uint4*>(vs + sw128_off(kt, 4 * gt + c)) =
+                        make_uint4(pack2(f[0] - __uint_as_float(r[8 * c]), f[1] - __uint_as_float(r[8 * c + 1])),
+                                   pack2(f[2] - __uint_as_float(r[8 * c + 2]), f[3] - __uint_as_float(r[8 * c + 3])),
+                                   pack2(f[4] - __uint_as_float(r[8 * c + 4]), f[5] - __uint_as_float(r[8 * c + 5])),
+                                   pack2(f[6] - __uint_as_float(r[8 * c + 6]), f[7] - __uint_as_float(r[8 * c + 7])));
+                }
+            }
+        }
+        fence_async_smem();
+        ok = __syncthreads_and(ok);
+        if (tid == 0 && ok) {
+            for (int nb = 0; nb < 2; ++nb) tma_store_2d(&mP, sm + 32768 + nb * 16384, nb * 64, (int)(ch * 128));
+            if (!p.t.fwd_only) tma_store_2d(&mRm, vs, 0, (int)(ch * 128));
+            tma_store_commit();
+        }
+        if (tid == 0) tma_store_wait_read();           // shared memory must outlive the reads of the bulk stores
     } else {
         // unwinding: the value tile must have landed before the block may exit
         mbar_wait(&bar_in, 0, nullptr, 0);
@@ -617,16 +702,19 @@ int tc_intra_forward(const simt::Ws& w, const tc::TcWs& t, const void* q, const 
     a.q = static_cast<const __nv_bfloat16*>(q); a.k = static_cast<const __nv_bfloat16*>(k);
     a.g = g; a.beta = beta; a.gbf16 = gbf16; a.l2norm = l2norm; a.H = w.H; a.scale = scale; a.t = t; a.w = w;
     const uint64_t nch = (uint64_t)w.nslots * w.H;
-    CUtensorMap mv, mUT, mWT, mAT, mMt;
+    CUtensorMap mv, mUT, mWT, mAT, mMt, mE, mP, mRm;
     int rc = make_map_bf16(&mv, v, (uint64_t)tokens, (uint64_t)w.H * 128, 64, 64);
     rc |= make_map_bf16(&mUT, t.UT, nch * 128, 64, 64, 128);
     rc |= make_map_bf16(&mWT, t.WT, nch * 128, 64, 64, 128);
     rc |= make_map_bf16(&mAT, t.AT, nch * 64, 64, 64, 64);
     rc |= make_map_bf16(&mMt, t.fwd_only ? t.AT : t.Mt, nch * 64, 64, 64, 64);      // not stored in a forward-only call
+    rc |= make_map_bf16(&mE, t.E, nch * 64, 128, 64, 64);
+    rc |= make_map_bf16(&mP, t.Pn, nch * 128, 128, 64, 128);
+    rc |= make_map_bf16(&mRm, t.fwd_only ? t.WT : t.RmT, nch * 128, 64, 64, 128);      // not stored in a forward-only call
     if (rc) return KDA_ERR_CUDA;
     auto kern = gbf16 ? tc_intra_fwd_kernel<true> : tc_intra_fwd_kernel<false>;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kIntraFwdSmem) != cudaSuccess) return KDA_ERR_CUDA;
-    KDA_LAUNCH("tc_intra_fwd_kernel", st, kern<<<dim3(w.nslots, w.H), kNT, kIntraFwdSmem, st>>>(mv, mUT, mWT, mAT, mMt, a));
+    KDA_LAUNCH("tc_intra_fwd_kernel", st, kern<<<dim3(w.nslots, w.H), kNT, kIntraFwdSmem, st>>>(mv, mUT, mWT, mAT, mMt, mE, mP, mRm, a));
     return launch_status();
 }
 

@@ -5,7 +5,7 @@
 // and the adjoint recurrence of the backward is its transpose,
 //     dH^T = dec . dH'^T - dH'^T Pn^T + dO^T (R - A W).
 // Pn = W^T E and Rm = R - A W do not depend on the state, so they are computed for all chunks in parallel
-// (transition kernel) and the sequential part of a chunk step shrinks to ONE UMMA chain between two register passes:
+// (at the end of the intra-chunk forward kernel) and the sequential part of a chunk step shrinks to ONE UMMA chain between two register passes:
 //     pack state -> bf16 A operand | D = state-independent term (issued a step early) - state x Pn | state = dec . state + D
 // Everything else that used to sit inside the scans runs chunk-parallel on all SMs afterwards:
 //     forward   Z^T = U^T - (W H)^T,  O^T = (R H)^T + (A Z)^T      from the chunk-start states the scan stored
@@ -23,113 +23,6 @@ namespace kda {
 namespace tc {
 
 int make_map_bf16(CUtensorMap* m, const void* ptr, uint64_t rows, uint64_t cols, uint32_t box_cols, uint32_t box_rows);
-
-// ---------------------------------------------------------------------------------------------
-// transition kernel: Pn = W^T E  [k][k'],  RmT = R^T - W^T A^T  [k][i]      one CTA per chunk-head
-// ---------------------------------------------------------------------------------------------
-struct TransArgs {
-    const int* chunk_len;
-    const __nv_bfloat16* RT;
-    __nv_bfloat16 *Pn, *RmT;
-    int H;
-    int* status;
-};
-
-constexpr int kTransSmem = 16384 + 16384 + 8192 + 1024;   // W^T | E | A^T
-
-__global__ void __launch_bounds__(256, 2)
-    tc_transition_kernel(const __grid_constant__ CUtensorMap mW, const __grid_constant__ CUtensorMap mE,
-                         const __grid_constant__ CUtensorMap mAT, TransArgs p) {
-    extern __shared__ uint8_t smem_raw[];
-    uint8_t* sm = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);   // pointer arithmetic keeps the shared address space
-    __shared__ uint64_t bar_in, bar_mma;
-    __shared__ uint32_t tmem_slot;
-    const int slot = blockIdx.x, h = blockIdx.y;
-    if (p.chunk_len[slot] == 0) return;
-    const int ch = slot * p.H + h;
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int g = warp >> 2;                       // column half handled by this warpgroup
-    const int k = (warp & 3) * 32 + lane;          // key row = TMEM lane
-    if (tid == 0) {
-        mbar_init(&bar_in, 1);
-        mbar_init(&bar_mma, 1);
-        mbar_fence_init();
-        mbar_expect_tx(&bar_in, 16384 + 16384 + 8192);
-        tma_load_2d(sm, &mW, &bar_in, 0, ch * 128);                                    // W^T [key][token]
-        for (int nb = 0; nb < 2; ++nb) tma_load_2d(sm + 16384 + nb * 8192, &mE, &bar_in, nb * 64, ch * 64);
-        tma_load_2d(sm + 32768, &mAT, &bar_in, 0, ch * 64);
-    }
-    if (warp == 1) tmem_alloc(&tmem_slot, 256);
-    // this thread's part of R^T while the tiles fly: row k, tokens 32g .. 32g+31
-    uint4 rt[4];
-    {
-        const uint4* src = reinterpret_cast<const uint4*>(p.RT + (size_t)ch * 8192 + (size_t)k * 64 + 32 * g);
-#pragma unroll
-        for (int j = 0; j < 4; ++j) rt[j] = src[j];
-    }
-    tc_fence_before();
-    __syncthreads();
-    tc_fence_after();
-    const uint32_t tmem = tmem_slot;
-    const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
-    bool ok = true;
-    if (tid == 0) {
-        ok = mbar_wait(&bar_in, 0, p.status, 40);
-        if (ok) {
-            tc_fence_after();
-            const uint32_t a0 = smem_u32(sm), bE = smem_u32(sm + 16384), bA = smem_u32(sm + 32768);
-            const uint32_t id128 = umma_idesc_bf16(128, 128, kMajorK, kMajorMN);
-            const uint32_t id64 = umma_idesc_bf16(128, 64, kMajorK, kMajorMN);
-#pragma unroll
-            for (int k16 = 0; k16 < 4; ++k16)     // Pn = W^T E
-                umma_bf16_ss(tmem, umma_smem_desc_sw128(a0 + k16 * 32, 16, 1024),
-                             umma_smem_desc_sw128(bE + k16 * 2048, 8192, 1024), id128, k16 > 0);
-            if (p.RmT != nullptr) {
-#pragma unroll
-                for (int k16 = 0; k16 < 4; ++k16)     // (A W)^T = W^T A^T
-                    umma_bf16_ss(tmem + 128, umma_smem_desc_sw128(a0 + k16 * 32, 16, 1024),
-                                 umma_smem_desc_sw128(bA + k16 * 2048, 8192, 1024), id64, k16 > 0);
-            }
-            umma_commit(&bar_mma);
-        }
-    }
-    ok = mbar_wait(&bar_mma, 0, p.status, 41) && ok;
-    ok = __syncthreads_and(ok);
-    tc_fence_after();
-    if (ok) {
-        uint4* dp = reinterpret_cast<uint4*>(p.Pn + (size_t)ch * 16384 + (size_t)k * 128 + 64 * g);
-#pragma unroll
-        for (int b = 0; b < 2; ++b) {
-            uint32_t r[32];
-            tmem_ld32(tmem + lane_base + 64 * g + 32 * b, r);
-            tmem_ld_wait();
-#pragma unroll
-            for (int c = 0; c < 4; ++c)
-                dp[4 * b + c] = make_uint4(pack_bf16(__uint_as_float(r[8 * c]), __uint_as_float(r[8 * c + 1])),
-                                           pack_bf16(__uint_as_float(r[8 * c + 2]), __uint_as_float(r[8 * c + 3])),
-                                           pack_bf16(__uint_as_float(r[8 * c + 4]), __uint_as_float(r[8 * c + 5])),
-                                           pack_bf16(__uint_as_float(r[8 * c + 6]), __uint_as_float(r[8 * c + 7])));
-        }
-        if (p.RmT != nullptr) {      // null in a forward-only call: the adjoint scan's operand is not needed
-            uint32_t r[32];
-            tmem_ld32(tmem + lane_base + 128 + 32 * g, r);
-            tmem_ld_wait();
-            uint4* dr = reinterpret_cast<uint4*>(p.RmT + (size_t)ch * 8192 + (size_t)k * 64 + 32 * g);
-#pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                float f[8];
-                unpack_bf16x8(rt[c], f);
-                dr[c] = make_uint4(pack_bf16(f[0] - __uint_as_float(r[8 * c]), f[1] - __uint_as_float(r[8 * c + 1])),
-                                   pack_bf16(f[2] - __uint_as_float(r[8 * c + 2]), f[3] - __uint_as_float(r[8 * c + 3])),
-                                   pack_bf16(f[4] - __uint_as_float(r[8 * c + 4]), f[5] - __uint_as_float(r[8 * c + 5])),
-                                   pack_bf16(f[6] - __uint_as_float(r[8 * c + 6]), f[7] - __uint_as_float(r[8 * c + 7])));
-            }
-        }
-    }
-    tc_fence_before();
-    __syncthreads();
-    if (warp == 1) tmem_dealloc(tmem, 256);
-}
 
 // ---------------------------------------------------------------------------------------------
 // affine scan: one CTA per (sequence, head) walks the chunks in order (forward) or in reverse (backward)
@@ -963,15 +856,9 @@ int tc_scan_forward(const simt::Ws& w, const tc::TcWs& t, int n_seq, int tokens,
     else mG = mAT;
     if (rc) return KDA_ERR_CUDA;
     const int out_smem = fused_norm ? kChunkOutNormSmem : kChunkOutSmem;
-    if (cudaFuncSetAttribute(tc_transition_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kTransSmem) != cudaSuccess ||
-        cudaFuncSetAttribute(tc_affine_scan_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kAffineScanSmem) != cudaSuccess ||
+    if (cudaFuncSetAttribute(tc_affine_scan_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kAffineScanSmem) != cudaSuccess ||
         cudaFuncSetAttribute(tc_chunk_out_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kChunkOutNormSmem) != cudaSuccess)
         return KDA_ERR_CUDA;
-    TransArgs ta;
-    ta.chunk_len = w.chunk_len; ta.RT = t.RT; ta.Pn = t.Pn; ta.RmT = t.fwd_only ? nullptr : t.RmT; ta.H = w.H; ta.status = t.status;
-    KDA_LAUNCH("tc_transition_kernel", st,
-               tc_transition_kernel<<<dim3(w.nslots, w.H), 256, kTransSmem, st>>>(mW, mE, mAT, ta));
-    if (int e = launch_status()) return e;
     AffineScanArgs a;
     a.seq_chunk0 = w.seq_chunk0; a.chunk_tok0 = w.chunk_tok0; a.chunk_len = w.chunk_len; a.decay_end = t.decay_end; a.s_in = h0; a.s_out = final_state;
     a.H = w.H; a.status = t.status; a.nseg = t.nseg; a.seg_fin = t.seg_fin;
