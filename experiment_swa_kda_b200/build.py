@@ -47,23 +47,45 @@ def nvcc_path() -> str:
     return cand
 
 
+class _BuildLock:
+    """One builder at a time: the ranks of a multi-process launch all find a stale library at once; the first one
+    builds, the others wait on the lock and then find it fresh."""
+
+    def __enter__(self):
+        import fcntl
+        os.makedirs(LIBDIR, exist_ok=True)
+        self._f = open(os.path.join(LIBDIR, ".build.lock"), "w")
+        fcntl.flock(self._f, fcntl.LOCK_EX)
+        return self
+
+    def __exit__(self, *exc):
+        import fcntl
+        fcntl.flock(self._f, fcntl.LOCK_UN)
+        self._f.close()
+
+
 def build(force: bool = False, verbose: bool = False) -> str:
     if not force and not is_stale():
         return LIB
-    os.makedirs(LIBDIR, exist_ok=True)
-    cmd = [nvcc_path(), *ARCH_FLAGS, "-lineinfo", "-O3", "-std=c++17", "--shared", "-Xcompiler", "-fPIC",
-           "-lcuda", "-o", LIB, *sources()]
-    if verbose:
-        cmd.insert(1, "-Xptxas")
-        cmd.insert(2, "-v")
-    proc = subprocess.run(cmd, capture_output=True, text=True)
-    if proc.returncode != 0:
-        raise RuntimeError("nvcc failed:\n" + proc.stdout + proc.stderr)
-    if verbose:
-        sys.stderr.write(proc.stderr)
-    with open(RECEIPT, "w") as f:
-        json.dump({"library_path": LIB, "source_paths": sources(), "compiler_command": cmd,
-                   "target_arch": "sm_100a"}, f, indent=1)
+    with _BuildLock():
+        if not force and not is_stale():      # another process built it while this one waited
+            return LIB
+        tmp = LIB + f".{os.getpid()}.tmp"      # never leave a half-written library where a loader can find it
+        cmd = [nvcc_path(), *ARCH_FLAGS, "-lineinfo", "-O3", "-std=c++17", "--shared", "-Xcompiler", "-fPIC",
+               "-lcuda", "-o", tmp, *sources()]
+        if verbose:
+            cmd.insert(1, "-Xptxas")
+            cmd.insert(2, "-v")
+        proc = subprocess.run(cmd, capture_output=True, text=True)
+        if proc.returncode != 0:
+            raise RuntimeError("nvcc failed:\n" + proc.stdout + proc.stderr)
+        os.replace(tmp, LIB)
+        if verbose:
+            sys.stderr.write(proc.stderr)
+        cmd[cmd.index(tmp)] = LIB
+        with open(RECEIPT, "w") as f:
+            json.dump({"library_path": LIB, "source_paths": sources(), "compiler_command": cmd,
+                       "target_arch": "sm_100a"}, f, indent=1)
     return LIB
 
 
@@ -98,9 +120,15 @@ def build_torch_ops(force: bool = False) -> str:
            "-I" + os.path.join(os.path.dirname(PKG), "include"), "-I" + cuda_inc, *["-I" + i for i in ce.include_paths()],
            SHIM_SRC, "-o", SHIM_LIB, "-L" + tlib, "-ltorch", "-ltorch_cpu", "-ltorch_cuda", "-lc10", "-lc10_cuda",
            "-L" + LIBDIR, "-lkda_b200", "-Wl,-rpath,$ORIGIN", "-Wl,-rpath," + tlib]
-    proc = subprocess.run(cmd, capture_output=True, text=True)
-    if proc.returncode != 0:
-        raise RuntimeError("building libkda_b200_torch.so failed:\n" + proc.stdout + proc.stderr)
+    with _BuildLock():
+        if not force and not torch_ops_stale():
+            return SHIM_LIB
+        tmp = SHIM_LIB + f".{os.getpid()}.tmp"
+        cmd[cmd.index(SHIM_LIB)] = tmp
+        proc = subprocess.run(cmd, capture_output=True, text=True)
+        if proc.returncode != 0:
+            raise RuntimeError("building libkda_b200_torch.so failed:\n" + proc.stdout + proc.stderr)
+        os.replace(tmp, SHIM_LIB)
     return SHIM_LIB
 
 
