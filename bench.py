@@ -304,6 +304,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-graph", action="store_true", help="launch every step eagerly instead of replaying a CUDA graph")
+    ap.add_argument("--profile-warm", action="store_true", help="per-kernel pass without the L2 flush between steps (what a kernel costs inside the replayed graph, where its inputs were just written)")
     ap.add_argument("--no-sharded", action="store_true", help="skip the config-3 / config-4 sharded workloads attached to the line")
     ap.add_argument("--tokens", type=int, default=8 * 8192, help="packed tokens of the varlen workload")
     ap.add_argument("--workload", default="chain", choices=["chain", "varlen", "decode", "pointwise", "train"],
@@ -551,7 +552,8 @@ def main():
     torch.cuda.synchronize(dev)
     _lib.profile(True)
     for _ in range(args.steps):
-        flush.zero_()
+        if not args.profile_warm:
+            flush.zero_()
         chain.step()
     torch.cuda.synchronize(dev)
     rep = _lib.profile_report()

@@ -77,42 +77,46 @@ __global__ void gate_bwd_kernel(int tokens, int H, int K, int bf16, const void* 
     }
 }
 
-// stage 2: one block (1024 threads = 32 row segments x 32 columns) per head; fixed summation order
+// stage 2: one block per head, 1024 threads = 8 row segments x 128 columns (wider heads loop over column groups);
+// fixed summation order
 __global__ void __launch_bounds__(1024) gate_bwd_reduce_kernel(int nblk, int H, int K, const float* __restrict__ part_b,
-                                                               const float* __restrict__ part_a,
-                                                               float* __restrict__ ddt_bias, float* __restrict__ dA_log) {
-    __shared__ float redb[32][33], reda[32][33];
+                                                               const float* __restrict__ part_a, float* __restrict__ ddt_bias,
+                                                               float* __restrict__ dA_log) {
+    __shared__ float redb[8][128], reda[8][128];
+    __shared__ float wsum[4];
     const int h = blockIdx.x, HK = H * K;
-    const int lane = threadIdx.x & 31, seg = threadIdx.x >> 5;
-    float accA = 0.f;                      // seg 0 only: this lane's columns of sum_k (dr * x)
-    for (int k0 = 0; k0 < K; k0 += 32) {
-        const int kk = k0 + lane, c = h * K + kk;
+    const int col = threadIdx.x & 127, seg = threadIdx.x >> 7;
+    float accA = 0.f;                      // segment 0 only: this column's share of sum_k (dr * x), over all column groups
+    for (int k0 = 0; k0 < K; k0 += 128) {
+        const int kk = k0 + col, c = h * K + kk;
         float sb = 0.f, sa = 0.f;
         if (kk < K)
-            for (int b = seg; b < nblk; b += 32) {
+            for (int b = seg; b < nblk; b += 8) {
                 sb += part_b[(size_t)b * HK + c];
                 sa += part_a[(size_t)b * HK + c];
             }
-        redb[seg][lane] = sb;
-        reda[seg][lane] = sa;
+        redb[seg][col] = sb;
+        reda[seg][col] = sa;
         __syncthreads();
         if (seg == 0 && kk < K) {
             float tb = 0.f, ta = 0.f;
 #pragma unroll
-            for (int r = 0; r < 32; ++r) {
-                tb += redb[r][lane];
-                ta += reda[r][lane];
+            for (int r = 0; r < 8; ++r) {
+                tb += redb[r][col];
+                ta += reda[r][col];
             }
             ddt_bias[c] = tb;
             accA += ta;
         }
         __syncthreads();
     }
-    if (seg == 0) {
+    if (seg == 0) {                        // 4 warps hold the head's column sums: warp totals, then one thread
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) accA += __shfl_xor_sync(0xffffffffu, accA, o);
-        if (lane == 0) dA_log[h] = accA;
+        if ((col & 31) == 0) wsum[col >> 5] = accA;
     }
+    __syncthreads();
+    if (threadIdx.x == 0) dA_log[h] = (wsum[0] + wsum[1]) + (wsum[2] + wsum[3]);
 }
 
 // =============================================================================================
@@ -1094,6 +1098,140 @@ __global__ void __launch_bounds__(256) conv_bwd_tile_kernel(int B, int T, int C,
     }
 }
 
+// Backward, training path, bf16 with C % 128 == 0.  A thread owns 4 adjacent channels and a run of consecutive tokens
+// and streams down its rows once: x and dy rows arrive through a thread-private ring in shared memory filled by
+// asynchronous 8-byte copies kConvRingDepth rows ahead (no registers held for data in flight, no block-wide barrier in
+// the loop), the x window and the dz window live in registers as circular buffers with compile-time indices, and every
+// pre-activation, SiLU derivative, dweight and dx multiply-add is done exactly once per element.  Only the W-1 rows
+// either side of a run are touched twice.  Block = 8 warps = 8 runs x 128 channels; one dweight partial per block.
+constexpr int kConvRingDepth = 16;
+
+template <int W>
+__global__ void __launch_bounds__(256, 3) conv_bwd_ring_kernel(int B, int T, int C, int run, int silu, int wf32, ConvBwdItems items,
+                                                               float* __restrict__ dw_part) {
+    constexpr int D = kConvRingDepth;
+    extern __shared__ __align__(16) uint8_t ring_raw[];
+    uint2* ring = reinterpret_cast<uint2*>(ring_raw);          // [D][2: x | dy][256 threads]
+    float (*red)[W][128] = reinterpret_cast<float (*)[W][128]>(ring_raw);      // [8][W][128], once the ring is drained
+    const int p = threadIdx.x & 31, g = threadIdx.x >> 5;
+    const int c = (blockIdx.x * 32 + p) * 4;                   // C % 128 == 0: in range
+    const int item = blockIdx.z / B, b = blockIdx.z - item * B;
+    const int t0 = (blockIdx.y * 8 + g) * run;
+    const __nv_bfloat16* __restrict__ x = static_cast<const __nv_bfloat16*>(pick_item(items.x, item));
+    const void* __restrict__ wgt = pick_item(items.w, item);
+    const __nv_bfloat16* __restrict__ dy = static_cast<const __nv_bfloat16*>(pick_item(items.dy, item));
+    __nv_bfloat16* __restrict__ dx = static_cast<__nv_bfloat16*>(pick_item(items.dx, item));
+    float wv[W][4];
+    {
+        float flat[W * 4];
+        ld_wrun<W * 4, true>(flat, wgt, (size_t)c * W, wf32);
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+#pragma unroll
+            for (int m = 0; m < W; ++m) wv[m][e] = flat[e * W + m];
+    }
+    float dwv[W][4];
+#pragma unroll
+    for (int m = 0; m < W; ++m)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) dwv[m][e] = 0.f;
+    auto widen = [](const uint2& u, float (&f)[4]) {
+        const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.x));
+        const float2 b2 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.y));
+        f[0] = a.x; f[1] = a.y; f[2] = b2.x; f[3] = b2.y;
+    };
+    if (t0 < T) {
+        // stream step j handles token tx = t0 - (W-1) + j: x[tx] enters the window; from tx >= t0 on dz[tx] is formed;
+        // from tx >= t0 + W-1 on dx[tx - (W-1)] leaves.  Steps run to a multiple of W so the circular indices are static.
+        const int nr = ((run + 2 * (W - 1) + W - 1) / W) * W;
+        const size_t rowbase = (size_t)b * T;
+        const uint32_t slot0 = (uint32_t)__cvta_generic_to_shared(ring + threadIdx.x);
+        auto issue = [&](int j) {
+            if (j < nr) {
+                const int tx = min(max(t0 - (W - 1) + j, 0), T - 1);
+                const size_t off = (rowbase + tx) * C + c;
+                const uint32_t dst = slot0 + (uint32_t)((j % D) * 2) * 256u * 8u;
+                asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(dst), "l"(x + off) : "memory");
+                asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(dst + 256u * 8u), "l"(dy + off) : "memory");
+            }
+            asm volatile("cp.async.commit_group;" ::: "memory");
+        };
+#pragma unroll 1
+        for (int j = 0; j < D - 1; ++j) issue(j);
+        float xc[W][4], dzc[W][4];
+#pragma unroll
+        for (int m = 0; m < W; ++m)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) xc[m][e] = dzc[m][e] = 0.f;
+#pragma unroll 1
+        for (int jj = 0; jj < nr; jj += W) {
+#pragma unroll
+            for (int u = 0; u < W; ++u) {
+                const int j = jj + u;
+                issue(j + D - 1);                  // refills the slot whose row was consumed one step ago
+                asm volatile("cp.async.wait_group %0;" ::"n"(D - 1) : "memory");
+                const int tx = t0 - (W - 1) + j;
+                const uint2 xr = ring[((j % D) * 2) * 256 + threadIdx.x];
+                const uint2 gr = ring[((j % D) * 2 + 1) * 256 + threadIdx.x];
+                widen(xr, xc[u]);
+                if (tx < 0 || tx >= T) {
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) xc[u][e] = 0.f;
+                }
+                float gy[4];
+                widen(gr, gy);
+                const bool live = tx >= t0 && tx < T;             // dz[tx] exists and belongs to this run's window
+                const bool own = live && tx < t0 + run;           // ... and its dweight is this run's
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    float z = 0.f;
+#pragma unroll
+                    for (int m = 0; m < W; ++m) z += wv[m][e] * xc[(u + 1 + m) % W][e];      // x[tx - (W-1) + m]
+                    float dzv = gy[e];
+                    if (silu) {
+                        const float sg = sigmoid_t<true>(z);
+                        dzv *= sg * (1.f + z * (1.f - sg));
+                    }
+                    dzv = live ? dzv : 0.f;
+                    dzc[u][e] = dzv;
+                    if (own) {
+#pragma unroll
+                        for (int m = 0; m < W; ++m) dwv[m][e] += dzv * xc[(u + 1 + m) % W][e];
+                    }
+                }
+                const int td = tx - (W - 1);
+                if (td >= t0 && td < t0 + run && td < T) {
+                    float a[4];
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        a[e] = 0.f;
+#pragma unroll
+                        for (int m = 0; m < W; ++m) a[e] += wv[m][e] * dzc[(u - m + W) % W][e];  // dz[tx - m]
+                    }
+                    st_cvec<4, true>(dx, (rowbase + td) * C + c, a);
+                }
+            }
+        }
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+    }
+    __syncthreads();                               // every warp has drained its ring: the memory becomes the partials
+#pragma unroll
+    for (int m = 0; m < W; ++m)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) red[g][m][4 * p + e] = dwv[m][e];
+    __syncthreads();
+    if (threadIdx.x < 128) {
+        const size_t pblk = (size_t)blockIdx.z * gridDim.y + blockIdx.y;
+#pragma unroll
+        for (int m = 0; m < W; ++m) {
+            float a = 0.f;
+#pragma unroll
+            for (int r = 0; r < 8; ++r) a += red[r][m][threadIdx.x];
+            dw_part[(pblk * C + blockIdx.x * 128 + threadIdx.x) * W + m] = a;
+        }
+    }
+}
+
 // =============================================================================================
 // gated RMSNorm:  y = x * inv * w * sigmoid(gate),  inv = rsqrt(mean(x^2) + eps).  One warp per row.
 // =============================================================================================
@@ -1523,8 +1661,18 @@ int conv_fwd_fast(int n, int B, int T, int C, int bf16, int wf32, int silu, cons
 template <int W>
 int conv_bwd_fast(int n, int B, int T, int C, int bf16, int wf32, int silu, const pw::ConvBwdItems& it, float* const* dwgt,
                   float* part, cudaStream_t st) {
-    const dim3 grid(ceil_div(C, pw::kConvTileC), ceil_div(T, pw::kConvTileT), B * n);
-    if (bf16) KDA_LAUNCH("conv_bwd_kernel", st, pw::conv_bwd_tile_kernel<W, true><<<grid, 256, 0, st>>>(B, T, C, silu, wf32, it, part));
+    dim3 grid(ceil_div(C, pw::kConvTileC), ceil_div(T, pw::kConvTileT), B * n);
+    // tokens per thread run of the streaming kernel: long runs amortise the W-1 halo rows; below ~12 warps per SM at
+    // 32-token runs the tile kernel (64 tokens x 64 channels per block, more and smaller blocks) is the faster one
+    const long long warps64 = (long long)(C / 128) * ceil_div(T, 64) * B * n;
+    if (bf16 && C % 128 == 0 && warps64 >= 148LL * 12) {
+        const int run = warps64 >= 148LL * 48 ? 64 : 32;
+        grid = dim3(C / 128, ceil_div(T, 8 * run), B * n);                  // never more partial rows than the tile kernel's
+        const size_t ring_bytes = (size_t)pw::kConvRingDepth * 2 * 256 * 8;
+        if (cudaFuncSetAttribute(pw::conv_bwd_ring_kernel<W>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ring_bytes) != cudaSuccess)
+            return KDA_ERR_CUDA;
+        KDA_LAUNCH("conv_bwd_kernel", st, pw::conv_bwd_ring_kernel<W><<<grid, 256, ring_bytes, st>>>(B, T, C, run, silu, wf32, it, part));
+    } else if (bf16) KDA_LAUNCH("conv_bwd_kernel", st, pw::conv_bwd_tile_kernel<W, true><<<grid, 256, 0, st>>>(B, T, C, silu, wf32, it, part));
     else KDA_LAUNCH("conv_bwd_kernel", st, pw::conv_bwd_tile_kernel<W, false><<<grid, 256, 0, st>>>(B, T, C, silu, wf32, it, part));
     const int nblk = grid.y * B;                  // partial rows per item
     pw::ColumnSumItems outs = {};

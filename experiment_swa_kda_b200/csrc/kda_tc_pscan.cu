@@ -403,6 +403,16 @@ __global__ void __launch_bounds__(256, 1)
     const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
     bool ok = true;
     for (int k = 1; k < p.nseg && ok; ++k) {
+        // the segment's local final state: its loads fly while S_k is split, stored and multiplied
+        float l[64];
+        {
+            const float4* Lp = reinterpret_cast<const float4*>(p.seg_fin + ((size_t)(rec * units + 2 * k - 1) * 128 + v) * 128 + 64 * g);
+#pragma unroll
+            for (int c = 0; c < 16; ++c) {
+                const float4 a = Lp[c];
+                l[4 * c] = a.x; l[4 * c + 1] = a.y; l[4 * c + 2] = a.z; l[4 * c + 3] = a.w;
+            }
+        }
         // S_k as hi + lo: the A operand of this product and, in global memory, of the chunk fix-ups of segment k
         uint4* ghi = reinterpret_cast<uint4*>(p.seg_start + (((size_t)rec * p.nseg + k) * 2) * 16384 + (size_t)v * 128 + 64 * g);
         uint4* glo = ghi + 16384 / 8;
@@ -431,16 +441,6 @@ __global__ void __launch_bounds__(256, 1)
                 tc_fence_after();
                 issue_hilo_product(tmem, sm, sm + 65536 + (k - 1) * 32768);
                 umma_commit(&bar_mma);
-            }
-        }
-        // the segment's local final state, while the product runs
-        float l[64];
-        {
-            const float4* Lp = reinterpret_cast<const float4*>(p.seg_fin + ((size_t)(rec * units + 2 * k - 1) * 128 + v) * 128 + 64 * g);
-#pragma unroll
-            for (int c = 0; c < 16; ++c) {
-                const float4 a = Lp[c];
-                l[4 * c] = a.x; l[4 * c + 1] = a.y; l[4 * c + 2] = a.z; l[4 * c + 3] = a.w;
             }
         }
         ok = mbar_wait(&bar_mma, (uint32_t)(k - 1) & 1, p.status, 83) && ok;
@@ -502,6 +502,12 @@ __global__ void __launch_bounds__(256, 2)
         }
     }
     if (warp == 1) tmem_alloc(&tmem_slot, 128);
+    // this thread's part of the local states (row v, keys 64 g .. 64 g + 63), fetched while the tiles fly and the
+    // product runs
+    uint4* io = reinterpret_cast<uint4*>(p.Hp + (size_t)ch * 16384 + (size_t)v * 128 + 64 * g);
+    uint4 loc[8];
+#pragma unroll
+    for (int c = 0; c < 8; ++c) loc[c] = io[c];
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -525,12 +531,11 @@ __global__ void __launch_bounds__(256, 2)
             uint32_t r[32];
             tmem_ld32(tmem + lane_base + 64 * g + 32 * b, r);
             tmem_ld_wait();
-            uint4* io = reinterpret_cast<uint4*>(p.Hp + (size_t)ch * 16384 + (size_t)v * 128 + 64 * g + 32 * b);
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
                 float l[8];
-                unpack_bf16x8(io[c], l);
-                io[c] = make_uint4(pack_bf16(__uint_as_float(r[8 * c]) + l[0], __uint_as_float(r[8 * c + 1]) + l[1]),
+                unpack_bf16x8(loc[4 * b + c], l);
+                io[4 * b + c] = make_uint4(pack_bf16(__uint_as_float(r[8 * c]) + l[0], __uint_as_float(r[8 * c + 1]) + l[1]),
                                    pack_bf16(__uint_as_float(r[8 * c + 2]) + l[2], __uint_as_float(r[8 * c + 3]) + l[3]),
                                    pack_bf16(__uint_as_float(r[8 * c + 4]) + l[4], __uint_as_float(r[8 * c + 5]) + l[5]),
                                    pack_bf16(__uint_as_float(r[8 * c + 6]) + l[6], __uint_as_float(r[8 * c + 7]) + l[7]));

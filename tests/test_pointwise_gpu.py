@@ -69,7 +69,12 @@ def test_conv_bf16_matches_oracle(B, T, C, state):
 
 
 @pytest.mark.parametrize("B,T,C,dtype", [(2, 4096, 384, torch.bfloat16), (1, 100, 20, torch.bfloat16), (2, 67, 384, torch.float32),
-                                         (3, 1, 64, torch.float32), (1, 5, 130, torch.bfloat16), (2, 129, 72, torch.float32)])
+                                         (3, 1, 64, torch.float32), (1, 5, 130, torch.bfloat16), (2, 129, 72, torch.float32),
+                                         # bf16 with C % 128 == 0: small sizes stay on the tile kernel, large ones take the
+                                         # streaming backward (32 and 64 tokens per thread run), all with ragged ends
+                                         (1, 1, 128, torch.bfloat16), (2, 3, 256, torch.bfloat16), (3, 67, 128, torch.bfloat16),
+                                         (2, 1031, 1024, torch.bfloat16), (2, 4099, 2048, torch.bfloat16),
+                                         (1, 30001, 2048, torch.bfloat16)])
 def test_conv_training_path_matches_oracle(B, T, C, dtype):
     """No carried-in window, no final state: the tiled forward / backward kernels (ragged T and C tails included)."""
     gen = torch.Generator().manual_seed(T * 7 + C)
