@@ -317,9 +317,13 @@ __global__ void __launch_bounds__(kAffineScanThreads, 1)
         }
         float* fin = split ? p.seg_fin + (size_t)unit * 16384 : (p.s_out ? p.s_out + ((size_t)seq * H + h) * 16384 : nullptr);
         if (ok && abort_flag == 0 && fin) {
-            float4* dst = reinterpret_cast<float4*>(fin + (size_t)v * 128 + col0);
+            // split units leave their final state thread-major (float4 j of state thread tid at [j][tid]: every warp
+            // store is one contiguous 512-byte run, and the fix-up's threads own the same elements); the scan's final
+            // state goes out in the caller's row-major layout
+            float4* dst = split ? reinterpret_cast<float4*>(fin) + tid : reinterpret_cast<float4*>(fin + (size_t)v * 128 + col0);
+            const int dstep = split ? 256 : 1;
 #pragma unroll
-            for (int j = 0; j < kScanCols / 4; ++j) dst[j] = make_float4(s[4 * j], s[4 * j + 1], s[4 * j + 2], s[4 * j + 3]);
+            for (int j = 0; j < kScanCols / 4; ++j) dst[j * dstep] = make_float4(s[4 * j], s[4 * j + 1], s[4 * j + 2], s[4 * j + 3]);
         }
     }
     tc_fence_before();
@@ -328,28 +332,20 @@ __global__ void __launch_bounds__(kAffineScanThreads, 1)
 }
 
 // ---------------------------------------------------------------------------------------------
-// split scans, second and third pass.
-//   boundary (one CTA per sequence-head): the true state at the start of every segment,
-//       S_1 = final state of unit 0;  S_{k+1} = S_k Pfin_k + Lfin_k;  the scan's final state = S_nseg
-//     a chain of nseg - 1 products with the running state in registers and every Pfin panel fetched up front;
-//     each S_k is left as two bf16 panels (hi, lo: their sum carries float32-class accuracy)
-//   chunks (one CTA per chunk-head of segments >= 1): the true state at the chunk's start,  (S_k hi + S_k lo) P + L
-// so that only P's own bf16 rounding touches the carried state.
+// split scans, second pass: from the units' local states to the true states (see tc_scan_fixup_kernel)
 // ---------------------------------------------------------------------------------------------
 struct ScanFixArgs {
     const int* seq_chunk0;
     const int* chunk_seq;
     const int* chunk_len;
     const float* seg_fin;      // [rec*units][128][128]
-    __nv_bfloat16* seg_start;  // [rec*nseg][2][128][128]
     __nv_bfloat16* Hp;         // [nch][128][128]: local states in, true states out
     float* s_out;              // final state of the scan, V-first [n_seq][H][128][128], or null
     int H, nseg, bwd;
     int* status;
 };
 
-constexpr int kFixSmem = 3 * 32768 + 1024;          // S_k hi | S_k lo | P
-constexpr int kBoundarySmem = 5 * 32768 + 1024;     // S_k hi | S_k lo | up to three Pfin panels
+constexpr int kFixSmem = 3 * 32768 + 1024;          // S hi | S lo | P
 
 // D[tmem] = (A_hi + A_lo) B: A K-major [128 v][128 k] in two bf16 terms, B = P [k][n] MN-major
 __device__ __forceinline__ void issue_hilo_product(uint32_t tmem, const uint8_t* a_hi, const uint8_t* b) {
@@ -365,116 +361,24 @@ __device__ __forceinline__ void issue_hilo_product(uint32_t tmem, const uint8_t*
     }
 }
 
-__global__ void __launch_bounds__(256, 1)
-    tc_scan_boundary_kernel(const __grid_constant__ CUtensorMap mF, ScanFixArgs p) {
-    extern __shared__ uint8_t smem_raw[];
-    uint8_t* sm = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);   // pointer arithmetic keeps the shared address space
-    __shared__ uint64_t bar_in[3], bar_mma;
-    __shared__ uint32_t tmem_slot;
-    const int seq = blockIdx.x, h = blockIdx.y, H = p.H, units = 2 * p.nseg - 1;
-    const int rec = seq * H + h;
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int g = warp >> 2;                        // key half handled by this warpgroup
-    const int v = (warp & 3) * 32 + lane;           // value row = TMEM lane
-    if (tid == 0) {
-        for (int k = 0; k < 3; ++k) mbar_init(&bar_in[k], 1);
-        mbar_init(&bar_mma, 1);
-        mbar_fence_init();
-        for (int k = 1; k < p.nseg; ++k) {          // every segment's final composite, up front
-            mbar_expect_tx(&bar_in[k - 1], 32768);
-            for (int nb = 0; nb < 2; ++nb)
-                tma_load_2d(sm + 65536 + (k - 1) * 32768 + nb * 16384, &mF, &bar_in[k - 1], nb * 64, (rec * units + 2 * k) * 128);
-        }
-    }
-    if (warp == 1) tmem_alloc(&tmem_slot, 128);
-    float cur[64];                                  // S_k[v][64 g .. 64 g + 63]
-    {
-        const float4* src = reinterpret_cast<const float4*>(p.seg_fin + ((size_t)rec * units * 128 + v) * 128 + 64 * g);
-#pragma unroll
-        for (int c = 0; c < 16; ++c) {
-            const float4 a = src[c];
-            cur[4 * c] = a.x; cur[4 * c + 1] = a.y; cur[4 * c + 2] = a.z; cur[4 * c + 3] = a.w;
-        }
-    }
-    tc_fence_before();
-    __syncthreads();
-    tc_fence_after();
-    const uint32_t tmem = tmem_slot;
-    const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
-    bool ok = true;
-    for (int k = 1; k < p.nseg && ok; ++k) {
-        // the segment's local final state: its loads fly while S_k is split, stored and multiplied
-        float l[64];
-        {
-            const float4* Lp = reinterpret_cast<const float4*>(p.seg_fin + ((size_t)(rec * units + 2 * k - 1) * 128 + v) * 128 + 64 * g);
-#pragma unroll
-            for (int c = 0; c < 16; ++c) {
-                const float4 a = Lp[c];
-                l[4 * c] = a.x; l[4 * c + 1] = a.y; l[4 * c + 2] = a.z; l[4 * c + 3] = a.w;
-            }
-        }
-        // S_k as hi + lo: the A operand of this product and, in global memory, of the chunk fix-ups of segment k
-        uint4* ghi = reinterpret_cast<uint4*>(p.seg_start + (((size_t)rec * p.nseg + k) * 2) * 16384 + (size_t)v * 128 + 64 * g);
-        uint4* glo = ghi + 16384 / 8;
-#pragma unroll
-        for (int c = 0; c < 8; ++c) {
-            uint32_t hi[4], lo[4];
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const __nv_bfloat162 hh = __floats2bfloat162_rn(cur[8 * c + 2 * e], cur[8 * c + 2 * e + 1]);
-                const float2 back = __bfloat1622float2(hh);
-                hi[e] = *reinterpret_cast<const uint32_t*>(&hh);
-                lo[e] = pack_bf16(cur[8 * c + 2 * e] - back.x, cur[8 * c + 2 * e + 1] - back.y);
-            }
-            const uint4 uh = make_uint4(hi[0], hi[1], hi[2], hi[3]), ul = make_uint4(lo[0], lo[1], lo[2], lo[3]);
-            *reinterpret_cast<uint4*>(sm + g * 16384 + sw128_off(v, c)) = uh;
-            *reinterpret_cast<uint4*>(sm + 32768 + g * 16384 + sw128_off(v, c)) = ul;
-            ghi[c] = uh;
-            glo[c] = ul;
-        }
-        fence_async_smem();
-        tc_fence_before();
-        __syncthreads();
-        if (tid == 0) {
-            ok = mbar_wait(&bar_in[k - 1], 0, p.status, 82);
-            if (ok) {
-                tc_fence_after();
-                issue_hilo_product(tmem, sm, sm + 65536 + (k - 1) * 32768);
-                umma_commit(&bar_mma);
-            }
-        }
-        ok = mbar_wait(&bar_mma, (uint32_t)(k - 1) & 1, p.status, 83) && ok;
-        ok = __syncthreads_and(ok);
-        tc_fence_after();
-        if (ok) {
-#pragma unroll
-            for (int b = 0; b < 2; ++b) {
-                uint32_t r[32];
-                tmem_ld32(tmem + lane_base + 64 * g + 32 * b, r);
-                tmem_ld_wait();
-#pragma unroll
-                for (int j = 0; j < 32; ++j) cur[32 * b + j] = __uint_as_float(r[j]) + l[32 * b + j];
-            }
-        }
-        tc_fence_before();
-        __syncthreads();      // the next product overwrites the operand buffers and the accumulator
-        tc_fence_after();
-    }
-    if (ok && p.s_out != nullptr) {                 // S_nseg: the scan's final state
-        float4* dst = reinterpret_cast<float4*>(p.s_out + ((size_t)rec * 128 + v) * 128 + 64 * g);
-#pragma unroll
-        for (int c = 0; c < 16; ++c) dst[c] = make_float4(cur[4 * c], cur[4 * c + 1], cur[4 * c + 2], cur[4 * c + 3]);
-    }
-    if (warp == 1) tmem_dealloc(tmem, 128);
-}
-
+// Chunk-parallel fix-up of a split scan, one CTA per chunk-head of segments 1 .. nseg-1 (2 CTAs per SM).  The true state
+// at the start of segment k obeys S_1 = final state of segment 0, S_{j+1} = S_j Pfin_j + Lfin_j (final composite and final
+// local state of segment j); every CTA of segment k walks that short chain itself (k - 1 products; the panels sit in L2
+// and all CTAs run side by side, which costs less than a separate launch chaining them once on a handful of SMs), then
+// adds S_k Pp_c to the local state the scan published for its chunk.  S is carried between products as a bf16 hi + lo
+// pair in shared memory (the A operand), so the correction keeps float32-class accuracy.  The CTA of the sequence's last
+// step goes one product further and writes the scan's final state.
+// A thread owns one accumulator row (TMEM lane), so nothing it touches in global memory is addressed row-per-thread:
+// the float32 states come thread-major (see the scan kernel), the chunk's bf16 panel comes and goes by TMA through the
+// B-operand buffer, and the final state is transposed through shared memory.
 __global__ void __launch_bounds__(256, 2)
-    tc_scan_fixup_kernel(const __grid_constant__ CUtensorMap mPp, const __grid_constant__ CUtensorMap mSs, ScanFixArgs p) {
+    tc_scan_fixup_kernel(const __grid_constant__ CUtensorMap mPp, const __grid_constant__ CUtensorMap mF,
+                         const __grid_constant__ CUtensorMap mHp, ScanFixArgs p) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* sm = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);   // pointer arithmetic keeps the shared address space
     __shared__ uint64_t bar_in, bar_mma;
     __shared__ uint32_t tmem_slot;
-    const int h = blockIdx.y, H = p.H;
+    const int h = blockIdx.y, H = p.H, units = 2 * p.nseg - 1;
     const int slot = blockIdx.x;
     if (p.chunk_len[slot] == 0) return;
     const int seq = p.chunk_seq[slot];
@@ -486,62 +390,156 @@ __global__ void __launch_bounds__(256, 2)
     if (k == 0) return;                             // segment 0 holds true states already
     const int rec = seq * H + h;
     const int ch = slot * H + h;
+    const bool last = step == n_total - 1 && p.s_out != nullptr;      // this CTA also forms the scan's final state
+    const int nprod = k + (last ? 1 : 0);           // chain products 0 .. k-2, own product k-1, final-state product k
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int g = warp >> 2;
-    const int v = (warp & 3) * 32 + lane;
+    const int g = warp >> 2;                        // key half handled by this warpgroup
+    const int v = (warp & 3) * 32 + lane;           // value row = TMEM lane;  tid == g * 128 + v
+    uint8_t* Pbuf = sm + 65536;
+    uint32_t inph = 0;                              // completed phases of bar_in (uniform)
+    auto load_panel = [&](const CUtensorMap* map, int row) {
+        mbar_expect_tx(&bar_in, 32768);
+        for (int nb = 0; nb < 2; ++nb) tma_load_2d(Pbuf + nb * 16384, map, &bar_in, nb * 64, row);
+    };
+    auto load_p = [&](int t) {                      // B operand of product t
+        if (t == k - 1) load_panel(&mPp, ch * 128);
+        else load_panel(&mF, (rec * units + 2 * (t == k ? k : t + 1)) * 128);
+    };
     if (tid == 0) {
         mbar_init(&bar_in, 1);
         mbar_init(&bar_mma, 1);
         mbar_fence_init();
-        mbar_expect_tx(&bar_in, 3 * 32768);
-        const int srow = (rec * p.nseg + k) * 2 * 128;
-        for (int nb = 0; nb < 2; ++nb) {
-            tma_load_2d(sm + nb * 16384, &mSs, &bar_in, nb * 64, srow);                 // S_k hi
-            tma_load_2d(sm + 32768 + nb * 16384, &mSs, &bar_in, nb * 64, srow + 128);   // S_k lo
-            tma_load_2d(sm + 65536 + nb * 16384, &mPp, &bar_in, nb * 64, ch * 128);     // P of this chunk
-        }
+        if (k == 1) load_panel(&mHp, ch * 128);     // the first product is the chunk's own: its local state comes first
+        else load_p(0);
     }
     if (warp == 1) tmem_alloc(&tmem_slot, 128);
-    // this thread's part of the local states (row v, keys 64 g .. 64 g + 63), fetched while the tiles fly and the
-    // product runs
-    uint4* io = reinterpret_cast<uint4*>(p.Hp + (size_t)ch * 16384 + (size_t)v * 128 + 64 * g);
-    uint4 loc[8];
+    auto split_store = [&](const float (&x)[32], int b) {      // 32 keys starting at 64 g + 32 b -> hi / lo operand panels
 #pragma unroll
-    for (int c = 0; c < 8; ++c) loc[c] = io[c];
+        for (int c = 0; c < 4; ++c) {
+            uint32_t hi[4], lo[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const __nv_bfloat162 hh = __floats2bfloat162_rn(x[8 * c + 2 * e], x[8 * c + 2 * e + 1]);
+                const float2 back = __bfloat1622float2(hh);
+                hi[e] = *reinterpret_cast<const uint32_t*>(&hh);
+                lo[e] = pack_bf16(x[8 * c + 2 * e] - back.x, x[8 * c + 2 * e + 1] - back.y);
+            }
+            *reinterpret_cast<uint4*>(sm + g * 16384 + sw128_off(v, 4 * b + c)) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+            *reinterpret_cast<uint4*>(sm + 32768 + g * 16384 + sw128_off(v, 4 * b + c)) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+        }
+    };
+    auto load_f32 = [&](const float* unit_base, float (&x)[32], int b) {     // thread-major float32 state of a scan unit
+        const float4* src = reinterpret_cast<const float4*>(unit_base) + tid;
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+            const float4 a = src[(8 * b + c) * 256];
+            x[4 * c] = a.x; x[4 * c + 1] = a.y; x[4 * c + 2] = a.z; x[4 * c + 3] = a.w;
+        }
+    };
+    // S_1 = final state of segment 0
+#pragma unroll
+    for (int b = 0; b < 2; ++b) {
+        float x[32];
+        load_f32(p.seg_fin + (size_t)rec * units * 16384, x, b);
+        split_store(x, b);
+    }
+    fence_async_smem();
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = tmem_slot;
     const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
     bool ok = true;
-    if (tid == 0) {
-        ok = mbar_wait(&bar_in, 0, p.status, 80);
-        if (ok) {
-            tc_fence_after();
-            issue_hilo_product(tmem, sm, sm + 65536);
-            umma_commit(&bar_mma);
+    for (int t = 0; t < nprod && ok; ++t) {
+        const bool own = t == k - 1;
+        float add[2][32];                           // what is added to the product
+        if (own) {
+            // the chunk's local state sits in the B-operand buffer (TMA): take this thread's row, then make room for P
+            ok = mbar_wait(&bar_in, inph & 1, p.status, 82);
+            ++inph;
+            if (ok) {
+#pragma unroll
+                for (int c = 0; c < 8; ++c) {
+                    float l[8];
+                    unpack_bf16x8(*reinterpret_cast<const uint4*>(Pbuf + g * 16384 + sw128_off(v, c)), l);
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) add[c >> 2][8 * (c & 3) + e] = l[e];
+                }
+            }
+            fence_async_smem();
+            ok = __syncthreads_and(ok);
+            if (ok && tid == 0) load_p(t);
+        } else {
+            // the final local state of the segment this chain step crosses (float32, thread-major): flies during the product
+            const float* L = p.seg_fin + (size_t)(rec * units + 2 * (t == k ? k : t + 1) - 1) * 16384;
+            load_f32(L, add[0], 0);
+            load_f32(L, add[1], 1);
         }
-    }
-    ok = mbar_wait(&bar_mma, 0, p.status, 81) && ok;
-    ok = __syncthreads_and(ok);
-    tc_fence_after();
-    if (ok) {
+        if (tid == 0 && ok) {
+            ok = mbar_wait(&bar_in, inph & 1, p.status, 80);
+            if (ok) {
+                tc_fence_after();
+                issue_hilo_product(tmem, sm, Pbuf);
+                umma_commit(&bar_mma);
+            }
+        }
+        ++inph;
+        if (ok) ok = mbar_wait(&bar_mma, (uint32_t)t & 1, p.status, 81);
+        ok = __syncthreads_and(ok);                 // the product has read both operand buffers
+        tc_fence_after();
+        if (ok && tid == 0 && !own && t + 1 < nprod) {            // next panel into the free buffer while this result is read out
+            if (t + 1 == k - 1) load_panel(&mHp, ch * 128);
+            else load_p(t + 1);
+        }
+        if (ok) {
 #pragma unroll
-        for (int b = 0; b < 2; ++b) {
-            uint32_t r[32];
-            tmem_ld32(tmem + lane_base + 64 * g + 32 * b, r);
-            tmem_ld_wait();
+            for (int b = 0; b < 2; ++b) {
+                uint32_t r[32];
+                tmem_ld32(tmem + lane_base + 64 * g + 32 * b, r);
+                tmem_ld_wait();
+                float x[32];
 #pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                float l[8];
-                unpack_bf16x8(loc[4 * b + c], l);
-                io[4 * b + c] = make_uint4(pack_bf16(__uint_as_float(r[8 * c]) + l[0], __uint_as_float(r[8 * c + 1]) + l[1]),
-                                   pack_bf16(__uint_as_float(r[8 * c + 2]) + l[2], __uint_as_float(r[8 * c + 3]) + l[3]),
-                                   pack_bf16(__uint_as_float(r[8 * c + 4]) + l[4], __uint_as_float(r[8 * c + 5]) + l[5]),
-                                   pack_bf16(__uint_as_float(r[8 * c + 6]) + l[6], __uint_as_float(r[8 * c + 7]) + l[7]));
+                for (int j = 0; j < 32; ++j) x[j] = __uint_as_float(r[j]) + add[b][j];
+                if (own) {                          // the chunk's true state -> B-operand buffer -> TMA store; S_k stays put
+#pragma unroll
+                    for (int c = 0; c < 4; ++c)
+                        *reinterpret_cast<uint4*>(Pbuf + g * 16384 + sw128_off(v, 4 * b + c)) =
+                            make_uint4(pack_bf16(x[8 * c], x[8 * c + 1]), pack_bf16(x[8 * c + 2], x[8 * c + 3]),
+                                       pack_bf16(x[8 * c + 4], x[8 * c + 5]), pack_bf16(x[8 * c + 6], x[8 * c + 7]));
+                } else if (t == k) {
+                    // the scan's final state, row-major for the caller: rows through the dead operand panels (16-byte
+                    // pieces XOR-swizzled by row so that the stores spread over the banks), written out below
+#pragma unroll
+                    for (int c = 0; c < 8; ++c)
+                        *reinterpret_cast<float4*>(sm + v * 512 + (((16 * g + 8 * b + c) ^ (v & 7)) << 4)) =
+                            make_float4(x[4 * c], x[4 * c + 1], x[4 * c + 2], x[4 * c + 3]);
+                } else {
+                    split_store(x, b);              // S_{t+2}: the next product's A operand
+                }
+            }
+        }
+        fence_async_smem();
+        tc_fence_before();
+        __syncthreads();                            // operand panels rewritten, accumulator read: next product may go
+        tc_fence_after();
+        if (ok && own && tid == 0) {
+            for (int nb = 0; nb < 2; ++nb) tma_store_2d(&mHp, Pbuf + nb * 16384, nb * 64, ch * 128);
+            tma_store_commit();
+            if (t + 1 < nprod) {                    // the final-state product follows: its panel needs the buffer
+                tma_store_wait_read();
+                load_p(t + 1);
+            }
+        }
+        if (ok && t == k) {
+            float4* dst = reinterpret_cast<float4*>(p.s_out + (size_t)rec * 16384);
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                const int f = i * 256 + tid, row = f >> 5, c16 = f & 31;       // float4 f of the row-major 128 x 128 tile
+                dst[f] = *reinterpret_cast<const float4*>(sm + row * 512 + ((c16 ^ (row & 7)) << 4));
             }
         }
     }
+    if (tid == 0) tma_store_wait_read();            // shared memory must outlive the reads of the bulk store
     tc_fence_before();
     __syncthreads();
     if (warp == 1) tmem_dealloc(tmem, 128);
@@ -829,17 +827,15 @@ __global__ void __launch_bounds__(256, 3)
 static int scan_fixup(const simt::Ws& w, const tc::TcWs& t, int n_seq, __nv_bfloat16* panels, float* s_out, int bwd,
                       const CUtensorMap& mPp, const CUtensorMap& mF, cudaStream_t st) {
     using namespace tc;
-    CUtensorMap mSs;
-    if (make_map_bf16(&mSs, t.seg_start, (uint64_t)n_seq * w.H * t.nseg * 2 * 128, 128, 64, 128)) return KDA_ERR_CUDA;
-    if (cudaFuncSetAttribute(tc_scan_fixup_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kFixSmem) != cudaSuccess ||
-        cudaFuncSetAttribute(tc_scan_boundary_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kBoundarySmem) != cudaSuccess)
+    (void)n_seq;
+    if (cudaFuncSetAttribute(tc_scan_fixup_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kFixSmem) != cudaSuccess)
         return KDA_ERR_CUDA;
     ScanFixArgs f;
-    f.seq_chunk0 = w.seq_chunk0; f.chunk_seq = w.chunk_seq; f.chunk_len = w.chunk_len; f.seg_fin = t.seg_fin; f.seg_start = t.seg_start;
+    f.seq_chunk0 = w.seq_chunk0; f.chunk_seq = w.chunk_seq; f.chunk_len = w.chunk_len; f.seg_fin = t.seg_fin;
     f.Hp = panels; f.s_out = s_out; f.H = w.H; f.nseg = t.nseg; f.bwd = bwd; f.status = t.status;
-    KDA_LAUNCH("tc_scan_boundary_kernel", st, tc_scan_boundary_kernel<<<dim3(n_seq, w.H), 256, kBoundarySmem, st>>>(mF, f));
-    if (int e = launch_status()) return e;
-    KDA_LAUNCH("tc_scan_fixup_kernel", st, tc_scan_fixup_kernel<<<dim3(w.nslots, w.H), 256, kFixSmem, st>>>(mPp, mSs, f));
+    CUtensorMap mHp;
+    if (make_map_bf16(&mHp, panels, (uint64_t)w.nslots * w.H * 128, 128, 64, 128)) return KDA_ERR_CUDA;
+    KDA_LAUNCH("tc_scan_fixup_kernel", st, tc_scan_fixup_kernel<<<dim3(w.nslots, w.H), 256, kFixSmem, st>>>(mPp, mF, mHp, f));
     return launch_status();
 }
 

@@ -24,8 +24,6 @@ struct TcWs {
     __nv_bfloat16* Pp;          // [nch][128][128]  split scans only: composite state-to-state maps at each chunk start
     __nv_bfloat16* fin_panel;   // [n_seq*H*units][128][128]  split scans only: final state of every scan unit as a bf16 panel
     float* seg_fin;             // [n_seq*H*units][128][128]  split scans only: the same in float32
-    __nv_bfloat16* seg_start;   // [n_seq*H*nseg][2][128][128] split scans only: true state at the start of each segment as two
-                                //                             bf16 panels (hi, lo) whose sum carries float32-class accuracy
     int nseg;                   // scan segments per (sequence, head): 1 (no split), 2 or 4; units = 2 * nseg - 1
     float* decay_end;           // [nch][128]       exp(G_end)
     int* status;                // device status word (0 = ok); points at the workspace's word (simt::Ws::status)
@@ -77,7 +75,6 @@ inline TcWs carve_tc(const KdaChunkShape& sh, void* mem, size_t* bytes = nullptr
     t.Pp = c.take<__nv_bfloat16>(t.nseg > 1 ? nch * 16384 : 0);
     t.fin_panel = c.take<__nv_bfloat16>(units * 16384);
     t.seg_fin = c.take<float>(units * 16384);
-    t.seg_start = c.take<__nv_bfloat16>(t.nseg > 1 ? (size_t)sh.n_seq * sh.heads * t.nseg * 2 * 16384 : 0);
     t.decay_end = c.take<float>(nch * 128);
     t.status = c.take<int>(64);
     t.fwd_only = sh.forward_only ? 1 : 0;
