@@ -572,7 +572,8 @@ constexpr int kChunkOutNormSmem = kOutG + 16384 + 1024;      // + the norm gate'
 __global__ void __launch_bounds__(256, 2)
     tc_chunk_out_kernel(const __grid_constant__ CUtensorMap mH, const __grid_constant__ CUtensorMap mW,
                         const __grid_constant__ CUtensorMap mR, const __grid_constant__ CUtensorMap mUT,
-                        const __grid_constant__ CUtensorMap mAT, const __grid_constant__ CUtensorMap mG, ChunkOutArgs p) {
+                        const __grid_constant__ CUtensorMap mAT, const __grid_constant__ CUtensorMap mG,
+                        const __grid_constant__ CUtensorMap mZT, ChunkOutArgs p) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* sm = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);   // pointer arithmetic keeps the shared address space
     uint8_t* Zop = sm + kOutZ;                     // [128 rows x 128 B] K-major A operand
@@ -630,7 +631,6 @@ __global__ void __launch_bounds__(256, 2)
         uint32_t r[32];
         tmem_ld32(tmem + lane_base + 32 * g, r);
         tmem_ld_wait();
-        uint4* zdst = reinterpret_cast<uint4*>(p.ZT + (size_t)ch * 8192 + (size_t)v * 64 + 32 * g);
 #pragma unroll
         for (int q4 = 0; q4 < 4; ++q4) {
             const int c16 = g * 4 + q4;
@@ -642,13 +642,16 @@ __global__ void __launch_bounds__(256, 2)
             z.z = pack_bf16(u[4] - __uint_as_float(r[8 * q4 + 4]), u[5] - __uint_as_float(r[8 * q4 + 5]));
             z.w = pack_bf16(u[6] - __uint_as_float(r[8 * q4 + 6]), u[7] - __uint_as_float(r[8 * q4 + 7]));
             *reinterpret_cast<uint4*>(Zop + sw128_off(v, c16)) = z;
-            if (ok && p.ZT != nullptr) zdst[q4] = z;      // kept for the backward only
         }
     }
     fence_async_smem();
     tc_fence_before();
     ok = __syncthreads_and(ok);
     if (tid == 0 && ok) {
+        if (p.ZT != nullptr) {                      // kept for the backward only: the operand tile is the panel, as TMA lays it out
+            tma_store_2d(&mZT, Zop, 0, ch * 128);
+            tma_store_commit();
+        }
         tc_fence_after();
         const uint32_t a0 = smem_u32(Zop), b0 = smem_u32(sm + kOutA);
         const uint32_t idesc = umma_idesc_bf16(128, 64, kMajorK, kMajorMN);
@@ -714,6 +717,7 @@ __global__ void __launch_bounds__(256, 2)
             }
         }
     }
+    if (tid == 0) tma_store_wait_read();            // the Z^T tile must outlive the reads of its bulk store
     tc_fence_before();
     __syncthreads();
     if (warp == 1) tmem_dealloc(tmem, 256);
@@ -736,7 +740,8 @@ constexpr int kChunkDzSmem = kDzA + 8192 + 1024;
 
 __global__ void __launch_bounds__(256, 3)
     tc_chunk_dz_kernel(const __grid_constant__ CUtensorMap mdH, const __grid_constant__ CUtensorMap mE,
-                       const __grid_constant__ CUtensorMap mdO, const __grid_constant__ CUtensorMap mAT, ChunkDzArgs p) {
+                       const __grid_constant__ CUtensorMap mdO, const __grid_constant__ CUtensorMap mAT,
+                       const __grid_constant__ CUtensorMap mdZT, ChunkDzArgs p) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* sm = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);   // pointer arithmetic keeps the shared address space
     __shared__ uint64_t bar_in, bar_mma;
@@ -805,16 +810,24 @@ __global__ void __launch_bounds__(256, 3)
         uint32_t r[32];
         tmem_ld32(tmem + lane_base + 32 * g, r);
         tmem_ld_wait();
-        uint4* dst = reinterpret_cast<uint4*>(p.dZT + (size_t)ch * 8192 + (size_t)v * 64 + 32 * g);
+        // the panel leaves through the dead dH' tile in the swizzled layout and one TMA store: a thread owns a row, and
+        // row-per-thread global stores would touch 32 sectors per warp instruction
 #pragma unroll
         for (int c = 0; c < 4; ++c)
-            dst[c] = make_uint4(pack_bf16(__uint_as_float(r[8 * c]), __uint_as_float(r[8 * c + 1])),
-                                pack_bf16(__uint_as_float(r[8 * c + 2]), __uint_as_float(r[8 * c + 3])),
-                                pack_bf16(__uint_as_float(r[8 * c + 4]), __uint_as_float(r[8 * c + 5])),
-                                pack_bf16(__uint_as_float(r[8 * c + 6]), __uint_as_float(r[8 * c + 7])));
+            *reinterpret_cast<uint4*>(sm + kDzH + sw128_off(v, 4 * g + c)) =
+                make_uint4(pack_bf16(__uint_as_float(r[8 * c]), __uint_as_float(r[8 * c + 1])),
+                           pack_bf16(__uint_as_float(r[8 * c + 2]), __uint_as_float(r[8 * c + 3])),
+                           pack_bf16(__uint_as_float(r[8 * c + 4]), __uint_as_float(r[8 * c + 5])),
+                           pack_bf16(__uint_as_float(r[8 * c + 6]), __uint_as_float(r[8 * c + 7])));
     }
+    fence_async_smem();
     tc_fence_before();
-    __syncthreads();
+    ok = __syncthreads_and(ok);
+    if (tid == 0 && ok) {
+        tma_store_2d(&mdZT, sm + kDzH, 0, ch * 128);
+        tma_store_commit();
+        tma_store_wait_read();
+    }
     if (warp == 1) tmem_dealloc(tmem, 64);
 }
 
@@ -843,7 +856,7 @@ int tc_scan_forward(const simt::Ws& w, const tc::TcWs& t, int n_seq, int tokens,
                     const tc::NormEpilogue& norm, cudaStream_t st) {
     using namespace tc;
     const uint64_t nch = (uint64_t)w.nslots * w.H;
-    CUtensorMap mW, mR, mE, mAT, mUT, mH, mP, mG;
+    CUtensorMap mW, mR, mE, mAT, mUT, mH, mP, mG, mZT;
     int rc = 0;
     rc |= make_map_bf16(&mW, t.WT, nch * 128, 64, 64, 128);
     rc |= make_map_bf16(&mR, t.RT, nch * 128, 64, 64, 128);
@@ -852,6 +865,7 @@ int tc_scan_forward(const simt::Ws& w, const tc::TcWs& t, int n_seq, int tokens,
     rc |= make_map_bf16(&mUT, t.UT, nch * 128, 64, 64, 128);
     rc |= make_map_bf16(&mH, t.Hp, nch * 128, 128, 64, 128);
     rc |= make_map_bf16(&mP, t.Pn, nch * 128, 128, 64, 128);
+    rc |= make_map_bf16(&mZT, t.fwd_only ? t.UT : t.ZT, nch * 128, 64, 64, 128);      // not stored in a forward-only call
     const bool fused_norm = norm.gate != nullptr;
     if (fused_norm) rc |= make_map_bf16(&mG, norm.gate, (uint64_t)tokens, (uint64_t)w.H * 128, 64, 64);
     else mG = mAT;
@@ -884,7 +898,7 @@ int tc_scan_forward(const simt::Ws& w, const tc::TcWs& t, int n_seq, int tokens,
     oa.status = t.status;
     oa.norm = norm;
     KDA_LAUNCH("tc_chunk_out_kernel", st,
-               tc_chunk_out_kernel<<<dim3(w.nslots, w.H), 256, out_smem, st>>>(mH, mW, mR, mUT, mAT, mG, oa));
+               tc_chunk_out_kernel<<<dim3(w.nslots, w.H), 256, out_smem, st>>>(mH, mW, mR, mUT, mAT, mG, mZT, oa));
     return launch_status();
 }
 
@@ -893,7 +907,7 @@ int tc_scan_backward(const simt::Ws& w, const simt::Scr& s, const tc::TcWs& t, i
     using namespace tc;
     (void)s;
     const uint64_t nch = (uint64_t)w.nslots * w.H;
-    CUtensorMap mE, mAT, mdO, mdH, mP, mRm;
+    CUtensorMap mE, mAT, mdO, mdH, mP, mRm, mdZT;
     int rc = 0;
     rc |= make_map_bf16(&mE, t.E, nch * 64, 128, 64, 64);
     rc |= make_map_bf16(&mAT, t.AT, nch * 64, 64, 64, 64);
@@ -901,6 +915,7 @@ int tc_scan_backward(const simt::Ws& w, const simt::Scr& s, const tc::TcWs& t, i
     rc |= make_map_bf16(&mdH, t.dHp, nch * 128, 128, 64, 128);
     rc |= make_map_bf16(&mP, t.Pn, nch * 128, 128, 64, 128);
     rc |= make_map_bf16(&mRm, t.RmT, nch * 128, 64, 64, 128);
+    rc |= make_map_bf16(&mdZT, t.dZT, nch * 128, 64, 64, 128);
     if (rc) return KDA_ERR_CUDA;
     if (cudaFuncSetAttribute(tc_affine_scan_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kAffineScanSmem) != cudaSuccess ||
         cudaFuncSetAttribute(tc_chunk_dz_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kChunkDzSmem) != cudaSuccess)
@@ -927,7 +942,7 @@ int tc_scan_backward(const simt::Ws& w, const simt::Scr& s, const tc::TcWs& t, i
     ChunkDzArgs da;
     da.chunk_tok0 = w.chunk_tok0; da.chunk_len = w.chunk_len; da.dZT = t.dZT; da.H = w.H; da.status = t.status;
     KDA_LAUNCH("tc_chunk_dz_kernel", st,
-               tc_chunk_dz_kernel<<<dim3(w.nslots, w.H), 256, kChunkDzSmem, st>>>(mdH, mE, mdO, mAT, da));
+               tc_chunk_dz_kernel<<<dim3(w.nslots, w.H), 256, kChunkDzSmem, st>>>(mdH, mE, mdO, mAT, mdZT, da));
     return launch_status();
 }
 
