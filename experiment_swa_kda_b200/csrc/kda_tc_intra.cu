@@ -63,6 +63,19 @@ __device__ __forceinline__ void sts8(float* p, const float (&f)[8]) {
     *reinterpret_cast<float4*>(p) = make_float4(f[0], f[1], f[2], f[3]);
     *reinterpret_cast<float4*>(p + 4) = make_float4(f[4], f[5], f[6], f[7]);
 }
+// Per-channel tables (rows of 128 floats read 8 channels per lane): channel ch sits at ((ch >> 2) & 1) * 64 +
+// (ch >> 3) * 4 + (ch & 3), i.e. the two float4 halves of a lane's 8 channels live in separate 64-float halves of the
+// row, so that each of the two 16-byte accesses has a 16-byte lane stride (32 bytes would use half the banks).
+// `row + 4 * cg` is the lane's address for channels 8 cg .. 8 cg + 7; element-wise passes over whole rows need no change
+// as long as every table of the pass is in this order.
+__device__ __forceinline__ void lds8c(const float* p, float (&f)[8]) {
+    const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 64);
+    f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+}
+__device__ __forceinline__ void sts8c(float* p, const float (&f)[8]) {
+    *reinterpret_cast<float4*>(p) = make_float4(f[0], f[1], f[2], f[3]);
+    *reinterpret_cast<float4*>(p + 64) = make_float4(f[4], f[5], f[6], f[7]);
+}
 __device__ __forceinline__ float fast_rcp(float x) {
     float y;
     asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -298,7 +311,7 @@ __global__ void __launch_bounds__(kNT, 2)
         float tot[8];
 #pragma unroll
         for (int c = 0; c < 8; ++c) tot[c] = G[3][c] + pre[c];
-        sts8(wtot + warp * 128 + 8 * cg, tot);
+        sts8c(wtot + warp * 128 + 4 * cg, tot);
 #pragma unroll
         for (int c = 0; c < 8; ++c) pre[c] = 0.f;
     }
@@ -343,7 +356,7 @@ __global__ void __launch_bounds__(kNT, 2)
 #pragma unroll
         for (int w2 = 0; w2 < 8; ++w2) {
             float t[8];
-            lds8(wtot + w2 * 128 + 8 * cg, t);
+            lds8c(wtot + w2 * 128 + 4 * cg, t);
 #pragma unroll
             for (int c = 0; c < 8; ++c) {
                 gend[c] += t[c];
@@ -354,9 +367,9 @@ __global__ void __launch_bounds__(kNT, 2)
         for (int j = 0; j < 4; ++j)
 #pragma unroll
             for (int c = 0; c < 8; ++c) G[j][c] += pre[c];
-        if ((rq & 3) == 0) sts8(cref + J * 128 + 8 * cg, G[0]);      // first row of block J
+        if ((rq & 3) == 0) sts8c(cref + J * 128 + 4 * cg, G[0]);      // first row of block J
         if (rq == 0) {
-            sts8(gends + 8 * cg, gend);
+            sts8c(gends + 4 * cg, gend);
             float e[8];
 #pragma unroll
             for (int c = 0; c < 8; ++c) e[c] = __expf(gend[c]);
@@ -379,7 +392,7 @@ __global__ void __launch_bounds__(kNT, 2)
     // ---- operand panels, one row at a time: 16-byte pieces of the swizzled layouts
     {
         float cJ[8];
-        lds8(cref + J * 128 + 8 * cg, cJ);
+        lds8c(cref + J * 128 + 4 * cg, cJ);
         uint8_t* X = sm + kFX + (J >> 1) * 16384;
         __nv_bfloat16* Eg = p.t.E + ch * 8192 + 8 * cg;
         uint32_t rt[8][2];                             // R^T: channel c, rows 4rq .. 4rq+3 as two bf16 pairs
@@ -389,8 +402,8 @@ __global__ void __launch_bounds__(kNT, 2)
             float fq[8], fk[8], ec[8], ee[8], f0[8], o8[8];
             unpack_bf16x8(qraw[j], fq);
             unpack_bf16x8(kraw[j], fk);
-            lds8(eC + J * 128 + 8 * cg, ec);
-            lds8(eEnd + J * 128 + 8 * cg, ee);
+            lds8c(eC + J * 128 + 4 * cg, ec);
+            lds8c(eEnd + J * 128 + 4 * cg, ee);
             float tq[8], inv[8];
 #pragma unroll
             for (int c = 0; c < 8; ++c) {
@@ -412,7 +425,7 @@ __global__ void __launch_bounds__(kNT, 2)
                 if (J == 0) {
                     *reinterpret_cast<uint4*>(Sst + piece_off(i, cg, 16384)) = pack8(f0);
                     float fb[8];
-                    lds8(fbk + 8 * cg, fb);
+                    lds8c(fbk + 4 * cg, fb);
 #pragma unroll
                     for (int c = 0; c < 8; ++c) o8[c] = f0[c] * fb[c];
                     *reinterpret_cast<uint4*>(Sst + piece_off(64 + i, cg, 16384)) = pack8(o8);
@@ -456,9 +469,9 @@ __global__ void __launch_bounds__(kNT, 2)
     bool ok = mbar_wait(&bar_am[0], 0, p.t.status, 31);
     {
         float c2[8];
-        lds8(cref + 2 * 128 + 8 * cg, c2);
+        lds8c(cref + 2 * 128 + 4 * cg, c2);
         float fb2[8];
-        lds8(fbk + 2 * 128 + 8 * cg, fb2);
+        lds8c(fbk + 2 * 128 + 4 * cg, fb2);
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             const int i = 4 * rq + j;
@@ -474,7 +487,7 @@ __global__ void __launch_bounds__(kNT, 2)
                 *reinterpret_cast<uint4*>(Sst + piece_off(i, cg, 16384)) = pack8(s2);
             } else {
                 float c3[8];
-                lds8(cref + 3 * 128 + 8 * cg, c3);
+                lds8c(cref + 3 * 128 + 4 * cg, c3);
 #pragma unroll
                 for (int c = 0; c < 8; ++c) s3[c] = fk[c] * ki[j] * __expf(c3[c] - G[j][c]);
             }
