@@ -234,7 +234,8 @@ __global__ void __launch_bounds__(kNT, 2)
     tc_intra_fwd_kernel(const __grid_constant__ CUtensorMap mv, const __grid_constant__ CUtensorMap mUT,
                         const __grid_constant__ CUtensorMap mWT, const __grid_constant__ CUtensorMap mAT,
                         const __grid_constant__ CUtensorMap mMt, const __grid_constant__ CUtensorMap mE,
-                        const __grid_constant__ CUtensorMap mP, const __grid_constant__ CUtensorMap mRm, IntraFwdArgs p) {
+                        const __grid_constant__ CUtensorMap mP, const __grid_constant__ CUtensorMap mRm,
+                        const __grid_constant__ CUtensorMap mTp, IntraFwdArgs p) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* sm = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);   // pointer arithmetic keeps the shared address space
     uint8_t* Sst = sm + kFS;
@@ -541,9 +542,11 @@ __global__ void __launch_bounds__(kNT, 2)
         unit_lower_inverse(Ms, Ts, tmp);
         if (tid == 0) tma_store_wait_read();       // the staging region becomes the T operands below
         __syncthreads();
-        // ---- T: bf16 K-major B operands (plain and column-scaled by beta) and the bf16 panel; 32 bytes of a row each
+        // ---- T: bf16 K-major B operands (plain and column-scaled by beta); 32 bytes of a row each, lanes on
+        // consecutive rows (272 bytes apart: every 16-byte access of a quarter-warp lands in its own banks).  The plain
+        // operand tile is the T panel as TMA lays it out, so the panel is stored from it below.
         {
-            const int i = tid >> 2, seg = tid & 3;
+            const int i = tid & 63, seg = tid >> 6;
             const float* src = Ts + i * kLDs + 16 * seg;
             const float* bb = bet + 16 * seg;
 #pragma unroll
@@ -553,7 +556,6 @@ __global__ void __launch_bounds__(kNT, 2)
                 lds8(bb + 8 * hh, b8);
                 const uint4 u = pack8(x);
                 *reinterpret_cast<uint4*>(Tb + sw128_off(i, 2 * seg + hh)) = u;
-                if (!p.t.fwd_only) *reinterpret_cast<uint4*>(p.t.Tp + ch * 4096 + i * 64 + 16 * seg + 8 * hh) = u;
 #pragma unroll
                 for (int c = 0; c < 8; ++c) x[c] *= b8[c];
                 *reinterpret_cast<uint4*>(Tbb + sw128_off(i, 2 * seg + hh)) = pack8(x);
@@ -574,6 +576,10 @@ __global__ void __launch_bounds__(kNT, 2)
         tc_fence_before();
         ok = __syncthreads_and(ok);
         if (tid == 0 && ok) {
+            if (!p.t.fwd_only) {                   // kept for the backward only
+                tma_store_2d(&mTp, Tb, 0, (int)(ch * 64));
+                tma_store_commit();
+            }
             tc_fence_after();
             const uint32_t idesc = umma_idesc_bf16(128, 64, kMajorMN, kMajorK);
             const uint32_t b0 = smem_u32(Tb), b1 = smem_u32(Tbb);
@@ -715,19 +721,20 @@ int tc_intra_forward(const simt::Ws& w, const tc::TcWs& t, const void* q, const 
     a.q = static_cast<const __nv_bfloat16*>(q); a.k = static_cast<const __nv_bfloat16*>(k);
     a.g = g; a.beta = beta; a.gbf16 = gbf16; a.l2norm = l2norm; a.H = w.H; a.scale = scale; a.t = t; a.w = w;
     const uint64_t nch = (uint64_t)w.nslots * w.H;
-    CUtensorMap mv, mUT, mWT, mAT, mMt, mE, mP, mRm;
+    CUtensorMap mv, mUT, mWT, mAT, mMt, mE, mP, mRm, mTp;
     int rc = make_map_bf16(&mv, v, (uint64_t)tokens, (uint64_t)w.H * 128, 64, 64);
     rc |= make_map_bf16(&mUT, t.UT, nch * 128, 64, 64, 128);
     rc |= make_map_bf16(&mWT, t.WT, nch * 128, 64, 64, 128);
     rc |= make_map_bf16(&mAT, t.AT, nch * 64, 64, 64, 64);
     rc |= make_map_bf16(&mMt, t.fwd_only ? t.AT : t.Mt, nch * 64, 64, 64, 64);      // not stored in a forward-only call
     rc |= make_map_bf16(&mE, t.E, nch * 64, 128, 64, 64);
+    rc |= make_map_bf16(&mTp, t.fwd_only ? t.AT : t.Tp, nch * 64, 64, 64, 64);      // not stored in a forward-only call
     rc |= make_map_bf16(&mP, t.Pn, nch * 128, 128, 64, 128);
     rc |= make_map_bf16(&mRm, t.fwd_only ? t.WT : t.RmT, nch * 128, 64, 64, 128);      // not stored in a forward-only call
     if (rc) return KDA_ERR_CUDA;
     auto kern = gbf16 ? tc_intra_fwd_kernel<true> : tc_intra_fwd_kernel<false>;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kIntraFwdSmem) != cudaSuccess) return KDA_ERR_CUDA;
-    KDA_LAUNCH("tc_intra_fwd_kernel", st, kern<<<dim3(w.nslots, w.H), kNT, kIntraFwdSmem, st>>>(mv, mUT, mWT, mAT, mMt, mE, mP, mRm, a));
+    KDA_LAUNCH("tc_intra_fwd_kernel", st, kern<<<dim3(w.nslots, w.H), kNT, kIntraFwdSmem, st>>>(mv, mUT, mWT, mAT, mMt, mE, mP, mRm, mTp, a));
     return launch_status();
 }
 
