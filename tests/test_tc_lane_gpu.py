@@ -174,13 +174,14 @@ def test_non_finite_tokens_of_the_next_packed_sequence_do_not_leak_into_a_ragged
         assert torch.equal(a[:, :100], b)
 
 
-def test_split_scans_agree_with_the_single_chain_and_the_oracle():
-    """A long fixed-length batch with few (sequence, head) recurrences runs every state scan as three units (first half,
-    second half from zero, second half's composite maps) plus a chunk-parallel fix-up; the same tokens handed over as a
-    packed batch (cu_seqlens) take the single 64-step-per-4096-token chain.  Both must agree with each other closely and
-    with the oracle inside the bar: outputs, final state (non-zero initial state) and every gradient."""
+@pytest.mark.parametrize("T", [2048 + 64 * 3 + 17, 1024 + 64 * 4 + 5])      # 36 chunks -> 4 segments, 21 chunks -> 2 segments
+def test_split_scans_agree_with_the_single_chain_and_the_oracle(T):
+    """A long fixed-length batch with few (sequence, head) recurrences runs every state scan as 2 nseg - 1 units side by
+    side (segment 0 from the true state; every later segment once from zero and once as composite maps) plus a
+    chunk-parallel fix-up that walks the short chain of segment-start states itself; the same tokens handed over as a
+    packed batch (cu_seqlens) take the single chain.  Both must agree with each other closely and with the oracle inside
+    the bar: outputs, final state (non-zero initial state, ragged tail) and every gradient."""
     m = _kda_mod()
-    T = 2048 + 64 * 3 + 17                     # 36 chunks, ragged tail
     d = O.make_inputs(1, T, 2, 128, 128, seed=91, with_state=True)
     gen = torch.Generator().manual_seed(4)
     do = torch.randn(1, T, 2, 128, generator=gen).bfloat16().to(D0)
