@@ -339,8 +339,7 @@ __global__ void __launch_bounds__(512, 1)
                          umma_smem_desc_sw128(bT + k16 * 2048, 8192, 1024), id_k_mn, k16 > 0);
         umma_commit(&bar_mma);
     }
-    ok = ok && mbar_wait(&bar_mma, 1, p.status, 42);
-    ok = __syncthreads_and(ok);
+    ok = ok && mbar_wait(&bar_mma, 1, p.status, 42);      // no block-wide barrier: the next phase touches nothing another thread still reads
     tc_fence_after();
 
     // ================================================================ phase 3: X, Y, dM
@@ -392,8 +391,7 @@ __global__ void __launch_bounds__(512, 1)
                          umma_smem_desc_sw128(smem_u32(XT) + k16 * 32, 16, 1024), id, k16 > 0);
         umma_commit(&bar_mma);
     }
-    ok = ok && mbar_wait(&bar_mma, 0, p.status, 43);
-    ok = __syncthreads_and(ok);
+    ok = ok && mbar_wait(&bar_mma, 0, p.status, 43);      // no block-wide barrier: the next phase touches nothing another thread still reads
     tc_fence_after();
     {
         float t[16];
@@ -417,8 +415,7 @@ __global__ void __launch_bounds__(512, 1)
                          umma_smem_desc_sw128(smem_u32(Ts) + k16 * 32, 16, 1024), id, k16 > 0);
         umma_commit(&bar_mma);
     }
-    ok = ok && mbar_wait(&bar_mma, 1, p.status, 44);
-    ok = __syncthreads_and(ok);
+    ok = ok && mbar_wait(&bar_mma, 1, p.status, 44);      // no block-wide barrier: the next phase touches nothing another thread still reads
     tc_fence_after();
 
     // ================================================================ phase 4: pull-back operands
@@ -531,8 +528,7 @@ __global__ void __launch_bounds__(512, 1)
         }
         umma_commit(&bar_mma);
     }
-    ok = ok && mbar_wait(&bar_mma, 0, p.status, 45);
-    ok = __syncthreads_and(ok);
+    ok = ok && mbar_wait(&bar_mma, 0, p.status, 45);      // no block-wide barrier: the next phase touches nothing another thread still reads
     tc_fence_after();
 
     // ================================================================ phase 5: assemble the gradients
