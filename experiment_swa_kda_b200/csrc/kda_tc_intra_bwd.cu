@@ -272,8 +272,7 @@ __global__ void __launch_bounds__(512, 1)
         *reinterpret_cast<uint4*>(Qp + sw128_off(d, 2 * I)) = make_uint4(w[0], w[1], w[2], w[3]);
         *reinterpret_cast<uint4*>(Qp + sw128_off(d, 2 * I + 1)) = make_uint4(w[4], w[5], w[6], w[7]);
     }
-    ok = ok && mbar_wait(&bar_mma, 0, p.status, 41);
-    ok = __syncthreads_and(ok);
+    ok = ok && mbar_wait(&bar_mma, 0, p.status, 41);      // no block-wide barrier: see the dv staging below
     tc_fence_after();
 
     // ================================================================ phase 2a: first read-out
@@ -303,10 +302,11 @@ __global__ void __launch_bounds__(512, 1)
             dG[r] -= eE;
             ge_part += eE;
         }
-        // dv = beta dP, staged [token][channel] in the state-panel region (its products and dD are done) so that it
-        // leaves as 16-byte row segments
+        // dv = beta dP, staged [token][channel] so that it leaves as 16-byte row segments.  The staging area is the value
+        // tile: only the products that have just completed read it, so no thread needs to wait for the others here (the
+        // state panels, in contrast, are still being read by threads that are behind in the dD sums)
         tmem_ld16(tmem + lane_base + cDd + 16 * I, t);
-        __nv_bfloat16* tv = reinterpret_cast<__nv_bfloat16*>(sm + kR1);
+        __nv_bfloat16* tv = reinterpret_cast<__nv_bfloat16*>(vs);
 #pragma unroll
         for (int r = 0; r < 16; ++r) tv[(16 * I + r) * 128 + d] = __float2bfloat16(rowv[128 + 16 * I + r] * t[r]);
     }
@@ -314,7 +314,7 @@ __global__ void __launch_bounds__(512, 1)
     tc_fence_before();
     __syncthreads();
     if (ok) {
-        const __nv_bfloat16* tv = reinterpret_cast<const __nv_bfloat16*>(sm + kR1);
+        const __nv_bfloat16* tv = reinterpret_cast<const __nv_bfloat16*>(vs);
         const int c = tid & 15;
 #pragma unroll
         for (int pass = 0; pass < 2; ++pass) {
