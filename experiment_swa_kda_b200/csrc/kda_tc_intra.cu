@@ -657,9 +657,8 @@ __global__ void __launch_bounds__(kNT, 2)
                 umma_commit(&bar_uw);
             }
         }
-        if (ok) ok = mbar_wait(&bar_uw, 1, p.t.status, 34);
-        ok = __syncthreads_and(ok);
-        tc_fence_after();
+        if (ok) ok = mbar_wait(&bar_uw, 1, p.t.status, 34);      // no block-wide barrier: the staging below overwrites only what
+        tc_fence_after();                                         // the completed products were the last to read
         if (ok) {
             // both results leave through shared memory in the swizzled layout (Pn over the dead T operands and inverse
             // scratch, Rm^T over the E tile the products have finished reading) and are stored by TMA
