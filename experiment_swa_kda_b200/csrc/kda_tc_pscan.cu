@@ -341,7 +341,7 @@ struct ScanFixArgs {
     const float* seg_fin;      // [rec*units][128][128]
     __nv_bfloat16* Hp;         // [nch][128][128]: local states in, true states out
     float* s_out;              // final state of the scan, V-first [n_seq][H][128][128], or null
-    int H, nseg, bwd;
+    int H, nseg, bwd, nslots;
     int* status;
 };
 
@@ -366,8 +366,9 @@ __device__ __forceinline__ void issue_hilo_product(uint32_t tmem, const uint8_t*
 // local state of segment j); every CTA of segment k walks that short chain itself (k - 1 products; the panels sit in L2
 // and all CTAs run side by side, which costs less than a separate launch chaining them once on a handful of SMs), then
 // adds S_k Pp_c to the local state the scan published for its chunk.  S is carried between products as a bf16 hi + lo
-// pair in shared memory (the A operand), so the correction keeps float32-class accuracy.  The CTA of the sequence's last
-// step goes one product further and writes the scan's final state.
+// pair in shared memory (the A operand), so the correction keeps float32-class accuracy.  When the caller wants the scan's
+// final state, one more CTA per (sequence, head) walks the last segment's chain and applies that segment's final maps:
+// the same number of products as a chunk of that segment, so it does not lengthen the launch.
 // A thread owns one accumulator row (TMEM lane), so nothing it touches in global memory is addressed row-per-thread:
 // the float32 states come thread-major (see the scan kernel), the chunk's bf16 panel comes and goes by TMA through the
 // B-operand buffer, and the final state is transposed through shared memory.
@@ -379,19 +380,26 @@ __global__ void __launch_bounds__(256, 2)
     __shared__ uint64_t bar_in, bar_mma;
     __shared__ uint32_t tmem_slot;
     const int h = blockIdx.y, H = p.H, units = 2 * p.nseg - 1;
-    const int slot = blockIdx.x;
-    if (p.chunk_len[slot] == 0) return;
-    const int seq = p.chunk_seq[slot];
+    // blocks past the chunk slots (launched only when the caller wants the scan's final state) form that state, one per
+    // sequence: the chain of the last segment plus one product, the same length as a chunk's work in that segment
+    const bool fin = (int)blockIdx.x >= p.nslots;
+    const int slot = fin ? 0 : blockIdx.x;
+    if (!fin && p.chunk_len[slot] == 0) return;
+    const int seq = fin ? (int)blockIdx.x - p.nslots : p.chunk_seq[slot];
     const int c_begin = p.seq_chunk0[seq], c_end = p.seq_chunk0[seq + 1];
     const int n_total = c_end - c_begin;
-    const int step = p.bwd ? c_end - 1 - slot : slot - c_begin;
+    if (n_total == 0) return;
     int k = p.nseg - 1;
-    while (k > 0 && step < seg_begin(k, p.nseg, n_total)) --k;
-    if (k == 0) return;                             // segment 0 holds true states already
+    if (!fin) {
+        const int step = p.bwd ? c_end - 1 - slot : slot - c_begin;
+        while (k > 0 && step < seg_begin(k, p.nseg, n_total)) --k;
+        if (k == 0) return;                         // segment 0 holds true states already
+    }
     const int rec = seq * H + h;
     const int ch = slot * H + h;
-    const bool last = step == n_total - 1 && p.s_out != nullptr;      // this CTA also forms the scan's final state
-    const int nprod = k + (last ? 1 : 0);           // chain products 0 .. k-2, own product k-1, final-state product k
+    // products 0 .. k-2 walk the chain S_1 -> S_k; product k-1 is the chunk's own (S_k Pp_c) or, in a final-state block,
+    // S_k Pfin_k
+    const int nprod = k;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int g = warp >> 2;                        // key half handled by this warpgroup
     const int v = (warp & 3) * 32 + lane;           // value row = TMEM lane;  tid == g * 128 + v
@@ -402,14 +410,14 @@ __global__ void __launch_bounds__(256, 2)
         for (int nb = 0; nb < 2; ++nb) tma_load_2d(Pbuf + nb * 16384, map, &bar_in, nb * 64, row);
     };
     auto load_p = [&](int t) {                      // B operand of product t
-        if (t == k - 1) load_panel(&mPp, ch * 128);
-        else load_panel(&mF, (rec * units + 2 * (t == k ? k : t + 1)) * 128);
+        if (t == k - 1 && !fin) load_panel(&mPp, ch * 128);
+        else load_panel(&mF, (rec * units + 2 * (t + 1)) * 128);
     };
     if (tid == 0) {
         mbar_init(&bar_in, 1);
         mbar_init(&bar_mma, 1);
         mbar_fence_init();
-        if (k == 1) load_panel(&mHp, ch * 128);     // the first product is the chunk's own: its local state comes first
+        if (k == 1 && !fin) load_panel(&mHp, ch * 128);     // the first product is the chunk's own: its local state comes first
         else load_p(0);
     }
     if (warp == 1) tmem_alloc(&tmem_slot, 128);
@@ -451,7 +459,8 @@ __global__ void __launch_bounds__(256, 2)
     const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
     bool ok = true;
     for (int t = 0; t < nprod && ok; ++t) {
-        const bool own = t == k - 1;
+        const bool own = t == k - 1 && !fin;
+        const bool final_state = t == k - 1 && fin;
         float add[2][32];                           // what is added to the product
         if (own) {
             // the chunk's local state sits in the B-operand buffer (TMA): take this thread's row, then make room for P
@@ -471,7 +480,7 @@ __global__ void __launch_bounds__(256, 2)
             if (ok && tid == 0) load_p(t);
         } else {
             // the final local state of the segment this chain step crosses (float32, thread-major): flies during the product
-            const float* L = p.seg_fin + (size_t)(rec * units + 2 * (t == k ? k : t + 1) - 1) * 16384;
+            const float* L = p.seg_fin + (size_t)(rec * units + 2 * (t + 1) - 1) * 16384;
             load_f32(L, add[0], 0);
             load_f32(L, add[1], 1);
         }
@@ -487,8 +496,8 @@ __global__ void __launch_bounds__(256, 2)
         if (ok) ok = mbar_wait(&bar_mma, (uint32_t)t & 1, p.status, 81);
         ok = __syncthreads_and(ok);                 // the product has read both operand buffers
         tc_fence_after();
-        if (ok && tid == 0 && !own && t + 1 < nprod) {            // next panel into the free buffer while this result is read out
-            if (t + 1 == k - 1) load_panel(&mHp, ch * 128);
+        if (ok && tid == 0 && t + 1 < nprod) {      // next panel into the free buffer while this result is read out
+            if (t + 1 == k - 1 && !fin) load_panel(&mHp, ch * 128);
             else load_p(t + 1);
         }
         if (ok) {
@@ -506,7 +515,7 @@ __global__ void __launch_bounds__(256, 2)
                         *reinterpret_cast<uint4*>(Pbuf + g * 16384 + sw128_off(v, 4 * b + c)) =
                             make_uint4(pack_bf16(x[8 * c], x[8 * c + 1]), pack_bf16(x[8 * c + 2], x[8 * c + 3]),
                                        pack_bf16(x[8 * c + 4], x[8 * c + 5]), pack_bf16(x[8 * c + 6], x[8 * c + 7]));
-                } else if (t == k) {
+                } else if (final_state) {
                     // the scan's final state, row-major for the caller: rows through the dead operand panels (16-byte
                     // pieces XOR-swizzled by row so that the stores spread over the banks), written out below
 #pragma unroll
@@ -525,12 +534,8 @@ __global__ void __launch_bounds__(256, 2)
         if (ok && own && tid == 0) {
             for (int nb = 0; nb < 2; ++nb) tma_store_2d(&mHp, Pbuf + nb * 16384, nb * 64, ch * 128);
             tma_store_commit();
-            if (t + 1 < nprod) {                    // the final-state product follows: its panel needs the buffer
-                tma_store_wait_read();
-                load_p(t + 1);
-            }
         }
-        if (ok && t == k) {
+        if (ok && final_state) {
             float4* dst = reinterpret_cast<float4*>(p.s_out + (size_t)rec * 16384);
 #pragma unroll
             for (int i = 0; i < 16; ++i) {
@@ -840,15 +845,14 @@ __global__ void __launch_bounds__(256, 3)
 static int scan_fixup(const simt::Ws& w, const tc::TcWs& t, int n_seq, __nv_bfloat16* panels, float* s_out, int bwd,
                       const CUtensorMap& mPp, const CUtensorMap& mF, cudaStream_t st) {
     using namespace tc;
-    (void)n_seq;
     if (cudaFuncSetAttribute(tc_scan_fixup_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kFixSmem) != cudaSuccess)
         return KDA_ERR_CUDA;
     ScanFixArgs f;
     f.seq_chunk0 = w.seq_chunk0; f.chunk_seq = w.chunk_seq; f.chunk_len = w.chunk_len; f.seg_fin = t.seg_fin;
-    f.Hp = panels; f.s_out = s_out; f.H = w.H; f.nseg = t.nseg; f.bwd = bwd; f.status = t.status;
+    f.Hp = panels; f.s_out = s_out; f.H = w.H; f.nseg = t.nseg; f.bwd = bwd; f.nslots = w.nslots; f.status = t.status;
     CUtensorMap mHp;
     if (make_map_bf16(&mHp, panels, (uint64_t)w.nslots * w.H * 128, 128, 64, 128)) return KDA_ERR_CUDA;
-    KDA_LAUNCH("tc_scan_fixup_kernel", st, tc_scan_fixup_kernel<<<dim3(w.nslots, w.H), 256, kFixSmem, st>>>(mPp, mF, mHp, f));
+    KDA_LAUNCH("tc_scan_fixup_kernel", st, tc_scan_fixup_kernel<<<dim3(w.nslots + (s_out != nullptr ? n_seq : 0), w.H), 256, kFixSmem, st>>>(mPp, mF, mHp, f));
     return launch_status();
 }
 
