@@ -143,12 +143,28 @@ def run_decode(args, rank, world, local, dist):
     st = torch.cuda.current_stream(dev).cuda_stream
     p = lambda t: t.data_ptr()
 
-    def run(n):
+    def steps(stream):
         # one library call per NI steps: the per-token launches are issued from C, the state is updated in place
+        rc = lib.kda_decode_steps(NI, B, H, D, D, 1, 1, 1, D ** -0.5, p(q), p(k), p(v), p(g), p(beta), p(state), p(o), stream)
+        if rc:
+            raise RuntimeError(f"kda_decode_steps failed: {rc}")
+
+    graph = None
+    if not getattr(args, "no_graph", False):
+        # the NI-step call captured once and replayed, as a serving loop with fixed buffers would do: the launches of
+        # a replayed graph follow each other more closely than launches issued one by one
+        steps(st)
+        torch.cuda.synchronize(dev)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            steps(torch.cuda.current_stream(dev).cuda_stream)
+
+    def run(n):
         for _ in range(n // NI):
-            rc = lib.kda_decode_steps(NI, B, H, D, D, 1, 1, 1, D ** -0.5, p(q), p(k), p(v), p(g), p(beta), p(state), p(o), st)
-            if rc:
-                raise RuntimeError(f"kda_decode_steps failed: {rc}")
+            if graph is not None:
+                graph.replay()
+            else:
+                steps(st)
 
     def barrier():
         if world > 1:
@@ -177,7 +193,7 @@ def run_decode(args, rank, world, local, dist):
         "us_per_step": ms * 1e3, "tokens_per_s": Bt / (ms * 1e-3), "higher_is_better": True, "scaling": "strong",
         "dtype": "f32 state, bf16 activations", "data": "synthetic",
         "config": {"workload": f"config4 recurrent decode: batch {Bt} ({B}/GPU), H16, Dk=Dv=128, fp32 state read+written every step, "
-                               f"{n_steps} steps in one timed region", "launch": "kda_decode_steps: 64 steps per library call, one kernel launch per step, state in place", "l2": "state (256 MiB at N=1) larger than L2; at N=8 the 32 MiB "
+                               f"{n_steps} steps in one timed region", "launch": "kda_decode_steps: 64 steps per library call, one kernel launch per step, state in place; " + ("the call captured in a CUDA graph and replayed" if graph is not None else "eager"), "l2": "state (256 MiB at N=1) larger than L2; at N=8 the 32 MiB "
                                "per-GPU state can sit in L2, so the figure is effective bandwidth"},
         "bytes_per_step": bytes_step,
         "roofline": {"kernel": "decode_kernel", "bound": "hbm", "achieved": gbs / world, "peak": peaks["hbm_gbs"], "unit": "GB/s",
