@@ -387,9 +387,8 @@ __global__ void __launch_bounds__(256, 2)
     if (!fin && p.chunk_len[slot] == 0) return;
     const int seq = fin ? (int)blockIdx.x - p.nslots : p.chunk_seq[slot];
     const int c_begin = p.seq_chunk0[seq], c_end = p.seq_chunk0[seq + 1];
-    const int n_total = c_end - c_begin;
-    if (n_total == 0) return;
-    int k = p.nseg - 1;
+    const int n_total = c_end - c_begin;         // 0 for an empty sequence: its final state is its initial state, which the
+    int k = p.nseg - 1;                          // chain below reproduces (identity composites, zero local states)
     if (!fin) {
         const int step = p.bwd ? c_end - 1 - slot : slot - c_begin;
         while (k > 0 && step < seg_begin(k, p.nseg, n_total)) --k;

@@ -41,12 +41,16 @@ struct NormEpilogue {
     float* inv_rms;              // [tokens][H]
 };
 
-// Scans are split when a fixed-length batch has so few (sequence, head) recurrences that most SMs would idle behind
-// them, and the sequences are long enough for half a chain to outweigh the fix-up pass.
+// Scans are split when a batch has so few (sequence, head) recurrences that most SMs would idle behind them, and the
+// sequences are long enough for a shorter chain to outweigh the fix-up pass.  The decision uses the shape alone (a packed
+// batch is judged by its mean sequence length: the lengths themselves live on the device), so the forward and the
+// backward of a call agree; every sequence of the batch is cut into the same number of segments, short ones into
+// segments of one chunk or none.
 inline int scan_segments(const KdaChunkShape& sh) {
+    if (sh.n_seq <= 0) return 1;
     const bool fixed = sh.seq_len > 0 && (long long)sh.n_seq * sh.seq_len == sh.tokens;
-    if (!fixed) return 1;
-    const int rec = sh.n_seq * sh.heads, chunks = (sh.seq_len + 63) / 64;
+    const long long rec = (long long)sh.n_seq * sh.heads;
+    const long long chunks = fixed ? (sh.seq_len + 63) / 64 : (sh.tokens / 64) / sh.n_seq;
     if (rec * 7 <= 148 && chunks >= 32) return 4;
     if (rec * 3 <= 148 && chunks >= 16) return 2;
     return 1;

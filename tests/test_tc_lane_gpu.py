@@ -200,6 +200,21 @@ def test_split_scans_agree_with_the_single_chain_and_the_oracle(T):
     _run_activated(d)                           # the split path against the oracle
 
 
+@pytest.mark.parametrize("lens,H", [([64 * 40 + 5, 30, 64 * 70 + 1], 2),          # 6 recurrences, mean 37 chunks -> 4 segments
+                                    ([64 * 60 + 3, 0, 64 * 99, 1], 3),             # 12 recurrences, mean 39 chunks -> 4 segments
+                                    ([64 * 50, 64 * 3 + 9, 0, 64 * 19 + 63], 4)])  # 16 recurrences, mean 18 chunks -> 2 segments
+def test_split_scans_on_packed_batches_with_short_and_empty_sequences(lens, H):
+    """Packed batches with few sequences split their scans too (the decision uses the mean length), so a batch mixes long
+    sequences with ones of a single chunk or none: segments of one chunk or zero chunks, composite maps that stay the
+    identity, local states that stay zero.  Outputs, final states (non-zero initial states) and every gradient against
+    the oracle, sequence by sequence."""
+    cu = [0]
+    for n in lens:
+        cu.append(cu[-1] + n)
+    d = O.make_inputs(1, cu[-1], H, 128, 128, seed=300 + H, with_state=True, n_states=len(lens))
+    _run_activated(d, cu=cu)
+
+
 def test_output_norm_in_the_chunk_output_epilogue_equals_the_two_operators_in_sequence():
     """chunk_kda_norm (gated RMSNorm applied to the output tile inside the chunk-output kernel) against chunk_kda followed
     by RMSNormGated: identical y, final state and gradients (the epilogue repeats the stand-alone kernel's arithmetic),
