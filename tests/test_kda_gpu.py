@@ -278,12 +278,12 @@ def test_decode_1024_steps_in_library_calls_match_the_oracle_and_the_single_step
     assert torch.equal(torch.stack(outs), o) and torch.equal(cur, state)
 
 
-def test_prefill_then_decode_equals_one_shot_and_forward_only_path_matches_training_forward():
+@pytest.mark.parametrize("T,n", [(300, 9), (2100, 5)])      # the longer one runs its scans in four segments
+def test_prefill_then_decode_equals_one_shot_and_forward_only_path_matches_training_forward(T, n):
     """No-grad prefill (the forward-only kernels' path: no backward panels are written) over T tokens, then token-by-token
     decode from its final state, equals one call over T + n tokens; and the prefill output is bit-identical to the
     gradient-tracking forward."""
     m = kda_mod()
-    T, n = 300, 9
     d = O.make_inputs(2, T + n, 2, 128, 128, seed=61, with_state=True)
     x = to_dev(d, torch.bfloat16)
     with torch.no_grad():
