@@ -51,6 +51,37 @@ def update(model, opt, batches):
     return loss.detach()
 
 
+class GraphedMicroStep:
+    """One micro-step (forward, loss / n, backward into the parameters' existing .grad tensors) captured once in a CUDA
+    graph and replayed per micro-batch with the tokens copied into fixed buffers; the optimizer step stays eager (the
+    reference's own, with its NCCL collectives).  This is the first item the reference's plan lists for this caller once
+    the KDA calls are fast: at B200 speed the eager micro-step is bound by launching the model's ~1,000 small kernels."""
+
+    def __init__(self, model, batch, n):
+        x, y = batch
+        self.model, self.n = model, n
+        self.x, self.y = x.clone(), y.clone()
+        # gradients must exist before the capture so that the captured backward accumulates in place
+        for _ in range(2):
+            (model(self.x, self.y) / n).backward()
+        torch.cuda.synchronize()
+        model.zero_grad(set_to_none=False)
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph):
+            self.loss = model(self.x, self.y)
+            (self.loss / n).backward()
+        model.zero_grad(set_to_none=False)
+
+    def update(self, opt, batches):
+        for x, y in batches:
+            self.x.copy_(x)
+            self.y.copy_(y)
+            self.graph.replay()
+        opt.step()
+        self.model.zero_grad(set_to_none=False)
+        return self.loss.detach().clone()
+
+
 def import_reference():
     if not os.path.isdir(os.path.join(REF, "nanochat")):
         return "baseline/_ref holds no installed reference (python -m pip install --no-deps --target baseline/_ref <reference tree>)"
@@ -91,6 +122,15 @@ def run(args, rank, world, local):
             dist.barrier()
         torch.cuda.synchronize(dev)
 
+    graphed, graph_note = None, "eager micro-steps"
+    if not getattr(args, "no_graph", False):
+        try:
+            graphed = GraphedMicroStep(model, data[0][0], accum)
+            graph_note = "micro-step (forward + backward) captured in a CUDA graph and replayed; optimizer step eager"
+        except Exception as exc:      # noqa: BLE001 - the eager path is the fallback, and the line says which one ran
+            graphed, graph_note = None, f"eager micro-steps (graph capture failed: {type(exc).__name__}: {exc})"[:300]
+            torch.cuda.synchronize(dev)
+            model.zero_grad(set_to_none=True)
     times, losses = [], []
     l0 = _lib.launch_count()
     torch.cuda.reset_peak_memory_stats(dev)
@@ -98,7 +138,7 @@ def run(args, rank, world, local):
         barrier()
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         a.record()
-        loss = update(model, opt, data[u])
+        loss = graphed.update(opt, data[u]) if graphed is not None else update(model, opt, data[u])
         b.record()
         barrier()
         t = torch.tensor([a.elapsed_time(b)], dtype=torch.float64, device=dev)
@@ -116,8 +156,9 @@ def run(args, rank, world, local):
             "steps": n_updates - n_warm, "warmup": n_warm, "ms_per_step": med, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": "config2 nanochat-KDA training step: reference GPT (6 KDA layers, d_model 384 = 3x128, MLP 4x, vocab "
-                                   "65536) + MuonAdamW, B2 T4096 per GPU, grad-accum 4, seed 42, uniform tokens, eager bf16; KDA layers "
+                                   "65536) + MuonAdamW, B2 T4096 per GPU, grad-accum 4, seed 42, uniform tokens, bf16; KDA layers "
                                    "on libkda_b200 through torch.ops.nanochat_kda.*",
+                       "launch": graph_note,
                        "tokens_per_update": total, "parallelism": f"dp{world}" + (" (NCCL reduce-scatter / all-gather in MuonAdamW.step)" if world > 1 else ""),
                        "optimizer_kernels": "eager (TORCH_COMPILE_DISABLE=1)" if os.environ.get("TORCH_COMPILE_DISABLE") == "1" else "torch.compile",
                        "protocol": "7 updates, 2 warm-up, median of 5"},

@@ -41,3 +41,29 @@ def test_loss_sequence_matches_the_reference_backend_at_reduced_length():
     for a, b in zip(losses["project_cuda"], losses["reference"]):
         assert abs(a - b) <= 1e-2 * abs(b), losses
     assert losses["reference"][-1] < losses["reference"][0]      # and the step does train
+
+
+@pytest.mark.skipif(not os.path.isdir(os.path.join(REF, "nanochat")), reason="no installed reference under baseline/_ref")
+def test_graph_replayed_micro_steps_train_exactly_like_eager_ones():
+    """bench_train.GraphedMicroStep (forward + backward captured once, replayed per micro-batch, gradients accumulated
+    in place, optimizer step eager) gives the same loss sequence as the eager update, bit for bit: the operator library
+    is capturable (no host synchronisation, the forward's sidecar found again at capture time)."""
+    sys.path.insert(0, ROOT)
+    import bench_train
+    assert bench_train.import_reference() is None
+    dev = torch.device("cuda:0")
+    T, B, accum, updates = 256, 2, 2, 3
+    gen = torch.Generator().manual_seed(7)
+    data = [[(torch.randint(0, 65536, (B, T), generator=gen).to(dev), torch.randint(0, 65536, (B, T), generator=gen).to(dev))
+             for _ in range(accum)] for _ in range(updates)]
+    losses = []
+    for graphed in (False, True):
+        model, opt = bench_train.build(dev, T, "project_cuda")
+        if graphed:
+            step = bench_train.GraphedMicroStep(model, data[0][0], accum)
+            losses.append([float(step.update(opt, batch).item()) for batch in data])
+        else:
+            losses.append([float(bench_train.update(model, opt, batch).item()) for batch in data])
+        del model, opt
+        torch.cuda.empty_cache()
+    assert losses[0] == losses[1], losses
