@@ -307,9 +307,10 @@ def main():
     ap.add_argument("--profile-warm", action="store_true", help="per-kernel pass without the L2 flush between steps (what a kernel costs inside the replayed graph, where its inputs were just written)")
     ap.add_argument("--no-sharded", action="store_true", help="skip the config-3 / config-4 sharded workloads attached to the line")
     ap.add_argument("--tokens", type=int, default=8 * 8192, help="packed tokens of the varlen workload")
-    ap.add_argument("--workload", default="chain", choices=["chain", "varlen", "decode", "pointwise", "train"],
+    ap.add_argument("--workload", default="chain", choices=["chain", "varlen", "decode", "pointwise", "train", "prefill"],
                     help="chain = config 1 (default, the driver's line); varlen = config 3; decode = config 4; pointwise = conv / gated RMSNorm at 256 MiB tensors; "
-                         "train = config 2 (the reference's GPT + MuonAdamW step on these kernels)")
+                         "train = config 2 (the reference's GPT + MuonAdamW step on these kernels); prefill = no-grad forward with the "
+                         "convolutions as their own launch vs inside the intra-chunk kernel")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

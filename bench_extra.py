@@ -15,6 +15,7 @@ from __future__ import annotations
 
 import json
 import os
+import sys
 
 import torch
 
@@ -253,13 +254,69 @@ def run_pointwise(args, rank, world, local, dist):
     return line
 
 
+def run_prefill(args, rank, world, local, dist):
+    """No-grad prefill of one layer's operator chain at the config-1 shape, two ways: the three convolutions as their own
+    launch followed by the forward-only chunk forward, and the convolutions folded into the intra-chunk kernel
+    (kda_chunk_fwd_conv: q, k, v never written).  Same inputs, identical outputs; CUDA-graph replay, L2 flushed between
+    steps, median."""
+    from experiment_swa_kda_b200 import ops, _lib
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import kda_oracle as O
+    dev = torch.device(f"cuda:{local}")
+    B, T, H, D = 2, 4096, 3, 128
+    d = O.make_inputs(B, T, H, D, D, seed=3)
+    g, beta = d["g"].bfloat16().to(dev), d["beta"].bfloat16().to(dev)
+    gen = torch.Generator().manual_seed(5)
+    xs = [torch.randn(B, T, H * D, generator=gen).bfloat16().to(dev) for _ in range(3)]
+    ws = [((torch.rand(H * D, 4, generator=gen) * 2 - 1) * 0.3).to(dev) for _ in range(3)]
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    sh4 = (B, T, H, D)
+
+    def unfused():
+        with torch.no_grad():
+            q, k, v = ops.ConvMultiFunction.apply(True, 3, *xs, *ws)
+        return ops.chunk_kda_fwd(q.view(sh4), k.view(sh4), v.view(sh4), g, beta, None, None, D ** -0.5, True, True, _lib.LANE_TC, forward_only=True)[:2]
+
+    def fused():
+        return ops.chunk_kda_conv_fwd(xs[0].view(sh4), xs[1].view(sh4), xs[2].view(sh4), *ws, g, beta, None, None, D ** -0.5, True, True)
+
+    res, outs = {}, {}
+    for name, fn in (("convolutions_then_forward", unfused), ("convolutions_in_forward_kernel", fused)):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize(dev)
+        l0 = _lib.launch_count()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            outs[name] = fn()
+        launches = _lib.launch_count() - l0
+        times = []
+        for _ in range(max(args.steps, 10)):
+            flush.zero_()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            graph.replay()
+            b.record()
+            torch.cuda.synchronize(dev)
+            times.append(a.elapsed_time(b) * 1e3)
+        times.sort()
+        res[name] = {"us": times[len(times) // 2], "launches": launches}
+    same = all(torch.equal(a, b) for a, b in zip(outs["convolutions_then_forward"], outs["convolutions_in_forward_kernel"]))
+    if rank != 0:
+        return None
+    return {"metric": "kda_prefill_us", "value": res["convolutions_in_forward_kernel"]["us"], "unit": "us", "n_gpus": world,
+            "higher_is_better": False, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": "no-grad prefill, conv4+SiLU(q,k,v) -> chunked KDA forward with final state, B2 T4096 H3 D128"},
+            "variants": res, "outputs_identical": bool(same)}
+
+
 def run(args, rank, world, local):
     import torch.distributed as dist
     dev = torch.device(f"cuda:{local}")
     torch.cuda.set_device(dev)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
-    line = {"varlen": run_varlen, "decode": run_decode, "pointwise": run_pointwise}[args.workload](args, rank, world, local, dist)
+    line = {"varlen": run_varlen, "decode": run_decode, "pointwise": run_pointwise, "prefill": run_prefill}[args.workload](args, rank, world, local, dist)
     if line is not None:
         print(json.dumps(line), flush=True)
     if world > 1:

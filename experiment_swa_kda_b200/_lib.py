@@ -30,6 +30,7 @@ _SIGNATURES = {
     "kda_chunk_workspace_bytes": (C.c_size_t, [C.POINTER(ChunkShape)]),
     "kda_chunk_bwd_scratch_bytes": (C.c_size_t, [C.POINTER(ChunkShape)]),
     "kda_chunk_fwd": (C.c_int, [C.POINTER(ChunkShape)] + [_P] * 10 + [C.c_size_t, _P]),
+    "kda_chunk_fwd_conv": (C.c_int, [C.POINTER(ChunkShape)] + [_P] * 6 + [C.c_int32, C.c_int32] + [_P] * 7 + [C.c_size_t, _P]),
     "kda_chunk_fwd_norm": (C.c_int, [C.POINTER(ChunkShape)] + [_P] * 10 + [C.c_size_t, _P, _P, C.c_float, _P, _P, _P]),
     "kda_chunk_bwd": (C.c_int, [C.POINTER(ChunkShape)] + [_P] * 9 + [C.c_size_t, _P, C.c_size_t] + [_P] * 7),
     "kda_chunk_status": (C.c_int, [C.POINTER(ChunkShape), _P, _P]),

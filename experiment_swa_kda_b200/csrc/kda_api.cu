@@ -14,7 +14,7 @@
 namespace kda {
 int simt_chunk_fwd(const KdaChunkShape* sh, const void* q, const void* k, const void* v, const void* g, const void* beta,
                    const float* h0, const int32_t* cu, void* o, float* final_state, void* workspace, cudaStream_t st,
-                   const tc::NormEpilogue* norm);
+                   const tc::NormEpilogue* norm, const tc::ConvPrep* conv = nullptr);
 int chunk_status(const KdaChunkShape* sh, const void* workspace, cudaStream_t st);
 int chunk_status_async(const KdaChunkShape* sh, const void* workspace, int32_t* host_word, cudaStream_t st);
 int status_word_to_code(int v);
@@ -88,6 +88,25 @@ extern "C" int kda_chunk_fwd(const KdaChunkShape* shape, const void* q, const vo
         workspace_bytes < kda_chunk_workspace_bytes(shape))
         return KDA_ERR_WORKSPACE;
     return simt_chunk_fwd(shape, q, k, v, g, beta, h0, cu_seqlens, o, final_state, workspace, (cudaStream_t)stream, nullptr);
+}
+
+extern "C" int kda_chunk_fwd_conv(const KdaChunkShape* shape, const void* xq, const void* xk, const void* xv, const void* wq,
+                                  const void* wk, const void* wv, int32_t conv_width, int32_t weight_dtype, const void* g,
+                                  const void* beta, const float* h0, const int32_t* cu_seqlens, void* o, float* final_state,
+                                  void* workspace, size_t workspace_bytes, void* stream) {
+    int rc = check_shape(shape, cu_seqlens);
+    if (rc) return rc;
+    // the convolution lives in the tensor-core lane's forward kernel, width 4 with SiLU, and only where nothing is kept for
+    // a backward (which would need the activations in memory)
+    if (shape->lane != KDA_LANE_TC || !shape->forward_only || conv_width != 4) return KDA_ERR_UNSUPPORTED;
+    if (shape->tokens > 0 && (!xq || !xk || !xv || !wq || !wk || !wv || !g || !beta || !o)) return KDA_ERR_NULL;
+    if (!workspace || (reinterpret_cast<uintptr_t>(workspace) % 256) != 0 || workspace_bytes < kda_chunk_workspace_bytes(shape))
+        return KDA_ERR_WORKSPACE;
+    if ((reinterpret_cast<uintptr_t>(xq) | reinterpret_cast<uintptr_t>(xk) | reinterpret_cast<uintptr_t>(xv) | reinterpret_cast<uintptr_t>(wq) |
+         reinterpret_cast<uintptr_t>(wk) | reinterpret_cast<uintptr_t>(wv)) % 16 != 0)
+        return KDA_ERR_UNSUPPORTED;
+    tc::ConvPrep cp{{wq, wk, wv}, weight_dtype == KDA_DTYPE_F32 ? 1 : 0};
+    return simt_chunk_fwd(shape, xq, xk, xv, g, beta, h0, cu_seqlens, o, final_state, workspace, (cudaStream_t)stream, nullptr, &cp);
 }
 
 extern "C" int kda_chunk_fwd_norm(const KdaChunkShape* shape, const void* q, const void* k, const void* v, const void* g,

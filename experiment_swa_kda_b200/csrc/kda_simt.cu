@@ -937,7 +937,7 @@ using simt::Ws;
 int tc_scan_forward(const simt::Ws& w, const tc::TcWs& t, int n_seq, int tokens, const float* h0, float* final_state, void* o,
                     const tc::NormEpilogue& norm, cudaStream_t st);
 int tc_intra_forward(const simt::Ws& w, const tc::TcWs& t, const void* q, const void* k, const void* v, const void* g,
-                     const void* beta, int gbf16, int l2norm, float scale, int tokens, cudaStream_t st);
+                     const void* beta, int gbf16, int l2norm, float scale, int tokens, const tc::ConvPrep* conv, cudaStream_t st);
 int tc_scan_backward(const simt::Ws& w, const simt::Scr& s, const tc::TcWs& t, int n_seq, int tokens, const void* d_o,
                      const float* d_final, float* dh0, cudaStream_t st);
 int tc_intra_backward(const simt::Ws& w, const tc::TcWs& t, int tokens, const void* q, const void* k, const void* v,
@@ -955,8 +955,9 @@ static int set_smem(Kern kern, size_t bytes) {
 
 int simt_chunk_fwd(const KdaChunkShape* sh, const void* q, const void* k, const void* v, const void* g, const void* beta,
                    const float* h0, const int32_t* cu, void* o, float* final_state, void* workspace, cudaStream_t st,
-                   const tc::NormEpilogue* norm) {
+                   const tc::NormEpilogue* norm, const tc::ConvPrep* conv) {
     Ws w = simt::carve_ws(*sh, workspace);
+    if (conv != nullptr && (sh->lane != KDA_LANE_TC || !sh->forward_only)) return KDA_ERR_UNSUPPORTED;
     if (norm != nullptr && norm->gate != nullptr && sh->lane != KDA_LANE_TC) return KDA_ERR_UNSUPPORTED;
     const int bf16 = sh->io_dtype == KDA_DTYPE_BF16, gbf16 = sh->gate_dtype == KDA_DTYPE_BF16;
     const int KT = w.Kp / 64, VT = w.Vp / 64;
@@ -968,7 +969,7 @@ int simt_chunk_fwd(const KdaChunkShape* sh, const void* q, const void* k, const 
         t.status = w.status;      // one status word per workspace, shared by both lanes
         KDA_LAUNCH("chunk_table_kernel", st, simt::chunk_table_kernel<<<1, 256, 0, st>>>(w, cu, sh->n_seq, sh->seq_len, sh->tokens, w.status));
         if (w.nslots > 0) {
-            int rc = tc_intra_forward(w, t, q, k, v, g, beta, gbf16, sh->l2norm, sh->scale, sh->tokens, st);
+            int rc = tc_intra_forward(w, t, q, k, v, g, beta, gbf16, sh->l2norm, sh->scale, sh->tokens, conv, st);
             if (rc) return rc;
             rc = tc_scan_forward(w, t, sh->n_seq, sh->tokens, h0, final_state, o,
                                  norm != nullptr ? *norm : tc::NormEpilogue{nullptr, nullptr, 0.f, nullptr, nullptr}, st);

@@ -215,6 +215,8 @@ struct IntraFwdArgs {
     float scale;
     TcWs t;
     simt::Ws w;                       // per-row scalars (inverse norms, beta) kept for the backward
+    const __nv_bfloat16* xv;          // CONV only: the v convolution's input (q, k above are the q, k convolutions' inputs)
+    ConvPrep conv;
 };
 
 // shared-memory map (bytes from a 1024-aligned base)
@@ -229,7 +231,44 @@ constexpr int kFMs = 0, kFTs = 64 * kLDs * 4, kFTmp = 2 * 64 * kLDs * 4, kFTb = 
 static_assert(kFTmp + 32 * kLDs * 4 <= kFTb, "inverse scratch overlaps the T operands");
 constexpr int kIntraFwdSmem = kFTab + kTabFloats * 4 + 1024;
 
-template <bool GBF16>
+// y = silu(sum_m w[m] x[t - 3 + m]) for this thread's 4 rows x 8 channels from the 7 input rows it needs, in the
+// arithmetic of the stand-alone convolution kernel (float32 accumulation in tap order, hardware-tanh sigmoid, one
+// rounding to bf16), so that the fused call reproduces "convolution, then forward" bit for bit.
+__device__ __forceinline__ void conv4_silu_rows(const uint4 (&xr)[7], const void* wgt, size_t wbase, int wf32, uint4 (&out)[4]) {
+    float w[8][4];
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+        if (wf32) {
+            const float4 f = __ldg(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(wgt) + wbase + 4 * c));
+            w[c][0] = __bfloat162float(__float2bfloat16(f.x)); w[c][1] = __bfloat162float(__float2bfloat16(f.y));
+            w[c][2] = __bfloat162float(__float2bfloat16(f.z)); w[c][3] = __bfloat162float(__float2bfloat16(f.w));
+        } else {
+            const uint2 u = __ldg(reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(wgt) + wbase + 4 * c));
+            const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.x));
+            const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.y));
+            w[c][0] = a.x; w[c][1] = a.y; w[c][2] = b.x; w[c][3] = b.y;
+        }
+    }
+    float x[7][8];
+#pragma unroll
+    for (int j = 0; j < 7; ++j) unpack_bf16x8(xr[j], x[j]);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        float y[8];
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+            float z = 0.f;
+#pragma unroll
+            for (int m = 0; m < 4; ++m) z += w[c][m] * x[j + m][c];
+            float th;
+            asm("tanh.approx.f32 %0, %1;" : "=f"(th) : "f"(0.5f * z));
+            y[c] = z * fmaf(0.5f, th, 0.5f);
+        }
+        out[j] = pack8(y);
+    }
+}
+
+template <bool GBF16, bool CONV>
 __global__ void __launch_bounds__(kNT, 2)
     tc_intra_fwd_kernel(const __grid_constant__ CUtensorMap mv, const __grid_constant__ CUtensorMap mUT,
                         const __grid_constant__ CUtensorMap mWT, const __grid_constant__ CUtensorMap mAT,
@@ -274,8 +313,10 @@ __global__ void __launch_bounds__(kNT, 2)
         mbar_init(&bar_uw, 1);
         mbar_init(&bar_tr, 1);
         mbar_fence_init();
-        mbar_expect_tx(&bar_in, 16384);
-        for (int kb = 0; kb < 2; ++kb) tma_load_2d(vs + kb * 8192, &mv, &bar_in, h * 128 + kb * 64, tok0);
+        if (!CONV) {
+            mbar_expect_tx(&bar_in, 16384);
+            for (int kb = 0; kb < 2; ++kb) tma_load_2d(vs + kb * 8192, &mv, &bar_in, h * 128 + kb * 64, tok0);
+        }
     }
     if (warp == 1) tmem_alloc(&tmem_slot, 256);
 
@@ -285,12 +326,43 @@ __global__ void __launch_bounds__(kNT, 2)
     float G[4][8];
     uint4 qraw[4], kraw[4];
     float brow[4];
+    if constexpr (CONV) {
+        // the three convolutions, one after the other (7 input rows for 4 output rows; the rows before the chunk belong to
+        // the previous chunk of the same sequence, or are the zero padding at a sequence start); v goes straight into the
+        // operand tile that TMA would have filled
+        const bool first = p.w.seq_chunk0[p.w.chunk_seq[slot]] == slot;
+        const size_t wbase = ((size_t)h * 128 + 8 * cg) * 4;
+        auto rows = [&](const __nv_bfloat16* x, uint4 (&xr)[7]) {
+#pragma unroll
+            for (int jj = 0; jj < 7; ++jj) {
+                const int i = 4 * rq - 3 + jj;
+                const long long ic = min(i, len - 1);      // rows past the tail feed masked outputs only
+                xr[jj] = (i >= 0 || !first) ? __ldg(reinterpret_cast<const uint4*>(x + (long long)base + ic * (long long)rstride))
+                                            : make_uint4(0, 0, 0, 0);
+            }
+        };
+        uint4 xr[7];
+        rows(p.q, xr);
+        conv4_silu_rows(xr, p.conv.w[0], wbase, p.conv.wf32, qraw);
+        rows(p.k, xr);
+        conv4_silu_rows(xr, p.conv.w[1], wbase, p.conv.wf32, kraw);
+        rows(p.xv, xr);
+        uint4 vr[4];
+        conv4_silu_rows(xr, p.conv.w[2], wbase, p.conv.wf32, vr);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int i = 4 * rq + j;
+            *reinterpret_cast<uint4*>(vs + piece_off(i, cg, 8192)) = i < len ? vr[j] : make_uint4(0, 0, 0, 0);
+        }
+    }
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
         const int i = 4 * rq + j, ic = min(i, len - 1);
         ld8(p.g, base + (size_t)ic * rstride, GBF16, G[j]);
-        qraw[j] = __ldg(reinterpret_cast<const uint4*>(p.q + base + (size_t)ic * rstride));
-        kraw[j] = __ldg(reinterpret_cast<const uint4*>(p.k + base + (size_t)ic * rstride));
+        if constexpr (!CONV) {
+            qraw[j] = __ldg(reinterpret_cast<const uint4*>(p.q + base + (size_t)ic * rstride));
+            kraw[j] = __ldg(reinterpret_cast<const uint4*>(p.k + base + (size_t)ic * rstride));
+        }
         brow[j] = ld_io(p.beta, (size_t)(tok0 + ic) * H + h, GBF16);
         if (i >= len) {
 #pragma unroll
@@ -562,8 +634,8 @@ __global__ void __launch_bounds__(kNT, 2)
             }
         }
         // the value tile: wait for it, blank the rows past a ragged tail (they hold other tokens)
-        ok = mbar_wait(&bar_in, 0, p.t.status, 30);
-        if (len < 64 && ok) {
+        if (!CONV) ok = mbar_wait(&bar_in, 0, p.t.status, 30);
+        if (!CONV && len < 64 && ok) {
             for (int idx = tid; idx < (64 - len) * 16; idx += kNT) {
                 const int r = len + (idx >> 4), c = idx & 15;
                 *reinterpret_cast<uint4*>(vs + (c >> 3) * 8192 + sw128_off(r, c & 7)) = make_uint4(0, 0, 0, 0);
@@ -702,7 +774,7 @@ __global__ void __launch_bounds__(kNT, 2)
         if (tid == 0) tma_store_wait_read();           // shared memory must outlive the reads of the bulk stores
     } else {
         // unwinding: the value tile must have landed before the block may exit
-        mbar_wait(&bar_in, 0, nullptr, 0);
+        if (!CONV) mbar_wait(&bar_in, 0, nullptr, 0);
         if (tid == 0) tma_store_wait_read();
     }
     tc_fence_before();
@@ -713,12 +785,15 @@ __global__ void __launch_bounds__(kNT, 2)
 }  // namespace tc
 
 int tc_intra_forward(const simt::Ws& w, const tc::TcWs& t, const void* q, const void* k, const void* v, const void* g,
-                     const void* beta, int gbf16, int l2norm, float scale, int tokens, cudaStream_t st) {
+                     const void* beta, int gbf16, int l2norm, float scale, int tokens, const tc::ConvPrep* conv, cudaStream_t st) {
     using namespace tc;
     IntraFwdArgs a;
     a.chunk_tok0 = w.chunk_tok0; a.chunk_len = w.chunk_len;
     a.q = static_cast<const __nv_bfloat16*>(q); a.k = static_cast<const __nv_bfloat16*>(k);
     a.g = g; a.beta = beta; a.gbf16 = gbf16; a.l2norm = l2norm; a.H = w.H; a.scale = scale; a.t = t; a.w = w;
+    a.xv = static_cast<const __nv_bfloat16*>(v);
+    a.conv = conv != nullptr ? *conv : tc::ConvPrep{{nullptr, nullptr, nullptr}, 0};
+    if (conv != nullptr && !t.fwd_only) return KDA_ERR_UNSUPPORTED;      // a backward would need q, k, v in memory
     const uint64_t nch = (uint64_t)w.nslots * w.H;
     CUtensorMap mv, mUT, mWT, mAT, mMt, mE, mP, mRm, mTp;
     int rc = make_map_bf16(&mv, v, (uint64_t)tokens, (uint64_t)w.H * 128, 64, 64);
@@ -731,7 +806,8 @@ int tc_intra_forward(const simt::Ws& w, const tc::TcWs& t, const void* q, const 
     rc |= make_map_bf16(&mP, t.Pn, nch * 128, 128, 64, 128);
     rc |= make_map_bf16(&mRm, t.fwd_only ? t.WT : t.RmT, nch * 128, 64, 64, 128);      // not stored in a forward-only call
     if (rc) return KDA_ERR_CUDA;
-    auto kern = gbf16 ? tc_intra_fwd_kernel<true> : tc_intra_fwd_kernel<false>;
+    auto kern = conv != nullptr ? (gbf16 ? tc_intra_fwd_kernel<true, true> : tc_intra_fwd_kernel<false, true>)
+                                : (gbf16 ? tc_intra_fwd_kernel<true, false> : tc_intra_fwd_kernel<false, false>);
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kIntraFwdSmem) != cudaSuccess) return KDA_ERR_CUDA;
     KDA_LAUNCH("tc_intra_fwd_kernel", st, kern<<<dim3(w.nslots, w.H), kNT, kIntraFwdSmem, st>>>(mv, mUT, mWT, mAT, mMt, mE, mP, mRm, mTp, a));
     return launch_status();

@@ -8,6 +8,13 @@
 namespace kda {
 namespace tc {
 
+// Short causal convolution (width 4, SiLU) folded into the intra-chunk forward of a forward-only call: q, k, v of that
+// call are the convolutions' INPUTS and the kernel forms the activations itself, so they are never written to memory.
+struct ConvPrep {
+    const void* w[3];       // weights of the q, k, v convolutions, [H*128][4]
+    int wf32;               // 1: float32 weights (rounded to bf16 as loaded, like the stand-alone kernel), 0: bf16
+};
+
 struct TcWs {
     __nv_bfloat16 *WT, *RT;     // [nch][128][64]   rows = key, cols = token
     __nv_bfloat16* E;           // [nch][64][128]   rows = token, cols = key

@@ -147,6 +147,35 @@ def chunk_kda_fwd(q, k, v, g, beta, h0, cu_seqlens, scale, l2norm, want_final, l
     return o, fs, (sh, ws)
 
 
+def chunk_kda_conv_fwd(xq, xk, xv, wq, wk, wv, g, beta, h0, cu_seqlens, scale, l2norm, want_final):
+    """No-grad forward with the three short convolutions (width 4, SiLU, zero padding at every sequence start) folded
+    into the intra-chunk kernel: xq, xk, xv [B,T,H,128] bf16 are the convolutions' inputs, wq, wk, wv [H*128,4] their
+    weights (float32 or bf16).  Tensor-core lane only.  Returns (o, final_state or None), bit-identical to
+    conv_fwd x3 followed by chunk_kda_fwd(forward_only=True)."""
+    lib = _lib.load()
+    dev = _need_cuda(xq, xk, xv, wq, wk, wv, g, beta, h0, cu_seqlens)
+    poll_status(dev)
+    B, T, H, K = xq.shape
+    if cu_seqlens is not None:
+        n_seq, seq_len = cu_seqlens.numel() - 1, 0
+    else:
+        n_seq, seq_len = B, T
+    sh = _shape(xq, xv, g, n_seq, seq_len, scale, l2norm, _lib.LANE_TC, True)
+    ws_ = [w.contiguous() for w in (wq, wk, wv)]
+    if len({w.dtype for w in ws_}) != 1 or ws_[0].dtype not in (torch.float32, torch.bfloat16) or any(w.shape != (H * K, 4) for w in ws_):
+        raise ValueError("convolution weights must share one dtype (float32 or bfloat16) and have shape [H*K, 4]")
+    o = torch.empty(B, T, H, K, dtype=xv.dtype, device=dev)
+    fs = torch.empty(n_seq, H, K, K, dtype=torch.float32, device=dev) if want_final else None
+    ws = _bytes(lib.kda_chunk_workspace_bytes(sh), dev)
+    with torch.cuda.device(dev):
+        rc = lib.kda_chunk_fwd_conv(sh, _ptr(xq), _ptr(xk), _ptr(xv), _ptr(ws_[0]), _ptr(ws_[1]), _ptr(ws_[2]), 4,
+                                    _lib.DTYPE_F32 if ws_[0].dtype == torch.float32 else _lib.DTYPE_BF16, _ptr(g), _ptr(beta),
+                                    _ptr(h0), _ptr(cu_seqlens), _ptr(o), _ptr(fs), _ptr(ws), ws.numel(), _stream(dev))
+        _lib.check(rc, "kda_chunk_fwd_conv")
+        _queue_status(sh, ws, dev)
+    return o, fs
+
+
 def chunk_kda_bwd(q, k, v, g, beta, cu_seqlens, do, dfs, saved, want_dh0):
     lib = _lib.load()
     sh, ws = saved

@@ -84,6 +84,19 @@ int kda_chunk_fwd(const KdaChunkShape* shape, const void* q, const void* k, cons
                   const void* beta, const float* h0, const int32_t* cu_seqlens, void* o, float* final_state,
                   void* workspace, size_t workspace_bytes, void* stream);
 
+/* The no-grad forward with the layer's three short convolutions folded in: xq, xk, xv [tokens,H,128] bf16 are the
+ * INPUTS of the q, k, v convolutions (width 4, SiLU, no carried-in window: zero padding at every sequence start), wq, wk,
+ * wv [H*128,4] their weights (weight_dtype KDA_DTYPE_F32: rounded to bf16 as loaded, or KDA_DTYPE_BF16); the activations
+ * are formed inside the intra-chunk kernel and never written to memory.  o and final_state equal
+ * kda_conv_fwd x3 followed by kda_chunk_fwd bit for bit.  Tensor-core lane with forward_only = 1 only (a backward would
+ * need the activations), otherwise KDA_ERR_UNSUPPORTED.  Fuses the operator boundary between
+ * causal_convolution_forward and chunk_forward (nanochat/mixers/kda.py:745-767); no counterpart operator in the
+ * reference. */
+int kda_chunk_fwd_conv(const KdaChunkShape* shape, const void* xq, const void* xk, const void* xv, const void* wq,
+                       const void* wk, const void* wv, int32_t conv_width, int32_t weight_dtype, const void* g,
+                       const void* beta, const float* h0, const int32_t* cu_seqlens, void* o, float* final_state,
+                       void* workspace, size_t workspace_bytes, void* stream);
+
 /* The forward with the layer's gated RMSNorm applied in the output kernel's epilogue, while the output tile is still on
  * chip (tensor-core lane only, otherwise KDA_ERR_UNSUPPORTED and the caller runs kda_rmsnorm_gate_fwd itself):
  *   y = o * rsqrt(mean_v(o^2) + eps) * norm_weight * sigmoid(gate),   gate, y [tokens,H,V] bf16, inv_rms [tokens,H] float32.

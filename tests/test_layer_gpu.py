@@ -144,3 +144,35 @@ def test_in_place_decode_token_equals_the_non_mutating_recurrent_path():
             for a, b in ((owned.memory, ref_state.memory), (owned.q_conv, ref_state.q_conv), (owned.k_conv, ref_state.k_conv),
                          (owned.v_conv, ref_state.v_conv)):
                 assert torch.equal(a, b)
+
+
+def test_no_grad_prefill_with_convolutions_inside_the_forward_kernel_equals_the_training_forward():
+    """With `fuse_prefill_conv` set, a no_grad forward with no incoming state takes the fused prefill path (convolutions
+    inside the intra-chunk kernel): output, memory and the three convolution caches equal those of the
+    gradient-tracking forward, and decoding on from either state gives the same tokens."""
+    layer = _layer(7).eval()
+    x = torch.randn(2, 150, HID, generator=torch.Generator().manual_seed(5)).bfloat16().to(D0)
+    from experiment_swa_kda_b200 import _lib
+    with torch.no_grad():
+        n0 = _lib.launch_count()
+        layer(x[:, :143], state=None, output_final_state=True, mode="project_chunk")
+        n1 = _lib.launch_count()
+        layer.fuse_prefill_conv = True
+        y_fused, st_fused = layer(x[:, :143], state=None, output_final_state=True, mode="project_chunk")
+        n2 = _lib.launch_count()
+        layer.fuse_prefill_conv = False
+    assert n2 - n1 == (n1 - n0) - 3          # the three convolution launches are gone
+    y_train, st_train = layer(x[:, :143].clone().requires_grad_(True), state=None, output_final_state=True, mode="project_chunk")
+    assert torch.equal(y_fused, y_train.detach())
+    for a, b in ((st_fused.memory, st_train.memory), (st_fused.q_conv, st_train.q_conv), (st_fused.k_conv, st_train.k_conv),
+                 (st_fused.v_conv, st_train.v_conv)):
+        assert torch.equal(a, b.detach())
+    with torch.no_grad():
+        a, _ = layer(x[:, 143:144], state=st_fused, output_final_state=True, mode="project_recurrent")
+        b, _ = layer(x[:, 143:144], state=KDAStateDetach(st_train), output_final_state=True, mode="project_recurrent")
+    assert torch.equal(a, b)
+
+
+def KDAStateDetach(s):
+    from experiment_swa_kda_b200 import KDAState
+    return KDAState(s.memory.detach(), s.q_conv.detach(), s.k_conv.detach(), s.v_conv.detach())

@@ -215,6 +215,36 @@ def test_split_scans_on_packed_batches_with_short_and_empty_sequences(lens, H):
     _run_activated(d, cu=cu)
 
 
+@pytest.mark.parametrize("lens,H,wdtype", [([300], 2, torch.float32), ([1], 1, torch.float32), ([3, 64, 65, 130, 2], 3, torch.bfloat16),
+                                           ([64 * 34 + 7, 5], 2, torch.float32)])
+def test_convolutions_inside_the_forward_kernel_equal_convolutions_then_forward(lens, H, wdtype):
+    """kda_chunk_fwd_conv (q, k, v never written to memory: the intra-chunk kernel forms them from the convolutions'
+    inputs, reading the three rows before a chunk from the previous chunk of the same sequence and zeros at a sequence
+    start) against the three stand-alone convolutions followed by the forward-only chunk forward: identical output and
+    final state, bit for bit, over one-token, sub-chunk, chunk-boundary, multi-chunk and split-scan lengths, fixed and
+    packed layouts, float32 and bf16 weights."""
+    from experiment_swa_kda_b200 import ops, _lib
+    gen = torch.Generator().manual_seed(sum(lens) + H)
+    T, C = sum(lens), H * 128
+    edges = [0]
+    for n in lens:
+        edges.append(edges[-1] + n)
+    cu = torch.tensor(edges, dtype=torch.int32, device=D0) if len(lens) > 1 else None
+    d = O.make_inputs(1, T, H, 128, 128, seed=7 + T, with_state=True, n_states=len(lens))
+    g, beta, h0 = d["g"].bfloat16().to(D0), d["beta"].bfloat16().to(D0), d["h0"].float().to(D0)
+    xs = [torch.randn(1, T, C, generator=gen).bfloat16().to(D0) for _ in range(3)]
+    ws = [((torch.rand(C, 4, generator=gen) * 2 - 1) * 0.5).to(wdtype).to(D0) for _ in range(3)]
+    # reference: each sequence convolved on its own (zero padding at its start), then the forward-only chunk forward
+    acts = []
+    for x, w in zip(xs, ws):
+        parts = [ops.conv_fwd(x[:, a:b].contiguous(), w, None, False)[0] for a, b in zip(edges[:-1], edges[1:]) if b > a]
+        acts.append(torch.cat(parts, 1).reshape(1, T, H, 128))
+    want_o, want_s, _ = ops.chunk_kda_fwd(acts[0], acts[1], acts[2], g, beta, h0, cu, 128 ** -0.5, True, True, _lib.LANE_TC, forward_only=True)
+    got_o, got_s = ops.chunk_kda_conv_fwd(xs[0].reshape(1, T, H, 128), xs[1].reshape(1, T, H, 128), xs[2].reshape(1, T, H, 128), *ws, g, beta,
+                                          h0, cu, 128 ** -0.5, True, True)
+    assert torch.equal(got_o, want_o) and torch.equal(got_s, want_s)
+
+
 def test_output_norm_in_the_chunk_output_epilogue_equals_the_two_operators_in_sequence():
     """chunk_kda_norm (gated RMSNorm applied to the output tile inside the chunk-output kernel) against chunk_kda followed
     by RMSNormGated: identical y, final state and gradients (the epilogue repeats the stand-alone kernel's arithmetic),
