@@ -154,7 +154,8 @@ def run(args, rank, world, local):
         line = {
             "metric": "nanochat_kda_train_tokens_per_s", "value": total / (med * 1e-3), "unit": "tokens/s", "n_gpus": world,
             "steps": n_updates - n_warm, "warmup": n_warm, "ms_per_step": med, "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            # the reference's published figure for this exact workload (one GB10, docs/BENCHMARK.md:58-63); whole-job value over it
+            "vs_baseline": total / (med * 1e-3) / GB10_TOKENS_PER_S, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": "config2 nanochat-KDA training step: reference GPT (6 KDA layers, d_model 384 = 3x128, MLP 4x, vocab "
                                    "65536) + MuonAdamW, B2 T4096 per GPU, grad-accum 4, seed 42, uniform tokens, bf16; KDA layers "
                                    "on libkda_b200 through torch.ops.nanochat_kda.*",
